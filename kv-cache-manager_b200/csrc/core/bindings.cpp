@@ -1,0 +1,351 @@
+// Python bindings of the CPU core (module name: kvcm_core).  The engine, the replay tool and
+// the tests all drive the same C++ objects; Python never re-implements their logic.
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "batch.h"
+#include "block_allocator.h"
+#include "hash.h"
+#include "kv_manager.h"
+#include "paged_manager.h"
+#include "prefix_cache.h"
+#include "scheduler.h"
+#include "sequence.h"
+
+namespace py = pybind11;
+using namespace kvcm;
+
+namespace {
+
+std::vector<BatchEntry> entries_from_plan(const std::vector<ScheduledSeq>& plan) {
+  std::vector<BatchEntry> entries;
+  entries.reserve(plan.size());
+  for (const ScheduledSeq& p : plan) {
+    BatchEntry e;
+    e.seq = p.seq;
+    e.start = p.start;
+    e.num_tokens = p.num_tokens;
+    if (p.wants_logits) e.want.push_back(p.num_tokens - 1);
+    entries.push_back(std::move(e));
+  }
+  return entries;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(kvcm_core, m) {
+  m.doc() = "CPU core: page allocator, prefix cache, cache managers, state slots, scheduler, batch builder";
+
+  m.def("xxh64", [](py::bytes data, uint64_t seed) {
+    const std::string s = data;
+    return XXH64::digest(s.data(), s.size(), seed);
+  }, py::arg("data"), py::arg("seed") = 0);
+  m.def("page_hash", [](uint64_t parent, const std::vector<int32_t>& tokens) {
+    return page_hash(parent, tokens.data(), static_cast<int>(tokens.size()));
+  });
+
+  py::class_<SamplingParams>(m, "SamplingParams")
+      .def(py::init<>())
+      .def_readwrite("temperature", &SamplingParams::temperature)
+      .def_readwrite("seed", &SamplingParams::seed);
+
+  py::class_<Sequence>(m, "Sequence")
+      .def(py::init<>())
+      .def_readwrite("id", &Sequence::id)
+      .def_readwrite("tokens", &Sequence::tokens)
+      .def_readwrite("prompt_len", &Sequence::prompt_len)
+      .def_readwrite("max_new_tokens", &Sequence::max_new_tokens)
+      .def_readwrite("num_computed", &Sequence::num_computed)
+      .def_readwrite("tables", &Sequence::tables)
+      .def_readonly("window_freed", &Sequence::window_freed)
+      .def_readonly("page_hashes", &Sequence::page_hashes)
+      .def_readwrite("cached_tokens", &Sequence::cached_tokens)
+      .def_readwrite("state_slot", &Sequence::state_slot)
+      .def_readwrite("sampling", &Sequence::sampling)
+      .def_readwrite("arrival", &Sequence::arrival)
+      .def_readwrite("admitted", &Sequence::admitted)
+      .def_readwrite("first_token", &Sequence::first_token)
+      .def_readwrite("finished", &Sequence::finished)
+      .def_readwrite("rejected", &Sequence::rejected)
+      .def_readwrite("num_preemptions", &Sequence::num_preemptions)
+      .def_readwrite("prefill_tokens_computed", &Sequence::prefill_tokens_computed)
+      .def_readwrite("prefill_tokens_saved", &Sequence::prefill_tokens_saved)
+      .def("length", &Sequence::length)
+      .def("num_generated", &Sequence::num_generated)
+      .def("append_token", [](Sequence& s, int32_t t) { s.tokens.push_back(t); })
+      .def("extend_tokens", [](Sequence& s, const std::vector<int32_t>& t) {
+        s.tokens.insert(s.tokens.end(), t.begin(), t.end());
+      })
+      .def("token_at", [](const Sequence& s, int i) { return s.tokens.at(i); })
+      .def("generated", [](const Sequence& s) {
+        return std::vector<int32_t>(s.tokens.begin() + s.prompt_len, s.tokens.end());
+      })
+      .def("table", [](const Sequence& s, int g) { return s.tables.at(g); });
+
+  py::class_<BlockAllocator>(m, "BlockAllocator")
+      .def(py::init<int>())
+      .def("allocate", &BlockAllocator::allocate)
+      .def("free", &BlockAllocator::free)
+      .def("incref", &BlockAllocator::incref)
+      .def("decref", &BlockAllocator::decref)
+      .def("push_free", &BlockAllocator::push_free)
+      .def("revive", &BlockAllocator::revive)
+      .def("refcount", &BlockAllocator::refcount)
+      .def("is_free", &BlockAllocator::is_free)
+      .def("num_free", &BlockAllocator::num_free)
+      .def("num_blocks", &BlockAllocator::num_blocks);
+
+  py::class_<PrefixCacheStats>(m, "PrefixCacheStats")
+      .def_readonly("queried_blocks", &PrefixCacheStats::queried_blocks)
+      .def_readonly("hit_blocks", &PrefixCacheStats::hit_blocks)
+      .def_readonly("inserted_blocks", &PrefixCacheStats::inserted_blocks)
+      .def_readonly("evictions", &PrefixCacheStats::evictions)
+      .def_readonly("duplicate_inserts", &PrefixCacheStats::duplicate_inserts);
+
+  py::class_<PrefixCache>(m, "PrefixCache")
+      .def(py::init<BlockAllocator&, int, bool>(), py::keep_alive<1, 2>())
+      .def("enabled", &PrefixCache::enabled)
+      .def("allocate", &PrefixCache::allocate)
+      .def("release", &PrefixCache::release)
+      .def("match_and_acquire", [](PrefixCache& c, const std::vector<int32_t>& tokens, int num_blocks) {
+        std::vector<int32_t> pages;
+        std::vector<uint64_t> hashes;
+        c.match_and_acquire(tokens.data(), num_blocks, pages, hashes);
+        return py::make_tuple(pages, hashes);
+      })
+      .def("count_match", [](const PrefixCache& c, const std::vector<int32_t>& tokens, int num_blocks) {
+        int parked = 0;
+        const int hits = c.count_match(tokens.data(), num_blocks, &parked);
+        return py::make_tuple(hits, parked);
+      })
+      .def("insert", [](PrefixCache& c, int page, uint64_t parent, uint64_t hash,
+                        const std::vector<int32_t>& tokens) {
+        return c.insert(page, parent, hash, tokens.data());
+      })
+      .def("num_available", &PrefixCache::num_available)
+      .def("num_cached_free", &PrefixCache::num_cached_free)
+      .def("num_hashed", &PrefixCache::num_hashed)
+      .def("is_hashed", &PrefixCache::is_hashed)
+      .def("stats", &PrefixCache::stats)
+      .def("lru_order", &PrefixCache::lru_order);
+
+  py::class_<LayerGroupSpec>(m, "LayerGroupSpec")
+      .def(py::init([](int window) { LayerGroupSpec g; g.window = window; return g; }),
+           py::arg("window") = 0)
+      .def_readwrite("window", &LayerGroupSpec::window);
+
+  py::class_<KVStats>(m, "KVStats")
+      .def_readonly("num_blocks", &KVStats::num_blocks)
+      .def_readonly("block_size", &KVStats::block_size)
+      .def_readonly("blocks_in_use", &KVStats::blocks_in_use)
+      .def_readonly("blocks_cached_free", &KVStats::blocks_cached_free)
+      .def_readonly("allocated_slots", &KVStats::allocated_slots)
+      .def_readonly("used_slots", &KVStats::used_slots)
+      .def_readonly("tail_waste_slots", &KVStats::tail_waste_slots)
+      .def_readonly("reserved_unused_slots", &KVStats::reserved_unused_slots)
+      .def_readonly("block_table_entries", &KVStats::block_table_entries)
+      .def_readonly("num_seqs", &KVStats::num_seqs)
+      .def_readonly("prefix", &KVStats::prefix)
+      .def("fragmentation", &KVStats::fragmentation);
+
+  py::class_<KVManagerConfig>(m, "KVManagerConfig")
+      .def(py::init<>())
+      .def_readwrite("policy", &KVManagerConfig::policy)
+      .def_readwrite("num_blocks", &KVManagerConfig::num_blocks)
+      .def_readwrite("block_size", &KVManagerConfig::block_size)
+      .def_readwrite("max_seq_len", &KVManagerConfig::max_seq_len)
+      .def_readwrite("prefix_caching", &KVManagerConfig::prefix_caching)
+      .def_readwrite("watermark_blocks", &KVManagerConfig::watermark_blocks)
+      .def_readwrite("watermark_frac", &KVManagerConfig::watermark_frac)
+      .def_readwrite("groups", &KVManagerConfig::groups);
+
+  py::class_<KVManager>(m, "KVManager")
+      .def("name", &KVManager::name)
+      .def("block_size", &KVManager::block_size)
+      .def("num_blocks", &KVManager::num_blocks)
+      .def("max_seq_len", &KVManager::max_seq_len)
+      .def("num_groups", &KVManager::num_groups)
+      .def("group_window", [](const KVManager& k, int g) { return k.group(g).window; })
+      .def("can_admit", &KVManager::can_admit)
+      .def("admit", &KVManager::admit)
+      .def("ensure", &KVManager::ensure)
+      .def("commit", &KVManager::commit)
+      .def("release", &KVManager::release)
+      .def("blocks_in_use", &KVManager::blocks_in_use, py::arg("group") = 0)
+      .def("blocks_cached_free", &KVManager::blocks_cached_free)
+      .def("prefix_stats", &KVManager::prefix_stats)
+      .def("stats", [](const KVManager& k, const std::vector<const Sequence*>& live) { return k.stats(live); });
+
+  py::class_<PagedManager, KVManager>(m, "PagedManager")
+      .def(py::init<int, int, int, bool, int, std::vector<LayerGroupSpec>>(), py::arg("num_blocks"),
+           py::arg("block_size"), py::arg("max_seq_len"), py::arg("prefix_caching") = false,
+           py::arg("watermark_blocks") = 0,
+           py::arg("groups") = std::vector<LayerGroupSpec>{LayerGroupSpec{}})
+      .def("refcount", [](const PagedManager& p, int id, int g) { return p.allocator(g).refcount(id); },
+           py::arg("id"), py::arg("group") = 0)
+      .def("num_free", [](const PagedManager& p, int g) { return p.allocator(g).num_free(); },
+           py::arg("group") = 0)
+      .def("num_available", [](const PagedManager& p, int g) { return p.cache(g).num_available(); },
+           py::arg("group") = 0)
+      .def("lru_order", [](const PagedManager& p) { return p.cache(0).lru_order(); })
+      .def("num_hashed", [](const PagedManager& p) { return p.cache(0).num_hashed(); });
+
+  py::class_<ContiguousManager, KVManager>(m, "ContiguousManager")
+      .def(py::init<int, int, int, std::vector<LayerGroupSpec>>(), py::arg("num_blocks"),
+           py::arg("block_size"), py::arg("max_seq_len"),
+           py::arg("groups") = std::vector<LayerGroupSpec>{LayerGroupSpec{}})
+      .def("reserve_blocks", &ContiguousManager::reserve_blocks)
+      .def("num_free_extents", &ContiguousManager::num_free_extents);
+
+  m.def("make_kv_manager", &make_kv_manager);
+
+  py::class_<StateSlots>(m, "StateSlots")
+      .def(py::init<int>())
+      .def("take", &StateSlots::take)
+      .def("give_back", &StateSlots::give_back)
+      .def("num_slots", &StateSlots::num_slots)
+      .def("num_taken", &StateSlots::num_taken)
+      .def("is_taken", &StateSlots::is_taken);
+
+  py::class_<SchedulerConfig>(m, "SchedulerConfig")
+      .def(py::init<>())
+      .def_readwrite("max_num_seqs", &SchedulerConfig::max_num_seqs)
+      .def_readwrite("max_batched_tokens", &SchedulerConfig::max_batched_tokens)
+      .def_readwrite("prefill_chunk", &SchedulerConfig::prefill_chunk)
+      .def_readwrite("chunked_prefill", &SchedulerConfig::chunked_prefill)
+      .def_readwrite("eos_token_id", &SchedulerConfig::eos_token_id);
+
+  py::class_<ScheduledSeq>(m, "ScheduledSeq")
+      .def_property_readonly("seq", [](const ScheduledSeq& p) { return p.seq; },
+                             py::return_value_policy::reference)
+      .def_readonly("start", &ScheduledSeq::start)
+      .def_readonly("num_tokens", &ScheduledSeq::num_tokens)
+      .def_readonly("is_prefill", &ScheduledSeq::is_prefill)
+      .def_readonly("wants_logits", &ScheduledSeq::wants_logits);
+
+  py::class_<SchedulerCounters>(m, "SchedulerCounters")
+      .def_readonly("steps", &SchedulerCounters::steps)
+      .def_readonly("preemptions", &SchedulerCounters::preemptions)
+      .def_readonly("admissions", &SchedulerCounters::admissions)
+      .def_readonly("admission_blocked_steps", &SchedulerCounters::admission_blocked_steps)
+      .def_readonly("rejected", &SchedulerCounters::rejected)
+      .def_readonly("prefill_tokens", &SchedulerCounters::prefill_tokens)
+      .def_readonly("decode_tokens", &SchedulerCounters::decode_tokens)
+      .def_readonly("prefill_tokens_saved", &SchedulerCounters::prefill_tokens_saved)
+      .def_readonly("batch_size_sum", &SchedulerCounters::batch_size_sum)
+      .def_readonly("max_running", &SchedulerCounters::max_running);
+
+  py::class_<BatchLayout>(m, "BatchLayout")
+      .def_readonly("rows", &BatchLayout::rows)
+      .def_readonly("seqs", &BatchLayout::seqs)
+      .def_readonly("logit_rows", &BatchLayout::logit_rows)
+      .def_readonly("groups", &BatchLayout::groups)
+      .def_readonly("max_blocks", &BatchLayout::max_blocks)
+      .def_readonly("real_rows", &BatchLayout::real_rows)
+      .def_readonly("real_seqs", &BatchLayout::real_seqs)
+      .def_readonly("decode_seqs", &BatchLayout::decode_seqs)
+      .def_readonly("prefill_rows", &BatchLayout::prefill_rows)
+      .def_readonly("prefill_tiles", &BatchLayout::prefill_tiles)
+      .def_readonly("tile_rows", &BatchLayout::tile_rows)
+      .def_readonly("max_ctx", &BatchLayout::max_ctx)
+      .def_readonly("max_decode_ctx", &BatchLayout::max_decode_ctx)
+      .def_readonly("max_q_len", &BatchLayout::max_q_len)
+      .def_readonly("off_tokens", &BatchLayout::off_tokens)
+      .def_readonly("off_positions", &BatchLayout::off_positions)
+      .def_readonly("off_row_seq", &BatchLayout::off_row_seq)
+      .def_readonly("off_slot_mapping", &BatchLayout::off_slot_mapping)
+      .def_readonly("off_seq_q_start", &BatchLayout::off_seq_q_start)
+      .def_readonly("off_seq_q_len", &BatchLayout::off_seq_q_len)
+      .def_readonly("off_seq_ctx_len", &BatchLayout::off_seq_ctx_len)
+      .def_readonly("off_seq_state_slot", &BatchLayout::off_seq_state_slot)
+      .def_readonly("off_logit_rows", &BatchLayout::off_logit_rows)
+      .def_readonly("off_tile_seq", &BatchLayout::off_tile_seq)
+      .def_readonly("off_tile_q0", &BatchLayout::off_tile_q0)
+      .def_readonly("off_block_tables", &BatchLayout::off_block_tables)
+      .def_readonly("total_ints", &BatchLayout::total_ints)
+      .def_readonly("entry_order", &BatchLayout::entry_order);
+
+  py::class_<BatchBuilder>(m, "BatchBuilder")
+      .def(py::init<int, int, int, int>(), py::arg("block_size"), py::arg("max_blocks_per_seq"),
+           py::arg("num_groups"), py::arg("tile_rows"))
+      .def("capacity_for", &BatchBuilder::capacity_for)
+      // entries: list of (Sequence, start, num_tokens, [wanted places]); `address` is the host
+      // address of an int32 buffer of `capacity` elements (e.g. a pinned torch tensor).
+      .def("build", [](const BatchBuilder& b, const std::vector<std::tuple<const Sequence*, int, int, std::vector<int32_t>>>& items,
+                       uintptr_t address, int64_t capacity, int pad_rows, int pad_seqs) {
+        std::vector<BatchEntry> entries;
+        entries.reserve(items.size());
+        for (const auto& it : items) {
+          BatchEntry e;
+          e.seq = std::get<0>(it);
+          e.start = std::get<1>(it);
+          e.num_tokens = std::get<2>(it);
+          e.want = std::get<3>(it);
+          entries.push_back(std::move(e));
+        }
+        return b.build(entries, reinterpret_cast<int32_t*>(address), capacity, pad_rows, pad_seqs);
+      }, py::arg("entries"), py::arg("address"), py::arg("capacity"), py::arg("pad_rows") = 0,
+         py::arg("pad_seqs") = 0);
+
+  py::class_<Scheduler>(m, "Scheduler")
+      .def(py::init<KVManager&, SchedulerConfig>(), py::keep_alive<1, 2>())
+      .def("add_request", [](Scheduler& s, int64_t id, const std::vector<int32_t>& tokens,
+                             int max_new_tokens, float temperature, uint64_t seed, double arrival) {
+        auto q = std::make_unique<Sequence>();
+        q->id = id;
+        q->tokens = tokens;
+        q->prompt_len = static_cast<int>(tokens.size());
+        q->max_new_tokens = max_new_tokens;
+        q->sampling.temperature = temperature;
+        q->sampling.seed = seed;
+        q->arrival = arrival;
+        s.add(std::move(q));
+      }, py::arg("id"), py::arg("tokens"), py::arg("max_new_tokens"), py::arg("temperature") = 0.f,
+         py::arg("seed") = 0, py::arg("arrival") = 0.0)
+      .def("schedule", [](Scheduler& s, double now) { return s.schedule(now); },
+           py::return_value_policy::reference_internal)
+      .def("plan", &Scheduler::plan, py::return_value_policy::reference_internal)
+      // (rows, entries, entries that sample, prompt tokens, single-row entries) of the current plan
+      .def("plan_summary", [](const Scheduler& s) {
+        int rows = 0, wants = 0, prefill = 0, singles = 0;
+        for (const auto& p : s.plan()) {
+          rows += p.num_tokens;
+          wants += p.wants_logits;
+          if (p.is_prefill) prefill += p.num_tokens;
+          singles += p.num_tokens == 1;
+        }
+        return py::make_tuple(rows, static_cast<int>(s.plan().size()), wants, prefill, singles);
+      })
+      // Per plan entry that samples: (request id, position of the drawn token, temperature, seed)
+      .def("plan_sampling", [](const Scheduler& s) {
+        std::vector<int64_t> ids; std::vector<int32_t> pos; std::vector<float> temp; std::vector<uint64_t> seed;
+        for (const auto& p : s.plan()) {
+          if (!p.wants_logits) continue;
+          ids.push_back(p.seq->id);
+          pos.push_back(p.start + p.num_tokens);
+          temp.push_back(p.seq->sampling.temperature);
+          seed.push_back(p.seq->sampling.seed);
+        }
+        return py::make_tuple(ids, pos, temp, seed);
+      })
+      .def("build_batch", [](const Scheduler& s, const BatchBuilder& b, uintptr_t address,
+                             int64_t capacity, int pad_rows, int pad_seqs) {
+        return b.build(entries_from_plan(s.plan()), reinterpret_cast<int32_t*>(address), capacity,
+                       pad_rows, pad_seqs);
+      }, py::arg("builder"), py::arg("address"), py::arg("capacity"), py::arg("pad_rows") = 0,
+         py::arg("pad_seqs") = 0)
+      .def("update", &Scheduler::update)
+      .def("take_finished", [](Scheduler& s) {
+        py::list out;
+        for (auto& q : s.take_finished()) out.append(py::cast(std::move(q)));
+        return out;
+      })
+      .def("idle", &Scheduler::idle)
+      .def("num_waiting", &Scheduler::num_waiting)
+      .def("num_running", &Scheduler::num_running)
+      .def("live", &Scheduler::live, py::return_value_policy::reference_internal)
+      .def("counters", &Scheduler::counters)
+      .def("reset_counters", &Scheduler::reset_counters)
+      .def("slots_taken", [](const Scheduler& s) { return s.slots().num_taken(); })
+      .def("kv_stats", [](Scheduler& s) { return s.kv().stats(s.live()); });
+}

@@ -1,0 +1,209 @@
+// Row-wise kernels of the forward pass: embedding gather, RMSNorm fused with the residual add
+// that precedes it, rotary position encoding fused with the write of K and V into cache pages,
+// and SiLU(gate)*up.  Each is instantiated for float (the true 32-bit path) and bfloat16.
+// Statistics, angles and the residual stream are always float.
+//
+// Formulas after the reference's kernels (src/cuda/kernels.cu:27-88, src/cuda/kv_cache.cu:19-38);
+// the fusions (residual+norm, rotary+cache write) are this engine's own.
+#include "common.cuh"
+
+namespace kvcm {
+
+// ------------------------------------------------------------------------------ embedding
+// x[t, :] = float(table[ids[t], :]).  An id outside [0, vocab) yields a row of NaN: loud, not wrong.
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                             float* __restrict__ x, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* dst = x + size_t(t) * hidden;
+  if (id < 0 || id >= vocab) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = __int_as_float(0x7fc00000);
+    return;
+  }
+  const T* src = table + size_t(id) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ldf(src + i);
+}
+
+// -------------------------------------------------------------------------------- RMSNorm
+// Optional residual add first: x[r] += delta[r] (written back when rows are not gathered).
+// inv = rsqrt(mean(x^2) + eps); out = round(w * round(x * inv)) in the storage type
+// (the reference rounds the normalised value before the weight, src/cuda/kernels.cu:46-48).
+// `rows` (optional) gathers: output row r is computed from input row rows[r]; nothing is
+// written back to x then.  The weight may be float or T (a tensor stored in 32 bits stays so).
+template <typename T, typename W>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const W* __restrict__ weight,
+               T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  extern __shared__ float row_cache[];            // hidden floats: the (updated) row
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* xr = x + size_t(src) * hidden;
+  const T* dr = delta ? delta + size_t(src) * hidden : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = xr[i];
+    if (dr) {
+      v += ldf(dr + i);
+      if (!rows) xr[i] = v;
+    }
+    row_cache[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / float(hidden) + eps);
+  T* o = out + size_t(r) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float normed = Store<T>::round(row_cache[i] * inv);
+    stf(o + i, ldf(weight + i) * normed);
+  }
+}
+
+// Adds the pending delta into the residual stream without a norm: x += delta.
+template <typename T>
+__global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t n) {
+  for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x)
+    x[i] += ldf(delta + i);
+}
+
+// ------------------------------------------------------------- rotary + cache page write
+// One block per row.  Rotates the first `rotary_dim` elements of every q head and k head of the
+// fused row [q heads | k heads | v heads] in place, then copies the (rotated) k heads and the v
+// heads into the page slot of the row.  angle = pos * inv_freq[j] with inv_freq given by the
+// caller (float), sin/cos in float.  Pairing: rotate-half (j, j + rotary_dim/2) or interleaved
+// (2j, 2j+1).  Cache layout per layer: [page][kv head][slot in page][head_dim].
+// slot < 0: the row writes nothing (padding).  write_cache = 0: only the q heads are rotated.
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int rotary_dim, int interleaved,
+                                  const int* __restrict__ slot_mapping, T* __restrict__ k_cache,
+                                  T* __restrict__ v_cache, int nh, int nkv, int hd, int block_size,
+                                  int write_cache) {
+  const int t = blockIdx.x;
+  T* row = qkv + size_t(t) * row_stride;
+  const int half = rotary_dim / 2;
+  const int rot_heads = write_cache ? nh + nkv : nh;
+  if (inv_freq != nullptr && half > 0) {
+    const float pos = float(positions[t]);
+    for (int i = threadIdx.x; i < rot_heads * half; i += blockDim.x) {
+      const int h = i / half, j = i - h * half;
+      float sn, cs;
+      sincosf(pos * inv_freq[j], &sn, &cs);
+      T* base = row + size_t(h) * hd;
+      const int ia = interleaved ? 2 * j : j;
+      const int ib = interleaved ? 2 * j + 1 : j + half;
+      const float a = ldf(base + ia), b = ldf(base + ib);
+      stf(base + ia, a * cs - b * sn);
+      stf(base + ib, b * cs + a * sn);
+    }
+  }
+  if (!write_cache) return;
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  __syncthreads();                       // rotated k must be visible to the copying threads
+  const int page = slot / block_size, off = slot - page * block_size;
+  const T* ksrc = row + size_t(nh) * hd;
+  const T* vsrc = ksrc + size_t(nkv) * hd;
+  for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) {
+    const int h = i / hd, d = i - h * hd;
+    const size_t dst = ((size_t(page) * nkv + h) * block_size + off) * hd + d;
+    k_cache[dst] = ksrc[i];
+    v_cache[dst] = vsrc[i];
+  }
+}
+
+// --------------------------------------------------------------------------- SiLU(g) * u
+// gate = columns [0, I) of the fused product, up = columns [I, 2I).  silu is rounded to the
+// storage type before the product (src/cuda/kernels.cu:72-82).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+  const int t = blockIdx.x;
+  const T* g = gate_up + size_t(t) * 2 * inter;
+  const T* u = g + inter;
+  T* o = out + size_t(t) * inter;
+  for (int i = threadIdx.x; i < inter; i += blockDim.x) {
+    const float x = ldf(g + i);
+    const float s = Store<T>::round(x / (1.f + expf(-x)));
+    stf(o + i, s * ldf(u + i));
+  }
+}
+
+// Gathers rows of a [*, width] matrix of T into a dense [n, width] matrix (used for the rows
+// whose logits are wanted when a part needs them contiguous).
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows,
+                                   T* __restrict__ dst, int width) {
+  const T* s = src + size_t(rows[blockIdx.x]) * width;
+  T* d = dst + size_t(blockIdx.x) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) d[i] = s[i];
+}
+
+template <typename T>
+int launch_rmsnorm(float* x, const T* delta, const void* weight, int weight_is_f32, T* out,
+                   const int* rows, int n_rows, int hidden, float eps, cudaStream_t s) {
+  if (n_rows == 0) return 0;
+  const size_t smem = size_t(hidden) * sizeof(float);
+  if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
+  if (weight_is_f32) {
+    auto k = rmsnorm_kernel<T, float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    k<<<n_rows, 256, smem, s>>>(x, delta, static_cast<const float*>(weight), out, rows, hidden, eps);
+  } else {
+    auto k = rmsnorm_kernel<T, T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    k<<<n_rows, 256, smem, s>>>(x, delta, static_cast<const T*>(weight), out, rows, hidden, eps);
+  }
+  return KVCM_LAUNCH_RESULT();
+}
+
+}  // namespace kvcm
+
+using namespace kvcm;
+
+#define KVCM_INSTANTIATE(SUFFIX, T)                                                                   \
+  KVCM_API int kvcm_embed_##SUFFIX(const int* ids, const void* table, float* x, int rows, int hidden, \
+                                   int vocab, void* stream) {                                         \
+    if (rows == 0) return 0;                                                                          \
+    embed_kernel<T><<<rows, 256, 0, (cudaStream_t)stream>>>(ids, (const T*)table, x, hidden, vocab);  \
+    return KVCM_LAUNCH_RESULT();                                                                      \
+  }                                                                                                   \
+  KVCM_API int kvcm_rmsnorm_##SUFFIX(float* x, const void* delta, const void* weight,                 \
+                                     int weight_is_f32, void* out, const int* rows, int n_rows,       \
+                                     int hidden, float eps, void* stream) {                           \
+    return launch_rmsnorm<T>(x, (const T*)delta, weight, weight_is_f32, (T*)out, rows, n_rows,        \
+                             hidden, eps, (cudaStream_t)stream);                                      \
+  }                                                                                                   \
+  KVCM_API int kvcm_add_residual_##SUFFIX(float* x, const void* delta, long long n, void* stream) {   \
+    if (n == 0) return 0;                                                                             \
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);                        \
+    add_residual_kernel<T><<<blocks, 256, 0, (cudaStream_t)stream>>>(x, (const T*)delta, (size_t)n);  \
+    return KVCM_LAUNCH_RESULT();                                                                      \
+  }                                                                                                   \
+  KVCM_API int kvcm_rope_cache_##SUFFIX(void* qkv, int row_stride, const int* positions,              \
+                                        const float* inv_freq, int rotary_dim, int interleaved,       \
+                                        const int* slot_mapping, void* k_cache, void* v_cache,        \
+                                        int rows, int nh, int nkv, int hd, int block_size,            \
+                                        int write_cache, void* stream) {                              \
+    if (rows == 0) return 0;                                                                          \
+    if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return KVCM_ERR_UNSUPPORTED;           \
+    rope_cache_kernel<T><<<rows, 256, 0, (cudaStream_t)stream>>>(                                     \
+        (T*)qkv, row_stride, positions, inv_freq, rotary_dim, interleaved, slot_mapping,              \
+        (T*)k_cache, (T*)v_cache, nh, nkv, hd, block_size, write_cache);                              \
+    return KVCM_LAUNCH_RESULT();                                                                      \
+  }                                                                                                   \
+  KVCM_API int kvcm_silu_mul_##SUFFIX(const void* gate_up, void* out, int rows, int inter,            \
+                                      void* stream) {                                                 \
+    if (rows == 0) return 0;                                                                          \
+    silu_mul_kernel<T><<<rows, 256, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)out, inter);    \
+    return KVCM_LAUNCH_RESULT();                                                                      \
+  }                                                                                                   \
+  KVCM_API int kvcm_gather_rows_##SUFFIX(const void* src, const int* rows, void* dst, int n,          \
+                                         int width, void* stream) {                                   \
+    if (n == 0) return 0;                                                                             \
+    gather_rows_kernel<T><<<n, 256, 0, (cudaStream_t)stream>>>((const T*)src, rows, (T*)dst, width);  \
+    return KVCM_LAUNCH_RESULT();                                                                      \
+  }
+
+KVCM_INSTANTIATE(f32, float)
+KVCM_INSTANTIATE(bf16, bf16)

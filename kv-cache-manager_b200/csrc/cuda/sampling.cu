@@ -1,0 +1,147 @@
+// Picking the next token from float logits: greedy argmax (lowest index among equal maxima, as
+// the reference's kernel, src/cuda/kernels.cu:90-119) and temperature sampling (not in the
+// reference, which is greedy only).
+//
+// Temperature sampling draws from softmax(logits / T) by inverse CDF.  The uniform number is a
+// pure function of (seed, request id, position of the drawn token), so a request's tokens do not
+// depend on what else is in the batch, on how its prompt was cut, or on preemption:
+//     z = seed ^ (id * 0x9E3779B97F4A7C15) ^ (position * 0xBF58476D1CE4E5B9)
+//     z = splitmix64 finaliser(z + 0x9E3779B97F4A7C15);   u = (z >> 40) * 2^-24
+// The vocabulary is cut into 1024 consecutive segments; segment sums are scanned in order, the
+// segment that holds u * total is scanned element by element.  Softmax in float.
+#include "common.cuh"
+
+namespace kvcm {
+
+constexpr int kSampleThreads = 1024;
+
+__device__ __forceinline__ void argmax_merge(float& bv, int& bi, float ov, int oi) {
+  if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+}
+
+// Block-wide argmax of a row; every thread returns the same (value, index).
+__device__ void block_argmax(const float* __restrict__ row, int vocab, float& best, int& index,
+                             float* sv, int* si) {
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = row[i];
+    if (v > bv) { bv = v; bi = i; }          // ascending i: the first maximum is kept
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_merge(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    bv = lane < nwarps ? sv[lane] : -INFINITY;
+    bi = lane < nwarps ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      argmax_merge(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if (lane == 0) { sv[0] = bv; si[0] = bi; }
+  }
+  __syncthreads();
+  best = sv[0];
+  index = si[0];
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kSampleThreads)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  float best;
+  int index;
+  block_argmax(logits + size_t(blockIdx.x) * vocab, vocab, best, index, sv, si);
+  if (threadIdx.x == 0) out[blockIdx.x] = index;
+}
+
+__device__ __forceinline__ float sampling_uniform(unsigned long long seed, long long id, int position) {
+  unsigned long long z = seed ^ (static_cast<unsigned long long>(id) * 0x9E3779B97F4A7C15ULL) ^
+                         (static_cast<unsigned long long>(static_cast<long long>(position)) * 0xBF58476D1CE4E5B9ULL);
+  z += 0x9E3779B97F4A7C15ULL;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+  z ^= z >> 31;
+  return static_cast<float>(z >> 40) * (1.0f / 16777216.0f);
+}
+
+__global__ void __launch_bounds__(kSampleThreads)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+              const unsigned long long* __restrict__ seed, const long long* __restrict__ request_id,
+              const int* __restrict__ position, int* __restrict__ out, int vocab) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ float part[kSampleThreads];
+  __shared__ int chosen_segment;
+  __shared__ float segment_base, target;
+  const int r = blockIdx.x;
+  const float* row = logits + size_t(r) * vocab;
+  float best;
+  int index;
+  block_argmax(row, vocab, best, index, sv, si);
+  const float temp = temperature[r];
+  if (!(temp > 0.f)) {
+    if (threadIdx.x == 0) out[r] = index;
+    return;
+  }
+  const float inv_t = 1.f / temp;
+  const int seg = (vocab + kSampleThreads - 1) / kSampleThreads;
+  const int begin = min(threadIdx.x * seg, vocab), end = min(begin + seg, vocab);
+  float s = 0.f;
+  for (int i = begin; i < end; ++i) s += expf((row[i] - best) * inv_t);
+  part[threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int i = 0; i < kSampleThreads; ++i) total += part[i];
+    const float want = sampling_uniform(seed[r], request_id[r], position[r]) * total;
+    float run = 0.f;
+    int pick = -1;
+    for (int i = 0; i < kSampleThreads; ++i) {
+      if (part[i] > 0.f) {
+        pick = i;                                   // last non-empty segment so far: the fallback
+        if (want < run + part[i]) break;
+      }
+      run += part[i];
+    }
+    if (pick >= 0 && !(want < run + part[pick])) {  // rounding pushed `want` past the end
+      run = 0.f;
+      for (int i = 0; i < pick; ++i) run += part[i];
+    }
+    chosen_segment = pick;
+    segment_base = run;
+    target = want;
+  }
+  __syncthreads();
+  if (threadIdx.x == chosen_segment) {
+    float run = segment_base;
+    int pick = end - 1;
+    for (int i = begin; i < end; ++i) {
+      run += expf((row[i] - best) * inv_t);
+      if (target < run) { pick = i; break; }
+    }
+    out[r] = pick;
+  }
+}
+
+}  // namespace kvcm
+
+using namespace kvcm;
+
+KVCM_API int kvcm_argmax_f32(const float* logits, int* out, int rows, int vocab, void* stream) {
+  if (rows == 0) return 0;
+  argmax_kernel<<<rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits, out, vocab);
+  return KVCM_LAUNCH_RESULT();
+}
+
+KVCM_API int kvcm_sample_f32(const float* logits, const float* temperature,
+                             const unsigned long long* seed, const long long* request_id,
+                             const int* position, int* out, int rows, int vocab, void* stream) {
+  if (rows == 0) return 0;
+  sample_kernel<<<rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits, temperature, seed,
+                                                                   request_id, position, out, vocab);
+  return KVCM_LAUNCH_RESULT();
+}

@@ -1,0 +1,256 @@
+"""Python face of ``libkvcm_cuda.so``: one function per exported launcher.
+
+Every function checks what the kernel assumes (device, dtype, contiguity, shapes), passes raw
+pointers and the current torch CUDA stream, and raises ``KernelError`` on a non-zero return.
+There is no fallback of any kind: without the compiled library, or with tensors that are not
+on a CUDA device, these functions raise.  ``launch_count()`` counts launches of this library's
+kernels (used by the benchmark's ``gpu_launches``).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_cuda
+
+_SUFFIX = {torch.float32: "f32", torch.bfloat16: "bf16"}
+_ERR_UNSUPPORTED = 10001
+_launches = 0
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def _lib():
+    return load_cuda()
+
+
+def _suffix(t: torch.Tensor) -> str:
+    try:
+        return _SUFFIX[t.dtype]
+    except KeyError:
+        raise KernelError(f"kernels exist for float32 and bfloat16 storage, not {t.dtype}") from None
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel called with a tensor that is not on a CUDA device "
+                              "(this engine has no CPU path)")
+
+
+def _check(rc: int, name: str, detail: str = "") -> None:
+    global _launches
+    _launches += 1
+    if rc == 0:
+        return
+    if rc == _ERR_UNSUPPORTED:
+        raise KernelError(f"{name}: sizes not supported by this kernel {detail}")
+    raise KernelError(f"{name}: CUDA error {rc} at launch {detail}")
+
+
+_I32 = torch.int32
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor) -> None:
+    """x[t,:] = float(table[ids[t],:]); x is float32 [T, H]."""
+    _cuda(ids, table, x)
+    T, H = x.shape
+    _need(ids.dtype == _I32 and ids.numel() >= T, "embed: ids must be int32 [T]")
+    _need(x.dtype == torch.float32 and x.is_contiguous() and table.is_contiguous(), "embed: layout")
+    _need(table.shape[1] == H, "embed: table width != hidden")
+    fn = getattr(_lib(), "kvcm_embed_" + _suffix(table))
+    _check(fn(_p(ids), _p(table), _p(x), T, H, table.shape[0], _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+            out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """Optional x += delta, then out = weight * round(x * rsqrt(mean(x^2)+eps)).
+
+    x float32 [T,H] (updated in place unless ``rows`` gathers); delta/out in the storage dtype;
+    weight in the storage dtype or float32."""
+    _cuda(x, delta, weight, out, rows)
+    H = x.shape[1]
+    n = out.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "rmsnorm: x must be contiguous float32")
+    _need(out.is_contiguous() and out.shape[1] == H and weight.numel() == H, "rmsnorm: shapes")
+    _need(delta is None or (delta.dtype == out.dtype and delta.is_contiguous()
+                            and delta.shape == x.shape), "rmsnorm: delta must match x in shape")
+    _need(weight.dtype in (torch.float32, out.dtype), "rmsnorm: weight dtype")
+    if rows is None:
+        _need(n == x.shape[0], "rmsnorm: out rows != x rows")
+    else:
+        _need(rows.dtype == _I32 and rows.numel() >= n, "rmsnorm: rows must be int32 [n]")
+    fn = getattr(_lib(), "kvcm_rmsnorm_" + _suffix(out))
+    wf32 = int(weight.dtype == torch.float32)
+    _check(fn(_p(x), _p(delta), _p(weight), wf32, _p(out), _p(rows), n, H,
+              ctypes.c_float(eps), _stream()), "rmsnorm", f"(hidden={H})")
+
+
+def add_residual(x: torch.Tensor, delta: torch.Tensor) -> None:
+    _cuda(x, delta)
+    _need(x.dtype == torch.float32 and x.is_contiguous() and delta.is_contiguous()
+          and x.shape == delta.shape, "add_residual: shapes")
+    fn = getattr(_lib(), "kvcm_add_residual_" + _suffix(delta))
+    _check(fn(_p(x), _p(delta), ctypes.c_longlong(x.numel()), _stream()), "add_residual")
+
+
+def rope_cache(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+               rotary_dim: int, interleaved: bool, slot_mapping: Optional[torch.Tensor],
+               k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+               nh: int, nkv: int, hd: int, block_size: int, write_cache: bool = True) -> None:
+    """Rotary encoding of the q and k heads of the fused rows in place, then K and V of each row
+    are written to its page slot.  k_cache/v_cache: one layer, [pages, nkv, block, hd]."""
+    _cuda(qkv, positions, inv_freq, slot_mapping, k_cache, v_cache)
+    T = qkv.shape[0]
+    _need(qkv.stride(1) == 1 and qkv.shape[1] >= (nh + 2 * nkv) * hd, "rope_cache: qkv row too short")
+    _need(positions.dtype == _I32 and positions.numel() >= T, "rope_cache: positions int32 [T]")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 >= rotary_dim,
+              "rope_cache: inv_freq must be float32 [rotary_dim/2]")
+    if write_cache:
+        _need(slot_mapping is not None and slot_mapping.dtype == _I32 and slot_mapping.numel() >= T,
+              "rope_cache: slot_mapping int32 [T]")
+        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype and k_cache.is_contiguous()
+              and v_cache.is_contiguous(), "rope_cache: cache dtype/layout")
+        _need(tuple(k_cache.shape[1:]) == (nkv, block_size, hd), "rope_cache: cache page shape")
+    fn = getattr(_lib(), "kvcm_rope_cache_" + _suffix(qkv))
+    _check(fn(_p(qkv), qkv.stride(0), _p(positions), _p(inv_freq), rotary_dim, int(interleaved),
+              _p(slot_mapping), _p(k_cache), _p(v_cache), T, nh, nkv, hd, block_size,
+              int(write_cache), _stream()), "rope_cache", f"(rotary_dim={rotary_dim}, hd={hd})")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(gate_up, out)
+    T, I = out.shape
+    _need(gate_up.is_contiguous() and out.is_contiguous() and gate_up.shape == (T, 2 * I)
+          and gate_up.dtype == out.dtype, "silu_mul: gate_up must be [T, 2I]")
+    fn = getattr(_lib(), "kvcm_silu_mul_" + _suffix(out))
+    _check(fn(_p(gate_up), _p(out), T, I, _stream()), "silu_mul")
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, dst: torch.Tensor) -> None:
+    _cuda(src, rows, dst)
+    n, W = dst.shape
+    _need(src.is_contiguous() and dst.is_contiguous() and src.shape[1] == W and src.dtype == dst.dtype
+          and rows.dtype == _I32 and rows.numel() >= n, "gather_rows: shapes")
+    fn = getattr(_lib(), "kvcm_gather_rows_" + _suffix(dst))
+    _check(fn(_p(src), _p(rows), _p(dst), n, W, _stream()), "gather_rows")
+
+
+def gemm_plain(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
+    """y[M,N] = x[M,K] @ w[N,K]^T with float accumulation in a fixed k order (plain kernel)."""
+    _cuda(x, w, y)
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and y.shape == (M, N), "gemm_plain: shapes")
+    _need(x.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1, "gemm_plain: rows must be dense")
+    _need(x.dtype == w.dtype, "gemm_plain: operand dtypes differ")
+    if x.dtype == torch.float32:
+        _need(y.dtype == torch.float32, "gemm_plain: float32 operands need a float32 result")
+        name = "kvcm_gemm_plain_f32"
+    elif x.dtype == torch.bfloat16:
+        name = "kvcm_gemm_plain_bf16" if y.dtype == torch.bfloat16 else "kvcm_gemm_plain_bf16_f32out"
+        _need(y.dtype in (torch.bfloat16, torch.float32), "gemm_plain: result dtype")
+    else:
+        raise KernelError(f"gemm_plain: dtype {x.dtype}")
+    _check(getattr(_lib(), name)(_p(x), _p(w), _p(y), M, N, K, x.stride(0), w.stride(0), y.stride(0),
+                                 _stream()), "gemm_plain")
+
+
+def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    block_tables: torch.Tensor, row_seq: torch.Tensor, positions: torch.Tensor,
+                    nh: int, nkv: int, hd: int, scale: float, window: int = 0) -> None:
+    """Row-per-query paged attention.  q: [T, >= nh*hd] (row stride free), out: [T, nh*hd];
+    caches [pages, nkv, block, hd]; block_tables int32 [S, max_blocks]."""
+    _cuda(q, out, k_cache, v_cache, block_tables, row_seq, positions)
+    T = out.shape[0]
+    _need(q.stride(1) == 1 and out.stride(1) == 1, "attention: rows must be dense")
+    _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype, "attention: dtypes differ")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape[1] == nkv
+          and k_cache.shape[3] == hd, "attention: cache page shape")
+    _need(block_tables.dtype == _I32 and block_tables.is_contiguous() and block_tables.dim() == 2,
+          "attention: block_tables int32 [S, max_blocks]")
+    _need(row_seq.dtype == _I32 and positions.dtype == _I32 and row_seq.numel() >= T
+          and positions.numel() >= T, "attention: row_seq/positions int32 [T]")
+    fn = getattr(_lib(), "kvcm_attention_plain_" + _suffix(q))
+    _check(fn(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
+              block_tables.shape[1], _p(row_seq), _p(positions), T, nh, nkv, hd, k_cache.shape[2],
+              ctypes.c_float(scale), int(window), _stream()), "attention_plain", f"(hd={hd}, nh={nh}, nkv={nkv})")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(logits, out)
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and out.dtype == _I32
+          and out.numel() >= R, "argmax: logits float32 [R,V], out int32 [R]")
+    _check(_lib().kvcm_argmax_f32(_p(logits), _p(out), R, V, _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor,
+           request_id: torch.Tensor, position: torch.Tensor, out: torch.Tensor) -> None:
+    """Per row: temperature <= 0 -> argmax; else one draw from softmax(logits / temperature) with a
+    uniform number that depends only on (seed, request id, position)."""
+    _cuda(logits, temperature, seed, request_id, position, out)
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: logits float32 [R,V]")
+    _need(temperature.dtype == torch.float32 and seed.dtype == torch.int64
+          and request_id.dtype == torch.int64 and position.dtype == _I32 and out.dtype == _I32,
+          "sample: temperature f32, seed/request_id i64, position/out i32")
+    _need(min(temperature.numel(), seed.numel(), request_id.numel(), position.numel(),
+              out.numel()) >= R, "sample: per-row arrays shorter than the number of rows")
+    _check(_lib().kvcm_sample_f32(_p(logits), _p(temperature), _p(seed), _p(request_id),
+                                  _p(position), _p(out), R, V, _stream()), "sample")
+
+
+# ------------------------------------------------------------------ dispatch of attention
+
+def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    block_tables: torch.Tensor, ctx, nh: int, nkv: int, hd: int, scale: float,
+                    window: int = 0) -> None:
+    """Attention of all rows of a step.  Rows [0, ctx.decode_seqs) are single-row entries, the
+    rest are the rows of longer portions.  ``ctx.options['attention']``: 'plain' forces the plain
+    kernel for every row; float32 storage always uses it (the true 32-bit path)."""
+    mode = ctx.options.get("attention", "auto")
+    if mode == "plain" or q.dtype == torch.float32 or not fast_attention_supported(nh, nkv, hd, k_cache.shape[2]):
+        attention_plain(q, out, k_cache, v_cache, block_tables, ctx.row_seq, ctx.positions,
+                        nh, nkv, hd, scale, window)
+        return
+    nd = ctx.decode_seqs
+    if nd > 0:
+        attention_decode(q[:nd], out[:nd], k_cache, v_cache, block_tables, ctx, nh, nkv, hd, scale, window)
+    if ctx.rows > nd:
+        attention_prefill(q, out, k_cache, v_cache, block_tables, ctx, nh, nkv, hd, scale, window)
+
+
+def fast_attention_supported(nh: int, nkv: int, hd: int, block_size: int) -> bool:
+    return False
+
+
+def skinny_gemm_supported(M: int, N: int, K: int) -> bool:
+    return False

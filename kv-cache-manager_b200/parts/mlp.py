@@ -1,0 +1,28 @@
+"""Gated feed-forward: down( act(x Wg^T) * (x Wu^T) ), gate and up fused into one matrix
+[2I, H] (gate rows first) so that one product feeds the activation kernel
+(``src/model/llama.cpp:120-122``; activation ``src/cuda/kernels.cu:72-82``).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import library as K
+from .base import FEED_FORWARDS, FeedForward, StepContext
+from .linear import Linear
+
+
+@FEED_FORWARDS.register("gated_mlp")
+class GatedMLP(FeedForward):
+    def __init__(self, hidden: int, intermediate: int, activation: str = "silu") -> None:
+        super().__init__()
+        if activation != "silu":
+            raise ValueError(f"gated_mlp: activation '{activation}' has no kernel (only 'silu')")
+        self.hidden, self.intermediate = hidden, intermediate
+        self.gate_up = self.add_child("gate_up", Linear(hidden, 2 * intermediate))
+        self.down = self.add_child("down", Linear(intermediate, hidden))
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        gu = self.gate_up.forward(h, ctx)
+        act = torch.empty((h.shape[0], self.intermediate), dtype=h.dtype, device=h.device)
+        K.silu_mul(gu, act)
+        return self.down.forward(act, ctx)
