@@ -25,7 +25,8 @@ int64_t BatchBuilder::capacity_for(int rows, int seqs, int logit_rows) const {
 }
 
 BatchLayout BatchBuilder::build(const std::vector<BatchEntry>& entries, int32_t* out,
-                                int64_t capacity, int pad_rows, int pad_seqs) const {
+                                int64_t capacity, int pad_rows, int pad_seqs,
+                                int pad_logit_rows) const {
   BatchLayout L;
   const int n_entries = static_cast<int>(entries.size());
   L.entry_order.resize(n_entries);
@@ -64,7 +65,7 @@ BatchLayout BatchBuilder::build(const std::vector<BatchEntry>& entries, int32_t*
     throw std::invalid_argument("batch: padding is only defined for steps of single-row entries");
   if (L.rows - rows != L.seqs - n_entries && (pad_rows || pad_seqs))
     throw std::invalid_argument("batch: padding is for single-row entries (pad_rows - rows must equal pad_seqs - entries)");
-  L.logit_rows = wanted;
+  L.logit_rows = std::max(wanted, pad_logit_rows);
   L.groups = groups_;
   L.max_blocks = max_blocks_;
   L.tile_rows = tile_rows_;

@@ -11,7 +11,8 @@
 //   tile_seq[NT] tile_q0[NT]                    prefill work items: entry and first local row
 //   block_tables[G][S][max_blocks]              page tables, -1 where no page is held
 // Padding (decode steps replayed from a captured graph need fixed shapes): rows and entries up
-// to pad_rows / pad_seqs are filled with slot -1, context 0, token 0.
+// to pad_rows / pad_seqs are filled with slot -1, context 0, token 0; logit_rows is filled up to
+// pad_logit_rows with row 0 (those logits are computed and ignored).
 #pragma once
 #include <cstddef>
 #include <cstdint>
@@ -50,7 +51,7 @@ class BatchBuilder {
   // Fills `out` (capacity in int32s).  Throws std::invalid_argument / std::runtime_error when an
   // entry is inconsistent (no page for a position, portion outside the token list, ...).
   BatchLayout build(const std::vector<BatchEntry>& entries, int32_t* out, int64_t capacity,
-                    int pad_rows = 0, int pad_seqs = 0) const;
+                    int pad_rows = 0, int pad_seqs = 0, int pad_logit_rows = 0) const;
 
  private:
   int block_size_, max_blocks_, groups_, tile_rows_;

@@ -22,7 +22,7 @@ std::vector<BatchEntry> entries_from_plan(const std::vector<ScheduledSeq>& plan)
   entries.reserve(plan.size());
   for (const ScheduledSeq& p : plan) {
     BatchEntry e;
-    e.seq = p.seq;
+    e.seq = p.seq.get();
     e.start = p.start;
     e.num_tokens = p.num_tokens;
     if (p.wants_logits) e.want.push_back(p.num_tokens - 1);
@@ -49,7 +49,7 @@ PYBIND11_MODULE(kvcm_core, m) {
       .def_readwrite("temperature", &SamplingParams::temperature)
       .def_readwrite("seed", &SamplingParams::seed);
 
-  py::class_<Sequence>(m, "Sequence")
+  py::class_<Sequence, std::shared_ptr<Sequence>>(m, "Sequence")
       .def(py::init<>())
       .def_readwrite("id", &Sequence::id)
       .def_readwrite("tokens", &Sequence::tokens)
@@ -216,8 +216,7 @@ PYBIND11_MODULE(kvcm_core, m) {
       .def_readwrite("eos_token_id", &SchedulerConfig::eos_token_id);
 
   py::class_<ScheduledSeq>(m, "ScheduledSeq")
-      .def_property_readonly("seq", [](const ScheduledSeq& p) { return p.seq; },
-                             py::return_value_policy::reference)
+      .def_property_readonly("seq", [](const ScheduledSeq& p) { return p.seq; })
       .def_readonly("start", &ScheduledSeq::start)
       .def_readonly("num_tokens", &ScheduledSeq::num_tokens)
       .def_readonly("is_prefill", &ScheduledSeq::is_prefill)
@@ -272,7 +271,8 @@ PYBIND11_MODULE(kvcm_core, m) {
       // entries: list of (Sequence, start, num_tokens, [wanted places]); `address` is the host
       // address of an int32 buffer of `capacity` elements (e.g. a pinned torch tensor).
       .def("build", [](const BatchBuilder& b, const std::vector<std::tuple<const Sequence*, int, int, std::vector<int32_t>>>& items,
-                       uintptr_t address, int64_t capacity, int pad_rows, int pad_seqs) {
+                       uintptr_t address, int64_t capacity, int pad_rows, int pad_seqs,
+                       int pad_logit_rows) {
         std::vector<BatchEntry> entries;
         entries.reserve(items.size());
         for (const auto& it : items) {
@@ -283,15 +283,16 @@ PYBIND11_MODULE(kvcm_core, m) {
           e.want = std::get<3>(it);
           entries.push_back(std::move(e));
         }
-        return b.build(entries, reinterpret_cast<int32_t*>(address), capacity, pad_rows, pad_seqs);
+        return b.build(entries, reinterpret_cast<int32_t*>(address), capacity, pad_rows, pad_seqs,
+                       pad_logit_rows);
       }, py::arg("entries"), py::arg("address"), py::arg("capacity"), py::arg("pad_rows") = 0,
-         py::arg("pad_seqs") = 0);
+         py::arg("pad_seqs") = 0, py::arg("pad_logit_rows") = 0);
 
   py::class_<Scheduler>(m, "Scheduler")
       .def(py::init<KVManager&, SchedulerConfig>(), py::keep_alive<1, 2>())
       .def("add_request", [](Scheduler& s, int64_t id, const std::vector<int32_t>& tokens,
                              int max_new_tokens, float temperature, uint64_t seed, double arrival) {
-        auto q = std::make_unique<Sequence>();
+        auto q = std::make_shared<Sequence>();
         q->id = id;
         q->tokens = tokens;
         q->prompt_len = static_cast<int>(tokens.size());
@@ -329,16 +330,14 @@ PYBIND11_MODULE(kvcm_core, m) {
         return py::make_tuple(ids, pos, temp, seed);
       })
       .def("build_batch", [](const Scheduler& s, const BatchBuilder& b, uintptr_t address,
-                             int64_t capacity, int pad_rows, int pad_seqs) {
+                             int64_t capacity, int pad_rows, int pad_seqs, int pad_logit_rows) {
         return b.build(entries_from_plan(s.plan()), reinterpret_cast<int32_t*>(address), capacity,
-                       pad_rows, pad_seqs);
+                       pad_rows, pad_seqs, pad_logit_rows);
       }, py::arg("builder"), py::arg("address"), py::arg("capacity"), py::arg("pad_rows") = 0,
-         py::arg("pad_seqs") = 0)
+         py::arg("pad_seqs") = 0, py::arg("pad_logit_rows") = 0)
       .def("update", &Scheduler::update)
       .def("take_finished", [](Scheduler& s) {
-        py::list out;
-        for (auto& q : s.take_finished()) out.append(py::cast(std::move(q)));
-        return out;
+        return s.take_finished();
       })
       .def("idle", &Scheduler::idle)
       .def("num_waiting", &Scheduler::num_waiting)

@@ -11,7 +11,7 @@ Scheduler::Scheduler(KVManager& kv, SchedulerConfig cfg)
   if (cfg_.max_batched_tokens <= 0) throw std::invalid_argument("Scheduler: max_batched_tokens must be positive");
 }
 
-void Scheduler::add(std::unique_ptr<Sequence> seq) {
+void Scheduler::add(std::shared_ptr<Sequence> seq) {
   if (!seq || seq->tokens.empty()) throw std::invalid_argument("Scheduler::add: a request needs at least one token");
   if (seq->prompt_len <= 0) seq->prompt_len = seq->length();
   waiting_.push_back(std::move(seq));
@@ -39,7 +39,7 @@ int Scheduler::portion(const Sequence& s, int budget, bool plan_empty) const {
 }
 
 void Scheduler::evict_youngest() {
-  std::unique_ptr<Sequence> victim = std::move(running_.back());
+  std::shared_ptr<Sequence> victim = std::move(running_.back());
   running_.pop_back();
   kv_.release(*victim);                       // keys and values dropped, tokens kept
   if (victim->state_slot >= 0) { slots_.give_back(victim->state_slot); victim->state_slot = -1; }
@@ -61,7 +61,7 @@ const std::vector<ScheduledSeq>& Scheduler::schedule(double now) {
     if (n == 0) { ++i; continue; }            // no budget left for it in this step
     if (kv_.ensure(s, s.num_computed + n)) {
       const bool in_prompt = s.num_computed < s.prompt_len;
-      plan_.push_back({&s, s.num_computed, n, in_prompt, s.num_computed + n == s.length()});
+      plan_.push_back({running_[i], s.num_computed, n, in_prompt, s.num_computed + n == s.length()});
       budget -= n;
       if (in_prompt) { ctr_.prefill_tokens += n; s.prefill_tokens_computed += n; }
       else ctr_.decode_tokens += n;
@@ -101,7 +101,7 @@ const std::vector<ScheduledSeq>& Scheduler::schedule(double now) {
     }
     head.state_slot = slots_.take();
     if (head.admitted < 0) head.admitted = now;
-    plan_.push_back({&head, head.num_computed, n, true, head.num_computed + n == head.length()});
+    plan_.push_back({waiting_.front(), head.num_computed, n, true, head.num_computed + n == head.length()});
     budget -= n;
     ctr_.prefill_tokens += n;
     ctr_.prefill_tokens_saved += head.cached_tokens;
@@ -147,8 +147,8 @@ void Scheduler::update(const std::vector<int32_t>& sampled, double now) {
   plan_.clear();
 }
 
-std::vector<std::unique_ptr<Sequence>> Scheduler::take_finished() {
-  std::vector<std::unique_ptr<Sequence>> out;
+std::vector<std::shared_ptr<Sequence>> Scheduler::take_finished() {
+  std::vector<std::shared_ptr<Sequence>> out;
   out.swap(finished_);
   return out;
 }

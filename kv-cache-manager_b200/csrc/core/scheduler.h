@@ -33,7 +33,7 @@ struct SchedulerConfig {
 
 // One request's share of a step: compute tokens [start, start + num_tokens).
 struct ScheduledSeq {
-  Sequence* seq;
+  std::shared_ptr<Sequence> seq;   // shared with the queues (and with Python wrappers)
   int start;
   int num_tokens;
   bool is_prefill;     // the portion lies (at least partly) inside the prompt
@@ -50,11 +50,11 @@ class Scheduler {
  public:
   Scheduler(KVManager& kv, SchedulerConfig cfg);
 
-  void add(std::unique_ptr<Sequence> seq);
+  void add(std::shared_ptr<Sequence> seq);
   const std::vector<ScheduledSeq>& schedule(double now);
   // One sampled token for every plan entry with wants_logits, in plan order.
   void update(const std::vector<int32_t>& sampled, double now);
-  std::vector<std::unique_ptr<Sequence>> take_finished();
+  std::vector<std::shared_ptr<Sequence>> take_finished();
 
   bool idle() const { return waiting_.empty() && running_.empty(); }
   size_t num_waiting() const { return waiting_.size(); }
@@ -74,9 +74,9 @@ class Scheduler {
   KVManager& kv_;
   SchedulerConfig cfg_;
   StateSlots slots_;
-  std::deque<std::unique_ptr<Sequence>> waiting_;
-  std::deque<std::unique_ptr<Sequence>> running_;   // admission order: back = youngest
-  std::vector<std::unique_ptr<Sequence>> finished_;
+  std::deque<std::shared_ptr<Sequence>> waiting_;
+  std::deque<std::shared_ptr<Sequence>> running_;   // admission order: back = youngest
+  std::vector<std::shared_ptr<Sequence>> finished_;
   std::vector<ScheduledSeq> plan_;
   SchedulerCounters ctr_;
 };

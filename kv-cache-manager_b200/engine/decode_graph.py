@@ -1,0 +1,98 @@
+"""CUDA graphs for decode-only steps.
+
+A decode step of a small model is a few hundred short kernels; launched one by one their launch
+cost exceeds their run time.  A step in which every request brings exactly one token and samples
+greedily is therefore captured once per shape and replayed.  The shape of a captured step is
+(batch bucket, context bucket): the batch is padded to the bucket with rows that read and write
+nothing, and the bucket of the longest context fixes how the decode attention kernel splits the
+keys.  The integer arrays of the batch live in a buffer owned by the graph; a replay is one
+host-to-device copy into that buffer plus one graph launch.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Tuple
+
+import torch
+
+BATCH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+MIN_CTX_BUCKET = 256
+
+
+def batch_bucket(n: int) -> int:
+    for b in BATCH_BUCKETS:
+        if n <= b:
+            return b
+    return ((n + 255) // 256) * 256
+
+
+def ctx_bucket(n: int) -> int:
+    b = MIN_CTX_BUCKET
+    while b < n:
+        b *= 2
+    return b
+
+
+@dataclass
+class _Captured:
+    graph: torch.cuda.CUDAGraph
+    ints: torch.Tensor
+    sampled: torch.Tensor
+    total_ints: int
+
+
+class DecodeGraphs:
+    def __init__(self, runner, sampler) -> None:
+        self.runner, self.sampler = runner, sampler
+        self.captured: Dict[Tuple[int, int], _Captured] = {}
+        self.pool = None
+        self.replays = 0
+
+    def run(self, sched, n: int) -> torch.Tensor:
+        """Runs the scheduler's current plan (n single-row entries that all sample greedily).
+        Returns the sampled tokens on the device; the first n are real."""
+        r = self.runner
+        b = min(batch_bucket(n), max(r.max_seqs, n))
+        layout = r.build_from_scheduler(sched, pad_rows=b, pad_seqs=b, pad_logit_rows=b)
+        key = (b, ctx_bucket(layout.max_decode_ctx))
+        cap = self.captured.get(key)
+        if cap is None:
+            cap = self._capture(layout, key)
+        if int(layout.total_ints) != cap.total_ints:
+            raise RuntimeError("decode graph: batch layout changed for a captured shape")
+        r.upload(layout, into=cap.ints)
+        cap.graph.replay()
+        self.replays += 1
+        return cap.sampled
+
+    def _capture(self, layout, key) -> _Captured:
+        r = self.runner
+        n_ints = int(layout.total_ints)
+        ints = torch.zeros(n_ints, dtype=torch.int32, device=r.device)
+        sampled = torch.zeros(key[0], dtype=torch.int32, device=r.device)
+        r.upload(layout, into=ints)
+        ctx = r.context(layout, ints=ints)
+        ctx.max_decode_ctx = key[1]
+        ctx.max_ctx = key[1]
+        from ..kernels import library as K
+
+        def body():
+            logits = r.forward(ctx)
+            K.argmax(logits, sampled)
+
+        # One eager run on a side stream first: lazy initialisation (library handles, kernel
+        # attributes) must not happen inside a capture.
+        side = torch.cuda.Stream(device=r.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, pool=self.pool):
+            body()
+        if self.pool is None:
+            self.pool = graph.pool()
+        cap = _Captured(graph, ints, sampled, n_ints)
+        self.captured[key] = cap
+        return cap

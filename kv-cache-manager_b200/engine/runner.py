@@ -59,10 +59,11 @@ class ModelRunner:
         self._check_limits(layout)
         return layout
 
-    def build_from_scheduler(self, sched, pad_rows: int = 0, pad_seqs: int = 0):
+    def build_from_scheduler(self, sched, pad_rows: int = 0, pad_seqs: int = 0,
+                             pad_logit_rows: int = 0):
         self._wait_copy()
         layout = sched.build_batch(self.builder, self.host_ints.data_ptr(), self.capacity,
-                                   pad_rows, pad_seqs)
+                                   pad_rows, pad_seqs, pad_logit_rows)
         self._check_limits(layout)
         return layout
 

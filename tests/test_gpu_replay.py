@@ -1,0 +1,213 @@
+"""The engine against the plain implementation under every way of cutting the work, in float32
+and in bfloat16: each request alone and whole; most of it in one step and the last 32 tokens one
+by one; portions of changing size down to two tokens; and mixed, up to four live requests,
+portions of some beside decoded tokens of others, with so few pages that they are used again.
+In-process through the step function, and through ``bin/trace_run`` as a user runs it."""
+import itertools
+
+import pytest
+import torch
+
+import helpers
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"tiny-a": [5, 17, 33, 64, 100], "tiny-b": [1, 7, 40, 100, 150, 200]}
+CASES = [(n, d) for n in ("tiny-a", "tiny-b") for d in ("float32", "bfloat16")]
+
+
+@pytest.fixture(scope="module")
+def oracle(model_folders):
+    """(name, dtype, request index) -> plain logits [len, vocab] of the whole request."""
+    cache = {}
+
+    def get(name, dtype, i):
+        key = (name, dtype, i)
+        if key not in cache:
+            cfg, w = P.read_model_folder(model_folders(name, dtype))
+            toks = tokens_of(name, i)
+            cache[key] = P.llama_forward(cfg, w, toks, None if dtype == "float32" else torch.bfloat16)
+        return cache[key]
+    return get
+
+
+def tokens_of(name, i):
+    return helpers.random_tokens(LENGTHS[name][i], helpers.TINY[name]["cfg"]["vocab_size"], 100 + i)
+
+
+def replayer(model_folders, name, dtype, max_tokens, **kw):
+    return helpers.Replayer(model_folders(name, dtype), dtype, max_tokens,
+                            helpers.TINY[name]["block_size"], **kw)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_each_request_alone_and_whole(name, dtype, model_folders, oracle):
+    r = replayer(model_folders, name, dtype, 256)
+    for i in range(len(LENGTHS[name])):
+        toks = tokens_of(name, i)
+        got = r.step([dict(id=f"r{i}", tokens=toks, want=list(range(len(toks))))], end=[f"r{i}"])
+        helpers.assert_logits_close(got, oracle(name, dtype, i), dtype, f"{name} whole request {i}")
+    assert r.kv.blocks_in_use() == 0
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_prefill_then_last_32_tokens_one_by_one(name, dtype, model_folders, oracle):
+    r = replayer(model_folders, name, dtype, 256)
+    for i, n in enumerate(LENGTHS[name]):
+        if n < 34:
+            continue
+        toks = tokens_of(name, i)
+        head = n - 32
+        outs = [r.step([dict(id="x", tokens=toks[:head], want=list(range(head)))])]
+        for t in range(head, n):
+            outs.append(r.step([dict(id="x", tokens=[toks[t]], want=[0])], end=["x"] if t == n - 1 else []))
+        got = torch.cat(outs)
+        ref = oracle(name, dtype, i)
+        helpers.assert_logits_close(got[:head], ref[:head], dtype, f"{name} request {i} prefill")
+        helpers.assert_logits_close(got[head:], ref[head:], dtype, f"{name} request {i} decode")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_portions_of_changing_size_down_to_two_tokens(name, dtype, model_folders, oracle):
+    r = replayer(model_folders, name, dtype, 256)
+    sizes = itertools.cycle([7, 2, 13, 2, 5, 31, 3, 2, 17])
+    for i, n in enumerate(LENGTHS[name]):
+        toks = tokens_of(name, i)
+        outs, at = [], 0
+        while at < n:
+            k = min(next(sizes), n - at)
+            outs.append(r.step([dict(id="x", tokens=toks[at:at + k], want=list(range(k)))],
+                               end=["x"] if at + k == n else []))
+            at += k
+        helpers.assert_logits_close(torch.cat(outs), oracle(name, dtype, i), dtype,
+                                    f"{name} request {i} in portions")
+
+
+def mixed_trace(name):
+    """A schedule with up to four live requests: portions of some beside single tokens of others.
+    Returns (steps, place of every wanted row: (request, position))."""
+    n_req = len(LENGTHS[name])
+    toks = [tokens_of(name, i) for i in range(n_req)]
+    fed = [0] * n_req
+    sizes = itertools.cycle([9, 2, 21, 4, 2, 14])
+    waiting = list(range(n_req))
+    live, steps, places = [], [], []
+    step_no = 0
+    while waiting or live:
+        while waiting and len(live) < 4 and (step_no % 2 == 0 or not live):
+            live.append(waiting.pop(0))
+        entries, ended, where = [], [], []
+        for j, i in enumerate(list(live)):
+            n = len(toks[i])
+            left = n - fed[i]
+            # the last 6 tokens of every request go one by one (decode rows beside portions)
+            k = 1 if left <= 6 else min(next(sizes), left - 6)
+            if (step_no + j) % 5 == 4 and len(live) > 1:
+                continue                                   # left out of this step, goes on later
+            entries.append(dict(id=f"r{i}", tokens=toks[i][fed[i]:fed[i] + k], want=list(range(k))))
+            where += [(i, fed[i] + w) for w in range(k)]
+            fed[i] += k
+            if fed[i] == n:
+                ended.append(f"r{i}")
+                live.remove(i)
+        steps.append(dict(step=step_no, entries=entries, end=ended))
+        places.append(where)
+        step_no += 1
+    return steps, places
+
+
+def mixed_pool_tokens(name):
+    """The most tokens live at any time, each request's count rounded up to a multiple of 64."""
+    steps, _ = mixed_trace(name)
+    held, peak = {}, 0
+    for s in steps:
+        for e in s["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        peak = max(peak, sum(helpers.roundup(v, 64) for v in held.values()))
+        for rid in s["end"]:
+            held.pop(rid)
+    return peak
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_mixed_batches_with_pages_used_again(name, dtype, model_folders, oracle):
+    steps, places = mixed_trace(name)
+    assert max(len(s["entries"]) for s in steps) == 4
+    assert any(any(len(e["tokens"]) == 1 for e in s["entries"]) and any(len(e["tokens"]) > 1 for e in s["entries"])
+               for s in steps), "the trace must mix portions and single tokens"
+    r = replayer(model_folders, name, dtype, mixed_pool_tokens(name))
+    for s, where in zip(steps, places):
+        got = r.step(s["entries"], s["end"])
+        ref = torch.stack([oracle(name, dtype, i)[pos] for i, pos in where])
+        helpers.assert_logits_close(got, ref, dtype, f"{name} mixed step {s['step']}")
+    assert len(set(r.pages_seen)) <= r.kv.num_blocks()
+    assert any(len(owners) > 1 for owners in r.page_owners.values()), "no page was used again"
+    total_pages = sum(helpers.roundup(n, r.runner.block_size) // r.runner.block_size for n in LENGTHS[name])
+    assert total_pages > r.kv.num_blocks(), "the pool must be too small to hold every request at once"
+    assert r.kv.blocks_in_use() == 0
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_trace_tool_as_a_user_runs_it(name, dtype, model_folders, oracle, tmp_path):
+    steps, places = mixed_trace(name)
+    out = helpers.run_trace_tool(model_folders(name, dtype), dtype, steps, mixed_pool_tokens(name),
+                                 str(tmp_path), ["--block-size", str(helpers.TINY[name]["block_size"])])
+    for s, where in zip(steps, places):
+        ref = torch.stack([oracle(name, dtype, i)[pos] for i, pos in where])
+        helpers.assert_logits_close(torch.from_numpy(out[s["step"]]), ref, dtype,
+                                    f"{name} trace_run step {s['step']}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_tool_default_page_size_and_steps_without_wants(dtype, model_folders, oracle, tmp_path):
+    name = "tiny-a"
+    toks = tokens_of(name, 3)
+    steps = [dict(step=0, entries=[dict(id="a", tokens=toks[:40], want=[])], end=[]),
+             dict(step=1, entries=[dict(id="a", tokens=toks[40:], want=[0, 23])], end=["a"]),
+             dict(step=2, entries=[dict(id="b", tokens=toks[:3], want=[2])], end=["b"])]
+    out = helpers.run_trace_tool(model_folders(name, dtype), dtype, steps, 64, str(tmp_path))
+    ref = oracle(name, dtype, 3)
+    assert sorted(out) == [1, 2]
+    helpers.assert_logits_close(torch.from_numpy(out[1]), ref[[40, 63]], dtype, "wants in a later portion")
+    helpers.assert_logits_close(torch.from_numpy(out[2]), ref[[2]], dtype, "pages of a used again by b")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_first_tokens_of_a_sequence(name, dtype, model_folders, oracle):
+    """Positions 0, 1, 2: one key, no history, the first slot of the first page."""
+    r = replayer(model_folders, name, dtype, 64)
+    i = 2
+    toks = tokens_of(name, i)
+    outs = [r.step([dict(id="x", tokens=[toks[t]], want=[0])]) for t in range(3)]
+    helpers.assert_logits_close(torch.cat(outs), oracle(name, dtype, i)[:3], dtype, f"{name} first tokens")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_long_decoding(name, dtype, model_folders, oracle):
+    """Every token after the first decoded one by one, across many page edges."""
+    r = replayer(model_folders, name, dtype, 256)
+    i = len(LENGTHS[name]) - 1
+    toks = tokens_of(name, i)
+    outs = [r.step([dict(id="x", tokens=[t], want=[0])]) for t in toks]
+    helpers.assert_logits_close(torch.cat(outs), oracle(name, dtype, i), dtype, f"{name} long decoding")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuts_agree_bit_for_bit_with_plain_kernels(dtype, model_folders):
+    """With the plain kernels every row is computed by the same sums whatever the batch, so two
+    ways of cutting give equal bits; a difference here is a fault of the cache or the batch."""
+    name = "tiny-b"
+    opts = {"attention": "plain", "gemm": "plain"}
+    toks = tokens_of(name, 3)
+    a = replayer(model_folders, name, dtype, 128, options=opts)
+    whole = a.step([dict(id="x", tokens=toks, want=list(range(len(toks))))])
+    b = replayer(model_folders, name, dtype, 128, options=opts)
+    parts, at = [], 0
+    for k in itertools.cycle([5, 2, 1, 19]):
+        k = min(k, len(toks) - at)
+        parts.append(b.step([dict(id="x", tokens=toks[at:at + k], want=list(range(k)))]))
+        at += k
+        if at == len(toks):
+            break
+    assert torch.equal(torch.cat(parts), whole)
