@@ -174,7 +174,11 @@ PYBIND11_MODULE(kvcm_core, m) {
       .def("blocks_in_use", &KVManager::blocks_in_use, py::arg("group") = 0)
       .def("blocks_cached_free", &KVManager::blocks_cached_free)
       .def("prefix_stats", &KVManager::prefix_stats)
-      .def("stats", [](const KVManager& k, const std::vector<const Sequence*>& live) { return k.stats(live); });
+      .def("stats", [](const KVManager& k, const std::vector<std::shared_ptr<Sequence>>& live) {
+        std::vector<const Sequence*> raw;
+        for (const auto& q : live) raw.push_back(q.get());
+        return k.stats(raw);
+      });
 
   py::class_<PagedManager, KVManager>(m, "PagedManager")
       .def(py::init<int, int, int, bool, int, std::vector<LayerGroupSpec>>(), py::arg("num_blocks"),
@@ -342,7 +346,15 @@ PYBIND11_MODULE(kvcm_core, m) {
       .def("idle", &Scheduler::idle)
       .def("num_waiting", &Scheduler::num_waiting)
       .def("num_running", &Scheduler::num_running)
-      .def("live", &Scheduler::live, py::return_value_policy::reference_internal)
+      .def("live", [](const Scheduler& s) {
+        return std::vector<std::shared_ptr<Sequence>>(s.running().begin(), s.running().end());
+      })
+      // sum over running requests of the tokens whose keys and values are in the cache
+      .def("cached_tokens_total", [](const Scheduler& s) {
+        int64_t n = 0;
+        for (const auto& q : s.running()) n += q->num_computed;
+        return n;
+      })
       .def("counters", &Scheduler::counters)
       .def("reset_counters", &Scheduler::reset_counters)
       .def("slots_taken", [](const Scheduler& s) { return s.slots().num_taken(); })

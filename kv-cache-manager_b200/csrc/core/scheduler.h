@@ -61,6 +61,7 @@ class Scheduler {
   size_t num_running() const { return running_.size(); }
   const std::vector<ScheduledSeq>& plan() const { return plan_; }
   std::vector<const Sequence*> live() const;
+  const std::deque<std::shared_ptr<Sequence>>& running() const { return running_; }
   const SchedulerCounters& counters() const { return ctr_; }
   void reset_counters() { ctr_ = {}; }
   KVManager& kv() { return kv_; }

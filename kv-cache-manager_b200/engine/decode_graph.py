@@ -39,6 +39,7 @@ class _Captured:
     ints: torch.Tensor
     sampled: torch.Tensor
     total_ints: int
+    kernels: int = 0          # launches of this engine's kernels inside one replay
 
 
 class DecodeGraphs:
@@ -47,8 +48,9 @@ class DecodeGraphs:
         self.captured: Dict[Tuple[int, int], _Captured] = {}
         self.pool = None
         self.replays = 0
+        self.kernels_last = 0
 
-    def run(self, sched, n: int) -> torch.Tensor:
+    def run(self, sched, n: int, timer=None) -> torch.Tensor:
         """Runs the scheduler's current plan (n single-row entries that all sample greedily).
         Returns the sampled tokens on the device; the first n are real."""
         r = self.runner
@@ -61,8 +63,13 @@ class DecodeGraphs:
         if int(layout.total_ints) != cap.total_ints:
             raise RuntimeError("decode graph: batch layout changed for a captured shape")
         r.upload(layout, into=cap.ints)
+        if timer is not None:
+            timer.start()
         cap.graph.replay()
+        if timer is not None:
+            timer.stop()
         self.replays += 1
+        self.kernels_last = cap.kernels
         return cap.sampled
 
     def _capture(self, layout, key) -> _Captured:
@@ -89,10 +96,12 @@ class DecodeGraphs:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
+        before = K.launch_count()
         with torch.cuda.graph(graph, pool=self.pool):
             body()
+        kernels = K.launch_count() - before
         if self.pool is None:
             self.pool = graph.pool()
-        cap = _Captured(graph, ints, sampled, n_ints)
+        cap = _Captured(graph, ints, sampled, n_ints, kernels)
         self.captured[key] = cap
         return cap

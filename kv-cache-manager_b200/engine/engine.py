@@ -37,6 +37,31 @@ class StepInfo:
     graph: bool = False
 
 
+class DeviceTimer:
+    """CUDA events around the device work of each step (after the step's host-to-device copy,
+    up to and including sampling).  ``total_ms()`` synchronises and sums."""
+
+    def __init__(self) -> None:
+        self.pairs = []
+
+    def start(self) -> None:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self._open = e
+
+    def stop(self) -> None:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.pairs.append((self._open, e))
+
+    def total_ms(self) -> float:
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in self.pairs)
+
+    def reset(self) -> None:
+        self.pairs = []
+
+
 class Engine:
     def __init__(self, spec: ModelSpec, cfg: Optional[EngineConfig] = None) -> None:
         self.cfg = cfg = cfg or EngineConfig()
@@ -74,6 +99,7 @@ class Engine:
         self._next_id = 0
         self._t0 = time.perf_counter()
         self._has_state = plan.has_state
+        self.device_timer = None          # a DeviceTimer brackets the device work of every step
 
     @classmethod
     def from_folder(cls, folder: str, cfg: Optional[EngineConfig] = None) -> "Engine":
@@ -126,17 +152,22 @@ class Engine:
         if wants:
             ids, pos, temps, seeds = self.sched.plan_sampling()
             greedy_only = not any(t > 0 for t in temps)
+        timed = self.device_timer is not None
         if self.graphs is not None and singles == entries and wants == entries and greedy_only:
-            sampled_dev = self.graphs.run(self.sched, entries)
+            sampled_dev = self.graphs.run(self.sched, entries, self.device_timer)
             info.graph = True
         else:
             layout = self.runner.build_from_scheduler(self.sched)
             self.runner.upload(layout)
+            if timed:
+                self.device_timer.start()
             logits = self.runner.forward(self.runner.context(layout))
             sampled_dev = None
             if wants:
                 sampled_dev = (self.sampler.greedy(logits) if greedy_only else
                                self.sampler.sample(logits, ids, pos, temps, seeds))
+            if timed:
+                self.device_timer.stop()
         info.h2d_bytes = self.runner.h2d_bytes_last + (self.sampler.h2d_bytes_last if wants else 0)
         sampled: List[int] = sampled_dev[:wants].tolist() if wants else []   # the step's one sync
         info.d2h_bytes = 4 * wants
