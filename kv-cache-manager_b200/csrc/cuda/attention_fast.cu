@@ -1,0 +1,459 @@
+// bfloat16 attention over the paged cache on tensor cores (m16n8k16, float accumulate).
+//
+// decode  : one query token per request.  One block per (context partition, KV head x tile of 16
+//           query heads, request): the query heads that share a KV head are the 16 rows of the
+//           tile, so every key and value is read once for the whole group (the reference's kernel
+//           has the same aim, src/cuda/paged_attention.cu:3-4).  The context is split into
+//           partitions so that small batches still fill the GPU; partial (max, sum, output) are
+//           merged by a second kernel (as the reference's v2, :186-203).  With one partition the
+//           block writes the result itself (v1).
+// prefill : portions of more than one token.  One block per (64 query rows of a request, query
+//           head); keys up to each row's own position come from the pages, K and V of the portion
+//           included (they were written before), so a portion may start anywhere in a request.
+//           The reference has no such kernel (it runs prefill rows through the decode kernel,
+//           docs/design.md:113-114).
+// Any head_dim that is a multiple of 16 up to 256, any page size, any number of heads and groups,
+// optional window (keys t > position - window).  Scores are scaled in float after the product;
+// softmax by exp2 with log2(e) folded into the scale; probabilities are rounded to bfloat16 for
+// the P*V product, sums stay float.
+#include "attention_mma.cuh"
+
+namespace kvcm {
+
+constexpr int kAttnThreads = 128;     // 4 warps
+
+struct DecodeParams {
+  const bf16* q; int q_stride;
+  bf16* out; int out_stride;
+  const bf16* k_cache; const bf16* v_cache;
+  const int* block_tables; int max_blocks;
+  const int* seq_ctx_len;
+  float* part_o; float* part_ml;
+  int nh, nkv, block_size, window, part_size, num_parts;
+  float scale_log2;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads)
+attn_decode_kernel(DecodeParams p) {
+  constexpr int LD = HD + 8;
+  constexpr bool Q_IN_REGS = HD <= 128;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qtile = reinterpret_cast<bf16*>(smem_raw);                 // [16][LD]
+  bf16* kbuf = qtile + 16 * LD;                                    // [2][64][LD]
+  bf16* vbuf = kbuf + 2 * kKeyTile * LD;                           // [2][64][LD]
+
+  const int part = blockIdx.x, seq = blockIdx.z;
+  const int G = p.nh / p.nkv;
+  const int head_tiles = (G + 15) / 16;
+  const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y - kvh * head_tiles;
+  const int head0 = kvh * G + ht * 16;
+  const int heads_here = min(16, G - ht * 16);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  const int ctx = p.seq_ctx_len[seq];
+  const int lo = (p.window > 0 && ctx > p.window) ? ctx - p.window : 0;
+  const int begin = max(lo, part * p.part_size);
+  const int end = min(ctx, (part + 1) * p.part_size);
+  if (begin >= end) {                                              // nothing to read here
+    for (int i = tid; i < heads_here * HD; i += kAttnThreads) {
+      const int r = i / HD, d = i - r * HD;
+      if (p.num_parts == 1) {
+        p.out[size_t(seq) * p.out_stride + size_t(head0 + r) * HD + d] = __float2bfloat16_rn(0.f);
+      } else if (d == 0) {
+        float* ml = p.part_ml + ((size_t(seq) * p.nh + head0 + r) * p.num_parts + part) * 2;
+        ml[0] = -INFINITY;
+        ml[1] = 0.f;
+      }
+    }
+    return;
+  }
+  const int* table = p.block_tables + size_t(seq) * p.max_blocks;
+
+  for (int c = tid; c < 16 * (HD / 8); c += kAttnThreads) {        // Q tile, zero rows beyond the group
+    const int r = c / (HD / 8), ch = c - r * (HD / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < heads_here)
+      v = *reinterpret_cast<const uint4*>(p.q + size_t(seq) * p.q_stride + size_t(head0 + r) * HD + ch * 8);
+    *reinterpret_cast<uint4*>(qtile + r * LD + ch * 8) = v;
+  }
+
+  const int t_first = (begin / kKeyTile) * kKeyTile;
+  const int n_tiles = (end - t_first + kKeyTile - 1) / kKeyTile;
+  load_kv_tile<HD>(kbuf, p.k_cache, table, t_first, begin, end, kvh, p.nkv, p.block_size, tid, kAttnThreads);
+  load_kv_tile<HD>(vbuf, p.v_cache, table, t_first, begin, end, kvh, p.nkv, p.block_size, tid, kAttnThreads);
+  cp_async_commit();
+  __syncthreads();                                                 // qtile is written
+
+  uint32_t qa[Q_IN_REGS ? HD / 16 : 1][4];
+  if constexpr (Q_IN_REGS) load_q_frags<HD>(reinterpret_cast<uint32_t(&)[HD / 16][4]>(qa), qtile, lane);
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+  for (int i = 0; i < n_tiles; ++i) {
+    const int t0 = t_first + i * kKeyTile;
+    if (i + 1 < n_tiles) {
+      const int nb = (i + 1) & 1;
+      load_kv_tile<HD>(kbuf + nb * kKeyTile * LD, p.k_cache, table, t0 + kKeyTile, begin, end, kvh, p.nkv,
+                       p.block_size, tid, kAttnThreads);
+      load_kv_tile<HD>(vbuf + nb * kKeyTile * LD, p.v_cache, table, t0 + kKeyTile, begin, end, kvh, p.nkv,
+                       p.block_size, tid, kAttnThreads);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int kb = t0 + warp * 16;                                 // this warp's 16 keys
+    if (kb < end && kb + 16 > begin) {
+      const bf16* kt = kbuf + (i & 1) * kKeyTile * LD + warp * 16 * LD;
+      const bf16* vt = vbuf + (i & 1) * kKeyTile * LD + warp * 16 * LD;
+      float s[2][4];
+      if constexpr (Q_IN_REGS) {
+        qk_16x16<HD>(s, reinterpret_cast<const uint32_t(&)[HD / 16][4]>(qa), kt, lane);
+      } else {
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) s[a][b] = 0.f;
+        const int krow = (lane & 7) + ((lane >> 4) << 3), kcol = ((lane >> 3) & 1) << 3;
+#pragma unroll 4
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          uint32_t a[4], b[4];
+          ldmatrix_x4(a, qtile + (lane & 15) * LD + kk * 16 + ((lane >> 4) << 3));
+          ldmatrix_x4(b, kt + krow * LD + kk * 16 + kcol);
+          mma_bf16(s[0], a, b[0], b[1]);
+          mma_bf16(s[1], a, b[2], b[3]);
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int key = kb + 8 * h + 2 * t4 + (j & 1);
+          s[h][j] = (key >= begin && key < end) ? s[h][j] * p.scale_log2 : -INFINITY;
+        }
+      uint32_t pa[4];
+      softmax_step<HD>(s, m, l, o, pa);
+      pv_16x16<HD>(o, pa, vt, lane);
+    }
+    __syncthreads();                                               // the buffer is loaded again next round
+  }
+
+  // ---- merge the four warps (each saw different keys) through shared memory
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  float* mo = reinterpret_cast<float*>(kbuf);                       // [4][16][HD]
+  float* mm = mo + 4 * 16 * HD;                                     // [4][16]
+  float* mlsum = mm + 4 * 16;                                       // [4][16]
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) {
+    float* base = mo + (warp * 16) * HD + d * 8 + 2 * t4;
+    base[g * HD] = o[d][0];
+    base[g * HD + 1] = o[d][1];
+    base[(g + 8) * HD] = o[d][2];
+    base[(g + 8) * HD + 1] = o[d][3];
+  }
+  if (t4 == 0) {
+    mm[warp * 16 + g] = m[0];
+    mm[warp * 16 + g + 8] = m[1];
+    mlsum[warp * 16 + g] = l[0];
+    mlsum[warp * 16 + g + 8] = l[1];
+  }
+  __syncthreads();
+  for (int i = tid; i < heads_here * HD; i += kAttnThreads) {
+    const int r = i / HD, d = i - r * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mm[w * 16 + r]);
+    float acc = 0.f, L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = mm[w * 16 + r];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      acc += f * mo[(w * 16 + r) * HD + d];
+      L += f * mlsum[w * 16 + r];
+    }
+    const int head = head0 + r;
+    if (p.num_parts == 1) {
+      p.out[size_t(seq) * p.out_stride + size_t(head) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    } else {
+      const size_t idx = (size_t(seq) * p.nh + head) * p.num_parts + part;
+      p.part_o[idx * HD + d] = acc;
+      if (d == 0) {
+        p.part_ml[idx * 2] = M;
+        p.part_ml[idx * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// Merges the partitions of one (request, head): out = sum_p 2^(m_p - M) o_p / sum_p 2^(m_p - M) l_p.
+__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         bf16* __restrict__ out, int out_stride, int nh, int hd, int num_parts) {
+  const int seq = blockIdx.x, head = blockIdx.y;
+  const size_t base = (size_t(seq) * nh + head) * num_parts;
+  float M = -INFINITY;
+  for (int i = 0; i < num_parts; ++i) M = fmaxf(M, part_ml[(base + i) * 2]);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f, L = 0.f;
+    for (int i = 0; i < num_parts; ++i) {
+      const float mp = part_ml[(base + i) * 2];
+      if (mp == -INFINITY) continue;
+      const float f = exp2f(mp - M);
+      acc += f * part_o[(base + i) * hd + d];
+      L += f * part_ml[(base + i) * 2 + 1];
+    }
+    out[size_t(seq) * out_stride + size_t(head) * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+}
+
+// ------------------------------------------------------------------------------- prefill
+
+struct PrefillParams {
+  const bf16* q; int q_stride;
+  bf16* out; int out_stride;
+  const bf16* k_cache; const bf16* v_cache;
+  const int* block_tables; int max_blocks;
+  const int* tile_seq; const int* tile_q0;
+  const int* seq_q_start; const int* seq_q_len; const int* seq_ctx_len;
+  int nh, nkv, block_size, window;
+  float scale_log2;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads)
+attn_prefill_kernel(PrefillParams p) {
+  constexpr int LD = HD + 8;
+  constexpr bool Q_IN_REGS = HD <= 128;
+  constexpr int BM = 64;                                            // query rows per block
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qtile = reinterpret_cast<bf16*>(smem_raw);                  // [64][LD]
+  bf16* kbuf = qtile + BM * LD;                                     // [2][64][LD]
+  bf16* vbuf = kbuf + 2 * kKeyTile * LD;
+
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int kvh = head / (p.nh / p.nkv);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int seq = p.tile_seq[tile], q0 = p.tile_q0[tile];
+  const int q_start = p.seq_q_start[seq], q_len = p.seq_q_len[seq], ctx = p.seq_ctx_len[seq];
+  const int rows_here = min(BM, q_len - q0);
+  const int pos0 = ctx - q_len + q0;                                // position of the tile's first row
+  const int hi = pos0 + rows_here;                                  // keys [lo, hi) matter to the tile
+  const int lo = (p.window > 0) ? max(0, pos0 - p.window + 1) : 0;
+  const int* table = p.block_tables + size_t(seq) * p.max_blocks;
+
+  for (int c = tid; c < BM * (HD / 8); c += kAttnThreads) {
+    const int r = c / (HD / 8), ch = c - r * (HD / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows_here)
+      v = *reinterpret_cast<const uint4*>(p.q + size_t(q_start + q0 + r) * p.q_stride + size_t(head) * HD + ch * 8);
+    *reinterpret_cast<uint4*>(qtile + r * LD + ch * 8) = v;
+  }
+  const int t_first = (lo / kKeyTile) * kKeyTile;
+  const int n_tiles = (hi - t_first + kKeyTile - 1) / kKeyTile;
+  load_kv_tile<HD>(kbuf, p.k_cache, table, t_first, lo, hi, kvh, p.nkv, p.block_size, tid, kAttnThreads);
+  load_kv_tile<HD>(vbuf, p.v_cache, table, t_first, lo, hi, kvh, p.nkv, p.block_size, tid, kAttnThreads);
+  cp_async_commit();
+  __syncthreads();
+
+  const bf16* qw = qtile + warp * 16 * LD;
+  uint32_t qa[Q_IN_REGS ? HD / 16 : 1][4];
+  if constexpr (Q_IN_REGS) load_q_frags<HD>(reinterpret_cast<uint32_t(&)[HD / 16][4]>(qa), qw, lane);
+
+  const int row_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};   // positions of this thread's rows
+  const bool warp_live = warp * 16 < rows_here;
+  const int warp_last_pos = pos0 + min(warp * 16 + 15, rows_here - 1);
+  const int warp_first_lo = (p.window > 0) ? pos0 + warp * 16 - p.window + 1 : 0;
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+  for (int i = 0; i < n_tiles; ++i) {
+    const int t0 = t_first + i * kKeyTile;
+    if (i + 1 < n_tiles) {
+      const int nb = (i + 1) & 1;
+      load_kv_tile<HD>(kbuf + nb * kKeyTile * LD, p.k_cache, table, t0 + kKeyTile, lo, hi, kvh, p.nkv,
+                       p.block_size, tid, kAttnThreads);
+      load_kv_tile<HD>(vbuf + nb * kKeyTile * LD, p.v_cache, table, t0 + kKeyTile, lo, hi, kvh, p.nkv,
+                       p.block_size, tid, kAttnThreads);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (warp_live) {
+#pragma unroll 1
+      for (int sub = 0; sub < kKeyTile / 16; ++sub) {
+        const int kb = t0 + sub * 16;
+        if (kb > warp_last_pos || kb >= hi || kb + 16 <= max(lo, warp_first_lo)) continue;   // all masked
+        const bf16* kt = kbuf + (i & 1) * kKeyTile * LD + sub * 16 * LD;
+        const bf16* vt = vbuf + (i & 1) * kKeyTile * LD + sub * 16 * LD;
+        float s[2][4];
+        if constexpr (Q_IN_REGS) {
+          qk_16x16<HD>(s, reinterpret_cast<const uint32_t(&)[HD / 16][4]>(qa), kt, lane);
+        } else {
+#pragma unroll
+          for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) s[a][b] = 0.f;
+          const int krow = (lane & 7) + ((lane >> 4) << 3), kcol = ((lane >> 3) & 1) << 3;
+#pragma unroll 4
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            uint32_t a[4], b[4];
+            ldmatrix_x4(a, qw + (lane & 15) * LD + kk * 16 + ((lane >> 4) << 3));
+            ldmatrix_x4(b, kt + krow * LD + kk * 16 + kcol);
+            mma_bf16(s[0], a, b[0], b[1]);
+            mma_bf16(s[1], a, b[2], b[3]);
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int key = kb + 8 * h + 2 * t4 + (j & 1);
+            const int rp = row_pos[j >> 1];
+            const bool ok = key <= rp && key >= lo && key < hi && (p.window <= 0 || key > rp - p.window);
+            s[h][j] = ok ? s[h][j] * p.scale_log2 : -INFINITY;
+          }
+        uint32_t pa[4];
+        softmax_step<HD>(s, m, l, o, pa);
+        pv_16x16<HD>(o, pa, vt, lane);
+      }
+    }
+    __syncthreads();
+  }
+  if (!warp_live) return;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int local = warp * 16 + g + 8 * r;
+    if (local >= rows_here) continue;
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    bf16* dst = p.out + size_t(q_start + q0 + local) * p.out_stride + size_t(head) * HD + 2 * t4;
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d)
+      *reinterpret_cast<uint32_t*>(dst + d * 8) = pack_bf16(o[d][2 * r] * inv, o[d][2 * r + 1] * inv);
+  }
+}
+
+template <int HD> size_t decode_smem() {
+  const size_t tiles = size_t(16 + 4 * kKeyTile) * (HD + 8) * sizeof(bf16);
+  const size_t merge = size_t(16) * (HD + 8) * sizeof(bf16) + (size_t(4) * 16 * HD + 2 * 4 * 16) * sizeof(float);
+  return tiles > merge ? tiles : merge;
+}
+template <int HD> size_t prefill_smem() { return size_t(64 + 4 * kKeyTile) * (HD + 8) * sizeof(bf16); }
+
+template <int HD>
+int launch_decode(const DecodeParams& p, int seqs, cudaStream_t s) {
+  auto kernel = attn_decode_kernel<HD>;
+  const size_t smem = decode_smem<HD>();
+  static bool configured = false;                                  // per instantiation, set once
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  const int G = p.nh / p.nkv;
+  dim3 grid(p.num_parts, p.nkv * ((G + 15) / 16), seqs);
+  kernel<<<grid, kAttnThreads, smem, s>>>(p);
+  return KVCM_LAUNCH_RESULT();
+}
+
+template <int HD>
+int launch_prefill(const PrefillParams& p, int tiles, cudaStream_t s) {
+  auto kernel = attn_prefill_kernel<HD>;
+  const size_t smem = prefill_smem<HD>();
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  dim3 grid(tiles, p.nh);
+  kernel<<<grid, kAttnThreads, smem, s>>>(p);
+  return KVCM_LAUNCH_RESULT();
+}
+
+#define KVCM_FOR_HEAD_DIMS(X) \
+  X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128) X(160) X(192) X(224) X(256)
+
+}  // namespace kvcm
+
+using namespace kvcm;
+
+// 1 if the tensor-core kernels take this head_dim (else the caller uses the plain kernel).
+KVCM_API int kvcm_attention_fast_supports(int hd) {
+#define X(N) if (hd == N) return 1;
+  KVCM_FOR_HEAD_DIMS(X)
+#undef X
+  return 0;
+}
+
+// Floats of scratch the decode kernel needs for `seqs` requests split into `num_parts`.
+KVCM_API long long kvcm_attention_decode_scratch_floats(int seqs, int nh, int hd, int num_parts) {
+  return num_parts <= 1 ? 0 : (long long)seqs * nh * num_parts * (hd + 2);
+}
+
+KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                        const void* k_cache, const void* v_cache, const int* block_tables,
+                                        int max_blocks, const int* seq_ctx_len, int seqs, int nh, int nkv,
+                                        int hd, int block_size, float scale, int window, int part_size,
+                                        int num_parts, float* scratch, void* stream) {
+  if (seqs == 0) return 0;
+  if (nkv <= 0 || nh % nkv || part_size <= 0 || part_size % kKeyTile || num_parts < 1) return KVCM_ERR_UNSUPPORTED;
+  if (num_parts > 1 && scratch == nullptr) return KVCM_ERR_UNSUPPORTED;
+  DecodeParams p;
+  p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.out_stride = out_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.block_tables = block_tables; p.max_blocks = max_blocks; p.seq_ctx_len = seq_ctx_len;
+  p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)seqs * nh * num_parts * hd : nullptr;
+  p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
+  p.part_size = part_size; p.num_parts = num_parts;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  int rc = KVCM_ERR_UNSUPPORTED;
+#define X(N) if (hd == N) rc = launch_decode<N>(p, seqs, (cudaStream_t)stream);
+  KVCM_FOR_HEAD_DIMS(X)
+#undef X
+  if (rc != 0 || num_parts == 1) return rc;
+  attn_decode_merge_kernel<<<dim3(seqs, nh), hd < 64 ? 32 : 64, 0, (cudaStream_t)stream>>>(
+      p.part_o, p.part_ml, p.out, out_stride, nh, hd, num_parts);
+  return KVCM_LAUNCH_RESULT();
+}
+
+KVCM_API int kvcm_attention_prefill_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                         const void* k_cache, const void* v_cache, const int* block_tables,
+                                         int max_blocks, const int* tile_seq, const int* tile_q0,
+                                         const int* seq_q_start, const int* seq_q_len, const int* seq_ctx_len,
+                                         int tiles, int nh, int nkv, int hd, int block_size, float scale,
+                                         int window, void* stream) {
+  if (tiles == 0) return 0;
+  if (nkv <= 0 || nh % nkv) return KVCM_ERR_UNSUPPORTED;
+  PrefillParams p;
+  p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.out_stride = out_stride;
+  p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.block_tables = block_tables; p.max_blocks = max_blocks; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
+  p.seq_q_start = seq_q_start; p.seq_q_len = seq_q_len; p.seq_ctx_len = seq_ctx_len;
+  p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  int rc = KVCM_ERR_UNSUPPORTED;
+#define X(N) if (hd == N) rc = launch_prefill<N>(p, tiles, (cudaStream_t)stream);
+  KVCM_FOR_HEAD_DIMS(X)
+#undef X
+  return rc;
+}

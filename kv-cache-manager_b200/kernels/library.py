@@ -249,7 +249,86 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
 
 
 def fast_attention_supported(nh: int, nkv: int, hd: int, block_size: int) -> bool:
-    return False
+    return nkv > 0 and nh % nkv == 0 and bool(_lib().kvcm_attention_fast_supports(int(hd)))
+
+
+_SM_COUNT = {}
+
+
+def sm_count(device) -> int:
+    d = torch.device(device)
+    if d not in _SM_COUNT:
+        _SM_COUNT[d] = torch.cuda.get_device_properties(d).multi_processor_count
+    return _SM_COUNT[d]
+
+
+KEY_TILE = 64
+
+
+def decode_partitions(seqs: int, nh: int, nkv: int, max_ctx: int, device, version: str = "auto"):
+    """How the decode kernel splits the context: (keys per partition, number of partitions).
+
+    'v1': the whole context in one block per (request, KV head).  'v2'/'auto': enough partitions
+    that the grid has about two blocks per SM, each at least 256 keys long (the reference fixes
+    512 keys per partition, src/cuda/paged_attention.cu:22; a B200 has 148 SMs to fill)."""
+    max_ctx = max(int(max_ctx), 1)
+    whole = (max_ctx + KEY_TILE - 1) // KEY_TILE * KEY_TILE
+    if version == "v1":
+        return whole, 1
+    G = nh // nkv
+    blocks = max(1, seqs * nkv * ((G + 15) // 16))
+    want = max(1, (2 * sm_count(device) + blocks - 1) // blocks)
+    most = max(1, max_ctx // 256)
+    parts = max(1, min(want, most))
+    size = ((max_ctx + parts - 1) // parts + KEY_TILE - 1) // KEY_TILE * KEY_TILE
+    parts = (max_ctx + size - 1) // size
+    return size, parts
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     block_tables: torch.Tensor, ctx, nh: int, nkv: int, hd: int, scale: float,
+                     window: int = 0) -> None:
+    """Single-row entries: q/out hold one row per request, in the order of the batch's entries."""
+    _cuda(q, out, k_cache, v_cache, block_tables)
+    S = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16,
+          "attention_decode: bfloat16 only")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous(),
+          "attention_decode: layout")
+    _need(q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0, "attention_decode: q rows must be 16-byte aligned")
+    size, parts = decode_partitions(S, nh, nkv, ctx.max_decode_ctx, q.device,
+                                    ctx.options.get("attn_version", "auto"))
+    scratch = None
+    if parts > 1:
+        n = S * nh * parts * (hd + 2)          # partial outputs + (max, sum) per partition
+        scratch = torch.empty(n, dtype=torch.float32, device=q.device)
+    rc = _lib().kvcm_attention_decode_bf16(
+        _p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
+        block_tables.shape[1], _p(ctx.seq_ctx_len), S, nh, nkv, hd, k_cache.shape[2],
+        ctypes.c_float(scale), int(window), size, parts, _p(scratch), _stream())
+    _check(rc, "attention_decode", f"(hd={hd}, nh={nh}, nkv={nkv})")
+    if parts > 1:
+        global _launches
+        _launches += 1                      # the merge kernel
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      block_tables: torch.Tensor, ctx, nh: int, nkv: int, hd: int, scale: float,
+                      window: int = 0) -> None:
+    """Rows of portions longer than one token; q/out are the step's full row arrays."""
+    _cuda(q, out, k_cache, v_cache, block_tables)
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16,
+          "attention_prefill: bfloat16 only")
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous(),
+          "attention_prefill: layout")
+    _need(q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0, "attention_prefill: q rows must be 16-byte aligned")
+    _need(ctx.tile_rows == 64, "attention_prefill: the batch must be tiled in 64 query rows")
+    rc = _lib().kvcm_attention_prefill_bf16(
+        _p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
+        block_tables.shape[1], _p(ctx.tile_seq), _p(ctx.tile_q0), _p(ctx.seq_q_start), _p(ctx.seq_q_len),
+        _p(ctx.seq_ctx_len), ctx.prefill_tiles, nh, nkv, hd, k_cache.shape[2], ctypes.c_float(scale),
+        int(window), _stream())
+    _check(rc, "attention_prefill", f"(hd={hd}, nh={nh}, nkv={nkv})")
 
 
 def skinny_gemm_supported(M: int, N: int, K: int) -> bool:

@@ -1,0 +1,405 @@
+"""Each kernel alone against a plain PyTorch reference of the same operation (float64 on the
+CPU), at sizes other than the engine's: head sizes in steps of 16, odd numbers of heads and
+groups, widths and vocabularies that are no power of two, several page sizes.  Where random
+inputs would hide a fault (a far key among hundreds, a window's edge, a page's edge) the
+inputs are made so that it shows."""
+import math
+import types
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def K():
+    from kvcm.kernels import library
+    return library
+
+
+def tol(dtype, ref):
+    return 1e-5 * max(1.0, ref.abs().max().item()) if dtype == "float32" else 0.02 * max(ref.abs().max().item(), 1e-3)
+
+
+def close(got, ref, dtype, what=""):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    assert torch.isfinite(got).all(), what
+    d = (got - ref).abs().max().item()
+    assert d <= tol(dtype, ref), f"{what}: max diff {d:.3e} > {tol(dtype, ref):.3e}"
+
+
+# ------------------------------------------------------------------------- small kernels
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding(dtype):
+    V, H = 301, 70
+    table = torch.randn(V, H).to(DT[dtype]).to(DEV)
+    ids = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=DEV)
+    x = torch.empty(5, H, dtype=torch.float32, device=DEV)
+    K().embed(ids, table, x)
+    assert torch.equal(x.cpu(), table.float().cpu()[ids.cpu().long()])
+    bad = torch.tensor([V], dtype=torch.int32, device=DEV)
+    y = torch.zeros(1, H, dtype=torch.float32, device=DEV)
+    K().embed(bad, table, y)
+    assert torch.isnan(y).all()                       # out of range: loud, not wrong
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,eps", [(70, 1e-5), (2048, 1e-6), (5000, 1e-3)])
+def test_rmsnorm_with_residual_and_gather(dtype, H, eps):
+    T = 9
+    dt = DT[dtype]
+    x = torch.randn(T, H) * 3
+    delta = torch.randn(T, H).to(dt)
+    w = (1 + 0.2 * torch.randn(H)).to(dt)
+    xd = x.clone().to(DEV)
+    out = torch.empty(T, H, dtype=dt, device=DEV)
+    K().rmsnorm(xd, delta.to(DEV), w.to(DEV), out, eps)
+    x_new = x.double() + delta.double()
+    close(xd, x_new, "float32", "residual written back")
+    normed = x_new * torch.rsqrt((x_new ** 2).mean(-1, keepdim=True) + eps)
+    if dtype == "bfloat16":
+        normed = normed.to(dt).double()
+    close(out, w.double() * normed, dtype, "rmsnorm")
+    # gather: only rows 7 and 2, nothing written back, weight kept in float32
+    xg = x.clone().to(DEV)
+    rows = torch.tensor([7, 2], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, H, dtype=dt, device=DEV)
+    K().rmsnorm(xg, delta.to(DEV), w.float().to(DEV), out2, eps, rows)
+    assert torch.equal(xg.cpu(), x)
+    close(out2, (w.double() * normed)[[7, 2]], dtype, "rmsnorm gather")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul_and_add_residual(dtype):
+    dt = DT[dtype]
+    T, I = 5, 173
+    gu = (torch.randn(T, 2 * I) * 2).to(dt)
+    out = torch.empty(T, I, dtype=dt, device=DEV)
+    K().silu_mul(gu.to(DEV), out)
+    g, u = gu[:, :I].double(), gu[:, I:].double()
+    close(out, g * torch.sigmoid(g) * u, dtype, "silu_mul")
+    x = torch.randn(T, I)
+    xd = x.clone().to(DEV)
+    K().add_residual(xd, gu[:, :I].contiguous().to(DEV))
+    close(xd, x.double() + g, "float32", "add_residual")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hd,rot,inter,theta", [(16, 16, False, 1e4), (48, 48, False, 5e5),
+                                                (64, 32, False, 1e4), (32, 32, True, 1e4)])
+def test_rope_and_cache_write(dtype, hd, rot, inter, theta):
+    dt = DT[dtype]
+    nh, nkv, B, T = 5, 3, 8, 11
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width + 16).to(dt)[:, :width]          # padded row stride
+    pos = torch.tensor([0, 1, 7, 8, 1999, 3, 100, 15, 16, 17, 2], dtype=torch.int32)
+    pages = 6
+    perm = torch.randperm(pages * B)[:T].to(torch.int32)
+    perm[4] = -1                                                # a row that writes nothing
+    kc = torch.zeros(pages, nkv, B, hd, dtype=dt, device=DEV)
+    vc = torch.zeros_like(kc)
+    inv = (1.0 / torch.pow(torch.tensor(theta, dtype=torch.float64),
+                           2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float()
+    qd = qkv.to(DEV)
+    K().rope_cache(qd, pos.to(DEV), inv.to(DEV), rot, inter, perm.to(DEV), kc, vc, nh, nkv, hd, B)
+    # reference
+    x = qkv.double().reshape(T, nh + 2 * nkv, hd).clone()
+    # the angle is formed in float32 (position * frequency), as the engine and the reference do
+    ang = (pos.float()[:, None] * inv[None, :]).double()
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    heads = x[:, :nh + nkv]
+    if inter:
+        a, b = heads[..., 0:rot:2].clone(), heads[..., 1:rot:2].clone()
+        heads[..., 0:rot:2], heads[..., 1:rot:2] = a * c - b * s, b * c + a * s
+    else:
+        a, b = heads[..., :rot // 2].clone(), heads[..., rot // 2:rot].clone()
+        heads[..., :rot // 2], heads[..., rot // 2:rot] = a * c - b * s, b * c + a * s
+    close(qd.reshape(T, -1, hd)[:, :nh + nkv], heads, dtype, "rotated q and k")
+    assert torch.equal(qd.cpu().reshape(T, -1, hd)[:, nh + nkv:], qkv.reshape(T, -1, hd)[:, nh + nkv:])  # v untouched
+    got_k, got_v = kc.cpu(), vc.cpu()
+    rotated = qd.cpu().reshape(T, -1, hd)
+    expect_k, expect_v = torch.zeros_like(got_k), torch.zeros_like(got_v)
+    for t in range(T):
+        sl = int(perm[t])
+        if sl < 0:
+            continue
+        expect_k[sl // B, :, sl % B] = rotated[t, nh:nh + nkv]
+        expect_v[sl // B, :, sl % B] = rotated[t, nh + nkv:]
+    assert torch.equal(got_k, expect_k) and torch.equal(got_v, expect_v)      # exact copies, nothing else touched
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 7, 5), (3, 100, 172), (70, 130, 96), (64, 64, 64), (129, 33, 250)])
+def test_plain_gemm(M, N, Kd):
+    for dtype in ("float32", "bfloat16"):
+        dt = DT[dtype]
+        x, w = torch.randn(M, Kd).to(dt), torch.randn(N, Kd).to(dt)
+        y = torch.empty(M, N, dtype=dt, device=DEV)
+        K().gemm_plain(x.to(DEV), w.to(DEV), y)
+        close(y, x.double() @ w.double().T, dtype, f"gemm {M}x{N}x{Kd} {dtype}")
+    y32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    K().gemm_plain(x.to(DEV), w.to(DEV), y32)
+    close(y32, x.double() @ w.double().T, "float32", "bf16 operands, float result")
+
+
+def test_plain_gemm_rows_do_not_depend_on_the_batch():
+    x, w = torch.randn(37, 300, device=DEV), torch.randn(90, 300, device=DEV)
+    full = torch.empty(37, 90, device=DEV)
+    K().gemm_plain(x, w, full)
+    one = torch.empty(1, 90, device=DEV)
+    K().gemm_plain(x[20:21].contiguous(), w, one)
+    assert torch.equal(full[20:21], one)
+
+
+def test_argmax_ties_and_edges():
+    V = 1000
+    lg = torch.randn(5, V)
+    lg[0, 17] = lg[0, 900] = 50.0          # tie: lowest index
+    lg[1, V - 1] = 60.0                    # last index
+    lg[2, 0] = 60.0
+    lg[3] = -5.0                           # all equal
+    out = torch.zeros(5, dtype=torch.int32, device=DEV)
+    K().argmax(lg.to(DEV), out)
+    assert out.cpu().tolist()[:4] == [17, V - 1, 0, 0] and out[4].item() == int(lg[4].argmax())
+
+
+@pytest.mark.parametrize("V", [257, 1000, 32003])
+def test_temperature_sampling_matches_the_inverse_cdf(V):
+    from kvcm.sampling import uniform_for
+    R = 16
+    lg = (torch.randn(R, V) * 3)
+    temp = torch.tensor([0.8, 1.0, 0.3, 2.0] * 4)
+    temp[5] = 0.0                                                # greedy row
+    seed = torch.arange(R, dtype=torch.int64) * 7919 + 3
+    rid = torch.arange(R, dtype=torch.int64) + 100
+    pos = torch.arange(R, dtype=torch.int32) * 13
+    out = torch.zeros(R, dtype=torch.int32, device=DEV)
+    K().sample(lg.to(DEV), temp.to(DEV), seed.to(DEV), rid.to(DEV), pos.to(DEV), out)
+    got = out.cpu().tolist()
+    assert got[5] == int(lg[5].argmax())
+    for r in range(R):
+        if temp[r] == 0:
+            continue
+        p = torch.softmax(lg[r].double() / float(temp[r]), 0)
+        c = torch.cumsum(p, 0)
+        u = uniform_for(int(seed[r]), int(rid[r]), int(pos[r]))
+        t = got[r]
+        lo = float(c[t - 1]) if t else 0.0
+        assert lo - 1e-5 <= u <= float(c[t]) + 1e-5, (r, t, u, lo, float(c[t]))
+    out2 = torch.zeros(R, dtype=torch.int32, device=DEV)
+    K().sample(lg.to(DEV), temp.to(DEV), seed.to(DEV), rid.to(DEV), pos.to(DEV), out2)
+    assert torch.equal(out, out2)                                 # the same draw every time
+
+
+def test_sampling_distribution_is_right():
+    V, R = 50, 4096
+    row = torch.randn(V) * 2
+    lg = row.repeat(R, 1).to(DEV)
+    out = torch.zeros(R, dtype=torch.int32, device=DEV)
+    K().sample(lg, torch.full((R,), 0.7, device=DEV), torch.zeros(R, dtype=torch.int64, device=DEV),
+               torch.arange(R, dtype=torch.int64, device=DEV), torch.zeros(R, dtype=torch.int32, device=DEV), out)
+    freq = torch.bincount(out.cpu().long(), minlength=V).double() / R
+    p = torch.softmax(row.double() / 0.7, 0)
+    assert (freq - p).abs().max().item() < 4 * math.sqrt(0.25 / R)
+
+
+# ----------------------------------------------------------------------------- attention
+
+def paged_case(seq_lens, q_lens, nh, nkv, hd, B, dtype, seed=0, spare=7):
+    """Random requests in a shuffled page pool with unreferenced spare pages (as the reference's
+    attention test does, tests/test_paged_attention.cu:41,56).  Returns device tensors, a context
+    object and the dense K/V per request for the reference."""
+    g = torch.Generator().manual_seed(seed)
+    dt = DT[dtype]
+    need = [(n + B - 1) // B for n in seq_lens]
+    pages = sum(need) + spare
+    perm = torch.randperm(pages, generator=g).tolist()
+    max_blocks = max(need) + 1
+    kc = torch.randn(pages, nkv, B, hd, generator=g).to(dt)      # spare pages hold junk, not zeros
+    vc = torch.randn(pages, nkv, B, hd, generator=g).to(dt)
+    tables = torch.full((len(seq_lens), max_blocks), -1, dtype=torch.int32)
+    dense = []
+    at = 0
+    for i, n in enumerate(seq_lens):
+        ids = perm[at:at + need[i]]
+        at += need[i]
+        tables[i, :need[i]] = torch.tensor(ids, dtype=torch.int32)
+        kd = torch.randn(n, nkv, hd, generator=g).to(dt)
+        vd = torch.randn(n, nkv, hd, generator=g).to(dt)
+        for t in range(n):
+            kc[ids[t // B], :, t % B] = kd[t]
+            vc[ids[t // B], :, t % B] = vd[t]
+        dense.append((kd, vd))
+    # rows: single-row entries first (the builder's order)
+    order = sorted(range(len(seq_lens)), key=lambda i: q_lens[i] != 1)
+    T = sum(q_lens)
+    q = torch.randn(T, nh * hd + 32, generator=g).to(dt)[:, :nh * hd]      # strided rows
+    row_seq, positions, q_start, tile_seq, tile_q0 = [], [], [], [], []
+    for si, i in enumerate(order):
+        q_start.append(len(row_seq))
+        for j in range(q_lens[i]):
+            row_seq.append(si)
+            positions.append(seq_lens[i] - q_lens[i] + j)
+        if q_lens[i] > 1:
+            for q0 in range(0, q_lens[i], 64):
+                tile_seq.append(si)
+                tile_q0.append(q0)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    nd = sum(1 for x in q_lens if x == 1)
+    ctx = types.SimpleNamespace(
+        rows=T, seqs=len(seq_lens), decode_seqs=nd, prefill_tiles=len(tile_seq), tile_rows=64,
+        max_ctx=max(seq_lens), max_decode_ctx=max([seq_lens[i] for i in order[:nd]] or [1]),
+        row_seq=i32(row_seq), positions=i32(positions), seq_q_start=i32(q_start),
+        seq_q_len=i32([q_lens[i] for i in order]), seq_ctx_len=i32([seq_lens[i] for i in order]),
+        tile_seq=i32(tile_seq or [0]), tile_q0=i32(tile_q0 or [0]), options={})
+    return dict(q=q.to(DEV), kc=kc.to(DEV), vc=vc.to(DEV), tables=tables[order].contiguous().to(DEV), ctx=ctx,
+                dense=[dense[i] for i in order], order=order, q_cpu=q, row_seq=row_seq, positions=positions)
+
+
+def reference_attention(case, nh, nkv, hd, scale, window):
+    q = case["q_cpu"].double().reshape(-1, nh, hd)
+    out = torch.zeros(q.shape[0], nh, hd, dtype=torch.float64)
+    G = nh // nkv
+    for r, (si, pos) in enumerate(zip(case["row_seq"], case["positions"])):
+        kd, vd = case["dense"][si]
+        lo = max(0, pos + 1 - window) if window else 0
+        for h in range(nh):
+            k, v = kd[lo:pos + 1, h // G].double(), vd[lo:pos + 1, h // G].double()
+            p = torch.softmax((q[r, h] * scale) @ k.T, 0)
+            out[r, h] = p @ v
+    return out.reshape(q.shape[0], nh * hd)
+
+
+SHAPES = [(4, 2, 16, 16), (3, 1, 32, 8), (5, 5, 48, 16), (8, 2, 64, 32), (6, 3, 80, 16),
+          (32, 4, 64, 16), (20, 1, 64, 16), (4, 4, 128, 64), (2, 1, 256, 16), (9, 3, 112, 4)]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,B", SHAPES)
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_kernels_on_a_mixed_batch(nh, nkv, hd, B, window):
+    """Decode rows at contexts around page and tile edges beside portions that start anywhere."""
+    seq_lens = [1, 15, 16, 17, 63, 64, 65, 300, 129, 200, 70]
+    q_lens = [1, 1, 1, 1, 1, 1, 1, 1, 129, 2, 70]
+    scale = 1.0 / math.sqrt(hd)
+    for dtype in ("float32", "bfloat16"):
+        case = paged_case(seq_lens, q_lens, nh, nkv, hd, B, dtype, seed=nh * 100 + hd)
+        ref = reference_attention(case, nh, nkv, hd, scale, window)
+        out = torch.zeros(case["ctx"].rows, nh * hd, dtype=DT[dtype], device=DEV)
+        K().attention_plain(case["q"], out, case["kc"], case["vc"], case["tables"], case["ctx"].row_seq,
+                            case["ctx"].positions, nh, nkv, hd, scale, window)
+        close(out, ref, dtype, f"plain {dtype}")
+        if dtype == "bfloat16":
+            assert K().fast_attention_supported(nh, nkv, hd, B)
+            for version in ("v1", "v2"):
+                case["ctx"].options = {"attn_version": version}
+                fast = torch.zeros_like(out)
+                K().paged_attention(case["q"], fast, case["kc"], case["vc"], case["tables"], case["ctx"],
+                                    nh, nkv, hd, scale, window)
+                close(fast, ref, dtype, f"fast {version}")
+
+
+def test_decode_attention_long_contexts_and_many_partitions():
+    nh, nkv, hd, B = 32, 4, 64, 16
+    seq_lens = [2047, 2048, 1, 4097, 513]
+    case = paged_case(seq_lens, [1] * 5, nh, nkv, hd, B, "bfloat16", seed=3)
+    ref = reference_attention(case, nh, nkv, hd, 0.125, 0)
+    for version in ("v1", "v2"):
+        case["ctx"].options = {"attn_version": version}
+        out = torch.zeros(5, nh * hd, dtype=torch.bfloat16, device=DEV)
+        K().paged_attention(case["q"], out, case["kc"], case["vc"], case["tables"], case["ctx"], nh, nkv, hd, 0.125, 0)
+        close(out, ref, "bfloat16", version)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("needle", [0, 15, 16, 63, 64, 255, 256, 700, 998])
+def test_one_far_key_among_hundreds_decides_the_output(dtype, needle):
+    """One key is made to match the query so strongly that the output must be its value; a kernel
+    that misses it (a page's edge, a partition's edge, the first or last key) returns an average."""
+    nh, nkv, hd, B, n = 4, 2, 64, 16, 999
+    case = paged_case([n], [1], nh, nkv, hd, B, dtype, seed=needle)
+    q = case["q_cpu"].clone()
+    kd, vd = case["dense"][0]
+    for h in range(nh):
+        q[0, h * hd:(h + 1) * hd] = 6.0 * kd[needle, h // 2] / kd[needle, h // 2].float().norm() * math.sqrt(hd)
+    case["q"], case["q_cpu"] = q.to(DEV), q
+    ref = reference_attention(case, nh, nkv, hd, 1 / math.sqrt(hd), 0)
+    want = torch.cat([vd[needle, h // 2] for h in range(nh)]).double()
+    assert (ref[0] - want).abs().max() < 0.05                      # the reference itself picks the needle
+    for mode in (["plain"] if dtype == "float32" else ["plain", "v1", "v2"]):
+        case["ctx"].options = {"attention": "plain"} if mode == "plain" else {"attn_version": mode}
+        out = torch.zeros(1, nh * hd, dtype=DT[dtype], device=DEV)
+        K().paged_attention(case["q"], out, case["kc"], case["vc"], case["tables"], case["ctx"],
+                            nh, nkv, hd, 1 / math.sqrt(hd), 0)
+        close(out, ref, dtype, f"{mode} needle at {needle}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_edge_is_exact(dtype):
+    """The key just outside the window would dominate if it were read; the key just inside must
+    be read.  Checked for decode rows and for rows of a portion."""
+    nh, nkv, hd, B, W = 2, 1, 32, 8, 40
+    for q_len in (1, 50):
+        n = 200
+        case = paged_case([n], [q_len], nh, nkv, hd, B, dtype, seed=q_len)
+        kd, vd = case["dense"][0]
+        q = case["q_cpu"].clone()
+        last = len(case["positions"]) - 1
+        pos = case["positions"][last]
+        outside, inside = pos - W, pos - W + 1
+        # the last row's query points at the key just outside the window
+        for h in range(nh):
+            q[last, h * hd:(h + 1) * hd] = 6.0 * kd[outside, 0] / kd[outside, 0].float().norm() * math.sqrt(hd)
+        case["q"], case["q_cpu"] = q.to(DEV), q
+        ref_w = reference_attention(case, nh, nkv, hd, 1 / math.sqrt(hd), W)
+        ref_all = reference_attention(case, nh, nkv, hd, 1 / math.sqrt(hd), 0)
+        assert (ref_w[last] - ref_all[last]).abs().max() > 0.3       # reading it would show
+        for mode in (["plain"] if dtype == "float32" else ["plain", "v2"]):
+            case["ctx"].options = {"attention": "plain"} if mode == "plain" else {"attn_version": mode}
+            out = torch.zeros(case["ctx"].rows, nh * hd, dtype=DT[dtype], device=DEV)
+            K().paged_attention(case["q"], out, case["kc"], case["vc"], case["tables"], case["ctx"],
+                                nh, nkv, hd, 1 / math.sqrt(hd), W)
+            close(out, ref_w, dtype, f"{mode} window edge q_len={q_len}")
+
+
+def test_layout_does_not_change_bits():
+    """Shuffled pages and sequential pages give equal bits (the reference checks the same,
+    tests/test_paged_attention.cu:208-228)."""
+    nh, nkv, hd, B = 8, 2, 64, 16
+    a = paged_case([300, 77], [1, 77], nh, nkv, hd, B, "bfloat16", seed=5, spare=9)
+    b = paged_case([300, 77], [1, 77], nh, nkv, hd, B, "bfloat16", seed=5, spare=9)
+    # rebuild b's pool in sequential order
+    pages = b["kc"].shape[0]
+    kc, vc = torch.zeros_like(b["kc"]), torch.zeros_like(b["vc"])
+    tables = b["tables"].clone().cpu()
+    nxt = 0
+    for i in range(tables.shape[0]):
+        for j in range(tables.shape[1]):
+            if tables[i, j] >= 0:
+                kc[nxt], vc[nxt] = b["kc"][tables[i, j]], b["vc"][tables[i, j]]
+                tables[i, j] = nxt
+                nxt += 1
+    outs = []
+    for case, k_, v_, t_ in ((a, a["kc"], a["vc"], a["tables"]), (b, kc, vc, tables.to(DEV))):
+        out = torch.zeros(case["ctx"].rows, nh * hd, dtype=torch.bfloat16, device=DEV)
+        K().paged_attention(case["q"], out, k_, v_, t_, case["ctx"], nh, nkv, hd, 0.125, 0)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_unsupported_sizes_are_refused_not_miscomputed():
+    lib = K()
+    assert not lib.fast_attention_supported(4, 2, 24, 16)        # head_dim not a multiple of 16
+    assert not lib.fast_attention_supported(5, 2, 64, 16)        # heads not a multiple of KV heads
+    case = paged_case([40], [1], 4, 2, 24, 8, "bfloat16")
+    out = torch.zeros(1, 96, dtype=torch.bfloat16, device=DEV)
+    # the dispatcher falls back to the plain kernel, which takes any head_dim
+    lib.paged_attention(case["q"], out, case["kc"], case["vc"], case["tables"], case["ctx"], 4, 2, 24, 0.2, 0)
+    close(out, reference_attention(case, 4, 2, 24, 0.2, 0), "bfloat16", "hd=24 through the plain kernel")
+    with pytest.raises(lib.KernelError):
+        lib.attention_plain(case["q"], out, case["kc"], case["vc"], case["tables"], case["ctx"].row_seq,
+                            case["ctx"].positions, 5, 2, 24, 0.2, 0)
+    with pytest.raises(lib.KernelError):
+        lib.rmsnorm(torch.zeros(2, 8), None, torch.ones(8), torch.zeros(2, 8), 1e-5)     # CPU tensors
