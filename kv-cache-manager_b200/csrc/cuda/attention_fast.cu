@@ -17,6 +17,7 @@
 // softmax by exp2 with log2(e) folded into the scale; probabilities are rounded to bfloat16 for
 // the P*V product, sums stay float.
 #include "attention_mma.cuh"
+#include "pdl.cuh"
 
 namespace kvcm {
 
@@ -43,6 +44,8 @@ attn_decode_kernel(DecodeParams p) {
   bf16* kbuf = qtile + 16 * LD;                                    // [2][64][LD]
   bf16* vbuf = kbuf + 2 * kKeyTile * LD;                           // [2][64][LD]
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int part = blockIdx.x, seq = blockIdx.z;
   const int G = p.nh / p.nkv;
   const int head_tiles = (G + 15) / 16;
@@ -198,6 +201,8 @@ attn_decode_kernel(DecodeParams p) {
 // Merges the partitions of one (request, head): out = sum_p 2^(m_p - M) o_p / sum_p 2^(m_p - M) l_p.
 __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, int out_stride, int nh, int hd, int num_parts) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int seq = blockIdx.x, head = blockIdx.y;
   const size_t base = (size_t(seq) * nh + head) * num_parts;
   float M = -INFINITY;
@@ -239,6 +244,8 @@ attn_prefill_kernel(PrefillParams p) {
   bf16* kbuf = qtile + BM * LD;                                     // [2][64][LD]
   bf16* vbuf = kbuf + 2 * kKeyTile * LD;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int tile = blockIdx.x, head = blockIdx.y;
   const int kvh = head / (p.nh / p.nkv);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -371,8 +378,7 @@ int launch_decode(const DecodeParams& p, int seqs, cudaStream_t s) {
   }
   const int G = p.nh / p.nkv;
   dim3 grid(p.num_parts, p.nkv * ((G + 15) / 16), seqs);
-  kernel<<<grid, kAttnThreads, smem, s>>>(p);
-  return KVCM_LAUNCH_RESULT();
+  return pdl_launch(kernel, grid, dim3(kAttnThreads), smem, s, p);
 }
 
 template <int HD>
@@ -386,8 +392,7 @@ int launch_prefill(const PrefillParams& p, int tiles, cudaStream_t s) {
     configured = true;
   }
   dim3 grid(tiles, p.nh);
-  kernel<<<grid, kAttnThreads, smem, s>>>(p);
-  return KVCM_LAUNCH_RESULT();
+  return pdl_launch(kernel, grid, dim3(kAttnThreads), smem, s, p);
 }
 
 #define KVCM_FOR_HEAD_DIMS(X) \
@@ -431,9 +436,8 @@ KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, 
   KVCM_FOR_HEAD_DIMS(X)
 #undef X
   if (rc != 0 || num_parts == 1) return rc;
-  attn_decode_merge_kernel<<<dim3(seqs, nh), hd < 64 ? 32 : 64, 0, (cudaStream_t)stream>>>(
-      p.part_o, p.part_ml, p.out, out_stride, nh, hd, num_parts);
-  return KVCM_LAUNCH_RESULT();
+  return pdl_launch(attn_decode_merge_kernel, dim3(seqs, nh), dim3(hd < 64 ? 32 : 64), 0, (cudaStream_t)stream,
+                    (const float*)p.part_o, (const float*)p.part_ml, p.out, out_stride, nh, hd, num_parts);
 }
 
 KVCM_API int kvcm_attention_prefill_bf16(const void* q, int q_stride, void* out, int out_stride,

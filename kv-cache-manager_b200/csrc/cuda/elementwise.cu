@@ -6,6 +6,7 @@
 // Formulas after the reference's kernels (src/cuda/kernels.cu:27-88, src/cuda/kv_cache.cu:19-38);
 // the fusions (residual+norm, rotary+cache write) are this engine's own.
 #include "common.cuh"
+#include "pdl.cuh"
 
 namespace kvcm {
 
@@ -14,15 +15,14 @@ namespace kvcm {
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ x, int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= hidden) return;
   const int id = ids[t];
   float* dst = x + size_t(t) * hidden;
-  if (id < 0 || id >= vocab) {
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = __int_as_float(0x7fc00000);
-    return;
-  }
-  const T* src = table + size_t(id) * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ldf(src + i);
+  dst[i] = (id < 0 || id >= vocab) ? __int_as_float(0x7fc00000) : ldf(table + size_t(id) * hidden + i);
 }
 
 // -------------------------------------------------------------------------------- RMSNorm
@@ -37,6 +37,8 @@ rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const W* __re
                T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[33];
   extern __shared__ float row_cache[];            // hidden floats: the (updated) row
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* xr = x + size_t(src) * hidden;
@@ -60,6 +62,49 @@ rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const W* __re
   }
 }
 
+// The same for rows of at most 256 * 4 * VEC elements with hidden % 4 == 0: the row stays in
+// registers (float4 loads), one pass over global memory.
+template <typename T, typename W, int VEC>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const W* __restrict__ weight,
+                   T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* xr = x + size_t(src) * hidden;
+  const T* dr = delta ? delta + size_t(src) * hidden : nullptr;
+  float4 v[VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    const int i = (k * 256 + threadIdx.x) * 4;
+    v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < hidden) {
+      v[k] = *reinterpret_cast<const float4*>(xr + i);
+      if (dr) {
+        v[k].x += ldf(dr + i); v[k].y += ldf(dr + i + 1); v[k].z += ldf(dr + i + 2); v[k].w += ldf(dr + i + 3);
+        if (!rows) *reinterpret_cast<float4*>(xr + i) = v[k];
+      }
+      ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / float(hidden) + eps);
+  T* o = out + size_t(r) * hidden;
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    const int i = (k * 256 + threadIdx.x) * 4;
+    if (i < hidden) {
+      stf(o + i, ldf(weight + i) * Store<T>::round(v[k].x * inv));
+      stf(o + i + 1, ldf(weight + i + 1) * Store<T>::round(v[k].y * inv));
+      stf(o + i + 2, ldf(weight + i + 2) * Store<T>::round(v[k].z * inv));
+      stf(o + i + 3, ldf(weight + i + 3) * Store<T>::round(v[k].w * inv));
+    }
+  }
+}
+
 // Adds the pending delta into the residual stream without a norm: x += delta.
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t n) {
@@ -80,17 +125,21 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
                                   const int* __restrict__ slot_mapping, T* __restrict__ k_cache,
                                   T* __restrict__ v_cache, int nh, int nkv, int hd, int block_size,
                                   int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  // one warp per head of the fused row: q heads [0, nh), k heads [nh, nh+nkv), v heads after them
   const int t = blockIdx.x;
-  T* row = qkv + size_t(t) * row_stride;
+  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = write_cache ? nh + 2 * nkv : nh;
+  if (head >= heads) return;
+  T* base = qkv + size_t(t) * row_stride + size_t(head) * hd;
   const int half = rotary_dim / 2;
-  const int rot_heads = write_cache ? nh + nkv : nh;
-  if (inv_freq != nullptr && half > 0) {
+  if (head < nh + nkv && inv_freq != nullptr && half > 0) {
     const float pos = float(positions[t]);
-    for (int i = threadIdx.x; i < rot_heads * half; i += blockDim.x) {
-      const int h = i / half, j = i - h * half;
+    for (int j = lane; j < half; j += 32) {
       float sn, cs;
       sincosf(pos * inv_freq[j], &sn, &cs);
-      T* base = row + size_t(h) * hd;
       const int ia = interleaved ? 2 * j : j;
       const int ib = interleaved ? 2 * j + 1 : j + half;
       const float a = ldf(base + ia), b = ldf(base + ib);
@@ -98,19 +147,15 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
       stf(base + ib, b * cs + a * sn);
     }
   }
-  if (!write_cache) return;
+  if (head < nh || !write_cache) return;
   const int slot = slot_mapping[t];
   if (slot < 0) return;
-  __syncthreads();                       // rotated k must be visible to the copying threads
+  __syncwarp();                          // the rotated values of this head are written by this warp
   const int page = slot / block_size, off = slot - page * block_size;
-  const T* ksrc = row + size_t(nh) * hd;
-  const T* vsrc = ksrc + size_t(nkv) * hd;
-  for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) {
-    const int h = i / hd, d = i - h * hd;
-    const size_t dst = ((size_t(page) * nkv + h) * block_size + off) * hd + d;
-    k_cache[dst] = ksrc[i];
-    v_cache[dst] = vsrc[i];
-  }
+  const bool is_k = head < nh + nkv;
+  const int kvh = is_k ? head - nh : head - nh - nkv;
+  T* dst = (is_k ? k_cache : v_cache) + ((size_t(page) * nkv + kvh) * block_size + off) * hd;
+  for (int d = lane; d < hd; d += 32) dst[d] = base[d];
 }
 
 // --------------------------------------------------------------------------- SiLU(g) * u
@@ -118,15 +163,15 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
 // storage type before the product (src/cuda/kernels.cu:72-82).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= inter) return;
   const T* g = gate_up + size_t(t) * 2 * inter;
-  const T* u = g + inter;
-  T* o = out + size_t(t) * inter;
-  for (int i = threadIdx.x; i < inter; i += blockDim.x) {
-    const float x = ldf(g + i);
-    const float s = Store<T>::round(x / (1.f + expf(-x)));
-    stf(o + i, s * ldf(u + i));
-  }
+  const float x = ldf(g + i);
+  const float s = Store<T>::round(x / (1.f + expf(-x)));
+  stf(out + size_t(t) * inter + i, s * ldf(g + inter + i));
 }
 
 // Gathers rows of a [*, width] matrix of T into a dense [n, width] matrix (used for the rows
@@ -139,22 +184,31 @@ __global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restr
   for (int i = threadIdx.x; i < width; i += blockDim.x) d[i] = s[i];
 }
 
+template <typename T, typename W>
+int launch_rmsnorm_w(float* x, const T* delta, const W* weight, T* out, const int* rows, int n_rows,
+                     int hidden, float eps, cudaStream_t s) {
+  if ((hidden % 4) == 0 && hidden <= 256 * 4 * 4 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    if (hidden <= 1024) return pdl_launch(rmsnorm_vec_kernel<T, W, 1>, dim3(n_rows), dim3(256), 0, s, x, delta, weight, out, rows, hidden, eps);
+    if (hidden <= 2048) return pdl_launch(rmsnorm_vec_kernel<T, W, 2>, dim3(n_rows), dim3(256), 0, s, x, delta, weight, out, rows, hidden, eps);
+    return pdl_launch(rmsnorm_vec_kernel<T, W, 4>, dim3(n_rows), dim3(256), 0, s, x, delta, weight, out, rows, hidden, eps);
+  }
+  const size_t smem = size_t(hidden) * sizeof(float);
+  if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
+  auto k = rmsnorm_kernel<T, W>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return int(e);
+  }
+  return pdl_launch(k, dim3(n_rows), dim3(256), smem, s, x, delta, weight, out, rows, hidden, eps);
+}
+
 template <typename T>
 int launch_rmsnorm(float* x, const T* delta, const void* weight, int weight_is_f32, T* out,
                    const int* rows, int n_rows, int hidden, float eps, cudaStream_t s) {
   if (n_rows == 0) return 0;
-  const size_t smem = size_t(hidden) * sizeof(float);
-  if (smem > 200 * 1024) return KVCM_ERR_UNSUPPORTED;
-  if (weight_is_f32) {
-    auto k = rmsnorm_kernel<T, float>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    k<<<n_rows, 256, smem, s>>>(x, delta, static_cast<const float*>(weight), out, rows, hidden, eps);
-  } else {
-    auto k = rmsnorm_kernel<T, T>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    k<<<n_rows, 256, smem, s>>>(x, delta, static_cast<const T*>(weight), out, rows, hidden, eps);
-  }
-  return KVCM_LAUNCH_RESULT();
+  if (weight_is_f32)
+    return launch_rmsnorm_w<T, float>(x, delta, static_cast<const float*>(weight), out, rows, n_rows, hidden, eps, s);
+  return launch_rmsnorm_w<T, T>(x, delta, static_cast<const T*>(weight), out, rows, n_rows, hidden, eps, s);
 }
 
 }  // namespace kvcm
@@ -165,8 +219,8 @@ using namespace kvcm;
   KVCM_API int kvcm_embed_##SUFFIX(const int* ids, const void* table, float* x, int rows, int hidden, \
                                    int vocab, void* stream) {                                         \
     if (rows == 0) return 0;                                                                          \
-    embed_kernel<T><<<rows, 256, 0, (cudaStream_t)stream>>>(ids, (const T*)table, x, hidden, vocab);  \
-    return KVCM_LAUNCH_RESULT();                                                                      \
+    return pdl_launch(embed_kernel<T>, dim3(rows, (hidden + 255) / 256), dim3(256), 0,               \
+                      (cudaStream_t)stream, ids, (const T*)table, x, hidden, vocab);                 \
   }                                                                                                   \
   KVCM_API int kvcm_rmsnorm_##SUFFIX(float* x, const void* delta, const void* weight,                 \
                                      int weight_is_f32, void* out, const int* rows, int n_rows,       \
@@ -187,16 +241,17 @@ using namespace kvcm;
                                         int write_cache, void* stream) {                              \
     if (rows == 0) return 0;                                                                          \
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return KVCM_ERR_UNSUPPORTED;           \
-    rope_cache_kernel<T><<<rows, 256, 0, (cudaStream_t)stream>>>(                                     \
-        (T*)qkv, row_stride, positions, inv_freq, rotary_dim, interleaved, slot_mapping,              \
-        (T*)k_cache, (T*)v_cache, nh, nkv, hd, block_size, write_cache);                              \
-    return KVCM_LAUNCH_RESULT();                                                                      \
+    const int heads = write_cache ? nh + 2 * nkv : nh;                                                \
+    return pdl_launch(rope_cache_kernel<T>, dim3(rows, (heads + 3) / 4), dim3(128), 0,                \
+                      (cudaStream_t)stream, (T*)qkv, row_stride, positions, inv_freq, rotary_dim,     \
+                      interleaved, slot_mapping, (T*)k_cache, (T*)v_cache, nh, nkv, hd, block_size,   \
+                      write_cache);                                                                   \
   }                                                                                                   \
   KVCM_API int kvcm_silu_mul_##SUFFIX(const void* gate_up, void* out, int rows, int inter,            \
                                       void* stream) {                                                 \
     if (rows == 0) return 0;                                                                          \
-    silu_mul_kernel<T><<<rows, 256, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)out, inter);    \
-    return KVCM_LAUNCH_RESULT();                                                                      \
+    return pdl_launch(silu_mul_kernel<T>, dim3(rows, (inter + 255) / 256), dim3(256), 0,              \
+                      (cudaStream_t)stream, (const T*)gate_up, (T*)out, inter);                       \
   }                                                                                                   \
   KVCM_API int kvcm_gather_rows_##SUFFIX(const void* src, const int* rows, void* dst, int n,          \
                                          int width, void* stream) {                                   \

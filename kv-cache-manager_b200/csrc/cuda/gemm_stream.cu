@@ -1,0 +1,293 @@
+// Weight-streaming matrix product for a handful of rows (decode), TMA-pipelined:
+//     Y[M, N] = X[M, K] * W[N, K]^T,   M <= 16, bfloat16 operands, float accumulation.
+//
+// With so few rows the product is bound by reading W once from HBM, and HBM only delivers its
+// bandwidth with megabytes in flight.  So W is not loaded by the computing threads at all: one
+// producer thread per block issues bulk asynchronous copies (cp.async.bulk, completion on an
+// mbarrier) of [16 rows x 512 k] pieces of W into a ring of up to twelve shared-memory stages ahead
+// of the consumers (as many as shared memory holds: 100-190 KB in flight per SM), and keeps issuing across tile boundaries.  Four consumer warps take the tensor-
+// core product (m16n8k16, "swap AB": 16 rows of W are the 16-row operand, the batch rows are the
+// 8 columns) out of the ring, each warp one quarter of a stage along k; their partial sums are
+// added in warp order per tile, so results are reproducible bit for bit.
+//  * Blocks are persistent: block b takes tiles b, b + grid, ...; the grid is about one block
+//    per SM so that the ring of every SM stays full.
+//  * Launched as a programmatic dependent: the producer fills the whole ring BEFORE the kernel
+//    waits for its predecessor (weights are constants), so HBM streams while the previous kernel
+//    still runs; X (which the predecessor wrote) is staged after the wait.
+//  * Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host
+//    reads (kvcm_stream_error), lets copies in flight land and leaves.
+// The k index inside a 32-wide block is permuted identically for both operands (thread t of a
+// quad owns k = 8t..8t+7), which makes every shared-memory read of W and X a 16-byte vector.
+// The reference calls cuBLAS here (src/model/llama.cpp:45-52).
+#include "common.cuh"
+#include "pdl.cuh"
+
+namespace kvcm {
+
+constexpr int kStreamConsumers = 4;                    // consumer warps
+constexpr int kStreamThreads = 32 * (kStreamConsumers + 1);
+constexpr int kMaxStages = 12;                         // ring depth is chosen per launch to fill shared memory
+constexpr int kChunk = 1024;                           // k elements per stage
+constexpr int kRowBytes = kChunk * 2 + 16;             // padded stage row: odd multiple of 16 bytes
+constexpr int kStageBytes = 16 * kRowBytes;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // every wait gives up after two seconds
+
+__device__ int g_stream_error = 0;                     // 0 = ok; else (code << 16) | block
+
+struct StreamParams {
+  const bf16* W; int N, K, ldw;
+  const bf16* X; int ldx, M;
+  void* Y; int ldy;
+  int stages;                                          // ring depth (2..kMaxStages)
+};
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(s32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(s32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+  return t;
+}
+// Bounded wait for the phase with the given parity.  False = gave up after kWaitLimitNs.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns = kWaitLimitNs) {
+  unsigned long long start = 0;
+  for (unsigned spin = 0;; ++spin) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(s32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+    if ((spin & 63) == 63) {
+      const unsigned long long now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > limit_ns) return false;
+    }
+  }
+}
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mma_stream(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int MT, typename OutT>
+__global__ void __launch_bounds__(kStreamThreads)
+gemm_stream_kernel(StreamParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int Kc = (p.K + kChunk - 1) / kChunk;                 // stages per tile
+  const int Kp = Kc * kChunk + 8;                             // padded row of the staged X
+  const int kStages = p.stages;
+  unsigned char* ring = smem_raw;                             // [stages][16][kRowBytes]
+  bf16* xs = reinterpret_cast<bf16*>(ring + kStages * kStageBytes);          // [MT*8][Kp]
+  float* red = reinterpret_cast<float*>(xs + MT * 8 * Kp);                   // [2][4 warps][16][MT*8]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * kStreamConsumers * 16 * MT * 8);
+  uint64_t* empty = full + kMaxStages;
+  __shared__ volatile int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_tiles = (p.N + 15) / 16;
+  const int my_tiles = blockIdx.x < n_tiles ? (n_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
+  const int total = my_tiles * Kc;                            // stages this block consumes
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kStreamConsumers); }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  // Producer warp: lane 0 announces the bytes of a stage, lanes 0..15 each copy one row of it
+  // (sixteen copies issued side by side).  Stage i holds rows of tile (i / Kc) at k-chunk (i % Kc).
+  auto issue = [&](int i) {
+    const int s = i % kStages;
+    const int tile = blockIdx.x + (i / Kc) * gridDim.x;
+    const int k0 = (i % Kc) * kChunk;
+    const int kbytes = min(kChunk, p.K - k0) * 2;
+    const int rows = min(16, p.N - tile * 16);
+    if (lane == 0) mbar_expect_tx(&full[s], uint32_t(rows) * kbytes);
+    __syncwarp();
+    if (lane < rows)
+      bulk_copy(ring + s * kStageBytes + lane * kRowBytes,
+                p.W + (size_t(tile) * 16 + lane) * p.ldw + k0, kbytes, &full[s]);
+  };
+
+  int issued = 0;
+  if (warp == kStreamConsumers)
+    for (; issued < min(total, kStages); ++issued) issue(issued);          // fill the ring: weights are constants
+  pdl_wait();                                                               // ... the predecessor wrote X
+
+  if (warp == kStreamConsumers) {
+    for (; issued < total; ++issued) {
+      const int s = issued % kStages;
+      int ok = 1;
+      if (lane == 0) {
+        ok = !abort_flag && mbar_wait(&empty[s], ((issued / kStages) - 1) & 1);   // consumers freed the slot?
+        if (!ok && !abort_flag) {
+          atomicExch(&g_stream_error, (1 << 16) | int(blockIdx.x));
+          abort_flag = 1;
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      issue(issued);
+    }
+    // Stay until every copy this block issued has landed (shared memory must not be handed to
+    // another block with copies still in flight).  Immediate in a healthy run: the consumers
+    // have already seen these phases complete.
+    if (lane == 0)
+      for (int s = 0; s < kStages; ++s) {
+        const int fills = issued > s ? (issued - s - 1) / kStages + 1 : 0;
+        if (fills > 0) mbar_wait(&full[s], (fills - 1) & 1, kWaitLimitNs / 4);
+      }
+  } else {
+    // ---- consumers: stage X (all copies in flight at once, zero fill beyond M and K)
+    const int chunks = Kp / 8;
+    for (int c = tid; c < MT * 8 * chunks; c += 32 * kStreamConsumers) {
+      const int m = c / chunks, ch = c - m * chunks;
+      const bool live = m < p.M && ch * 8 < p.K;
+      const bf16* src = live ? p.X + size_t(m) * p.ldx + ch * 8 : p.X;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s32(xs + m * Kp + ch * 8)), "l"(src), "r"(live ? 16 : 0));
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kStreamConsumers));
+
+    const int g = lane >> 2, t4 = lane & 3;
+    OutT* Y = reinterpret_cast<OutT*>(p.Y);
+    int i = 0;
+    for (int tl = 0; tl < my_tiles; ++tl) {
+      const int tile = blockIdx.x + tl * gridDim.x;
+      float acc[MT][4];
+#pragma unroll
+      for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+      for (int kc = 0; kc < Kc; ++kc, ++i) {
+        const int s = i % kStages;
+        if (!abort_flag && !mbar_wait(&full[s], (i / kStages) & 1)) {
+          if (lane == 0) atomicExch(&g_stream_error, (2 << 16) | int(blockIdx.x));
+          abort_flag = 1;                              // everyone stops waiting, nobody leaves a barrier alone
+        }
+        if (abort_flag) continue;
+        const unsigned char* st = ring + s * kStageBytes;
+        const int kbase = kc * kChunk + warp * (kChunk / kStreamConsumers);    // this warp's quarter
+#pragma unroll
+        for (int kb = 0; kb < kChunk / kStreamConsumers / 32; ++kb) {
+          if (kbase + kb * 32 >= p.K) break;           // warp-uniform: the whole k-block lies beyond K
+          const int koff = warp * (kChunk / kStreamConsumers) + kb * 32 + 8 * t4;
+          uint4 va = *reinterpret_cast<const uint4*>(st + g * kRowBytes + koff * 2);
+          uint4 vb = *reinterpret_cast<const uint4*>(st + (g + 8) * kRowBytes + koff * 2);
+          if (kc * kChunk + koff >= p.K) {             // this thread's 8 columns lie beyond K: stale bytes
+            va = make_uint4(0u, 0u, 0u, 0u);
+            vb = make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int j = 0; j < MT; ++j) {
+            const uint4 x = *reinterpret_cast<const uint4*>(xs + (8 * j + g) * Kp + kbase + kb * 32 + 8 * t4);
+            mma_stream(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
+            mma_stream(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);         // this warp is done with the slot
+      }
+      // acc[j]: c0,c1 = (W row g, batch 8j + 2t, +1); c2,c3 = (W row g+8, same batch rows)
+      float* mine = red + ((tl & 1) * kStreamConsumers + warp) * 16 * (MT * 8);
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        mine[g * (MT * 8) + 8 * j + 2 * t4] = acc[j][0];
+        mine[g * (MT * 8) + 8 * j + 2 * t4 + 1] = acc[j][1];
+        mine[(g + 8) * (MT * 8) + 8 * j + 2 * t4] = acc[j][2];
+        mine[(g + 8) * (MT * 8) + 8 * j + 2 * t4 + 1] = acc[j][3];
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kStreamConsumers));
+      const float* both = red + (tl & 1) * kStreamConsumers * 16 * (MT * 8);
+      for (int e = tid; e < 16 * MT * 8; e += 32 * kStreamConsumers) {
+        const int r = e / (MT * 8), m = e - r * (MT * 8);
+        const int n = tile * 16 + r;
+        if (n < p.N && m < p.M) {
+          float sum = 0.f;
+#pragma unroll
+          for (int w = 0; w < kStreamConsumers; ++w) sum += both[w * 16 * (MT * 8) + e];
+          stf(Y + size_t(m) * p.ldy + n, sum);
+        }
+      }
+      // the other half of `red` is used by the next tile; this half again two tiles on, after
+      // the barrier of the tile in between
+    }
+  }
+}
+
+constexpr size_t kStreamSmemBudget = 200 * 1024;
+
+// Shared memory of a launch with `stages` ring slots.
+static size_t stream_smem(int MT, int K, int stages) {
+  const int Kc = (K + kChunk - 1) / kChunk;
+  return size_t(stages) * kStageBytes + size_t(MT) * 8 * (Kc * kChunk + 8) * sizeof(bf16) +
+         size_t(2) * kStreamConsumers * 16 * MT * 8 * sizeof(float) + 2 * kMaxStages * sizeof(uint64_t);
+}
+
+template <int MT, typename OutT>
+int launch_stream(StreamParams p, int sm_count, cudaStream_t s) {
+  auto kernel = gemm_stream_kernel<MT, OutT>;
+  const int tiles = (p.N + 15) / 16;
+  const int Kc = (p.K + kChunk - 1) / kChunk;
+  // One block per SM; the ring takes what shared memory is left after X, but never more slots than
+  // the block has stages to load.
+  const int blocks = min(tiles, sm_count);
+  const int need = ((tiles + blocks - 1) / blocks) * Kc;
+  int stages = kMaxStages;
+  while (stages > 2 && (stream_smem(MT, p.K, stages) > kStreamSmemBudget || stages > need)) --stages;
+  const size_t smem = stream_smem(MT, p.K, stages);
+  if (smem > kStreamSmemBudget + 24 * 1024) return KVCM_ERR_UNSUPPORTED;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return int(e);
+    configured = smem;
+  }
+  p.stages = stages;
+  return pdl_launch(kernel, dim3(blocks), dim3(kStreamThreads), smem, s, p);
+}
+
+}  // namespace kvcm
+
+using namespace kvcm;
+
+KVCM_API int kvcm_gemm_stream_supports(int M, int N, int K) {
+  if (M < 1 || M > 16 || N < 1 || K < 8 || (K % 8)) return 0;
+  return stream_smem(M <= 8 ? 1 : 2, K, 2) <= kStreamSmemBudget + 24 * 1024;
+}
+
+// out_f32: 0 = bfloat16 result, 1 = float result.
+KVCM_API int kvcm_gemm_stream_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int ldx,
+                                   int ldw, int ldy, int out_f32, int sm_count, void* stream) {
+  if (M == 0 || N == 0) return 0;
+  if (!kvcm_gemm_stream_supports(M, N, K) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
+  StreamParams p{(const bf16*)W, N, K, ldw, (const bf16*)X, ldx, M, Y, ldy, 0};
+  cudaStream_t s = (cudaStream_t)stream;
+  if (M <= 8) return out_f32 ? launch_stream<1, float>(p, sm_count, s) : launch_stream<1, bf16>(p, sm_count, s);
+  return out_f32 ? launch_stream<2, float>(p, sm_count, s) : launch_stream<2, bf16>(p, sm_count, s);
+}
+
+// Reads and clears the error word of the streaming kernels (0 = no bounded wait ever ran out).
+KVCM_API int kvcm_stream_error(void) {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_stream_error, sizeof v) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_stream_error, &zero, sizeof zero);
+  return v;
+}

@@ -10,6 +10,7 @@
 // The vocabulary is cut into 1024 consecutive segments; segment sums are scanned in order, the
 // segment that holds u * total is scanned element by element.  Softmax in float.
 #include "common.cuh"
+#include "pdl.cuh"
 
 namespace kvcm {
 
@@ -24,9 +25,20 @@ __device__ void block_argmax(const float* __restrict__ row, int vocab, float& be
                              float* sv, int* si) {
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
-    if (v > bv) { bv = v; bi = i; }          // ascending i: the first maximum is kept
+  if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // four consecutive logits per load; within a thread indices still ascend
+    for (int i = threadIdx.x * 4; i < vocab; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row + i);
+      if (v.x > bv) { bv = v.x; bi = i; }
+      if (v.y > bv) { bv = v.y; bi = i + 1; }
+      if (v.z > bv) { bv = v.z; bi = i + 2; }
+      if (v.w > bv) { bv = v.w; bi = i + 3; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float v = row[i];
+      if (v > bv) { bv = v; bi = i; }          // ascending i: the first maximum is kept
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1)
@@ -52,6 +64,8 @@ __global__ void __launch_bounds__(kSampleThreads)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  pdl_launch_dependents();
+  pdl_wait();
   float best;
   int index;
   block_argmax(logits + size_t(blockIdx.x) * vocab, vocab, best, index, sv, si);
@@ -133,8 +147,7 @@ using namespace kvcm;
 
 KVCM_API int kvcm_argmax_f32(const float* logits, int* out, int rows, int vocab, void* stream) {
   if (rows == 0) return 0;
-  argmax_kernel<<<rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits, out, vocab);
-  return KVCM_LAUNCH_RESULT();
+  return pdl_launch(argmax_kernel, dim3(rows), dim3(kSampleThreads), 0, (cudaStream_t)stream, logits, out, vocab);
 }
 
 KVCM_API int kvcm_sample_f32(const float* logits, const float* temperature,

@@ -269,16 +269,17 @@ def decode_partitions(seqs: int, nh: int, nkv: int, max_ctx: int, device, versio
     """How the decode kernel splits the context: (keys per partition, number of partitions).
 
     'v1': the whole context in one block per (request, KV head).  'v2'/'auto': enough partitions
-    that the grid has about two blocks per SM, each at least 256 keys long (the reference fixes
-    512 keys per partition, src/cuda/paged_attention.cu:22; a B200 has 148 SMs to fill)."""
+    that the grid has about three blocks per SM, each at least 128 keys long (the reference fixes
+    512 keys per partition, src/cuda/paged_attention.cu:22; a B200 has 148 SMs to fill and a short
+    partition is one memory latency instead of several)."""
     max_ctx = max(int(max_ctx), 1)
     whole = (max_ctx + KEY_TILE - 1) // KEY_TILE * KEY_TILE
     if version == "v1":
         return whole, 1
     G = nh // nkv
     blocks = max(1, seqs * nkv * ((G + 15) // 16))
-    want = max(1, (2 * sm_count(device) + blocks - 1) // blocks)
-    most = max(1, max_ctx // 256)
+    want = max(1, (3 * sm_count(device) + blocks - 1) // blocks)
+    most = max(1, max_ctx // 128)
     parts = max(1, min(want, most))
     size = ((max_ctx + parts - 1) // parts + KEY_TILE - 1) // KEY_TILE * KEY_TILE
     parts = (max_ctx + size - 1) // size
@@ -332,4 +333,48 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
 
 
 def skinny_gemm_supported(M: int, N: int, K: int) -> bool:
-    return False
+    """True when the weight-streaming kernel takes this product (M <= 16, K a multiple of 8, X
+    fits shared memory)."""
+    return bool(_lib().kvcm_gemm_skinny_supports(int(M), int(N), int(K)))
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, kw: int = 0) -> None:
+    """y[M,N] = x[M,K] @ w[N,K]^T for M <= 16 (bfloat16 operands, float accumulation, bfloat16 or
+    float result).  ``kw``: warps that share a 16-row tile of w along K (0: chosen from the sizes)."""
+    _cuda(x, w, y)
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and y.shape == (M, N), "gemm_skinny: shapes")
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and y.dtype in (torch.bfloat16, torch.float32),
+          "gemm_skinny: bfloat16 operands, bfloat16 or float32 result")
+    _need(x.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1, "gemm_skinny: rows must be dense")
+    rc = _lib().kvcm_gemm_skinny_bf16(_p(x), _p(w), _p(y), M, N, K, x.stride(0), w.stride(0), y.stride(0),
+                                      int(y.dtype == torch.float32), int(kw), sm_count(x.device), _stream())
+    _check(rc, "gemm_skinny", f"(M={M}, N={N}, K={K})")
+
+
+def stream_gemm_supported(M: int, N: int, K: int) -> bool:
+    """True when the TMA-pipelined weight-streaming kernel takes this product."""
+    return bool(_lib().kvcm_gemm_stream_supports(int(M), int(N), int(K)))
+
+
+def gemm_stream(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
+    """y[M,N] = x[M,K] @ w[N,K]^T for M <= 16 with W streamed through a shared-memory ring by bulk
+    asynchronous copies (bfloat16 operands, float accumulation, bfloat16 or float result)."""
+    _cuda(x, w, y)
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and y.shape == (M, N), "gemm_stream: shapes")
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and y.dtype in (torch.bfloat16, torch.float32),
+          "gemm_stream: bfloat16 operands, bfloat16 or float32 result")
+    _need(x.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1, "gemm_stream: rows must be dense")
+    rc = _lib().kvcm_gemm_stream_bf16(_p(x), _p(w), _p(y), M, N, K, x.stride(0), w.stride(0), y.stride(0),
+                                      int(y.dtype == torch.float32), sm_count(x.device), _stream())
+    _check(rc, "gemm_stream", f"(M={M}, N={N}, K={K})")
+
+
+def stream_error() -> int:
+    """Error word of the streaming kernels: 0, or (code << 16 | block) of a bounded wait that ran
+    out (1: the producer waited for a free stage, 2: a consumer waited for data).  Reading clears it.
+    Synchronises the device."""
+    return int(_lib().kvcm_stream_error())

@@ -5,7 +5,8 @@ Which kernel runs is decided by the weight's dtype, never by the model:
 * float32 weight  -> this engine's plain float kernel (true 32-bit, fixed summation order);
 * bfloat16 weight -> the library GEMM (cuBLAS through ``torch.mm``), the same place where the
   reference calls cuBLAS, or this engine's own weight-streaming kernel for a handful of rows
-  (decode), or the plain kernel when ``options['gemm'] == 'plain'`` asks for the twin.
+  (decode), or the plain kernel when ``options['gemm'] == 'plain'`` asks for the twin
+  (``'library'`` forces cuBLAS, ``'skinny'`` the register-streaming variant).
 """
 from __future__ import annotations
 
@@ -15,6 +16,9 @@ import torch
 
 from ..kernels import library as K
 from .base import Part, StepContext
+
+
+STREAM_MAX_BYTES = 32 << 20
 
 
 class Linear(Part):
@@ -45,9 +49,17 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, options:
         y = torch.empty((M, N), dtype=out_dtype, device=x.device)
         K.gemm_plain(x, w, y)
         return y
-    if mode != "library" and K.skinny_gemm_supported(M, N, w.shape[1]):
+    if mode == "skinny" and K.skinny_gemm_supported(M, N, w.shape[1]):
         y = torch.empty((M, N), dtype=out_dtype, device=x.device)
         K.gemm_skinny(x, w, y)
+        return y
+    # A handful of rows (decode): this engine's weight-streaming kernel, for matrices up to
+    # STREAM_MAX_BYTES; measured on B200 it beats the library there (5-10 us against 7-15 us at
+    # 8-23 MB) while the library's kernels stream the largest matrices (46-131 MB) faster.
+    if mode != "library" and w.numel() * 2 <= STREAM_MAX_BYTES and K.stream_gemm_supported(M, N, w.shape[1]) \
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        K.gemm_stream(x, w, y)
         return y
     if out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
