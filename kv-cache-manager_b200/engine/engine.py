@@ -94,7 +94,8 @@ class Engine:
         s.prefill_chunk, s.chunked_prefill, s.eos_token_id = sc.prefill_chunk, sc.chunked_prefill, cfg.eos_token_id
         self.sched = core.Scheduler(self.kv, s)
         self.sampler = Sampler(cfg.device, max(self.max_logit_rows, sc.max_num_seqs))
-        self.graphs = DecodeGraphs(self.runner, self.sampler) if cfg.cuda_graphs else None
+        capturable = all(part.capturable for _, top in spec.parts() for _, part in top.named_parts())
+        self.graphs = DecodeGraphs(self.runner, self.sampler) if cfg.cuda_graphs and capturable else None
         self.vocab = spec.lm_head.vocab
         self._next_id = 0
         self._t0 = time.perf_counter()

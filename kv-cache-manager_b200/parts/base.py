@@ -38,7 +38,13 @@ class ParamSpec:
 
 
 class Part:
-    """Base of every part: named parameters, named children."""
+    """Base of every part: named parameters, named children.
+
+    ``capturable``: the part's forward only enqueues device work (no host synchronisation, no
+    host-side reading of device data), so a step that contains it may be recorded into a CUDA
+    graph.  A part that cannot promise this sets it to False and the engine replays no graphs."""
+
+    capturable = True
 
     def __init__(self) -> None:
         self._specs: Dict[str, ParamSpec] = {}
