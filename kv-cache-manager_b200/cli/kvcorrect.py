@@ -1,0 +1,102 @@
+"""kvcorrect: the correctness gate (after the reference's ``src/main_correct.cpp``, protocol
+``docs/design.md:122-134``).  The reference compares with stored outputs of another framework;
+here the oracle is the engine's own true 32-bit path, so the gate needs nothing but a model.
+
+Checks, each printed with PASS/FAIL; exit code 0 if all pass, 2 otherwise:
+ 1. bfloat16 vs float32 logits, teacher-forced through ``score``: top-1 agreement >= 98 % (a
+    disagreement counts only where the float32 top-1/top-2 gap exceeds --tie-margin) and the
+    error of the top-5 logits;
+ 2. greedy tokens of every prompt alone, on a pool fragmented beforehand so that page tables are
+    scattered, equal the tokens of all prompts in one batch;
+ 3. paged and contiguous policies give identical tokens;
+ 4. prefix caching on: hits > 0 and tokens identical to prefix caching off.
+Flags: --model DIR | --preset NAME, --tie-margin 0.05, --block-size 16, --steps 32, --prompts 8,
+--prompt-len 64, --attn.
+"""
+from __future__ import annotations
+
+import sys
+
+
+def main(argv=None) -> int:
+    from .args import Args
+    from .common import load_model_from_args
+    a = Args(argv)
+    try:
+        import torch
+        from .. import generate
+        from ..config import EngineConfig, KVManagerConfig, SchedulerConfig
+        from ..engine.engine import Engine
+        steps, n_prompts, plen = a.i32("steps", 32), a.i32("prompts", 8), a.i32("prompt-len", 64)
+        tie, B, attn = a.f64("tie-margin", 0.05), a.i32("block-size", 16), a.str("attn", "auto")
+        spec16 = load_model_from_args(a, "bfloat16")
+        spec32 = load_model_from_args(a, "float32")
+        a.warn_unused()
+        vocab = spec16.lm_head.vocab
+        g = torch.Generator().manual_seed(7)
+        shared = torch.randint(3, vocab, (max(plen // 2 // B * B, B),), generator=g).tolist()
+        prompts = [shared + torch.randint(3, vocab, (plen - len(shared) + i,), generator=g).tolist()
+                   for i in range(n_prompts)]
+        max_len = plen + n_prompts + steps + B
+
+        def engine(spec, dtype, **kw):
+            kv = KVManagerConfig(num_blocks=kw.pop("num_blocks", 4 * n_prompts * (max_len // B + 2)), block_size=B,
+                                 max_seq_len=kw.pop("max_seq_len", max_len), policy=kw.pop("policy", "paged"),
+                                 prefix_caching=kw.pop("prefix", False), watermark_blocks=0)
+            return Engine(spec, EngineConfig(kv=kv, sched=SchedulerConfig(max_num_seqs=16, max_batched_tokens=2048),
+                                             dtype=dtype, attn=attn))
+
+        ok = True
+
+        def report(name, passed, detail=""):
+            nonlocal ok
+            ok &= bool(passed)
+            print(f"[{'PASS' if passed else 'FAIL'}] {name} {detail}")
+
+        # 1. teacher-forced logits, bfloat16 against the true 32-bit path
+        e16, e32 = engine(spec16, "bfloat16"), engine(spec32, "float32")
+        agree = total = 0
+        errs = []
+        for p in prompts:
+            cont = generate(e32, [p], steps)[0]
+            l32, l16 = e32.score(p + cont).double(), e16.score(p + cont).double()
+            top = l32.topk(5, dim=-1)
+            gap = top.values[:, 0] - top.values[:, 1]
+            same = l16.argmax(-1) == top.indices[:, 0]
+            agree += int((same | (gap < tie)).sum())
+            total += l32.shape[0]
+            errs.append((l16.gather(1, top.indices) - top.values).abs())
+        e = torch.cat(errs)
+        report("bfloat16 vs float32, teacher-forced top-1", agree >= 0.98 * total,
+               f"{agree}/{total}; top-5 logit error mean {e.mean():.4f} max {e.max():.4f}")
+
+        # 2. alone on a fragmented pool vs all in one batch
+        solo_eng = engine(spec16, "bfloat16")
+        frag = [solo_eng.add_request([3 + (i % 5)] * (B + 1 + i % 3), 1) for i in range(12)]   # scatter the free list
+        solo_eng.run_until_idle()
+        solo_eng.take_finished()
+        solo = [generate(solo_eng, [p], steps)[0] for p in prompts]
+        batch = generate(engine(spec16, "bfloat16"), prompts, steps)
+        report("alone (scattered pages) = batch", solo == batch)
+
+        # 3. paged vs contiguous
+        cont_tokens = generate(engine(spec16, "bfloat16", policy="contiguous", max_seq_len=max_len,
+                                      num_blocks=(n_prompts + 1) * (max_len // B + 1)), prompts, steps)
+        report("paged = contiguous", cont_tokens == batch)
+
+        # 4. prefix caching on vs off
+        pe = engine(spec16, "bfloat16", prefix=True)
+        first = [generate(pe, [p], steps)[0] for p in prompts]
+        hits = pe.kv.prefix_stats().hit_blocks
+        report("prefix cache on = off", first == solo and hits > 0, f"({hits} page hits)")
+        again = generate(pe, [prompts[0]], steps)[0]
+        report("same prompt again from the cache", again == solo[0])
+        print("all checks passed" if ok else "SOME CHECKS FAILED")
+        return 0 if ok else 2
+    except Exception as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
