@@ -22,6 +22,8 @@
 namespace kvcm {
 
 constexpr int kAttnThreads = 128;     // 4 warps
+// Decode keeps STAGES key/value tiles in flight per block: 3 when few blocks must hide the memory
+// latency themselves, 2 (less shared memory, more blocks per SM) when the grid is large.
 
 struct DecodeParams {
   const bf16* q; int q_stride;
@@ -32,17 +34,18 @@ struct DecodeParams {
   float* part_o; float* part_ml;
   int nh, nkv, block_size, window, part_size, num_parts;
   float scale_log2;
+  int log2_block;                      // log2(block_size) when it is a power of two, else -1
 };
 
-template <int HD>
+template <int HD, int kKVStages>
 __global__ void __launch_bounds__(kAttnThreads)
 attn_decode_kernel(DecodeParams p) {
   constexpr int LD = HD + 8;
   constexpr bool Q_IN_REGS = HD <= 128;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qtile = reinterpret_cast<bf16*>(smem_raw);                 // [16][LD]
-  bf16* kbuf = qtile + 16 * LD;                                    // [2][64][LD]
-  bf16* vbuf = kbuf + 2 * kKeyTile * LD;                           // [2][64][LD]
+  bf16* kbuf = qtile + 16 * LD;                                    // [stages][64][LD]
+  bf16* vbuf = kbuf + kKVStages * kKeyTile * LD;                   // [stages][64][LD]
 
   pdl_launch_dependents();
   pdl_wait();
@@ -84,9 +87,18 @@ attn_decode_kernel(DecodeParams p) {
 
   const int t_first = (begin / kKeyTile) * kKeyTile;
   const int n_tiles = (end - t_first + kKeyTile - 1) / kKeyTile;
-  load_kv_tile<HD>(kbuf, p.k_cache, table, t_first, begin, end, kvh, p.nkv, p.block_size, tid, kAttnThreads);
-  load_kv_tile<HD>(vbuf, p.v_cache, table, t_first, begin, end, kvh, p.nkv, p.block_size, tid, kAttnThreads);
-  cp_async_commit();
+  auto load_stage = [&](int i) {                                   // tile i -> ring slot i % stages
+    const int sl = i % kKVStages;
+    if (i < n_tiles) {
+      load_kv_tile<HD>(kbuf + sl * kKeyTile * LD, p.k_cache, table, t_first + i * kKeyTile, begin, end, kvh, p.nkv,
+                       p.block_size, tid, kAttnThreads, p.log2_block);
+      load_kv_tile<HD>(vbuf + sl * kKeyTile * LD, p.v_cache, table, t_first + i * kKeyTile, begin, end, kvh, p.nkv,
+                       p.block_size, tid, kAttnThreads, p.log2_block);
+    }
+    cp_async_commit();                                             // one group per tile, empty ones too
+  };
+#pragma unroll
+  for (int i = 0; i < kKVStages - 1; ++i) load_stage(i);
   __syncthreads();                                                 // qtile is written
 
   uint32_t qa[Q_IN_REGS ? HD / 16 : 1][4];
@@ -99,22 +111,13 @@ attn_decode_kernel(DecodeParams p) {
 
   for (int i = 0; i < n_tiles; ++i) {
     const int t0 = t_first + i * kKeyTile;
-    if (i + 1 < n_tiles) {
-      const int nb = (i + 1) & 1;
-      load_kv_tile<HD>(kbuf + nb * kKeyTile * LD, p.k_cache, table, t0 + kKeyTile, begin, end, kvh, p.nkv,
-                       p.block_size, tid, kAttnThreads);
-      load_kv_tile<HD>(vbuf + nb * kKeyTile * LD, p.v_cache, table, t0 + kKeyTile, begin, end, kvh, p.nkv,
-                       p.block_size, tid, kAttnThreads);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    load_stage(i + kKVStages - 1);                                 // its slot was freed by the barrier that
+    cp_async_wait<kKVStages - 1>();                                // ended round i - 1; tile i has landed
     __syncthreads();
     const int kb = t0 + warp * 16;                                 // this warp's 16 keys
     if (kb < end && kb + 16 > begin) {
-      const bf16* kt = kbuf + (i & 1) * kKeyTile * LD + warp * 16 * LD;
-      const bf16* vt = vbuf + (i & 1) * kKeyTile * LD + warp * 16 * LD;
+      const bf16* kt = kbuf + (i % kKVStages) * kKeyTile * LD + warp * 16 * LD;
+      const bf16* vt = vbuf + (i % kKVStages) * kKeyTile * LD + warp * 16 * LD;
       float s[2][4];
       if constexpr (Q_IN_REGS) {
         qk_16x16<HD>(s, reinterpret_cast<const uint32_t(&)[HD / 16][4]>(qa), kt, lane);
@@ -147,6 +150,7 @@ attn_decode_kernel(DecodeParams p) {
     __syncthreads();                                               // the buffer is loaded again next round
   }
 
+  cp_async_wait<0>();
   // ---- merge the four warps (each saw different keys) through shared memory
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -359,17 +363,17 @@ attn_prefill_kernel(PrefillParams p) {
   }
 }
 
-template <int HD> size_t decode_smem() {
-  const size_t tiles = size_t(16 + 4 * kKeyTile) * (HD + 8) * sizeof(bf16);
+template <int HD, int kKVStages> size_t decode_smem() {
+  const size_t tiles = size_t(16 + 2 * kKVStages * kKeyTile) * (HD + 8) * sizeof(bf16);
   const size_t merge = size_t(16) * (HD + 8) * sizeof(bf16) + (size_t(4) * 16 * HD + 2 * 4 * 16) * sizeof(float);
   return tiles > merge ? tiles : merge;
 }
 template <int HD> size_t prefill_smem() { return size_t(64 + 4 * kKeyTile) * (HD + 8) * sizeof(bf16); }
 
-template <int HD>
-int launch_decode(const DecodeParams& p, int seqs, cudaStream_t s) {
-  auto kernel = attn_decode_kernel<HD>;
-  const size_t smem = decode_smem<HD>();
+template <int HD, int STAGES>
+int launch_decode_staged(const DecodeParams& p, int seqs, cudaStream_t s) {
+  auto kernel = attn_decode_kernel<HD, STAGES>;
+  const size_t smem = decode_smem<HD, STAGES>();
   static bool configured = false;                                  // per instantiation, set once
   if (!configured && smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -379,6 +383,14 @@ int launch_decode(const DecodeParams& p, int seqs, cudaStream_t s) {
   const int G = p.nh / p.nkv;
   dim3 grid(p.num_parts, p.nkv * ((G + 15) / 16), seqs);
   return pdl_launch(kernel, grid, dim3(kAttnThreads), smem, s, p);
+}
+
+template <int HD>
+int launch_decode(const DecodeParams& p, int seqs, int sm_count, cudaStream_t s) {
+  const int G = p.nh / p.nkv;
+  const long long blocks = (long long)p.num_parts * p.nkv * ((G + 15) / 16) * seqs;
+  if (blocks >= 4LL * sm_count) return launch_decode_staged<HD, 2>(p, seqs, s);
+  return launch_decode_staged<HD, 3>(p, seqs, s);
 }
 
 template <int HD>
@@ -421,6 +433,13 @@ KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, 
                                         int hd, int block_size, float scale, int window, int part_size,
                                         int num_parts, float* scratch, void* stream) {
   if (seqs == 0) return 0;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
   if (nkv <= 0 || nh % nkv || part_size <= 0 || part_size % kKeyTile || num_parts < 1) return KVCM_ERR_UNSUPPORTED;
   if (num_parts > 1 && scratch == nullptr) return KVCM_ERR_UNSUPPORTED;
   DecodeParams p;
@@ -431,8 +450,10 @@ KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, 
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
   p.part_size = part_size; p.num_parts = num_parts;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.log2_block = -1;
+  for (int b = 0; b < 16; ++b) if ((1 << b) == block_size) p.log2_block = b;
   int rc = KVCM_ERR_UNSUPPORTED;
-#define X(N) if (hd == N) rc = launch_decode<N>(p, seqs, (cudaStream_t)stream);
+#define X(N) if (hd == N) rc = launch_decode<N>(p, seqs, sm_count, (cudaStream_t)stream);
   KVCM_FOR_HEAD_DIMS(X)
 #undef X
   if (rc != 0 || num_parts == 1) return rc;

@@ -46,12 +46,35 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Copies keys [t0, t0 + kKeyTile) of one KV head from the paged cache into a shared tile
 // [kKeyTile][HD + 8].  Keys outside [lo, hi) are zero-filled (their scores are masked by the
 // caller; zero keeps 0 * value finite).  All `nthreads` threads of the block take part.
+// When the 16-byte chunks of a row divide the block evenly, a thread keeps one chunk column and
+// walks the rows, so the page lookup and the address arithmetic happen once per row, not per
+// chunk; `log2_block` >= 0 (a power-of-two page size) turns the division into a shift.
 template <int HD>
 __device__ __forceinline__ void load_kv_tile(bf16* __restrict__ tile, const bf16* __restrict__ cache,
                                              const int* __restrict__ table, int t0, int lo, int hi,
-                                             int kvh, int nkv, int block_size, int tid, int nthreads) {
+                                             int kvh, int nkv, int block_size, int tid, int nthreads,
+                                             int log2_block = -1) {
   constexpr int CH = HD / 8;                      // 16-byte chunks per row
   constexpr int LD = HD + 8;
+  if ((128 % CH) == 0 && nthreads == 128) {
+    constexpr int RPP = (128 % CH) == 0 ? 128 / CH : 1;      // rows per pass
+    const int ch = tid % CH, r0 = tid / CH;
+    const size_t head_off = size_t(kvh) * block_size * HD + ch * 8;
+    const size_t page_stride = size_t(nkv) * block_size * HD;
+#pragma unroll
+    for (int key = r0; key < kKeyTile; key += RPP) {
+      const int t = t0 + key;
+      bf16* dst = tile + key * LD + ch * 8;
+      if (t >= lo && t < hi) {
+        const int pi = log2_block >= 0 ? (t >> log2_block) : t / block_size;
+        const int off = log2_block >= 0 ? (t & (block_size - 1)) : t - pi * block_size;
+        cp_async16(dst, cache + size_t(table[pi]) * page_stride + head_off + size_t(off) * HD);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    return;
+  }
   for (int c = tid; c < kKeyTile * CH; c += nthreads) {
     const int key = c / CH, ch = c - key * CH;
     const int t = t0 + key;

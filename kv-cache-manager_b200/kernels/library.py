@@ -269,7 +269,7 @@ def decode_partitions(seqs: int, nh: int, nkv: int, max_ctx: int, device, versio
     """How the decode kernel splits the context: (keys per partition, number of partitions).
 
     'v1': the whole context in one block per (request, KV head).  'v2'/'auto': enough partitions
-    that the grid has about three blocks per SM, each at least 128 keys long (the reference fixes
+    that the grid has about five blocks per SM, each at least 128 keys long (the reference fixes
     512 keys per partition, src/cuda/paged_attention.cu:22; a B200 has 148 SMs to fill and a short
     partition is one memory latency instead of several)."""
     max_ctx = max(int(max_ctx), 1)
@@ -278,7 +278,7 @@ def decode_partitions(seqs: int, nh: int, nkv: int, max_ctx: int, device, versio
         return whole, 1
     G = nh // nkv
     blocks = max(1, seqs * nkv * ((G + 15) // 16))
-    want = max(1, (3 * sm_count(device) + blocks - 1) // blocks)
+    want = max(1, (5 * sm_count(device) + blocks - 1) // blocks)
     most = max(1, max_ctx // 128)
     parts = max(1, min(want, most))
     size = ((max_ctx + parts - 1) // parts + KEY_TILE - 1) // KEY_TILE * KEY_TILE
