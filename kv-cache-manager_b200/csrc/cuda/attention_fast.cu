@@ -304,43 +304,81 @@ attn_prefill_kernel(PrefillParams p) {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (warp_live) {
-#pragma unroll 1
-      for (int sub = 0; sub < kKeyTile / 16; ++sub) {
-        const int kb = t0 + sub * 16;
-        if (kb > warp_last_pos || kb >= hi || kb + 16 <= max(lo, warp_first_lo)) continue;   // all masked
-        const bf16* kt = kbuf + (i & 1) * kKeyTile * LD + sub * 16 * LD;
-        const bf16* vt = vbuf + (i & 1) * kKeyTile * LD + sub * 16 * LD;
-        float s[2][4];
+    if (warp_live && t0 <= warp_last_pos && t0 + kKeyTile > max(lo, warp_first_lo)) {
+      const bf16* kt = kbuf + (i & 1) * kKeyTile * LD;
+      const bf16* vt = vbuf + (i & 1) * kKeyTile * LD;
+      // scores of this warp's 16 rows against the tile's 64 keys: s[2*sub], s[2*sub+1] = keys of sub-block sub
+      float s[kKeyTile / 8][4];
+#pragma unroll
+      for (int n = 0; n < kKeyTile / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      const int krow = (lane & 7) + ((lane >> 4) << 3), kcol = ((lane >> 3) & 1) << 3;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+        uint32_t a[4];
         if constexpr (Q_IN_REGS) {
-          qk_16x16<HD>(s, reinterpret_cast<const uint32_t(&)[HD / 16][4]>(qa), kt, lane);
+          a[0] = qa[kk][0]; a[1] = qa[kk][1]; a[2] = qa[kk][2]; a[3] = qa[kk][3];
         } else {
-#pragma unroll
-          for (int a = 0; a < 2; ++a)
-#pragma unroll
-            for (int b = 0; b < 4; ++b) s[a][b] = 0.f;
-          const int krow = (lane & 7) + ((lane >> 4) << 3), kcol = ((lane >> 3) & 1) << 3;
-#pragma unroll 4
-          for (int kk = 0; kk < HD / 16; ++kk) {
-            uint32_t a[4], b[4];
-            ldmatrix_x4(a, qw + (lane & 15) * LD + kk * 16 + ((lane >> 4) << 3));
-            ldmatrix_x4(b, kt + krow * LD + kk * 16 + kcol);
-            mma_bf16(s[0], a, b[0], b[1]);
-            mma_bf16(s[1], a, b[2], b[3]);
-          }
+          ldmatrix_x4(a, qw + (lane & 15) * LD + kk * 16 + ((lane >> 4) << 3));
         }
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int sub = 0; sub < kKeyTile / 16; ++sub) {
+          if (t0 + sub * 16 > warp_last_pos) continue;               // warp-uniform: beyond every row of the warp
+          uint32_t b[4];
+          ldmatrix_x4(b, kt + (sub * 16 + krow) * LD + kk * 16 + kcol);
+          mma_bf16(s[2 * sub], a, b[0], b[1]);
+          mma_bf16(s[2 * sub + 1], a, b[2], b[3]);
+        }
+      }
+      // scale; mask only where the tile touches the diagonal, the window's edge or the key range's edge
+      const bool needs_mask = t0 + kKeyTile - 1 > pos0 + warp * 16 || t0 < lo ||
+                              (p.window > 0 && t0 <= warp_last_pos - p.window) || t0 + kKeyTile > hi;
+      float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int key = kb + 8 * h + 2 * t4 + (j & 1);
+      for (int n = 0; n < kKeyTile / 8; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float v = s[n][j] * p.scale_log2;
+          if (needs_mask) {
+            const int key = t0 + 8 * n + 2 * t4 + (j & 1);
             const int rp = row_pos[j >> 1];
             const bool ok = key <= rp && key >= lo && key < hi && (p.window <= 0 || key > rp - p.window);
-            s[h][j] = ok ? s[h][j] * p.scale_log2 : -INFINITY;
+            v = ok ? v : -INFINITY;
           }
-        uint32_t pa[4];
-        softmax_step<HD>(s, m, l, o, pa);
-        pv_16x16<HD>(o, pa, vt, lane);
+          s[n][j] = v;
+          mx[j >> 1] = fmaxf(mx[j >> 1], v);
+        }
+      float scale_old[2], m_new[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        m_new[r] = fmaxf(m[r], mx[r]);
+        scale_old[r] = (m_new[r] == -INFINITY) ? 1.f : exp2f(m[r] - m_new[r]);
+        m[r] = m_new[r];
+      }
+      float sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int n = 0; n < kKeyTile / 8; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = j >> 1;
+          const float e = (m_new[r] == -INFINITY) ? 0.f : exp2f(s[n][j] - m_new[r]);
+          s[n][j] = e;
+          sum[r] += e;
+        }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) l[r] = l[r] * scale_old[r] + sum[r];
+#pragma unroll
+      for (int d = 0; d < HD / 8; ++d) {
+        o[d][0] *= scale_old[0]; o[d][1] *= scale_old[0];
+        o[d][2] *= scale_old[1]; o[d][3] *= scale_old[1];
+      }
+#pragma unroll
+      for (int sub = 0; sub < kKeyTile / 16; ++sub) {
+        if (t0 + sub * 16 > warp_last_pos) continue;                 // those probabilities are all zero
+        uint32_t pa[4] = {pack_bf16(s[2 * sub][0], s[2 * sub][1]), pack_bf16(s[2 * sub][2], s[2 * sub][3]),
+                          pack_bf16(s[2 * sub + 1][0], s[2 * sub + 1][1]), pack_bf16(s[2 * sub + 1][2], s[2 * sub + 1][3])};
+        pv_16x16<HD>(o, pa, vt + sub * 16 * LD, lane);
       }
     }
     __syncthreads();

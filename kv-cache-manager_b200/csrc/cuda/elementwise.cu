@@ -120,42 +120,47 @@ __global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__
 // (2j, 2j+1).  Cache layout per layer: [page][kv head][slot in page][head_dim].
 // slot < 0: the row writes nothing (padding).  write_cache = 0: only the q heads are rotated.
 template <typename T>
-__global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
-                                  const float* __restrict__ inv_freq, int rotary_dim, int interleaved,
-                                  const int* __restrict__ slot_mapping, T* __restrict__ k_cache,
-                                  T* __restrict__ v_cache, int nh, int nkv, int hd, int block_size,
-                                  int write_cache) {
+__global__ void __launch_bounds__(256)
+rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                  const float* __restrict__ inv_freq, int rotary_dim, int interleaved,
+                  const int* __restrict__ slot_mapping, T* __restrict__ k_cache,
+                  T* __restrict__ v_cache, int nh, int nkv, int hd, int block_size,
+                  int write_cache) {
+  extern __shared__ float cs_table[];    // [rotary_dim/2] cos, then [rotary_dim/2] sin: once per row
   pdl_launch_dependents();
   pdl_wait();
-  // one warp per head of the fused row: q heads [0, nh), k heads [nh, nh+nkv), v heads after them
+  // one block per row; one warp per head at a time: q heads [0, nh), k heads [nh, nh+nkv), v after them
   const int t = blockIdx.x;
-  const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int heads = write_cache ? nh + 2 * nkv : nh;
-  if (head >= heads) return;
-  T* base = qkv + size_t(t) * row_stride + size_t(head) * hd;
   const int half = rotary_dim / 2;
-  if (head < nh + nkv && inv_freq != nullptr && half > 0) {
+  const bool rotate = inv_freq != nullptr && half > 0;
+  if (rotate) {
     const float pos = float(positions[t]);
-    for (int j = lane; j < half; j += 32) {
-      float sn, cs;
-      sincosf(pos * inv_freq[j], &sn, &cs);
-      const int ia = interleaved ? 2 * j : j;
-      const int ib = interleaved ? 2 * j + 1 : j + half;
-      const float a = ldf(base + ia), b = ldf(base + ib);
-      stf(base + ia, a * cs - b * sn);
-      stf(base + ib, b * cs + a * sn);
-    }
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &cs_table[half + j], &cs_table[j]);
   }
-  if (head < nh || !write_cache) return;
-  const int slot = slot_mapping[t];
-  if (slot < 0) return;
-  __syncwarp();                          // the rotated values of this head are written by this warp
-  const int page = slot / block_size, off = slot - page * block_size;
-  const bool is_k = head < nh + nkv;
-  const int kvh = is_k ? head - nh : head - nh - nkv;
-  T* dst = (is_k ? k_cache : v_cache) + ((size_t(page) * nkv + kvh) * block_size + off) * hd;
-  for (int d = lane; d < hd; d += 32) dst[d] = base[d];
+  __syncthreads();
+  const int slot = write_cache ? slot_mapping[t] : -1;
+  const int page = slot >= 0 ? slot / block_size : 0, off = slot >= 0 ? slot - page * block_size : 0;
+  for (int head = warp; head < heads; head += nwarps) {
+    T* base = qkv + size_t(t) * row_stride + size_t(head) * hd;
+    if (head < nh + nkv && rotate) {
+      for (int j = lane; j < half; j += 32) {
+        const float cs = cs_table[j], sn = cs_table[half + j];
+        const int ia = interleaved ? 2 * j : j;
+        const int ib = interleaved ? 2 * j + 1 : j + half;
+        const float a = ldf(base + ia), b = ldf(base + ib);
+        stf(base + ia, a * cs - b * sn);
+        stf(base + ib, b * cs + a * sn);
+      }
+    }
+    if (head < nh || slot < 0) continue;
+    __syncwarp();                        // the rotated values of this head are written by this warp
+    const bool is_k = head < nh + nkv;
+    const int kvh = is_k ? head - nh : head - nh - nkv;
+    T* dst = (is_k ? k_cache : v_cache) + ((size_t(page) * nkv + kvh) * block_size + off) * hd;
+    for (int d = lane; d < hd; d += 32) dst[d] = base[d];
+  }
 }
 
 // --------------------------------------------------------------------------- SiLU(g) * u
@@ -172,6 +177,41 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
   const float x = ldf(g + i);
   const float s = Store<T>::round(x / (1.f + expf(-x)));
   stf(out + size_t(t) * inter + i, s * ldf(g + inter + i));
+}
+
+// bfloat16, width a multiple of 8: eight elements per thread through 16-byte loads and stores.
+__global__ void silu_mul_vec_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= inter) return;
+  const bf16* g = gate_up + size_t(t) * 2 * inter;
+  const uint4 gv = *reinterpret_cast<const uint4*>(g + i);
+  const uint4 uv = *reinterpret_cast<const uint4*>(g + inter + i);
+  const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+  const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&uv);
+  uint4 ov;
+  __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 x = __bfloat1622float2(gp[k]), u = __bfloat1622float2(up[k]);
+    const float s0 = Store<bf16>::round(x.x / (1.f + expf(-x.x)));
+    const float s1 = Store<bf16>::round(x.y / (1.f + expf(-x.y)));
+    op[k] = __floats2bfloat162_rn(s0 * u.x, s1 * u.y);
+  }
+  *reinterpret_cast<uint4*>(out + size_t(t) * inter + i) = ov;
+}
+
+template <typename T>
+int launch_silu_mul(const T* gate_up, T* out, int rows, int inter, cudaStream_t s) {
+  return pdl_launch(silu_mul_kernel<T>, dim3(rows, (inter + 255) / 256), dim3(256), 0, s, gate_up, out, inter);
+}
+template <>
+int launch_silu_mul<bf16>(const bf16* gate_up, bf16* out, int rows, int inter, cudaStream_t s) {
+  if ((inter % 8) == 0 && ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0)
+    return pdl_launch(silu_mul_vec_kernel, dim3(rows, (inter / 8 + 255) / 256), dim3(256), 0, s, gate_up, out, inter);
+  return pdl_launch(silu_mul_kernel<bf16>, dim3(rows, (inter + 255) / 256), dim3(256), 0, s, gate_up, out, inter);
 }
 
 // Gathers rows of a [*, width] matrix of T into a dense [n, width] matrix (used for the rows
@@ -241,8 +281,7 @@ using namespace kvcm;
                                         int write_cache, void* stream) {                              \
     if (rows == 0) return 0;                                                                          \
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return KVCM_ERR_UNSUPPORTED;           \
-    const int heads = write_cache ? nh + 2 * nkv : nh;                                                \
-    return pdl_launch(rope_cache_kernel<T>, dim3(rows, (heads + 3) / 4), dim3(128), 0,                \
+    return pdl_launch(rope_cache_kernel<T>, dim3(rows), dim3(256), size_t(rotary_dim) * sizeof(float),\
                       (cudaStream_t)stream, (T*)qkv, row_stride, positions, inv_freq, rotary_dim,     \
                       interleaved, slot_mapping, (T*)k_cache, (T*)v_cache, nh, nkv, hd, block_size,   \
                       write_cache);                                                                   \
@@ -250,8 +289,7 @@ using namespace kvcm;
   KVCM_API int kvcm_silu_mul_##SUFFIX(const void* gate_up, void* out, int rows, int inter,            \
                                       void* stream) {                                                 \
     if (rows == 0) return 0;                                                                          \
-    return pdl_launch(silu_mul_kernel<T>, dim3(rows, (inter + 255) / 256), dim3(256), 0,              \
-                      (cudaStream_t)stream, (const T*)gate_up, (T*)out, inter);                       \
+    return launch_silu_mul<T>((const T*)gate_up, (T*)out, rows, inter, (cudaStream_t)stream);         \
   }                                                                                                   \
   KVCM_API int kvcm_gather_rows_##SUFFIX(const void* src, const int* rows, void* dst, int n,          \
                                          int width, void* stream) {                                   \
