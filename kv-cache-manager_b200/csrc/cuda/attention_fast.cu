@@ -90,10 +90,8 @@ attn_decode_kernel(DecodeParams p) {
   auto load_stage = [&](int i) {                                   // tile i -> ring slot i % stages
     const int sl = i % kKVStages;
     if (i < n_tiles) {
-      load_kv_tile<HD>(kbuf + sl * kKeyTile * LD, p.k_cache, table, t_first + i * kKeyTile, begin, end, kvh, p.nkv,
-                       p.block_size, tid, kAttnThreads, p.log2_block);
-      load_kv_tile<HD>(vbuf + sl * kKeyTile * LD, p.v_cache, table, t_first + i * kKeyTile, begin, end, kvh, p.nkv,
-                       p.block_size, tid, kAttnThreads, p.log2_block);
+      load_kv_tiles<HD>(kbuf + sl * kKeyTile * LD, vbuf + sl * kKeyTile * LD, p.k_cache, p.v_cache, table,
+                        t_first + i * kKeyTile, begin, end, kvh, p.nkv, p.block_size, tid, kAttnThreads, p.log2_block);
     }
     cp_async_commit();                                             // one group per tile, empty ones too
   };
@@ -235,6 +233,7 @@ struct PrefillParams {
   const int* seq_q_start; const int* seq_q_len; const int* seq_ctx_len;
   int nh, nkv, block_size, window;
   float scale_log2;
+  int log2_block;
 };
 
 template <int HD>
@@ -271,8 +270,8 @@ attn_prefill_kernel(PrefillParams p) {
   }
   const int t_first = (lo / kKeyTile) * kKeyTile;
   const int n_tiles = (hi - t_first + kKeyTile - 1) / kKeyTile;
-  load_kv_tile<HD>(kbuf, p.k_cache, table, t_first, lo, hi, kvh, p.nkv, p.block_size, tid, kAttnThreads);
-  load_kv_tile<HD>(vbuf, p.v_cache, table, t_first, lo, hi, kvh, p.nkv, p.block_size, tid, kAttnThreads);
+  load_kv_tiles<HD>(kbuf, vbuf, p.k_cache, p.v_cache, table, t_first, lo, hi, kvh, p.nkv, p.block_size, tid,
+                    kAttnThreads, p.log2_block);
   cp_async_commit();
   __syncthreads();
 
@@ -294,10 +293,8 @@ attn_prefill_kernel(PrefillParams p) {
     const int t0 = t_first + i * kKeyTile;
     if (i + 1 < n_tiles) {
       const int nb = (i + 1) & 1;
-      load_kv_tile<HD>(kbuf + nb * kKeyTile * LD, p.k_cache, table, t0 + kKeyTile, lo, hi, kvh, p.nkv,
-                       p.block_size, tid, kAttnThreads);
-      load_kv_tile<HD>(vbuf + nb * kKeyTile * LD, p.v_cache, table, t0 + kKeyTile, lo, hi, kvh, p.nkv,
-                       p.block_size, tid, kAttnThreads);
+      load_kv_tiles<HD>(kbuf + nb * kKeyTile * LD, vbuf + nb * kKeyTile * LD, p.k_cache, p.v_cache, table,
+                        t0 + kKeyTile, lo, hi, kvh, p.nkv, p.block_size, tid, kAttnThreads, p.log2_block);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -353,7 +350,7 @@ attn_prefill_kernel(PrefillParams p) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         m_new[r] = fmaxf(m[r], mx[r]);
-        scale_old[r] = (m_new[r] == -INFINITY) ? 1.f : exp2f(m[r] - m_new[r]);
+        scale_old[r] = (m_new[r] == -INFINITY) ? 1.f : fast_exp2(m[r] - m_new[r]);
         m[r] = m_new[r];
       }
       float sum[2] = {0.f, 0.f};
@@ -362,7 +359,7 @@ attn_prefill_kernel(PrefillParams p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int r = j >> 1;
-          const float e = (m_new[r] == -INFINITY) ? 0.f : exp2f(s[n][j] - m_new[r]);
+          const float e = (m_new[r] == -INFINITY) ? 0.f : fast_exp2(s[n][j] - m_new[r]);
           s[n][j] = e;
           sum[r] += e;
         }
@@ -514,6 +511,8 @@ KVCM_API int kvcm_attention_prefill_bf16(const void* q, int q_stride, void* out,
   p.seq_q_start = seq_q_start; p.seq_q_len = seq_q_len; p.seq_ctx_len = seq_ctx_len;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.log2_block = -1;
+  for (int b = 0; b < 16; ++b) if ((1 << b) == block_size) p.log2_block = b;
   int rc = KVCM_ERR_UNSUPPORTED;
 #define X(N) if (hd == N) rc = launch_prefill<N>(p, tiles, (cudaStream_t)stream);
   KVCM_FOR_HEAD_DIMS(X)

@@ -89,6 +89,60 @@ __device__ __forceinline__ void load_kv_tile(bf16* __restrict__ tile, const bf16
   }
 }
 
+// Loads the K tile and the V tile of keys [t0, t0 + kKeyTile) together (they share the page table
+// and every offset).  With 128 threads and a chunk count that divides them, a thread owns one
+// 16-byte column and a run of consecutive keys, so it looks a page up only when its run crosses
+// into the next page; everything else is one add per key.  Other shapes take load_kv_tile twice.
+template <int HD>
+__device__ __forceinline__ void load_kv_tiles(bf16* __restrict__ ktile, bf16* __restrict__ vtile,
+                                              const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                                              const int* __restrict__ table, int t0, int lo, int hi, int kvh,
+                                              int nkv, int block_size, int tid, int nthreads, int log2_block) {
+  constexpr int CH = HD / 8;
+  constexpr int LD = HD + 8;
+  if constexpr ((128 % CH) == 0 && (kKeyTile % (128 / CH)) == 0) {
+    if (nthreads == 128) {
+      constexpr int RUN = kKeyTile / (128 / CH);            // consecutive keys per thread
+      const int ch = tid % CH, first = (tid / CH) * RUN;
+      const size_t page_stride = size_t(nkv) * block_size * HD;
+      const size_t head_off = size_t(kvh) * block_size * HD + ch * 8;
+      int t = t0 + first;
+      int pi = log2_block >= 0 ? (t >> log2_block) : t / block_size;
+      int off = t - pi * block_size;
+      size_t src = 0;
+      bool have_page = false;
+      bf16* kd = ktile + first * LD + ch * 8;
+      bf16* vd = vtile + first * LD + ch * 8;
+#pragma unroll
+      for (int k = 0; k < RUN; ++k) {
+        if (t >= lo && t < hi) {
+          if (!have_page) {
+            src = size_t(table[pi]) * page_stride + head_off + size_t(off) * HD;
+            have_page = true;
+          }
+          cp_async16(kd, kcache + src);
+          cp_async16(vd, vcache + src);
+        } else {
+          *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        ++t; ++off; src += HD; kd += LD; vd += LD;
+        if (off == block_size) { off = 0; ++pi; have_page = false; }
+      }
+      return;
+    }
+  }
+  load_kv_tile<HD>(ktile, kcache, table, t0, lo, hi, kvh, nkv, block_size, tid, nthreads, log2_block);
+  load_kv_tile<HD>(vtile, vcache, table, t0, lo, hi, kvh, nkv, block_size, tid, nthreads, log2_block);
+}
+
+// 2^x by the hardware approximation (one instruction; softmax weights need no more).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // One warp: S(16 x 16 keys) = Q(16 x HD) * K(16 keys x HD)^T.  `qa` holds the A fragments of Q
 // for every 16-wide slice of HD; `ktile` points at the first of the 16 keys in the shared tile.
 // s[0] = keys 0..7, s[1] = keys 8..15 (accumulator layout).
@@ -155,7 +209,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[2][4], float (&m)[2], fl
   for (int r = 0; r < 2; ++r) {
     m_new[r] = fmaxf(m[r], mx[r]);
     // A row that has seen no key yet keeps m = -inf; exp2(-inf - -inf) must not become NaN.
-    scale_old[r] = (m_new[r] == -INFINITY) ? 1.f : exp2f(m[r] - m_new[r]);
+    scale_old[r] = (m_new[r] == -INFINITY) ? 1.f : fast_exp2(m[r] - m_new[r]);
     m[r] = m_new[r];
   }
   float p[2][4];
@@ -165,7 +219,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[2][4], float (&m)[2], fl
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int r = j >> 1;
-      const float e = (m_new[r] == -INFINITY) ? 0.f : exp2f(s[h][j] - m_new[r]);
+      const float e = (m_new[r] == -INFINITY) ? 0.f : fast_exp2(s[h][j] - m_new[r]);
       p[h][j] = e;
       sum[r] += e;
     }
