@@ -35,6 +35,13 @@ template <> struct Store<bf16> {
 template <typename T> __device__ __forceinline__ float ldf(const T* p) { return Store<T>::load(p); }
 template <typename T> __device__ __forceinline__ void stf(T* p, float v) { Store<T>::store(p, v); }
 
+// Rotation of one rotary pair, written with explicit roundings (no fused multiply-add) so that
+// every kernel that rotates gives the same bits.
+__device__ __forceinline__ void rotate_pair(float a, float b, float cs, float sn, float& ra, float& rb) {
+  ra = __fsub_rn(__fmul_rn(a, cs), __fmul_rn(b, sn));
+  rb = __fadd_rn(__fmul_rn(b, cs), __fmul_rn(a, sn));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

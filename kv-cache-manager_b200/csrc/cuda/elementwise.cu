@@ -150,8 +150,10 @@ rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ p
         const int ia = interleaved ? 2 * j : j;
         const int ib = interleaved ? 2 * j + 1 : j + half;
         const float a = ldf(base + ia), b = ldf(base + ib);
-        stf(base + ia, a * cs - b * sn);
-        stf(base + ib, b * cs + a * sn);
+        float ra, rb;
+        rotate_pair(a, b, cs, sn, ra, rb);
+        stf(base + ia, ra);
+        stf(base + ib, rb);
       }
     }
     if (head < nh || slot < 0) continue;

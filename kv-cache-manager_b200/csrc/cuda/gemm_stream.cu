@@ -5,9 +5,9 @@
 // bandwidth with megabytes in flight.  So W is not loaded by the computing threads at all: one
 // producer thread per block issues bulk asynchronous copies (cp.async.bulk, completion on an
 // mbarrier) of [16 rows x 512 k] pieces of W into a ring of up to twelve shared-memory stages ahead
-// of the consumers (as many as shared memory holds: 100-190 KB in flight per SM), and keeps issuing across tile boundaries.  Four consumer warps take the tensor-
+// of the consumers (as many as shared memory holds: 100-190 KB in flight per SM), and keeps issuing across tile boundaries.  Eight consumer warps take the tensor-
 // core product (m16n8k16, "swap AB": 16 rows of W are the 16-row operand, the batch rows are the
-// 8 columns) out of the ring, each warp one quarter of a stage along k; their partial sums are
+// 8 columns) out of the ring, each warp one eighth of a stage along k; their partial sums are
 // added in warp order per tile, so results are reproducible bit for bit.
 //  * Blocks are persistent: block b takes tiles b, b + grid, ...; the grid is about one block
 //    per SM so that the ring of every SM stays full.
@@ -24,7 +24,7 @@
 
 namespace kvcm {
 
-constexpr int kStreamConsumers = 4;                    // consumer warps
+constexpr int kStreamConsumers = 8;                    // consumer warps
 constexpr int kStreamThreads = 32 * (kStreamConsumers + 1);
 constexpr int kMaxStages = 12;                         // ring depth is chosen per launch to fill shared memory
 constexpr int kChunk = 1024;                           // k elements per stage
@@ -34,11 +34,30 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // every wait gives
 
 __device__ int g_stream_error = 0;                     // 0 = ok; else (code << 16) | block
 
+// What happens to a finished tile of 16 output columns x M rows.
+//  kStore    : y[m][n] = sum.
+//  kRopeCache: the 16 weight rows of a tile are 8 rows j..j+7 of a head and their rotary partners
+//              j + hd/2 .. (so one thread owns both halves of each pair): the sums are rounded to
+//              bfloat16 as the plain product would store them, q and k heads are rotated by
+//              position * inv_freq[j] (float sin/cos), q goes to y, k (rotated) and v go straight
+//              into the row's cache page slot.  Bit-for-bit what the separate product + rotary +
+//              cache-write kernels produce.
+//  kSiluMul  : the 16 weight rows are 8 gate rows i..i+7 and the 8 up rows I+i..: y[m][i] =
+//              round(round(silu(round(gate))) * round(up)), as the separate activation kernel.
+enum StreamEpilogue { kStore = 0, kRopeCache = 1, kSiluMul = 2 };
+
 struct StreamParams {
   const bf16* W; int N, K, ldw;
   const bf16* X; int ldx, M;
   void* Y; int ldy;
   int stages;                                          // ring depth (2..kMaxStages)
+  // rows of tile t: first 8 = (t / pair_blocks) * group_stride + 8 * (t % pair_blocks) + r,
+  //                 last 8 = those + pair_offset
+  int pair_blocks, group_stride, pair_offset;
+  // kRopeCache
+  const int* positions; const float* inv_freq; const int* slot_mapping;
+  bf16* k_cache; bf16* v_cache;
+  int nh, nkv, hd, block_size;
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -84,17 +103,32 @@ __device__ __forceinline__ void mma_stream(float (&d)[4], uint32_t a0, uint32_t 
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, typename OutT>
+__device__ __forceinline__ void cp_async_wait_dyn(int n) {       // wait until at most n groups are pending
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;\n" ::); break;
+    case 1: asm volatile("cp.async.wait_group 1;\n" ::); break;
+    case 2: asm volatile("cp.async.wait_group 2;\n" ::); break;
+    case 3: asm volatile("cp.async.wait_group 3;\n" ::); break;
+    case 4: asm volatile("cp.async.wait_group 4;\n" ::); break;
+    case 5: asm volatile("cp.async.wait_group 5;\n" ::); break;
+    case 6: asm volatile("cp.async.wait_group 6;\n" ::); break;
+    default: asm volatile("cp.async.wait_group 7;\n" ::); break;
+  }
+}
+
+template <int MT, typename OutT, int EPI>
 __global__ void __launch_bounds__(kStreamThreads)
 gemm_stream_kernel(StreamParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr int kConsumerThreads = 32 * kStreamConsumers;
+  constexpr int MB = MT * 8;                                  // batch rows held (padded)
   const int Kc = (p.K + kChunk - 1) / kChunk;                 // stages per tile
   const int Kp = Kc * kChunk + 8;                             // padded row of the staged X
   const int kStages = p.stages;
   unsigned char* ring = smem_raw;                             // [stages][16][kRowBytes]
-  bf16* xs = reinterpret_cast<bf16*>(ring + kStages * kStageBytes);          // [MT*8][Kp]
-  float* red = reinterpret_cast<float*>(xs + MT * 8 * Kp);                   // [2][4 warps][16][MT*8]
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * kStreamConsumers * 16 * MT * 8);
+  bf16* xs = reinterpret_cast<bf16*>(ring + kStages * kStageBytes);          // [MB][Kp]
+  float* red = reinterpret_cast<float*>(xs + MB * Kp);                       // [2][warps][16][MB]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * kStreamConsumers * 16 * MB);
   uint64_t* empty = full + kMaxStages;
   __shared__ volatile int abort_flag;
 
@@ -111,6 +145,12 @@ gemm_stream_kernel(StreamParams p) {
   __syncthreads();
   pdl_launch_dependents();
 
+  // weight row of local row r (0..15) of a tile
+  auto row_of = [&](int tile, int r) {
+    const int base = (tile / p.pair_blocks) * p.group_stride + 8 * (tile % p.pair_blocks);
+    return r < 8 ? base + r : base + p.pair_offset + (r - 8);
+  };
+
   // Producer warp: lane 0 announces the bytes of a stage, lanes 0..15 each copy one row of it
   // (sixteen copies issued side by side).  Stage i holds rows of tile (i / Kc) at k-chunk (i % Kc).
   auto issue = [&](int i) {
@@ -118,12 +158,12 @@ gemm_stream_kernel(StreamParams p) {
     const int tile = blockIdx.x + (i / Kc) * gridDim.x;
     const int k0 = (i % Kc) * kChunk;
     const int kbytes = min(kChunk, p.K - k0) * 2;
-    const int rows = min(16, p.N - tile * 16);
-    if (lane == 0) mbar_expect_tx(&full[s], uint32_t(rows) * kbytes);
+    const int row = lane < 16 ? row_of(tile, lane) : p.N;
+    const unsigned live = __ballot_sync(0xffffffffu, row < p.N);
+    if (lane == 0) mbar_expect_tx(&full[s], uint32_t(__popc(live)) * kbytes);
     __syncwarp();
-    if (lane < rows)
-      bulk_copy(ring + s * kStageBytes + lane * kRowBytes,
-                p.W + (size_t(tile) * 16 + lane) * p.ldw + k0, kbytes, &full[s]);
+    if (row < p.N)
+      bulk_copy(ring + s * kStageBytes + lane * kRowBytes, p.W + size_t(row) * p.ldw + k0, kbytes, &full[s]);
   };
 
   int issued = 0;
@@ -154,80 +194,127 @@ gemm_stream_kernel(StreamParams p) {
         const int fills = issued > s ? (issued - s - 1) / kStages + 1 : 0;
         if (fills > 0) mbar_wait(&full[s], (fills - 1) & 1, kWaitLimitNs / 4);
       }
-  } else {
-    // ---- consumers: stage X (all copies in flight at once, zero fill beyond M and K)
-    const int chunks = Kp / 8;
-    for (int c = tid; c < MT * 8 * chunks; c += 32 * kStreamConsumers) {
-      const int m = c / chunks, ch = c - m * chunks;
+    return;
+  }
+
+  // ---- consumers.  X is staged k-chunk by k-chunk (one copy group each, zero fill beyond M and
+  // K), so the first tile can start on chunk 0 while the later chunks are still arriving.
+  const int chunk_vecs = kChunk / 8;
+  for (int kc = 0; kc < Kc; ++kc) {
+    for (int c = tid; c < MB * chunk_vecs; c += kConsumerThreads) {
+      const int m = c / chunk_vecs, ch = kc * chunk_vecs + (c - m * chunk_vecs);
       const bool live = m < p.M && ch * 8 < p.K;
       const bf16* src = live ? p.X + size_t(m) * p.ldx + ch * 8 : p.X;
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s32(xs + m * Kp + ch * 8)), "l"(src), "r"(live ? 16 : 0));
     }
     asm volatile("cp.async.commit_group;\n" ::);
-    asm volatile("cp.async.wait_group 0;\n" ::);
-    asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kStreamConsumers));
+  }
 
-    const int g = lane >> 2, t4 = lane & 3;
-    OutT* Y = reinterpret_cast<OutT*>(p.Y);
-    int i = 0;
-    for (int tl = 0; tl < my_tiles; ++tl) {
-      const int tile = blockIdx.x + tl * gridDim.x;
-      float acc[MT][4];
+  const int g = lane >> 2, t4 = lane & 3;
+  constexpr int kPerWarp = kChunk / kStreamConsumers;          // k columns of a stage per warp
+  int i = 0;
+  for (int tl = 0; tl < my_tiles; ++tl) {
+    const int tile = blockIdx.x + tl * gridDim.x;
+    float acc[MT][4];
 #pragma unroll
-      for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-      for (int kc = 0; kc < Kc; ++kc, ++i) {
-        const int s = i % kStages;
-        if (!abort_flag && !mbar_wait(&full[s], (i / kStages) & 1)) {
-          if (lane == 0) atomicExch(&g_stream_error, (2 << 16) | int(blockIdx.x));
-          abort_flag = 1;                              // everyone stops waiting, nobody leaves a barrier alone
-        }
-        if (abort_flag) continue;
-        const unsigned char* st = ring + s * kStageBytes;
-        const int kbase = kc * kChunk + warp * (kChunk / kStreamConsumers);    // this warp's quarter
-#pragma unroll
-        for (int kb = 0; kb < kChunk / kStreamConsumers / 32; ++kb) {
-          if (kbase + kb * 32 >= p.K) break;           // warp-uniform: the whole k-block lies beyond K
-          const int koff = warp * (kChunk / kStreamConsumers) + kb * 32 + 8 * t4;
-          uint4 va = *reinterpret_cast<const uint4*>(st + g * kRowBytes + koff * 2);
-          uint4 vb = *reinterpret_cast<const uint4*>(st + (g + 8) * kRowBytes + koff * 2);
-          if (kc * kChunk + koff >= p.K) {             // this thread's 8 columns lie beyond K: stale bytes
-            va = make_uint4(0u, 0u, 0u, 0u);
-            vb = make_uint4(0u, 0u, 0u, 0u);
-          }
-#pragma unroll
-          for (int j = 0; j < MT; ++j) {
-            const uint4 x = *reinterpret_cast<const uint4*>(xs + (8 * j + g) * Kp + kbase + kb * 32 + 8 * t4);
-            mma_stream(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
-            mma_stream(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);         // this warp is done with the slot
+    for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int kc = 0; kc < Kc; ++kc, ++i) {
+      if (tl == 0) {                                           // this chunk of X has landed for everyone?
+        cp_async_wait_dyn(min(Kc - 1 - kc, 7));
+        asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
       }
-      // acc[j]: c0,c1 = (W row g, batch 8j + 2t, +1); c2,c3 = (W row g+8, same batch rows)
-      float* mine = red + ((tl & 1) * kStreamConsumers + warp) * 16 * (MT * 8);
-#pragma unroll
-      for (int j = 0; j < MT; ++j) {
-        mine[g * (MT * 8) + 8 * j + 2 * t4] = acc[j][0];
-        mine[g * (MT * 8) + 8 * j + 2 * t4 + 1] = acc[j][1];
-        mine[(g + 8) * (MT * 8) + 8 * j + 2 * t4] = acc[j][2];
-        mine[(g + 8) * (MT * 8) + 8 * j + 2 * t4 + 1] = acc[j][3];
+      const int s = i % kStages;
+      if (!abort_flag && !mbar_wait(&full[s], (i / kStages) & 1)) {
+        if (lane == 0) atomicExch(&g_stream_error, (2 << 16) | int(blockIdx.x));
+        abort_flag = 1;                                        // everyone stops waiting, nobody leaves a barrier alone
       }
-      asm volatile("bar.sync 1, %0;\n" ::"n"(32 * kStreamConsumers));
-      const float* both = red + (tl & 1) * kStreamConsumers * 16 * (MT * 8);
-      for (int e = tid; e < 16 * MT * 8; e += 32 * kStreamConsumers) {
-        const int r = e / (MT * 8), m = e - r * (MT * 8);
-        const int n = tile * 16 + r;
-        if (n < p.N && m < p.M) {
-          float sum = 0.f;
+      if (abort_flag) continue;
+      const unsigned char* st = ring + s * kStageBytes;
+      const int kbase = kc * kChunk + warp * kPerWarp;          // this warp's share of the stage
 #pragma unroll
-          for (int w = 0; w < kStreamConsumers; ++w) sum += both[w * 16 * (MT * 8) + e];
-          stf(Y + size_t(m) * p.ldy + n, sum);
+      for (int kb = 0; kb < kPerWarp / 32; ++kb) {
+        if (kbase + kb * 32 >= p.K) break;                     // warp-uniform: the whole k-block lies beyond K
+        const int koff = warp * kPerWarp + kb * 32 + 8 * t4;
+        uint4 va = *reinterpret_cast<const uint4*>(st + g * kRowBytes + koff * 2);
+        uint4 vb = *reinterpret_cast<const uint4*>(st + (g + 8) * kRowBytes + koff * 2);
+        if (kc * kChunk + koff >= p.K) {                       // this thread's 8 columns lie beyond K: stale bytes
+          va = make_uint4(0u, 0u, 0u, 0u);
+          vb = make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          const uint4 x = *reinterpret_cast<const uint4*>(xs + (8 * j + g) * Kp + kbase + kb * 32 + 8 * t4);
+          mma_stream(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
+          mma_stream(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
         }
       }
-      // the other half of `red` is used by the next tile; this half again two tiles on, after
-      // the barrier of the tile in between
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);                   // this warp is done with the slot
     }
+    // acc[j]: c0,c1 = (W row g, batch 8j + 2t, +1); c2,c3 = (W row g+8, same batch rows)
+    float* mine = red + ((tl & 1) * kStreamConsumers + warp) * 16 * MB;
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+      mine[g * MB + 8 * j + 2 * t4] = acc[j][0];
+      mine[g * MB + 8 * j + 2 * t4 + 1] = acc[j][1];
+      mine[(g + 8) * MB + 8 * j + 2 * t4] = acc[j][2];
+      mine[(g + 8) * MB + 8 * j + 2 * t4 + 1] = acc[j][3];
+    }
+    asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
+    // The partial sums of the warps are added in warp order: reproducible bit for bit.
+    const float* both = red + (tl & 1) * kStreamConsumers * 16 * MB;
+    auto total_of = [&](int r, int m) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kStreamConsumers; ++w) sum += both[(w * 16 + r) * MB + m];
+      return sum;
+    };
+    if constexpr (EPI == kStore) {
+      OutT* Y = reinterpret_cast<OutT*>(p.Y);
+      for (int e = tid; e < 16 * MB; e += kConsumerThreads) {
+        const int r = e / MB, m = e - r * MB;
+        const int n = row_of(tile, r);
+        if (n < p.N && m < p.M) stf(Y + size_t(m) * p.ldy + n, total_of(r, m));
+      }
+    } else {
+      bf16* Y = reinterpret_cast<bf16*>(p.Y);
+      for (int e = tid; e < 8 * MB; e += kConsumerThreads) {
+        const int pr = e / MB, m = e - pr * MB;
+        if (m >= p.M) continue;
+        const float xa = Store<bf16>::round(total_of(pr, m));       // what the plain product stores
+        const float xb = Store<bf16>::round(total_of(pr + 8, m));
+        if constexpr (EPI == kSiluMul) {
+          const float sl = Store<bf16>::round(xa / (1.f + expf(-xa)));
+          stf(Y + size_t(m) * p.ldy + 8 * tile + pr, sl * xb);
+        } else {
+          const int head = tile / p.pair_blocks;
+          const int j = 8 * (tile % p.pair_blocks) + pr;
+          const int half = p.hd / 2;
+          float ra = xa, rb = xb;
+          if (head < p.nh + p.nkv) {
+            float sn, cs;
+            sincosf(float(p.positions[m]) * p.inv_freq[j], &sn, &cs);
+            rotate_pair(xa, xb, cs, sn, ra, rb);
+          }
+          if (head < p.nh) {
+            stf(Y + size_t(m) * p.ldy + size_t(head) * p.hd + j, ra);
+            stf(Y + size_t(m) * p.ldy + size_t(head) * p.hd + j + half, rb);
+          } else {
+            const int slot = p.slot_mapping[m];
+            if (slot >= 0) {
+              const int page = slot / p.block_size, off = slot - page * p.block_size;
+              const bool is_k = head < p.nh + p.nkv;
+              const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+              bf16* dst = (is_k ? p.k_cache : p.v_cache) + ((size_t(page) * p.nkv + kvh) * p.block_size + off) * p.hd;
+              stf(dst + j, ra);
+              stf(dst + j + half, rb);
+            }
+          }
+        }
+      }
+    }
+    // the other half of `red` is used by the next tile; this half again two tiles on, after
+    // the barrier of the tile in between
   }
 }
 
@@ -240,9 +327,9 @@ static size_t stream_smem(int MT, int K, int stages) {
          size_t(2) * kStreamConsumers * 16 * MT * 8 * sizeof(float) + 2 * kMaxStages * sizeof(uint64_t);
 }
 
-template <int MT, typename OutT>
+template <int MT, typename OutT, int EPI>
 int launch_stream(StreamParams p, int sm_count, cudaStream_t s) {
-  auto kernel = gemm_stream_kernel<MT, OutT>;
+  auto kernel = gemm_stream_kernel<MT, OutT, EPI>;
   const int tiles = (p.N + 15) / 16;
   const int Kc = (p.K + kChunk - 1) / kChunk;
   // One block per SM; the ring takes what shared memory is left after X, but never more slots than
@@ -278,10 +365,50 @@ KVCM_API int kvcm_gemm_stream_bf16(const void* X, const void* W, void* Y, int M,
   if (M == 0 || N == 0) return 0;
   if (!kvcm_gemm_stream_supports(M, N, K) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
-  StreamParams p{(const bf16*)W, N, K, ldw, (const bf16*)X, ldx, M, Y, ldy, 0};
+  StreamParams p = {};
+  p.W = (const bf16*)W; p.N = N; p.K = K; p.ldw = ldw; p.X = (const bf16*)X; p.ldx = ldx; p.M = M;
+  p.Y = Y; p.ldy = ldy;
+  p.pair_blocks = 1; p.group_stride = 16; p.pair_offset = 8;          // identity: tile t = rows 16t .. 16t+15
   cudaStream_t s = (cudaStream_t)stream;
-  if (M <= 8) return out_f32 ? launch_stream<1, float>(p, sm_count, s) : launch_stream<1, bf16>(p, sm_count, s);
-  return out_f32 ? launch_stream<2, float>(p, sm_count, s) : launch_stream<2, bf16>(p, sm_count, s);
+  if (M <= 8) return out_f32 ? launch_stream<1, float, kStore>(p, sm_count, s) : launch_stream<1, bf16, kStore>(p, sm_count, s);
+  return out_f32 ? launch_stream<2, float, kStore>(p, sm_count, s) : launch_stream<2, bf16, kStore>(p, sm_count, s);
+}
+
+// Fused decode step of an attention layer's input side: qkv = X * Wqkv^T, rotary encoding of the q
+// and k heads (rotate-half pairing over the whole head), q written to Y [M, >= nh*hd], k and v
+// written into the rows' cache page slots.  Needs hd a multiple of 16.
+KVCM_API int kvcm_qkv_rope_cache_bf16(const void* X, const void* Wqkv, void* Yq, int M, int K, int ldx, int ldw,
+                                      int ldy, const int* positions, const float* inv_freq,
+                                      const int* slot_mapping, void* k_cache, void* v_cache, int nh, int nkv,
+                                      int hd, int block_size, int sm_count, void* stream) {
+  const int N = (nh + 2 * nkv) * hd;
+  if (M == 0) return 0;
+  if ((hd % 16) || !kvcm_gemm_stream_supports(M, N, K) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(Wqkv) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
+  StreamParams p = {};
+  p.W = (const bf16*)Wqkv; p.N = N; p.K = K; p.ldw = ldw; p.X = (const bf16*)X; p.ldx = ldx; p.M = M;
+  p.Y = Yq; p.ldy = ldy;
+  p.pair_blocks = hd / 16; p.group_stride = hd; p.pair_offset = hd / 2;
+  p.positions = positions; p.inv_freq = inv_freq; p.slot_mapping = slot_mapping;
+  p.k_cache = (bf16*)k_cache; p.v_cache = (bf16*)v_cache;
+  p.nh = nh; p.nkv = nkv; p.hd = hd; p.block_size = block_size;
+  cudaStream_t s = (cudaStream_t)stream;
+  return M <= 8 ? launch_stream<1, bf16, kRopeCache>(p, sm_count, s) : launch_stream<2, bf16, kRopeCache>(p, sm_count, s);
+}
+
+// Fused input side of a gated feed-forward: act[M, I] = silu(X Wg^T) * (X Wu^T) with Wg, Wu the
+// two halves of W [2I, K] (gate rows first).  Needs I a multiple of 8.
+KVCM_API int kvcm_gate_up_silu_bf16(const void* X, const void* W, void* Y, int M, int I, int K, int ldx, int ldw,
+                                    int ldy, int sm_count, void* stream) {
+  if (M == 0) return 0;
+  if ((I % 8) || !kvcm_gemm_stream_supports(M, 2 * I, K) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
+  StreamParams p = {};
+  p.W = (const bf16*)W; p.N = 2 * I; p.K = K; p.ldw = ldw; p.X = (const bf16*)X; p.ldx = ldx; p.M = M;
+  p.Y = Y; p.ldy = ldy;
+  p.pair_blocks = I / 8; p.group_stride = 0; p.pair_offset = I;
+  cudaStream_t s = (cudaStream_t)stream;
+  return M <= 8 ? launch_stream<1, bf16, kSiluMul>(p, sm_count, s) : launch_stream<2, bf16, kSiluMul>(p, sm_count, s);
 }
 
 // Reads and clears the error word of the streaming kernels (0 = no bounded wait ever ran out).

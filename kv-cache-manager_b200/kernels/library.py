@@ -378,3 +378,49 @@ def stream_error() -> int:
     out (1: the producer waited for a free stage, 2: a consumer waited for data).  Reading clears it.
     Synchronises the device."""
     return int(_lib().kvcm_stream_error())
+
+
+def qkv_rope_cache(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
+                   inv_freq: torch.Tensor, slot_mapping: torch.Tensor, k_cache: torch.Tensor,
+                   v_cache: torch.Tensor, nh: int, nkv: int, hd: int) -> None:
+    """Fused decode kernel: qkv product (M <= 16), rotate-half rotary encoding over the whole head,
+    q into ``q_out`` [M, nh*hd], k (rotated) and v into the rows' cache page slots.  Gives the same
+    bits as ``gemm_stream`` followed by ``rope_cache``."""
+    _cuda(x, w_qkv, q_out, positions, inv_freq, slot_mapping, k_cache, v_cache)
+    M, K = x.shape
+    _need(w_qkv.shape == ((nh + 2 * nkv) * hd, K) and q_out.shape[0] == M and q_out.shape[1] >= nh * hd,
+          "qkv_rope_cache: shapes")
+    _need(x.dtype == w_qkv.dtype == q_out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16,
+          "qkv_rope_cache: bfloat16 only")
+    _need(x.stride(1) == 1 and w_qkv.stride(1) == 1 and q_out.stride(1) == 1 and k_cache.is_contiguous()
+          and v_cache.is_contiguous(), "qkv_rope_cache: layout")
+    _need(tuple(k_cache.shape[1:]) == (nkv, k_cache.shape[2], hd), "qkv_rope_cache: cache page shape")
+    _need(positions.dtype == _I32 and slot_mapping.dtype == _I32 and positions.numel() >= M
+          and slot_mapping.numel() >= M, "qkv_rope_cache: positions/slot_mapping int32 [M]")
+    _need(inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == hd, "qkv_rope_cache: inv_freq float32 [hd/2]")
+    rc = _lib().kvcm_qkv_rope_cache_bf16(_p(x), _p(w_qkv), _p(q_out), M, K, x.stride(0), w_qkv.stride(0),
+                                         q_out.stride(0), _p(positions), _p(inv_freq), _p(slot_mapping),
+                                         _p(k_cache), _p(v_cache), nh, nkv, hd, k_cache.shape[2],
+                                         sm_count(x.device), _stream())
+    _check(rc, "qkv_rope_cache", f"(M={M}, K={K}, nh={nh}, nkv={nkv}, hd={hd})")
+
+
+def qkv_rope_cache_supported(M: int, K: int, nh: int, nkv: int, hd: int) -> bool:
+    return hd % 16 == 0 and stream_gemm_supported(M, (nh + 2 * nkv) * hd, K)
+
+
+def gate_up_silu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> None:
+    """Fused decode kernel: act[M, I] = silu(x Wg^T) * (x Wu^T), Wg/Wu the halves of w [2I, K]."""
+    _cuda(x, w_gate_up, act)
+    M, K = x.shape
+    I = act.shape[1]
+    _need(w_gate_up.shape == (2 * I, K) and act.shape[0] == M, "gate_up_silu: shapes")
+    _need(x.dtype == w_gate_up.dtype == act.dtype == torch.bfloat16, "gate_up_silu: bfloat16 only")
+    _need(x.stride(1) == 1 and w_gate_up.stride(1) == 1 and act.stride(1) == 1, "gate_up_silu: layout")
+    rc = _lib().kvcm_gate_up_silu_bf16(_p(x), _p(w_gate_up), _p(act), M, I, K, x.stride(0), w_gate_up.stride(0),
+                                       act.stride(0), sm_count(x.device), _stream())
+    _check(rc, "gate_up_silu", f"(M={M}, I={I}, K={K})")
+
+
+def gate_up_silu_supported(M: int, I: int, K: int) -> bool:
+    return I % 8 == 0 and stream_gemm_supported(M, 2 * I, K)

@@ -38,11 +38,24 @@ class PagedAttention(Mixer):
 
     def forward(self, h: torch.Tensor, ctx: StepContext, site: SiteCache) -> torch.Tensor:
         g = ctx.groups[site.group]
-        qkv = self.qkv.forward(h, ctx)
         pos = self.position
-        K.rope_cache(qkv, ctx.positions, pos.inv_freq, pos.rotary_dim, pos.interleaved,
-                     g.slot_mapping, site.k, site.v, self.nh, self.nkv, self.hd, g.block_size,
-                     write_cache=site.writes)
+        w = self.qkv.param("weight")
+        M = h.shape[0]
+        # A handful of rows (decode): one kernel does the product, the rotary encoding and the
+        # cache write; it gives the same bits as the three separate kernels below.
+        if (site.writes and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and ctx.options.get("gemm", "auto") == "auto" and ctx.options.get("fuse", True)
+                and pos.inv_freq is not None and pos.rotary_dim == self.hd and not pos.interleaved
+                and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
+                and K.qkv_rope_cache_supported(M, h.shape[1], self.nh, self.nkv, self.hd)):
+            qkv = torch.empty((M, self.nh * self.hd), dtype=h.dtype, device=h.device)
+            K.qkv_rope_cache(h, w, qkv, ctx.positions, pos.inv_freq, g.slot_mapping, site.k, site.v,
+                             self.nh, self.nkv, self.hd)
+        else:
+            qkv = self.qkv.forward(h, ctx)
+            K.rope_cache(qkv, ctx.positions, pos.inv_freq, pos.rotary_dim, pos.interleaved,
+                         g.slot_mapping, site.k, site.v, self.nh, self.nkv, self.hd, g.block_size,
+                         write_cache=site.writes)
         out = torch.empty((h.shape[0], self.nh * self.hd), dtype=h.dtype, device=h.device)
         K.paged_attention(qkv, out, site.k, site.v, g.block_tables, ctx, self.nh, self.nkv, self.hd,
                           self.scale, self.window)

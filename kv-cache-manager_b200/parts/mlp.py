@@ -22,7 +22,14 @@ class GatedMLP(FeedForward):
         self.down = self.add_child("down", Linear(intermediate, hidden))
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gu = self.gate_up.forward(h, ctx)
         act = torch.empty((h.shape[0], self.intermediate), dtype=h.dtype, device=h.device)
-        K.silu_mul(gu, act)
+        w = self.gate_up.param("weight")
+        # A handful of rows (decode): the gate/up product and the activation in one kernel (the
+        # same roundings as the two separate kernels).
+        if (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ctx.options.get("gemm", "auto") == "auto"
+                and ctx.options.get("fuse", True) and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
+                and K.gate_up_silu_supported(h.shape[0], self.intermediate, h.shape[1])):
+            K.gate_up_silu(h, w, act)
+        else:
+            K.silu_mul(self.gate_up.forward(h, ctx), act)
         return self.down.forward(act, ctx)

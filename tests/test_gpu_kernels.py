@@ -195,6 +195,58 @@ def test_streaming_gemm(M, N, Kd):
     assert torch.equal(y, y2)                                       # fixed summation order
 
 
+@pytest.mark.parametrize("M,H,nh,nkv,hd,B", [(1, 64, 4, 2, 16, 16), (8, 2048, 32, 4, 64, 16), (5, 96, 3, 1, 32, 8),
+                                              (16, 256, 6, 3, 48, 4), (3, 512, 2, 2, 128, 32)])
+def test_fused_qkv_rope_cache_gives_the_bits_of_the_separate_kernels(M, H, nh, nkv, hd, B):
+    lib = K()
+    assert lib.qkv_rope_cache_supported(M, H, nh, nkv, hd)
+    g = torch.Generator().manual_seed(M * 7 + hd)
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn((nh + 2 * nkv) * hd, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    pos = torch.randint(0, 3000, (M,), generator=g).to(torch.int32).to(DEV)
+    pages = 9
+    slots = torch.randperm(pages * B, generator=g)[:M].to(torch.int32)
+    if M > 2:
+        slots[1] = -1                                                # a row that writes nothing
+    slots = slots.to(DEV)
+    inv = (1.0 / torch.pow(torch.tensor(10000.0, dtype=torch.float64),
+                           2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().to(DEV)
+    # separate kernels
+    qkv = torch.empty(M, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, device=DEV)
+    lib.gemm_stream(x, w, qkv)
+    k1 = torch.zeros(pages, nkv, B, hd, dtype=torch.bfloat16, device=DEV)
+    v1 = torch.zeros_like(k1)
+    lib.rope_cache(qkv, pos, inv, hd, False, slots, k1, v1, nh, nkv, hd, B)
+    # fused
+    q2 = torch.full((M, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k2, v2 = torch.zeros_like(k1), torch.zeros_like(v1)
+    lib.qkv_rope_cache(x, w, q2, pos, inv, slots, k2, v2, nh, nkv, hd)
+    assert lib.stream_error() == 0
+    assert torch.equal(q2, qkv[:, :nh * hd]) and torch.equal(k2, k1) and torch.equal(v2, v1)
+    # and against float64
+    ref = (x.double().cpu() @ w.double().cpu().T)
+    close(qkv[:, (nh + nkv) * hd:], ref[:, (nh + nkv) * hd:], "bfloat16", "v part of the product")
+
+
+@pytest.mark.parametrize("M,H,I", [(1, 64, 24), (8, 2048, 5632), (5, 96, 256), (16, 128, 1000)])
+def test_fused_gate_up_silu_gives_the_bits_of_the_separate_kernels(M, H, I):
+    lib = K()
+    assert lib.gate_up_silu_supported(M, I, H) and not lib.gate_up_silu_supported(M, 172, H)
+    g = torch.Generator().manual_seed(I)
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
+    lib.gemm_stream(x, w, gu)
+    a1 = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    lib.silu_mul(gu, a1)
+    a2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lib.gate_up_silu(x, w, a2)
+    assert lib.stream_error() == 0
+    assert torch.equal(a1, a2)
+    gg = (x.double().cpu() @ w.double().cpu().T)
+    close(a2, gg[:, :I] * torch.sigmoid(gg[:, :I]) * gg[:, I:], "bfloat16", "against float64")
+
+
 def test_skinny_gemm_refuses_what_it_cannot_run():
     lib = K()
     assert not lib.skinny_gemm_supported(17, 64, 64)                # too many rows
