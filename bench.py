@@ -223,6 +223,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "prefill"],
+                    help="'prefill': run only the 2,048-token prefill step and print its numbers (for profiling)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -251,6 +253,12 @@ def main() -> int:
                                  max_len, graphs=not args.no_graphs)
     vocab = cfg.vocab_size
     m = model_bytes_and_flops(cfg, layers)
+    if args.only == "prefill":
+        ms, flops = prefill_run(spec, ec, vocab, cfg, layers, reps=3)
+        print(json.dumps({"prefill": {"value": round(PREFILL_TOKENS * 1e3 / ms, 1), "tokens": PREFILL_TOKENS,
+                                      "ms": round(ms, 3), "layers": layers,
+                                      "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}}))
+        return 0
 
     main_run = decode_run(spec, ec, vocab, args.batch, steps, warmup, sample_clocks=True)
     B = args.batch
