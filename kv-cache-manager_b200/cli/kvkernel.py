@@ -3,6 +3,7 @@ times decode attention only; here also the decode matrix products).
 
     kvkernel --family attention --ctx 512,2048 --batch 1,8,64 --block-size 16 --out attn.csv
     kvkernel --family gemm --batch 1,8 --hidden 2048 --ffn 5632 --vocab 32000
+    kvkernel --family gemm-large --rows 512,2048
 
 attention: for every (block size, batch, context): zero-filled K/V/Q, a sequential and a shuffled
 page table, variants paged/contiguous x v1/v2; 5 warm-up runs, ``--iters`` timed runs recorded in
@@ -115,6 +116,36 @@ def bench_gemm(a, out) -> None:
         raise RuntimeError(f"a bounded wait of the streaming kernel ran out (code {err >> 16}, block {err & 0xffff})")
 
 
+def bench_gemm_large(a, out) -> None:
+    """Prefill products (many rows): this engine's tcgen05 kernel against the library product."""
+    import torch
+    from ..kernels import library as K
+    H, I, V = a.i32("hidden", 2048), a.i32("ffn", 5632), a.i32("vocab", 32000)
+    nh, nkv, hd = a.i32("heads", 32), a.i32("kv-heads", 4), a.i32("head-dim", 64)
+    rows = a.ints("rows", "2048")
+    a.warn_unused()
+    shapes = [("qkv", (nh + 2 * nkv) * hd, H), ("o", H, nh * hd), ("gate_up", 2 * I, H), ("down", H, I)]
+    dev = "cuda:0"
+    if out:
+        out.write("rows,product,n,k,variant,us,tflops\n")
+    for M in rows:
+        for name, N, Kd in shapes:
+            w = (torch.randn(N, Kd, device=dev) * 0.05).to(torch.bfloat16)
+            x = torch.randn(M, Kd, device=dev).to(torch.bfloat16)
+            y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            res = {"library": graph_time_us([lambda: torch.mm(x, w.t(), out=y)] * 10),
+                   "tcgen05": graph_time_us([lambda: K.gemm_tcgen05(x, w, y)] * 10)}
+            fl = 2.0 * M * N * Kd
+            print(f"M={M:<5} {name:<8} [{N} x {Kd}] " +
+                  "  ".join(f"{k} {v:.1f} us ({fl / (v * 1e-6) / 1e12:.0f} TFLOP/s)" for k, v in res.items()))
+            if out:
+                for k, v in res.items():
+                    out.write(f"{M},{name},{N},{Kd},{k},{v:.3f},{fl / (v * 1e-6) / 1e12:.1f}\n")
+    err = K.tcgen05_error()
+    if err:
+        raise RuntimeError(f"a bounded wait of the tcgen05 kernel ran out (code {err >> 16}, block {err & 0xffff})")
+
+
 def main(argv=None) -> int:
     from .args import Args
     a = Args(argv)
@@ -126,8 +157,10 @@ def main(argv=None) -> int:
             bench_attention(a, out)
         elif family == "gemm":
             bench_gemm(a, out)
+        elif family == "gemm-large":
+            bench_gemm_large(a, out)
         else:
-            raise ValueError(f"unknown --family '{family}' (attention | gemm)")
+            raise ValueError(f"unknown --family '{family}' (attention | gemm | gemm-large)")
         if out:
             out.close()
     except Exception as e:

@@ -1,0 +1,279 @@
+// Matrix product for many rows (prefill) on the fifth-generation tensor cores:
+//     Y[M, N] = X[M, K] * W[N, K]^T,  bfloat16 operands, float accumulation in tensor memory.
+//
+// One block computes one 128 x 256 tile of Y:
+//  * warp 0, one thread: TMA.  Tiled tensor maps (cp.async.bulk.tensor.2d) bring a [128 x 64] piece
+//    of X and a [256 x 64] piece of W per k-step into a four-stage ring of shared memory, in the
+//    128-byte swizzled layout the tensor core reads; completion is counted on an mbarrier.
+//  * warp 1, one thread: tcgen05.mma (cta_group::1, kind::f16, M = 128, N = 256, K = 16), four per
+//    k-step, accumulating into 256 columns of tensor memory; tcgen05.commit hands each ring slot
+//    back to the producer when the products that read it are done, and signals the epilogue at
+//    the end.
+//  * warps 2-5: epilogue.  tcgen05.ld reads the accumulator (each warp its quarter of the 128
+//    lanes), converts and stores rows of Y (bfloat16 or float).
+// Out-of-range rows, columns and k are zero-filled by the TMA unit, so any M, N and any K that
+// is a multiple of 8 work.  Every wait on an mbarrier is bounded; when one runs out the block
+// records it (kvcm_tcgen05_error), stops waiting, frees its tensor memory and leaves.
+// The reference calls cuBLAS for these products (src/model/llama.cpp:45-52).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace kvcm {
+
+constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64, kTcStages = 4;
+constexpr int kTcThreads = 192;
+constexpr int kTcABytes = kTcBM * kTcBK * 2, kTcBBytes = kTcBN * kTcBK * 2;
+constexpr int kTcStageBytes = kTcABytes + kTcBBytes;
+constexpr unsigned long long kTcWaitLimitNs = 1000000000ull;   // every wait gives up after a second
+
+__device__ int g_tcgen05_error = 0;
+
+__device__ __forceinline__ uint32_t tc_s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ unsigned long long tc_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity) {
+  unsigned long long start = 0;
+  for (unsigned spin = 0;; ++spin) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(tc_s32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+    if ((spin & 63) == 63) {
+      const unsigned long long now = tc_now();
+      if (start == 0) start = now;
+      else if (now - start > kTcWaitLimitNs) return false;
+    }
+  }
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
+// start address / 16, stride between 8-row groups = 1024 bytes, descriptor version 1, swizzle code 2.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr & 0x3FFFF) >> 4);
+  d |= uint64_t(1) << 16;                       // leading byte offset (unused with this swizzle)
+  d |= uint64_t(1024 >> 4) << 32;               // stride byte offset
+  d |= uint64_t(1) << 46;                       // descriptor version
+  d |= uint64_t(2) << 61;                       // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N and M of the product.
+__host__ __device__ constexpr uint32_t tc_idesc(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kTcThreads)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    OutT* __restrict__ Y, int M, int N, int K, int ldy) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t full[kTcStages], empty[kTcStages], acc_ready;
+  __shared__ uint32_t tmem_base;
+  __shared__ volatile int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kTcBN, m0 = blockIdx.y * kTcBM;
+  const int nk = (K + kTcBK - 1) / kTcBK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kTcStages; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc_s32(&full[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc_s32(&empty[s])));
+    }
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc_s32(&acc_ready)));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {                                // one warp allocates 256 columns of tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_s32(&tmem_base)), "r"(kTcBN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem = tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int k = 0; k < nk && !abort_flag; ++k) {
+        const int s = k % kTcStages;
+        if (!tc_wait(&empty[s], ((k / kTcStages) & 1) ^ 1)) {
+          atomicExch(&g_tcgen05_error, (1 << 16) | int(blockIdx.x & 0xffff));
+          abort_flag = 1;
+          break;
+        }
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_s32(&full[s])), "r"(kTcStageBytes) : "memory");
+        unsigned char* a = ring + s * kTcStageBytes;
+        unsigned char* b = a + kTcABytes;
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                     ::"r"(tc_s32(a)), "l"(&map_x), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(m0) : "memory");
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                     ::"r"(tc_s32(b)), "l"(&map_w), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(n0) : "memory");
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc_idesc(kTcBM, kTcBN);
+      for (int k = 0; k < nk && !abort_flag; ++k) {
+        const int s = k % kTcStages;
+        if (!tc_wait(&full[s], (k / kTcStages) & 1)) {
+          atomicExch(&g_tcgen05_error, (2 << 16) | int(blockIdx.x & 0xffff));
+          abort_flag = 1;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t a_addr = tc_s32(ring + s * kTcStageBytes);
+        const uint64_t da = tc_smem_desc(a_addr), db = tc_smem_desc(a_addr + kTcABytes);
+#pragma unroll
+        for (int j = 0; j < kTcBK / 16; ++j) {
+          const uint32_t accumulate = (k > 0 || j > 0) ? 1u : 0u;
+          // +32 bytes along k inside the swizzled row = +2 in the descriptor's address field
+          asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                       ::"r"(tmem), "l"(da + uint64_t(2 * j)), "l"(db + uint64_t(2 * j)), "r"(idesc), "r"(accumulate) : "memory");
+        }
+        // the ring slot is free once these products have read it
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_s32(&empty[s])) : "memory");
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_s32(&acc_ready)) : "memory");
+    }
+  } else {
+    // ---- epilogue: this warp reads lanes 32*(warp % 4) .. +31 of the accumulator
+    bool ok = tc_wait(&acc_ready, 0);
+    if (!ok && lane == 0) atomicExch(&g_tcgen05_error, (3 << 16) | int(blockIdx.x & 0xffff));
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const int quarter = warp & 3;
+    const int row = m0 + quarter * 32 + lane;
+    if (ok && !abort_flag) {
+#pragma unroll 1
+      for (int c = 0; c < kTcBN / 32; ++c) {
+        uint32_t v[32];
+        const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(c * 32);
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                     "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                     "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                       "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                       "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                       "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                     : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        if (row < M) {
+          const int col0 = n0 + c * 32;
+          OutT* dst = Y + size_t(row) * ldy + col0;
+          if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            if constexpr (sizeof(OutT) == 2) {
+              uint4 packed[4];
+              __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(packed);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) h2[i] = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+#pragma unroll
+              for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(dst)[i] = packed[i];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < N) stf(dst + i, __uint_as_float(v[i]));
+          }
+        }
+      }
+    }
+  }
+  // every role ends here; tensor memory goes back before the block leaves
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTcBN));
+  }
+}
+
+// ---------------------------------------------------------------------------------- host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Row-major [rows, cols] bfloat16 matrix with `ld` elements between rows; boxes of [box_rows x 64].
+static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return KVCM_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
+  cuuint32_t box[2] = {cuuint32_t(kTcBK), cuuint32_t(box_rows)};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 20000 + int(r);
+}
+
+template <typename OutT>
+int launch_tcgen05(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
+                   cudaStream_t s) {
+  CUtensorMap mx, mw;
+  int rc = make_map(&mx, X, M, K, ldx, kTcBM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, N, K, ldw, kTcBN);
+  if (rc) return rc;
+  auto kernel = gemm_tcgen05_kernel<OutT>;
+  const size_t smem = size_t(kTcStages) * kTcStageBytes + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  dim3 grid((N + kTcBN - 1) / kTcBN, (M + kTcBM - 1) / kTcBM);
+  kernel<<<grid, kTcThreads, smem, s>>>(mx, mw, reinterpret_cast<OutT*>(Y), M, N, K, ldy);
+  return KVCM_LAUNCH_RESULT();
+}
+
+}  // namespace kvcm
+
+using namespace kvcm;
+
+KVCM_API int kvcm_gemm_tcgen05_supports(int M, int N, int K, int ldx, int ldw) {
+  return M >= 1 && N >= 1 && K >= 8 && (K % 8) == 0 && (ldx % 8) == 0 && (ldw % 8) == 0;
+}
+
+// out_f32: 0 = bfloat16 result, 1 = float result.
+KVCM_API int kvcm_gemm_tcgen05_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
+                                    int ldy, int out_f32, void* stream) {
+  if (M == 0 || N == 0) return 0;
+  if (!kvcm_gemm_tcgen05_supports(M, N, K, ldx, ldw)) return KVCM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return KVCM_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  return out_f32 ? launch_tcgen05<float>(X, W, Y, M, N, K, ldx, ldw, ldy, s)
+                 : launch_tcgen05<bf16>(X, W, Y, M, N, K, ldx, ldw, ldy, s);
+}
+
+// Reads and clears the error word (0 = no bounded wait ever ran out).  Synchronises the device.
+KVCM_API int kvcm_tcgen05_error(void) {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tcgen05_error, sizeof v) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_tcgen05_error, &zero, sizeof zero);
+  return v;
+}

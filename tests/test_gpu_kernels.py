@@ -247,6 +247,27 @@ def test_fused_gate_up_silu_gives_the_bits_of_the_separate_kernels(M, H, I):
     close(a2, gg[:, :I] * torch.sigmoid(gg[:, :I]) * gg[:, I:], "bfloat16", "against float64")
 
 
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (1, 8, 8), (100, 300, 136), (257, 129, 1000), (2048, 2560, 2048),
+                                    (640, 11264, 2048), (300, 2048, 5632), (17, 32003, 96)])
+def test_tcgen05_gemm(M, N, Kd):
+    """TMA tensor maps + tcgen05.mma + tensor memory against float64; ragged edges are zero-filled by
+    the TMA unit, so sizes need not be multiples of the 128 x 256 x 64 tile."""
+    lib = K()
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, Kd + 8, generator=g).to(torch.bfloat16).to(DEV)[:, :Kd]        # strided rows
+    w = (torch.randn(N, Kd, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    assert lib.tcgen05_gemm_supported(x, w)
+    ref = x.double().cpu() @ w.double().cpu().T
+    for out_dt in (torch.bfloat16, torch.float32):
+        y = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
+        lib.gemm_tcgen05(x, w, y)
+        assert lib.tcgen05_error() == 0
+        d = (y.double().cpu() - ref).abs().max().item()
+        bound = (0.01 if out_dt == torch.bfloat16 else 1e-3) * max(ref.abs().max().item(), 1e-3)
+        assert d <= bound, f"{out_dt}: {d} > {bound}"
+    assert not lib.tcgen05_gemm_supported(x[:, :Kd - 4], w[:, :Kd - 4])               # K not a multiple of 8
+
+
 def test_skinny_gemm_refuses_what_it_cannot_run():
     lib = K()
     assert not lib.skinny_gemm_supported(17, 64, 64)                # too many rows
