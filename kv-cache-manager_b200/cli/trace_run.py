@@ -32,7 +32,7 @@ def main(argv=None) -> int:
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--max-live", type=int, default=64, help="most requests live at a time")
     ap.add_argument("--attention", default="auto", choices=["auto", "plain"])
-    ap.add_argument("--gemm", default="auto", choices=["auto", "plain", "library", "skinny"])
+    ap.add_argument("--gemm", default="auto", choices=["auto", "plain", "library", "skinny", "tcgen05"])
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 

@@ -1,12 +1,14 @@
 // Matrix product for many rows (prefill) on the fifth-generation tensor cores:
 //     Y[M, N] = X[M, K] * W[N, K]^T,  bfloat16 operands, float accumulation in tensor memory.
 //
-// One block computes one 128 x 256 tile of Y:
+// Blocks are persistent (one per SM) and compute 128 x 256 tiles of Y (128 x 128 when that fills the
+// last round of blocks better), with two accumulators in tensor memory so that the epilogue of one
+// tile runs while the tensor core works on the next:
 //  * warp 0, one thread: TMA.  Tiled tensor maps (cp.async.bulk.tensor.2d) bring a [128 x 64] piece
-//    of X and a [256 x 64] piece of W per k-step into a four-stage ring of shared memory, in the
+//    of X and a [256 x 64] piece of W per k-step into a four-stage (six for the narrow tile) ring of shared memory, in the
 //    128-byte swizzled layout the tensor core reads; completion is counted on an mbarrier.
 //  * warp 1, one thread: tcgen05.mma (cta_group::1, kind::f16, M = 128, N = 256, K = 16), four per
-//    k-step, accumulating into 256 columns of tensor memory; tcgen05.commit hands each ring slot
+//    k-step, accumulating into one of the two accumulators (256 columns each) of tensor memory; tcgen05.commit hands each ring slot
 //    back to the producer when the products that read it are done, and signals the epilogue at
 //    the end.
 //  * warps 2-5: epilogue.  tcgen05.ld reads the accumulator (each warp its quarter of the 128
@@ -21,10 +23,9 @@
 
 namespace kvcm {
 
-constexpr int kTcBM = 128, kTcBN = 256, kTcBK = 64, kTcStages = 4;
+constexpr int kTcBM = 128, kTcBK = 64;
 constexpr int kTcThreads = 192;
-constexpr int kTcABytes = kTcBM * kTcBK * 2, kTcBBytes = kTcBN * kTcBK * 2;
-constexpr int kTcStageBytes = kTcABytes + kTcBBytes;
+constexpr int kTcABytes = kTcBM * kTcBK * 2;
 constexpr unsigned long long kTcWaitLimitNs = 1000000000ull;   // every wait gives up after a second
 
 __device__ int g_tcgen05_error = 0;
@@ -67,31 +68,42 @@ __host__ __device__ constexpr uint32_t tc_idesc(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
 }
 
-template <typename OutT>
+template <typename OutT, int BN>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     OutT* __restrict__ Y, int M, int N, int K, int ldy) {
+  constexpr int kBBytes = BN * kTcBK * 2;
+  constexpr int kStageBytes = kTcABytes + kBBytes;
+  constexpr int kStages = BN == 256 ? 4 : 6;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ __align__(8) uint64_t full[kTcStages], empty[kTcStages], acc_ready;
+  __shared__ __align__(8) uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base;
   __shared__ volatile int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kTcBN, m0 = blockIdx.y * kTcBM;
+  const int m_tiles = (M + kTcBM - 1) / kTcBM, n_tiles = (N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles;
   const int nk = (K + kTcBK - 1) / kTcBK;
+  // Persistent block: tiles blockIdx.x, + gridDim.x, ...  Neighbouring blocks take different column
+  // tiles of the same row tile: the blocks of a round share a few pieces of X and sweep W, all of
+  // which stays in L2 at these sizes.
+  const int my_tiles = int(blockIdx.x) < tiles ? (tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int s = 0; s < kTcStages; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc_s32(&full[s])));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc_s32(&empty[s])));
     }
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc_s32(&acc_ready)));
+    for (int a = 0; a < 2; ++a) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc_s32(&acc_full[a])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;\n" ::"r"(tc_s32(&acc_empty[a])));   // four epilogue warps
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 1) {                                // one warp allocates 256 columns of tensor memory
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_s32(&tmem_base)), "r"(kTcBN));
+  if (warp == 1) {                                // one warp allocates two accumulators of BN columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_s32(&tmem_base)), "r"(2 * BN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -101,60 +113,85 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int k = 0; k < nk && !abort_flag; ++k) {
-        const int s = k % kTcStages;
-        if (!tc_wait(&empty[s], ((k / kTcStages) & 1) ^ 1)) {
-          atomicExch(&g_tcgen05_error, (1 << 16) | int(blockIdx.x & 0xffff));
-          abort_flag = 1;
-          break;
+      int it = 0;                                  // running stage counter across tiles
+      for (int tl = 0; tl < my_tiles && !abort_flag; ++tl) {
+        const int t = int(blockIdx.x) + tl * int(gridDim.x);
+        const int m0 = (t / n_tiles) * kTcBM, n0 = (t % n_tiles) * BN;
+        for (int k = 0; k < nk; ++k, ++it) {
+          const int s = it % kStages;
+          if (!tc_wait(&empty[s], ((it / kStages) & 1) ^ 1)) {
+            atomicExch(&g_tcgen05_error, (1 << 16) | int(blockIdx.x & 0xffff));
+            abort_flag = 1;
+            break;
+          }
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_s32(&full[s])), "r"(kStageBytes) : "memory");
+          unsigned char* a = ring + s * kStageBytes;
+          unsigned char* b = a + kTcABytes;
+          asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                       ::"r"(tc_s32(a)), "l"(&map_x), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(m0) : "memory");
+          asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                       ::"r"(tc_s32(b)), "l"(&map_w), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(n0) : "memory");
         }
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_s32(&full[s])), "r"(kTcStageBytes) : "memory");
-        unsigned char* a = ring + s * kTcStageBytes;
-        unsigned char* b = a + kTcABytes;
-        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                     ::"r"(tc_s32(a)), "l"(&map_x), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(m0) : "memory");
-        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                     ::"r"(tc_s32(b)), "l"(&map_w), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(n0) : "memory");
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = tc_idesc(kTcBM, kTcBN);
-      for (int k = 0; k < nk && !abort_flag; ++k) {
-        const int s = k % kTcStages;
-        if (!tc_wait(&full[s], (k / kTcStages) & 1)) {
-          atomicExch(&g_tcgen05_error, (2 << 16) | int(blockIdx.x & 0xffff));
+      constexpr uint32_t idesc = tc_idesc(kTcBM, BN);
+      int it = 0;
+      for (int tl = 0; tl < my_tiles && !abort_flag; ++tl) {
+        const int acc = tl & 1;
+        // the epilogue must have drained this accumulator (two tiles ago)
+        if (!tc_wait(&acc_empty[acc], ((tl >> 1) & 1) ^ 1)) {
+          atomicExch(&g_tcgen05_error, (4 << 16) | int(blockIdx.x & 0xffff));
           abort_flag = 1;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t a_addr = tc_s32(ring + s * kTcStageBytes);
-        const uint64_t da = tc_smem_desc(a_addr), db = tc_smem_desc(a_addr + kTcABytes);
+        const uint32_t d_tmem = tmem + uint32_t(acc * BN);
+        for (int k = 0; k < nk; ++k, ++it) {
+          const int s = it % kStages;
+          if (!tc_wait(&full[s], (it / kStages) & 1)) {
+            atomicExch(&g_tcgen05_error, (2 << 16) | int(blockIdx.x & 0xffff));
+            abort_flag = 1;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t a_addr = tc_s32(ring + s * kStageBytes);
+          const uint64_t da = tc_smem_desc(a_addr), db = tc_smem_desc(a_addr + kTcABytes);
 #pragma unroll
-        for (int j = 0; j < kTcBK / 16; ++j) {
-          const uint32_t accumulate = (k > 0 || j > 0) ? 1u : 0u;
-          // +32 bytes along k inside the swizzled row = +2 in the descriptor's address field
-          asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                       ::"r"(tmem), "l"(da + uint64_t(2 * j)), "l"(db + uint64_t(2 * j)), "r"(idesc), "r"(accumulate) : "memory");
+          for (int j = 0; j < kTcBK / 16; ++j) {
+            const uint32_t accumulate = (k > 0 || j > 0) ? 1u : 0u;
+            // +32 bytes along k inside the swizzled row = +2 in the descriptor's address field
+            asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                         ::"r"(d_tmem), "l"(da + uint64_t(2 * j)), "l"(db + uint64_t(2 * j)), "r"(idesc), "r"(accumulate) : "memory");
+          }
+          // the ring slot is free once these products have read it
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_s32(&empty[s])) : "memory");
         }
-        // the ring slot is free once these products have read it
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_s32(&empty[s])) : "memory");
+        if (abort_flag) break;
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_s32(&acc_full[acc])) : "memory");
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_s32(&acc_ready)) : "memory");
     }
   } else {
-    // ---- epilogue: this warp reads lanes 32*(warp % 4) .. +31 of the accumulator
-    bool ok = tc_wait(&acc_ready, 0);
-    if (!ok && lane == 0) atomicExch(&g_tcgen05_error, (3 << 16) | int(blockIdx.x & 0xffff));
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    // ---- epilogue: this warp reads lanes 32*(warp % 4) .. +31 of the accumulator, while the
+    // tensor core already fills the other accumulator with the next tile
     const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    if (ok && !abort_flag) {
+    for (int tl = 0; tl < my_tiles; ++tl) {
+      const int acc = tl & 1;
+      const int t = int(blockIdx.x) + tl * int(gridDim.x);
+      const int m0 = (t / n_tiles) * kTcBM, n0 = (t % n_tiles) * BN;
+      if (abort_flag || !tc_wait(&acc_full[acc], (tl >> 1) & 1)) {
+        if (!abort_flag && lane == 0) atomicExch(&g_tcgen05_error, (3 << 16) | int(blockIdx.x & 0xffff));
+        abort_flag = 1;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
-      for (int c = 0; c < kTcBN / 32; ++c) {
+      for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
-        const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(c * 32);
+        const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(acc * BN + c * 32);
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
                      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
@@ -187,6 +224,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           }
         }
       }
+      // this warp has read its lanes of the accumulator: hand it back to the tensor core
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc_s32(&acc_empty[acc])) : "memory");
     }
   }
   // every role ends here; tensor memory goes back before the block leaves
@@ -194,7 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTcBN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(2 * BN));
   }
 }
 
@@ -230,25 +271,43 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
   return r == CUDA_SUCCESS ? 0 : 20000 + int(r);
 }
 
-template <typename OutT>
-int launch_tcgen05(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
-                   cudaStream_t s) {
+template <typename OutT, int BN>
+int launch_tcgen05_bn(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
+                      int sm_count, cudaStream_t s) {
   CUtensorMap mx, mw;
   int rc = make_map(&mx, X, M, K, ldx, kTcBM);
   if (rc) return rc;
-  rc = make_map(&mw, W, N, K, ldw, kTcBN);
+  rc = make_map(&mw, W, N, K, ldw, BN);
   if (rc) return rc;
-  auto kernel = gemm_tcgen05_kernel<OutT>;
-  const size_t smem = size_t(kTcStages) * kTcStageBytes + 1024;
+  auto kernel = gemm_tcgen05_kernel<OutT, BN>;
+  const size_t smem = size_t(BN == 256 ? 4 : 6) * (kTcABytes + BN * kTcBK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  dim3 grid((N + kTcBN - 1) / kTcBN, (M + kTcBM - 1) / kTcBM);
-  kernel<<<grid, kTcThreads, smem, s>>>(mx, mw, reinterpret_cast<OutT*>(Y), M, N, K, ldy);
+  const int tiles = ((N + BN - 1) / BN) * ((M + kTcBM - 1) / kTcBM);
+  kernel<<<dim3(tiles < sm_count ? tiles : sm_count), kTcThreads, smem, s>>>(mx, mw, reinterpret_cast<OutT*>(Y), M, N, K, ldy);
   return KVCM_LAUNCH_RESULT();
+}
+
+template <typename OutT>
+int launch_tcgen05(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
+                   cudaStream_t s) {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  // 128 x 256 tiles unless the narrower 128 x 128 tile fills the last round of blocks better.
+  const long long m_tiles = (M + kTcBM - 1) / kTcBM;
+  const long long t256 = m_tiles * ((N + 255) / 256), t128 = m_tiles * ((N + 127) / 128);
+  const long long cost256 = ((t256 + sm_count - 1) / sm_count) * 256, cost128 = ((t128 + sm_count - 1) / sm_count) * 128;
+  if (cost128 * 3 < cost256 * 2) return launch_tcgen05_bn<OutT, 128>(X, W, Y, M, N, K, ldx, ldw, ldy, sm_count, s);
+  return launch_tcgen05_bn<OutT, 256>(X, W, Y, M, N, K, ldx, ldw, ldy, sm_count, s);
 }
 
 }  // namespace kvcm

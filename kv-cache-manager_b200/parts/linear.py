@@ -3,10 +3,11 @@ layout of every matrix of the reference (``src/model/llama.cpp:45-52``).
 
 Which kernel runs is decided by the weight's dtype, never by the model:
 * float32 weight  -> this engine's plain float kernel (true 32-bit, fixed summation order);
-* bfloat16 weight -> the library GEMM (cuBLAS through ``torch.mm``), the same place where the
-  reference calls cuBLAS, or this engine's own weight-streaming kernel for a handful of rows
-  (decode), or the plain kernel when ``options['gemm'] == 'plain'`` asks for the twin
-  (``'library'`` forces cuBLAS, ``'skinny'`` the register-streaming variant).
+* bfloat16 weight -> this engine's weight-streaming kernel for a handful of rows (decode), its
+  tcgen05 kernel for many rows where the tiles fill the GPU (prefill), else the library GEMM
+  (cuBLAS through ``torch.mm``, the same place where the reference calls cuBLAS);
+  ``options['gemm']``: 'plain' forces the plain twin, 'library' cuBLAS, 'tcgen05' and 'skinny' the
+  respective kernels.
 """
 from __future__ import annotations
 
@@ -19,6 +20,7 @@ from .base import Part, StepContext
 
 
 STREAM_MAX_BYTES = 32 << 20
+TCGEN05_MIN_ROWS = 256
 
 
 class Linear(Part):
@@ -61,6 +63,20 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, options:
         y = torch.empty((M, N), dtype=out_dtype, device=x.device)
         K.gemm_stream(x, w, y)
         return y
+    # Many rows (prefill): this engine's tcgen05 kernel where its 128 x 256 tiles fill the SMs well
+    # (within about a tenth of the library's speed there), or always with options['gemm'] == 'tcgen05'.
+    if mode == "tcgen05" or (mode == "auto" and M >= TCGEN05_MIN_ROWS and _tiles_fill_well(M, N, x.device)):
+        if K.tcgen05_gemm_supported(x, w):
+            y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+            K.gemm_tcgen05(x, w, y)
+            return y
     if out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+def _tiles_fill_well(M: int, N: int, device) -> bool:
+    sms = K.sm_count(device)
+    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    rounds = (tiles + sms - 1) // sms
+    return tiles >= 96 and tiles >= 0.8 * rounds * sms

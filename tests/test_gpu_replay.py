@@ -211,3 +211,16 @@ def test_cuts_agree_bit_for_bit_with_plain_kernels(dtype, model_folders):
         if at == len(toks):
             break
     assert torch.equal(torch.cat(parts), whole)
+
+
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+def test_tcgen05_products_inside_the_engine(name, model_folders, oracle):
+    """The same requests with every many-row product forced onto the tcgen05 kernel."""
+    dtype = "bfloat16"
+    r = replayer(model_folders, name, dtype, 256, options={"gemm": "tcgen05"})
+    for i in (3, len(LENGTHS[name]) - 1):
+        toks = tokens_of(name, i)
+        got = r.step([dict(id="x", tokens=toks, want=list(range(len(toks))))], end=["x"])
+        helpers.assert_logits_close(got, oracle(name, dtype, i), dtype, f"{name} request {i} through tcgen05")
+    from kvcm.kernels import library as K
+    assert K.tcgen05_error() == 0
