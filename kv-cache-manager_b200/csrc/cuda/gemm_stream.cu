@@ -28,7 +28,10 @@ constexpr int kStreamConsumers = 8;                    // consumer warps
 constexpr int kStreamThreads = 32 * (kStreamConsumers + 1);
 constexpr int kMaxStages = 12;                         // ring depth is chosen per launch to fill shared memory
 constexpr int kChunk = 1024;                           // k elements per stage
-constexpr int kRowBytes = kChunk * 2 + 16;             // padded stage row: odd multiple of 16 bytes
+constexpr int kRowBytes = kChunk * 2 + 64;             // padded stage row: rows g and g+1 sit 64 bytes apart modulo 128,
+                                                       // so the eight lanes of a quarter-warp (two rows x four 16-byte
+                                                       // columns) read eight distinct bank groups
+constexpr int kXPad = 32;                              // the same for the staged X (elements)
 constexpr int kStageBytes = 16 * kRowBytes;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // every wait gives up after two seconds
 
@@ -123,7 +126,7 @@ gemm_stream_kernel(StreamParams p) {
   constexpr int kConsumerThreads = 32 * kStreamConsumers;
   constexpr int MB = MT * 8;                                  // batch rows held (padded)
   const int Kc = (p.K + kChunk - 1) / kChunk;                 // stages per tile
-  const int Kp = Kc * kChunk + 8;                             // padded row of the staged X
+  const int Kp = Kc * kChunk + kXPad;                         // padded row of the staged X
   const int kStages = p.stages;
   unsigned char* ring = smem_raw;                             // [stages][16][kRowBytes]
   bf16* xs = reinterpret_cast<bf16*>(ring + kStages * kStageBytes);          // [MB][Kp]
@@ -323,7 +326,7 @@ constexpr size_t kStreamSmemBudget = 200 * 1024;
 // Shared memory of a launch with `stages` ring slots.
 static size_t stream_smem(int MT, int K, int stages) {
   const int Kc = (K + kChunk - 1) / kChunk;
-  return size_t(stages) * kStageBytes + size_t(MT) * 8 * (Kc * kChunk + 8) * sizeof(bf16) +
+  return size_t(stages) * kStageBytes + size_t(MT) * 8 * (Kc * kChunk + kXPad) * sizeof(bf16) +
          size_t(2) * kStreamConsumers * 16 * MT * 8 * sizeof(float) + 2 * kMaxStages * sizeof(uint64_t);
 }
 
