@@ -12,7 +12,7 @@ extern "C" int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out
                                           const int* block_tables, int max_blocks,
                                           const int* seq_ctx_len, int seqs, int nh, int nkv, int hd,
                                           int block_size, float scale, int window, int part_size,
-                                          int num_parts, float* scratch, void* stream);
+                                          int num_parts, float* scratch, int cluster_merge, void* stream);
 
 namespace {
 
@@ -75,7 +75,7 @@ KVCM_API int kvcm_attention_decode_bf16_noalloc(const void* q, int q_stride, voi
   if (rc != 0) return rc;
   rc = kvcm_attention_decode_bf16(q, q_stride, out, out_stride, k_cache, v_cache, block_tables,
                                   max_blocks, seq_ctx_len, seqs, nh, nkv, hd, block_size, scale, window,
-                                  part_size, num_parts, scratch, stream);
+                                  part_size, num_parts, scratch, 0, stream);
   if (rc != 0)
     std::snprintf(last_error, sizeof last_error, "decode attention launch failed with code %d", rc);
   return rc;

@@ -5,8 +5,10 @@
 //           tile, so every key and value is read once for the whole group (the reference's kernel
 //           has the same aim, src/cuda/paged_attention.cu:3-4).  The context is split into
 //           partitions so that small batches still fill the GPU; partial (max, sum, output) are
-//           merged by a second kernel (as the reference's v2, :186-203).  With one partition the
-//           block writes the result itself (v1).
+//           merged as in the reference's v2 (:186-203): up to 8 partitions are the blocks of one
+//           thread-block cluster, which read one another's partial results from shared memory
+//           and each write a share of the outputs; more partitions go through global memory and
+//           a second kernel.  With one partition the block writes the result itself (v1).
 // prefill : portions of more than one token.  One block per (64 query rows of a request, query
 //           head); keys up to each row's own position come from the pages, K and V of the portion
 //           included (they were written before), so a portion may start anywhere in a request.
@@ -16,6 +18,8 @@
 // optional window (keys t > position - window).  Scores are scaled in float after the product;
 // softmax by exp2 with log2(e) folded into the scale; probabilities are rounded to bfloat16 for
 // the P*V product, sums stay float.
+#include <cooperative_groups.h>
+
 #include "attention_mma.cuh"
 #include "pdl.cuh"
 
@@ -35,7 +39,41 @@ struct DecodeParams {
   int nh, nkv, block_size, window, part_size, num_parts;
   float scale_log2;
   int log2_block;                      // log2(block_size) when it is a power of two, else -1
+  int cluster_merge;                   // the partitions of a (request, head group) are one cluster
 };
+
+constexpr int kMaxClusterParts = 8;      // the portable cluster size: any GPC can place it
+
+// Merge of the partitions inside a cluster.  Every block has put its partial result for the 16
+// heads of the tile into its own shared memory (bo [16][HD], bm [16] max, bl [16] sum; an empty
+// partition has max = -inf).  The outputs are dealt out over the blocks of the cluster; each
+// reads all partitions' values through distributed shared memory and adds them in partition
+// order, with the roundings of the merge kernel.
+template <int HD>
+__device__ __forceinline__ void cluster_merge_tail(const DecodeParams& p, int seq, int head0, int heads_here,
+                                                   float* bo, float* bm, float* bl) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();                                                  // every block's partial result is in place
+  const int P = p.num_parts;
+  for (int e = int(cluster.block_rank()) * kAttnThreads + threadIdx.x; e < heads_here * HD; e += P * kAttnThreads) {
+    const int r = e / HD, d = e - r * HD;
+    float M = -INFINITY;
+    for (int i = 0; i < P; ++i) M = fmaxf(M, *cluster.map_shared_rank(bm + r, i));
+    float acc = 0.f, L = 0.f;
+    for (int i = 0; i < P; ++i) {
+      const float mp = *cluster.map_shared_rank(bm + r, i);
+      const float lp = *cluster.map_shared_rank(bl + r, i);
+      const float op = *cluster.map_shared_rank(bo + r * HD + d, i);
+      const bool live = mp != -INFINITY;                           // an empty partition left no output
+      const float f = live ? exp2f(mp - M) : 0.f;
+      acc = live ? __fmaf_rn(f, op, acc) : acc;
+      L = live ? __fmaf_rn(f, lp, L) : L;
+    }
+    p.out[size_t(seq) * p.out_stride + size_t(head0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+  cluster.sync();                                                  // nobody leaves while its memory is read
+}
 
 template <int HD, int kKVStages>
 __global__ void __launch_bounds__(kAttnThreads)
@@ -62,6 +100,17 @@ attn_decode_kernel(DecodeParams p) {
   const int lo = (p.window > 0 && ctx > p.window) ? ctx - p.window : 0;
   const int begin = max(lo, part * p.part_size);
   const int end = min(ctx, (part + 1) * p.part_size);
+  float* mo = reinterpret_cast<float*>(kbuf);                       // [4][16][HD]   (after the key loop)
+  float* mm = mo + 4 * 16 * HD;                                     // [4][16]
+  float* mlsum = mm + 4 * 16;                                       // [4][16]
+  float* bo = mlsum + 4 * 16;                                       // [16][HD] the block's result (cluster merge)
+  float* bm = bo + 16 * HD;                                         // [16]
+  float* bl = bm + 16;                                              // [16]
+  if (begin >= end && p.cluster_merge) {                           // nothing to read here, but the cluster waits
+    if (tid < 16) { bm[tid] = -INFINITY; bl[tid] = 0.f; }
+    cluster_merge_tail<HD>(p, seq, head0, heads_here, bo, bm, bl);
+    return;
+  }
   if (begin >= end) {                                              // nothing to read here
     for (int i = tid; i < heads_here * HD; i += kAttnThreads) {
       const int r = i / HD, d = i - r * HD;
@@ -155,9 +204,6 @@ attn_decode_kernel(DecodeParams p) {
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
-  float* mo = reinterpret_cast<float*>(kbuf);                       // [4][16][HD]
-  float* mm = mo + 4 * 16 * HD;                                     // [4][16]
-  float* mlsum = mm + 4 * 16;                                       // [4][16]
 #pragma unroll
   for (int d = 0; d < HD / 8; ++d) {
     float* base = mo + (warp * 16) * HD + d * 8 + 2 * t4;
@@ -187,7 +233,13 @@ attn_decode_kernel(DecodeParams p) {
       L += f * mlsum[w * 16 + r];
     }
     const int head = head0 + r;
-    if (p.num_parts == 1) {
+    if (p.cluster_merge) {
+      bo[r * HD + d] = acc;
+      if (d == 0) {
+        bm[r] = M;
+        bl[r] = L;
+      }
+    } else if (p.num_parts == 1) {
       p.out[size_t(seq) * p.out_stride + size_t(head) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     } else {
       const size_t idx = (size_t(seq) * p.nh + head) * p.num_parts + part;
@@ -198,6 +250,7 @@ attn_decode_kernel(DecodeParams p) {
       }
     }
   }
+  if (p.cluster_merge) cluster_merge_tail<HD>(p, seq, head0, heads_here, bo, bm, bl);
 }
 
 // Merges the partitions of one (request, head): out = sum_p 2^(m_p - M) o_p / sum_p 2^(m_p - M) l_p.
@@ -215,8 +268,8 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
       const float mp = part_ml[(base + i) * 2];
       if (mp == -INFINITY) continue;
       const float f = exp2f(mp - M);
-      acc += f * part_o[(base + i) * hd + d];
-      L += f * part_ml[(base + i) * 2 + 1];
+      acc = __fmaf_rn(f, part_o[(base + i) * hd + d], acc);
+      L = __fmaf_rn(f, part_ml[(base + i) * 2 + 1], L);
     }
     out[size_t(seq) * out_stride + size_t(head) * hd + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
   }
@@ -400,7 +453,7 @@ attn_prefill_kernel(PrefillParams p) {
 
 template <int HD, int kKVStages> size_t decode_smem() {
   const size_t tiles = size_t(16 + 2 * kKVStages * kKeyTile) * (HD + 8) * sizeof(bf16);
-  const size_t merge = size_t(16) * (HD + 8) * sizeof(bf16) + (size_t(4) * 16 * HD + 2 * 4 * 16) * sizeof(float);
+  const size_t merge = size_t(16) * (HD + 8) * sizeof(bf16) + (size_t(5) * 16 * HD + 2 * 4 * 16 + 32) * sizeof(float);
   return tiles > merge ? tiles : merge;
 }
 template <int HD> size_t prefill_smem() { return size_t(64 + 4 * kKeyTile) * (HD + 8) * sizeof(bf16); }
@@ -417,6 +470,7 @@ int launch_decode_staged(const DecodeParams& p, int seqs, cudaStream_t s) {
   }
   const int G = p.nh / p.nkv;
   dim3 grid(p.num_parts, p.nkv * ((G + 15) / 16), seqs);
+  if (p.cluster_merge) return pdl_launch_cluster(kernel, grid, dim3(kAttnThreads), smem, s, p.num_parts, p);
   return pdl_launch(kernel, grid, dim3(kAttnThreads), smem, s, p);
 }
 
@@ -462,11 +516,16 @@ KVCM_API long long kvcm_attention_decode_scratch_floats(int seqs, int nh, int hd
   return num_parts <= 1 ? 0 : (long long)seqs * nh * num_parts * (hd + 2);
 }
 
+// Most partitions that one cluster merges; with more the caller must give scratch.
+KVCM_API int kvcm_attention_decode_cluster_parts(void) { return kMaxClusterParts; }
+
+// `scratch`: kvcm_attention_decode_scratch_floats() floats, needed when num_parts > 1 unless the
+// merge runs inside a cluster (cluster_merge != 0 and num_parts <= kvcm_attention_decode_cluster_parts()).
 KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
                                         const void* k_cache, const void* v_cache, const int* block_tables,
                                         int max_blocks, const int* seq_ctx_len, int seqs, int nh, int nkv,
                                         int hd, int block_size, float scale, int window, int part_size,
-                                        int num_parts, float* scratch, void* stream) {
+                                        int num_parts, float* scratch, int cluster_merge, void* stream) {
   if (seqs == 0) return 0;
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -476,14 +535,15 @@ KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, 
     if (sm_count <= 0) sm_count = 148;
   }
   if (nkv <= 0 || nh % nkv || part_size <= 0 || part_size % kKeyTile || num_parts < 1) return KVCM_ERR_UNSUPPORTED;
-  if (num_parts > 1 && scratch == nullptr) return KVCM_ERR_UNSUPPORTED;
+  if (cluster_merge && (num_parts < 2 || num_parts > kMaxClusterParts)) cluster_merge = 0;
+  if (num_parts > 1 && !cluster_merge && scratch == nullptr) return KVCM_ERR_UNSUPPORTED;
   DecodeParams p;
   p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.out_stride = out_stride;
   p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.seq_ctx_len = seq_ctx_len;
   p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)seqs * nh * num_parts * hd : nullptr;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
-  p.part_size = part_size; p.num_parts = num_parts;
+  p.part_size = part_size; p.num_parts = num_parts; p.cluster_merge = cluster_merge;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.log2_block = -1;
   for (int b = 0; b < 16; ++b) if ((1 << b) == block_size) p.log2_block = b;
@@ -491,7 +551,7 @@ KVCM_API int kvcm_attention_decode_bf16(const void* q, int q_stride, void* out, 
 #define X(N) if (hd == N) rc = launch_decode<N>(p, seqs, sm_count, (cudaStream_t)stream);
   KVCM_FOR_HEAD_DIMS(X)
 #undef X
-  if (rc != 0 || num_parts == 1) return rc;
+  if (rc != 0 || num_parts == 1 || cluster_merge) return rc;
   return pdl_launch(attn_decode_merge_kernel, dim3(seqs, nh), dim3(hd < 64 ? 32 : 64), 0, (cudaStream_t)stream,
                     (const float*)p.part_o, (const float*)p.part_ml, p.out, out_stride, nh, hd, num_parts);
 }

@@ -33,4 +33,26 @@ int pdl_launch(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t s
   return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, args...));
 }
 
+// The same with the grid cut into thread-block clusters of `cluster_x` blocks along x (which must
+// divide grid.x; at most 8).
+template <typename Kernel, typename... Args>
+int pdl_launch_cluster(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_x,
+                       Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cluster_x;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, args...));
+}
+
 }  // namespace kvcm

@@ -263,6 +263,7 @@ def sm_count(device) -> int:
 
 
 KEY_TILE = 64
+CLUSTER_PARTS = 8           # kvcm_attention_decode_cluster_parts()
 
 
 def decode_partitions(seqs: int, nh: int, nkv: int, max_ctx: int, device, version: str = "auto"):
@@ -300,15 +301,18 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     size, parts = decode_partitions(S, nh, nkv, ctx.max_decode_ctx, q.device,
                                     ctx.options.get("attn_version", "auto"))
     scratch = None
-    if parts > 1:
+    # Up to 8 partitions merge inside a thread-block cluster; more go through scratch memory
+    # and a merge kernel ('attn_merge': 'kernel' forces that path).
+    in_cluster = 1 < parts <= CLUSTER_PARTS and ctx.options.get("attn_merge", "cluster") == "cluster"
+    if parts > 1 and not in_cluster:
         n = S * nh * parts * (hd + 2)          # partial outputs + (max, sum) per partition
         scratch = torch.empty(n, dtype=torch.float32, device=q.device)
     rc = _lib().kvcm_attention_decode_bf16(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
         block_tables.shape[1], _p(ctx.seq_ctx_len), S, nh, nkv, hd, k_cache.shape[2],
-        ctypes.c_float(scale), int(window), size, parts, _p(scratch), _stream())
+        ctypes.c_float(scale), int(window), size, parts, _p(scratch), int(in_cluster), _stream())
     _check(rc, "attention_decode", f"(hd={hd}, nh={nh}, nkv={nkv})")
-    if parts > 1:
+    if parts > 1 and not in_cluster:
         global _launches
         _launches += 1                      # the merge kernel
 

@@ -418,12 +418,17 @@ def test_attention_kernels_on_a_mixed_batch(nh, nkv, hd, B, window):
         close(out, ref, dtype, f"plain {dtype}")
         if dtype == "bfloat16":
             assert K().fast_attention_supported(nh, nkv, hd, B)
-            for version in ("v1", "v2"):
-                case["ctx"].options = {"attn_version": version}
+            got = {}
+            for version in ("v1", "v2", "v2 merge kernel"):
+                case["ctx"].options = {"attn_version": version[:2],
+                                       "attn_merge": "kernel" if "kernel" in version else "cluster"}
                 fast = torch.zeros_like(out)
                 K().paged_attention(case["q"], fast, case["kc"], case["vc"], case["tables"], case["ctx"],
                                     nh, nkv, hd, scale, window)
                 close(fast, ref, dtype, f"fast {version}")
+                got[version] = fast
+            # merging inside the cluster and merging in a kernel of its own give the same bits
+            assert torch.equal(got["v2"], got["v2 merge kernel"])
 
 
 def test_decode_attention_long_contexts_and_many_partitions():
@@ -431,8 +436,8 @@ def test_decode_attention_long_contexts_and_many_partitions():
     seq_lens = [2047, 2048, 1, 4097, 513]
     case = paged_case(seq_lens, [1] * 5, nh, nkv, hd, B, "bfloat16", seed=3)
     ref = reference_attention(case, nh, nkv, hd, 0.125, 0)
-    for version in ("v1", "v2"):
-        case["ctx"].options = {"attn_version": version}
+    for version in ("v1", "v2", "v2 merge kernel"):
+        case["ctx"].options = {"attn_version": version[:2], "attn_merge": "kernel" if "kernel" in version else "cluster"}
         out = torch.zeros(5, nh * hd, dtype=torch.bfloat16, device=DEV)
         K().paged_attention(case["q"], out, case["kc"], case["vc"], case["tables"], case["ctx"], nh, nkv, hd, 0.125, 0)
         close(out, ref, "bfloat16", version)

@@ -35,7 +35,7 @@ def _call(lib, symbol, case, out, nh, nkv, hd, scale, part_size, parts, scratch=
             _p(case["tables"]), case["tables"].shape[1], _p(case["ctx"].seq_ctx_len), out.shape[0], nh, nkv,
             hd, case["kc"].shape[2], ctypes.c_float(scale), 0, part_size, parts]
     if scratch is not None:
-        args.append(_p(scratch))
+        args += [_p(scratch), 0]             # the merge through scratch memory, not inside a cluster
     args.append(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     return getattr(lib, symbol)(*args)
 
