@@ -42,6 +42,7 @@ struct DecodeParams {
   int cluster_merge;                   // the partitions of a (request, head group) are one cluster
 };
 
+constexpr int kTabMax = 512;         // page-table entries of a partition kept in shared memory
 constexpr int kMaxClusterParts = 8;      // the portable cluster size: any GPC can place it
 
 // Merge of the partitions inside a cluster.  Every block has put its partial result for the 16
@@ -75,6 +76,14 @@ __device__ __forceinline__ void cluster_merge_tail(const DecodeParams& p, int se
   cluster.sync();                                                  // nobody leaves while its memory is read
 }
 
+// Shared memory of the decode kernel without the page-table slice: the larger of the tiles of
+// the key loop and the buffers of the merge that reuse them.
+template <int HD, int kKVStages> constexpr size_t decode_core_smem() {
+  const size_t tiles = size_t(16 + 2 * kKVStages * kKeyTile) * (HD + 8) * sizeof(bf16);
+  const size_t merge = size_t(16) * (HD + 8) * sizeof(bf16) + (size_t(5) * 16 * HD + 2 * 4 * 16 + 32) * sizeof(float);
+  return tiles > merge ? tiles : merge;
+}
+
 template <int HD, int kKVStages>
 __global__ void __launch_bounds__(kAttnThreads)
 attn_decode_kernel(DecodeParams p) {
@@ -84,9 +93,12 @@ attn_decode_kernel(DecodeParams p) {
   bf16* qtile = reinterpret_cast<bf16*>(smem_raw);                 // [16][LD]
   bf16* kbuf = qtile + 16 * LD;                                    // [stages][64][LD]
   bf16* vbuf = kbuf + kKVStages * kKeyTile * LD;                   // [stages][64][LD]
+  int* stab = reinterpret_cast<int*>(smem_raw + decode_core_smem<HD, kKVStages>());   // [kTabMax]
 
+  // Until pdl_wait() only what no kernel of this step writes is read: the batch's integer arrays
+  // and the keys and values of earlier tokens.  The query and the newest key and value come from
+  // the kernel before this one.
   pdl_launch_dependents();
-  pdl_wait();
   const int part = blockIdx.x, seq = blockIdx.z;
   const int G = p.nh / p.nkv;
   const int head_tiles = (G + 15) / 16;
@@ -106,6 +118,7 @@ attn_decode_kernel(DecodeParams p) {
   float* bo = mlsum + 4 * 16;                                       // [16][HD] the block's result (cluster merge)
   float* bm = bo + 16 * HD;                                         // [16]
   float* bl = bm + 16;                                              // [16]
+  if (begin >= end) pdl_wait();
   if (begin >= end && p.cluster_merge) {                           // nothing to read here, but the cluster waits
     if (tid < 16) { bm[tid] = -INFINITY; bl[tid] = 0.f; }
     cluster_merge_tail<HD>(p, seq, head0, heads_here, bo, bm, bl);
@@ -124,14 +137,16 @@ attn_decode_kernel(DecodeParams p) {
     }
     return;
   }
+  // The partition's slice of the page table goes to shared memory first: one memory latency
+  // here instead of one inside every round of the key loop.
   const int* table = p.block_tables + size_t(seq) * p.max_blocks;
-
-  for (int c = tid; c < 16 * (HD / 8); c += kAttnThreads) {        // Q tile, zero rows beyond the group
-    const int r = c / (HD / 8), ch = c - r * (HD / 8);
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < heads_here)
-      v = *reinterpret_cast<const uint4*>(p.q + size_t(seq) * p.q_stride + size_t(head0 + r) * HD + ch * 8);
-    *reinterpret_cast<uint4*>(qtile + r * LD + ch * 8) = v;
+  {
+    const int first_page = begin / p.block_size, n_pages = (end - 1) / p.block_size - first_page + 1;
+    if (n_pages <= kTabMax) {
+      for (int j = tid; j < n_pages; j += kAttnThreads) stab[j] = table[first_page + j];
+      table = stab - first_page;
+      __syncthreads();
+    }
   }
 
   const int t_first = (begin / kKeyTile) * kKeyTile;
@@ -144,8 +159,22 @@ attn_decode_kernel(DecodeParams p) {
     }
     cp_async_commit();                                             // one group per tile, empty ones too
   };
-#pragma unroll
-  for (int i = 0; i < kKVStages - 1; ++i) load_stage(i);
+  // Tiles that lie wholly below the newest key (position ctx - 1, written by the kernel before
+  // this one) are requested before the wait; the rest of the first stages after it.
+  int ahead = 0;
+  for (; ahead < kKVStages - 1; ++ahead) {
+    if (t_first + (ahead + 1) * kKeyTile > ctx - 1) break;
+    load_stage(ahead);
+  }
+  pdl_wait();
+  for (int c = tid; c < 16 * (HD / 8); c += kAttnThreads) {        // Q tile, zero rows beyond the group
+    const int r = c / (HD / 8), ch = c - r * (HD / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < heads_here)
+      v = *reinterpret_cast<const uint4*>(p.q + size_t(seq) * p.q_stride + size_t(head0 + r) * HD + ch * 8);
+    *reinterpret_cast<uint4*>(qtile + r * LD + ch * 8) = v;
+  }
+  for (int i = ahead; i < kKVStages - 1; ++i) load_stage(i);
   __syncthreads();                                                 // qtile is written
 
   uint32_t qa[Q_IN_REGS ? HD / 16 : 1][4];
@@ -156,11 +185,18 @@ attn_decode_kernel(DecodeParams p) {
 #pragma unroll
   for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
+  // Where the 16-byte chunks of a key divide a warp, load_kv_tiles gives warp w exactly the keys
+  // it works on (16 w .. 16 w + 15 of every tile): the warps then need no barrier in the key loop
+  // and drift apart, each hiding the others' latencies.
+  constexpr bool kWarpPrivate = (32 % (HD / 8)) == 0;
+  auto round_barrier = [&]() {
+    if constexpr (kWarpPrivate) __syncwarp(); else __syncthreads();
+  };
   for (int i = 0; i < n_tiles; ++i) {
     const int t0 = t_first + i * kKeyTile;
     load_stage(i + kKVStages - 1);                                 // its slot was freed by the barrier that
     cp_async_wait<kKVStages - 1>();                                // ended round i - 1; tile i has landed
-    __syncthreads();
+    round_barrier();
     const int kb = t0 + warp * 16;                                 // this warp's 16 keys
     if (kb < end && kb + 16 > begin) {
       const bf16* kt = kbuf + (i % kKVStages) * kKeyTile * LD + warp * 16 * LD;
@@ -194,10 +230,11 @@ attn_decode_kernel(DecodeParams p) {
       softmax_step<HD>(s, m, l, o, pa);
       pv_16x16<HD>(o, pa, vt, lane);
     }
-    __syncthreads();                                               // the buffer is loaded again next round
+    round_barrier();                                               // the buffer is loaded again next round
   }
 
   cp_async_wait<0>();
+  __syncthreads();                                                 // the tiles give way to the merge buffers
   // ---- merge the four warps (each saw different keys) through shared memory
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -452,9 +489,7 @@ attn_prefill_kernel(PrefillParams p) {
 }
 
 template <int HD, int kKVStages> size_t decode_smem() {
-  const size_t tiles = size_t(16 + 2 * kKVStages * kKeyTile) * (HD + 8) * sizeof(bf16);
-  const size_t merge = size_t(16) * (HD + 8) * sizeof(bf16) + (size_t(5) * 16 * HD + 2 * 4 * 16 + 32) * sizeof(float);
-  return tiles > merge ? tiles : merge;
+  return decode_core_smem<HD, kKVStages>() + kTabMax * sizeof(int);
 }
 template <int HD> size_t prefill_smem() { return size_t(64 + 4 * kKeyTile) * (HD + 8) * sizeof(bf16); }
 
@@ -474,11 +509,30 @@ int launch_decode_staged(const DecodeParams& p, int seqs, cudaStream_t s) {
   return pdl_launch(kernel, grid, dim3(kAttnThreads), smem, s, p);
 }
 
+// Blocks of the three-stage decode kernel that the device holds at once (0 if it cannot say).
+template <int HD>
+int decode_resident_blocks(int sm_count) {
+  static int per_sm = -1;
+  if (per_sm < 0) {
+    auto kernel = attn_decode_kernel<HD, 3>;
+    const size_t smem = decode_smem<HD, 3>();
+    int n = 0;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) n = 0;
+    else if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kAttnThreads, smem) != cudaSuccess) n = 0;
+    per_sm = n;
+  }
+  return per_sm * sm_count;
+}
+
+// Three stages of keys in flight per block while all blocks are resident at once; a larger grid
+// takes the two-stage kernel, of which more blocks fit an SM (a second wave of blocks costs more
+// than the shallower pipeline).
 template <int HD>
 int launch_decode(const DecodeParams& p, int seqs, int sm_count, cudaStream_t s) {
   const int G = p.nh / p.nkv;
   const long long blocks = (long long)p.num_parts * p.nkv * ((G + 15) / 16) * seqs;
-  if (blocks >= 4LL * sm_count) return launch_decode_staged<HD, 2>(p, seqs, s);
+  if (blocks > decode_resident_blocks<HD>(sm_count)) return launch_decode_staged<HD, 2>(p, seqs, s);
   return launch_decode_staged<HD, 3>(p, seqs, s);
 }
 
@@ -514,6 +568,18 @@ KVCM_API int kvcm_attention_fast_supports(int hd) {
 // Floats of scratch the decode kernel needs for `seqs` requests split into `num_parts`.
 KVCM_API long long kvcm_attention_decode_scratch_floats(int seqs, int nh, int hd, int num_parts) {
   return num_parts <= 1 ? 0 : (long long)seqs * nh * num_parts * (hd + 2);
+}
+
+// Blocks of the decode kernel (partitions x KV heads x tiles of 16 query heads x requests) that
+// run at once with three stages of keys in flight; the caller sizes the partitions by it.
+KVCM_API int kvcm_attention_decode_resident_blocks(int hd) {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+#define X(N) if (hd == N) return decode_resident_blocks<N>(sms);
+  KVCM_FOR_HEAD_DIMS(X)
+#undef X
+  return 0;
 }
 
 // Most partitions that one cluster merges; with more the caller must give scratch.

@@ -19,6 +19,10 @@
 //    still runs; X (which the predecessor wrote) is staged after the wait.
 //  * Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host
 //    reads (kvcm_stream_error), lets copies in flight land and leaves.
+//  * Where every block has one tile only and K is long (the feed-forward's down projection), X is
+//    not staged in shared memory at all: no element of X is used twice by a block then, so the
+//    consumers read their pieces of X from L2 straight into registers, one stage ahead, and the
+//    ring gets the whole of shared memory (the block's entire tile of W is in flight at once).
 // The k index inside a 32-wide block is permuted identically for both operands (thread t of a
 // quad owns k = 8t..8t+7), which makes every shared-memory read of W and X a 16-byte vector.
 // The reference calls cuBLAS here (src/model/llama.cpp:45-52).
@@ -56,7 +60,7 @@ struct StreamParams {
   const bf16* W; int N, K, ldw;
   const bf16* X; int ldx, M;
   void* Y; int ldy;
-  int stages;                                          // ring depth (2..kMaxStages)
+  int stages;                                          // ring depth (1..kMaxStages)
   int chunk;                                           // k elements per stage (a multiple of kChunkUnit)
   // rows of tile t: first 8 = (t / pair_blocks) * group_stride + 8 * (t % pair_blocks) + r,
   //                 last 8 = those + pair_offset
@@ -123,7 +127,7 @@ __device__ __forceinline__ void cp_async_wait_dyn(int n) {       // wait until a
   }
 }
 
-template <int MT, typename OutT, int EPI>
+template <int MT, typename OutT, int EPI, bool XDIRECT>
 __global__ void __launch_bounds__(kStreamThreads)
 gemm_stream_kernel(StreamParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -132,7 +136,7 @@ gemm_stream_kernel(StreamParams p) {
   const int kChunk = p.chunk;
   const int kRowBytes = kChunk * 2 + kRowPad, kStageBytes = 16 * kRowBytes;
   const int Kc = (p.K + kChunk - 1) / kChunk;                 // stages per tile
-  const int Kp = Kc * kChunk + kXPad;                         // padded row of the staged X
+  const int Kp = XDIRECT ? 0 : Kc * kChunk + kXPad;            // padded row of the staged X
   const int kStages = p.stages;
   unsigned char* ring = smem_raw;                             // [stages][16][kRowBytes]
   bf16* xs = reinterpret_cast<bf16*>(ring + kStages * kStageBytes);          // [MB][Kp]
@@ -209,18 +213,34 @@ gemm_stream_kernel(StreamParams p) {
   // ---- consumers.  X is staged k-chunk by k-chunk (one copy group each, zero fill beyond M and
   // K), so the first tile can start on chunk 0 while the later chunks are still arriving.
   const int chunk_vecs = kChunk / 8;
-  for (int kc = 0; kc < Kc; ++kc) {
-    for (int c = tid; c < MB * chunk_vecs; c += kConsumerThreads) {
-      const int m = c / chunk_vecs, ch = kc * chunk_vecs + (c - m * chunk_vecs);
-      const bool live = m < p.M && ch * 8 < p.K;
-      const bf16* src = live ? p.X + size_t(m) * p.ldx + ch * 8 : p.X;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s32(xs + m * Kp + ch * 8)), "l"(src), "r"(live ? 16 : 0));
+  if constexpr (!XDIRECT) {
+    for (int kc = 0; kc < Kc; ++kc) {
+      for (int c = tid; c < MB * chunk_vecs; c += kConsumerThreads) {
+        const int m = c / chunk_vecs, ch = kc * chunk_vecs + (c - m * chunk_vecs);
+        const bool live = m < p.M && ch * 8 < p.K;
+        const bf16* src = live ? p.X + size_t(m) * p.ldx + ch * 8 : p.X;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s32(xs + m * Kp + ch * 8)), "l"(src), "r"(live ? 16 : 0));
+      }
+      asm volatile("cp.async.commit_group;\n" ::);
     }
-    asm volatile("cp.async.commit_group;\n" ::);
   }
 
   const int g = lane >> 2, t4 = lane & 3;
   const int kPerWarp = kChunk / kStreamConsumers;              // k columns of a stage per warp (a multiple of 32)
+  // XDIRECT: this thread's pieces of X for one stage (kXBlocks k-blocks of 32), zero beyond M and K.
+  constexpr int kXBlocks = kChunkShort / kStreamConsumers / 32;
+  uint4 xcur[XDIRECT ? MT : 1][XDIRECT ? kXBlocks : 1], xnext[XDIRECT ? MT : 1][XDIRECT ? kXBlocks : 1];
+  auto fetch_x = [&](uint4 (&dst)[XDIRECT ? MT : 1][XDIRECT ? kXBlocks : 1], int kc) {
+#pragma unroll
+    for (int j = 0; j < (XDIRECT ? MT : 1); ++j)
+#pragma unroll
+      for (int kb = 0; kb < (XDIRECT ? kXBlocks : 1); ++kb) {
+        const int m = 8 * j + g, k = kc * kChunk + warp * kPerWarp + kb * 32 + 8 * t4;
+        dst[j][kb] = (kc < Kc && m < p.M && k < p.K) ? __ldcg(reinterpret_cast<const uint4*>(p.X + size_t(m) * p.ldx + k))
+                                                      : make_uint4(0u, 0u, 0u, 0u);
+      }
+  };
+  if constexpr (XDIRECT) fetch_x(xcur, 0);
   int i = 0;
   for (int tl = 0; tl < my_tiles; ++tl) {
     const int tile = blockIdx.x + tl * gridDim.x;
@@ -228,7 +248,9 @@ gemm_stream_kernel(StreamParams p) {
 #pragma unroll
     for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     for (int kc = 0; kc < Kc; ++kc, ++i) {
-      if (tl == 0) {                                           // this chunk of X has landed for everyone?
+      if constexpr (XDIRECT) {
+        fetch_x(xnext, kc + 1);                                // in flight while this stage is worked on
+      } else if (tl == 0) {                                    // this chunk of X has landed for everyone?
         cp_async_wait_dyn(min(Kc - 1 - kc, 7));
         asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
       }
@@ -240,8 +262,10 @@ gemm_stream_kernel(StreamParams p) {
       if (abort_flag) continue;
       const unsigned char* st = ring + s * kStageBytes;
       const int kbase = kc * kChunk + warp * kPerWarp;          // this warp's share of the stage
+      // (XDIRECT: the chunk is the short one, so the trip count is a constant and xcur stays in registers)
+      const int n_kb = XDIRECT ? kXBlocks : kPerWarp / 32;
 #pragma unroll 4
-      for (int kb = 0; kb < kPerWarp / 32; ++kb) {
+      for (int kb = 0; kb < n_kb; ++kb) {
         if (kbase + kb * 32 >= p.K) break;                     // warp-uniform: the whole k-block lies beyond K
         const int koff = warp * kPerWarp + kb * 32 + 8 * t4;
         uint4 va = *reinterpret_cast<const uint4*>(st + g * kRowBytes + koff * 2);
@@ -252,13 +276,21 @@ gemm_stream_kernel(StreamParams p) {
         }
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
-          const uint4 x = *reinterpret_cast<const uint4*>(xs + (8 * j + g) * Kp + kbase + kb * 32 + 8 * t4);
+          uint4 x;
+          if constexpr (XDIRECT) x = xcur[j][kb];
+          else x = *reinterpret_cast<const uint4*>(xs + (8 * j + g) * Kp + kbase + kb * 32 + 8 * t4);
           mma_stream(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
           mma_stream(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);                   // this warp is done with the slot
+      if constexpr (XDIRECT) {
+#pragma unroll
+        for (int j = 0; j < MT; ++j)
+#pragma unroll
+          for (int kb = 0; kb < kXBlocks; ++kb) xcur[j][kb] = xnext[j][kb];
+      }
     }
     // acc[j]: c0,c1 = (W row g, batch 8j + 2t, +1); c2,c3 = (W row g+8, same batch rows)
     float* mine = red + ((tl & 1) * kStreamConsumers + warp) * 16 * MB;
@@ -328,6 +360,7 @@ gemm_stream_kernel(StreamParams p) {
 }
 
 constexpr size_t kStreamSmemLimit = 224 * 1024;        // of the 227 KB a block may have
+constexpr size_t kStreamSmemHalf = 112 * 1024;         // two such blocks share an SM
 
 // Shared memory of a launch with `stages` ring slots of `chunk` k elements.
 static size_t stream_smem(int MT, int K, int chunk, int stages) {
@@ -345,20 +378,28 @@ static int stream_chunk(int MT, int K) {
   return stream_smem(MT, K, piece, 2) <= kStreamSmemLimit ? piece : 0;
 }
 
-template <int MT, typename OutT, int EPI>
-int launch_stream(StreamParams p, int sm_count, cudaStream_t s) {
-  auto kernel = gemm_stream_kernel<MT, OutT, EPI>;
+// X straight from L2 (no staging): every block has one tile and K is longer than a whole-row stage.
+static bool stream_direct(int N, int K, int sm_count) { return (N + 15) / 16 <= sm_count && K > kChunkLong; }
+
+template <int MT, typename OutT, int EPI, bool XDIRECT>
+int launch_stream_as(StreamParams p, int sm_count, cudaStream_t s) {
+  auto kernel = gemm_stream_kernel<MT, OutT, EPI, XDIRECT>;
   const int tiles = (p.N + 15) / 16;
-  const int chunk = stream_chunk(MT, p.K);
+  const int chunk = XDIRECT ? kChunkShort : stream_chunk(MT, p.K);
   if (chunk == 0) return KVCM_ERR_UNSUPPORTED;
   const int Kc = (p.K + chunk - 1) / chunk;
   // One block per SM; the ring takes what shared memory is left after X, but never more slots than
   // the block has stages to load.
-  const int blocks = min(tiles, sm_count);
+  const int xk = XDIRECT ? 0 : p.K;                               // k extent of the staged X
+  int blocks = min(tiles, sm_count);
+  // A few tiles more than SMs, and a whole tile of W beside X takes less than half of an SM's
+  // shared memory: one block per tile, two to an SM, instead of a second round for a few blocks.
+  // (Small blocks also find room while the predecessor kernel is still running.)
+  if (tiles > sm_count && tiles <= 2 * sm_count && stream_smem(MT, xk, chunk, Kc) <= kStreamSmemHalf) blocks = tiles;
   const int need = ((tiles + blocks - 1) / blocks) * Kc;
   int stages = kMaxStages;
-  while (stages > 2 && (stream_smem(MT, p.K, chunk, stages) > kStreamSmemLimit || stages > need)) --stages;
-  const size_t smem = stream_smem(MT, p.K, chunk, stages);
+  while (stages > 1 && (stream_smem(MT, xk, chunk, stages) > kStreamSmemLimit || stages > need)) --stages;
+  const size_t smem = stream_smem(MT, xk, chunk, stages);
   if (smem > kStreamSmemLimit) return KVCM_ERR_UNSUPPORTED;
   p.chunk = chunk;
   static size_t configured = 0;
@@ -371,20 +412,42 @@ int launch_stream(StreamParams p, int sm_count, cudaStream_t s) {
   return pdl_launch(kernel, dim3(blocks), dim3(kStreamThreads), smem, s, p);
 }
 
+template <int MT, typename OutT, int EPI>
+int launch_stream(StreamParams p, int sm_count, cudaStream_t s) {
+  if constexpr (EPI == kStore) {
+    if (stream_direct(p.N, p.K, sm_count)) return launch_stream_as<MT, OutT, EPI, true>(p, sm_count, s);
+  }
+  return launch_stream_as<MT, OutT, EPI, false>(p, sm_count, s);
+}
+
 }  // namespace kvcm
 
 using namespace kvcm;
 
-KVCM_API int kvcm_gemm_stream_supports(int M, int N, int K) {
-  if (M < 1 || M > 16 || N < 1 || K < 8 || (K % 8)) return 0;
-  return stream_chunk(M <= 8 ? 1 : 2, K) != 0;
+static int current_sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0)
+      count = 148;
+  }
+  return count;
 }
+
+static bool stream_ok(int M, int N, int K, int sm_count, bool plain_store) {
+  if (M < 1 || M > 16 || N < 1 || K < 8 || (K % 8)) return false;
+  return stream_chunk(M <= 8 ? 1 : 2, K) != 0 || (plain_store && stream_direct(N, K, sm_count));
+}
+
+// The plain product (no fused epilogue) of these sizes on the current device.
+KVCM_API int kvcm_gemm_stream_supports(int M, int N, int K) { return stream_ok(M, N, K, current_sm_count(), true); }
 
 // out_f32: 0 = bfloat16 result, 1 = float result.
 KVCM_API int kvcm_gemm_stream_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int ldx,
                                    int ldw, int ldy, int out_f32, int sm_count, void* stream) {
   if (M == 0 || N == 0) return 0;
-  if (!kvcm_gemm_stream_supports(M, N, K) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
+  if (!stream_ok(M, N, K, sm_count, true) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
   StreamParams p = {};
   p.W = (const bf16*)W; p.N = N; p.K = K; p.ldw = ldw; p.X = (const bf16*)X; p.ldx = ldx; p.M = M;
@@ -404,7 +467,7 @@ KVCM_API int kvcm_qkv_rope_cache_bf16(const void* X, const void* Wqkv, void* Yq,
                                       int hd, int block_size, int sm_count, void* stream) {
   const int N = (nh + 2 * nkv) * hd;
   if (M == 0) return 0;
-  if ((hd % 16) || !kvcm_gemm_stream_supports(M, N, K) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
+  if ((hd % 16) || !stream_ok(M, N, K, sm_count, false) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(Wqkv) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
   StreamParams p = {};
   p.W = (const bf16*)Wqkv; p.N = N; p.K = K; p.ldw = ldw; p.X = (const bf16*)X; p.ldx = ldx; p.M = M;
@@ -422,7 +485,7 @@ KVCM_API int kvcm_qkv_rope_cache_bf16(const void* X, const void* Wqkv, void* Yq,
 KVCM_API int kvcm_gate_up_silu_bf16(const void* X, const void* W, void* Y, int M, int I, int K, int ldx, int ldw,
                                     int ldy, int sm_count, void* stream) {
   if (M == 0) return 0;
-  if ((I % 8) || !kvcm_gemm_stream_supports(M, 2 * I, K) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
+  if ((I % 8) || !stream_ok(M, 2 * I, K, sm_count, false) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
   StreamParams p = {};
   p.W = (const bf16*)W; p.N = 2 * I; p.K = K; p.ldw = ldw; p.X = (const bf16*)X; p.ldx = ldx; p.M = M;
@@ -431,6 +494,9 @@ KVCM_API int kvcm_gate_up_silu_bf16(const void* X, const void* W, void* Y, int M
   cudaStream_t s = (cudaStream_t)stream;
   return M <= 8 ? launch_stream<1, bf16, kSiluMul>(p, sm_count, s) : launch_stream<2, bf16, kSiluMul>(p, sm_count, s);
 }
+
+// The fused products (rotary/cache and gate/up epilogues) of these sizes: X is always staged there.
+KVCM_API int kvcm_gemm_stream_fused_supports(int M, int N, int K) { return stream_ok(M, N, K, current_sm_count(), false); }
 
 // Reads and clears the error word of the streaming kernels (0 = no bounded wait ever ran out).
 KVCM_API int kvcm_stream_error(void) {

@@ -266,22 +266,40 @@ KEY_TILE = 64
 CLUSTER_PARTS = 8           # kvcm_attention_decode_cluster_parts()
 
 
-def decode_partitions(seqs: int, nh: int, nkv: int, max_ctx: int, device, version: str = "auto"):
+_RESIDENT = {}
+
+
+def _decode_resident_blocks(hd: int, device) -> int:
+    key = (int(hd), torch.device(device))
+    if key not in _RESIDENT:
+        n = int(_lib().kvcm_attention_decode_resident_blocks(int(hd)))
+        _RESIDENT[key] = n if n > 0 else 3 * sm_count(device)
+    return _RESIDENT[key]
+
+
+def decode_partitions(seqs: int, nh: int, nkv: int, hd: int, max_ctx: int, device, version: str = "auto",
+                      force_parts: int = 0):
     """How the decode kernel splits the context: (keys per partition, number of partitions).
 
-    'v1': the whole context in one block per (request, KV head).  'v2'/'auto': enough partitions
-    that the grid has about five blocks per SM, each at least 128 keys long (the reference fixes
-    512 keys per partition, src/cuda/paged_attention.cu:22; a B200 has 148 SMs to fill and a short
-    partition is one memory latency instead of several)."""
+    'v1': the whole context in one block per (request, KV head).  'v2'/'auto': as many partitions
+    as keep the whole grid resident at once (a second wave of blocks costs more than longer
+    partitions), each at least 128 keys long, and no more than the 8 that merge inside one cluster
+    unless that would leave partitions of more than 512 keys.  Measured on a B200 over batches
+    1..128 and contexts 512..8192.  (The reference fixes 512 keys per partition,
+    src/cuda/paged_attention.cu:22.)  ``force_parts`` > 0 asks for that many partitions (tuning
+    and tests)."""
     max_ctx = max(int(max_ctx), 1)
     whole = (max_ctx + KEY_TILE - 1) // KEY_TILE * KEY_TILE
     if version == "v1":
         return whole, 1
     G = nh // nkv
     blocks = max(1, seqs * nkv * ((G + 15) // 16))
-    want = max(1, (5 * sm_count(device) + blocks - 1) // blocks)
-    most = max(1, max_ctx // 128)
-    parts = max(1, min(want, most))
+    if force_parts > 0:
+        parts = min(int(force_parts), max(1, whole // KEY_TILE))
+    else:
+        parts = max(1, min(_decode_resident_blocks(hd, device) // blocks, max_ctx // 128))
+        if parts > CLUSTER_PARTS:
+            parts = max(CLUSTER_PARTS, min(parts, (max_ctx + 511) // 512))
     size = ((max_ctx + parts - 1) // parts + KEY_TILE - 1) // KEY_TILE * KEY_TILE
     parts = (max_ctx + size - 1) // size
     return size, parts
@@ -298,8 +316,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
     _need(q.stride(1) == 1 and out.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous(),
           "attention_decode: layout")
     _need(q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0, "attention_decode: q rows must be 16-byte aligned")
-    size, parts = decode_partitions(S, nh, nkv, ctx.max_decode_ctx, q.device,
-                                    ctx.options.get("attn_version", "auto"))
+    size, parts = decode_partitions(S, nh, nkv, hd, ctx.max_decode_ctx, q.device,
+                                    ctx.options.get("attn_version", "auto"), int(ctx.options.get("attn_parts", 0)))
     scratch = None
     # Up to 8 partitions merge inside a thread-block cluster; more go through scratch memory
     # and a merge kernel ('attn_merge': 'kernel' forces that path).
@@ -410,7 +428,7 @@ def qkv_rope_cache(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, po
 
 
 def qkv_rope_cache_supported(M: int, K: int, nh: int, nkv: int, hd: int) -> bool:
-    return hd % 16 == 0 and stream_gemm_supported(M, (nh + 2 * nkv) * hd, K)
+    return hd % 16 == 0 and bool(_lib().kvcm_gemm_stream_fused_supports(int(M), int((nh + 2 * nkv) * hd), int(K)))
 
 
 def gate_up_silu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> None:
@@ -427,7 +445,7 @@ def gate_up_silu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) ->
 
 
 def gate_up_silu_supported(M: int, I: int, K: int) -> bool:
-    return I % 8 == 0 and stream_gemm_supported(M, 2 * I, K)
+    return I % 8 == 0 and bool(_lib().kvcm_gemm_stream_fused_supports(int(M), int(2 * I), int(K)))
 
 
 def tcgen05_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:

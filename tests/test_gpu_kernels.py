@@ -176,7 +176,10 @@ def test_skinny_gemm(M, N, Kd, kw):
 
 @pytest.mark.parametrize("M,N,Kd", [(1, 2048, 2048), (8, 2560, 2048), (3, 100, 176), (16, 37, 2048), (8, 37, 5632),
                                     (9, 515, 96), (8, 32003, 256), (5, 16, 8), (8, 11264, 2048),
-                                    (7, 4096, 1032), (2, 33, 520)])
+                                    (7, 4096, 1032), (2, 33, 520),
+                                    # one tile per block and a long K: X comes straight from L2
+                                    (8, 2048, 5632), (16, 2048, 5632), (11, 2368, 2120), (1, 520, 4104),
+                                    (8, 2400, 5632)])                # a tile too many for that: X is staged
 def test_streaming_gemm(M, N, Kd):
     lib = K()
     assert lib.stream_gemm_supported(M, N, Kd)
