@@ -1,0 +1,437 @@
+// Causal prefill attention over the paged cache on the fifth-generation tensor cores (head_dim 64).
+//
+// One block per (128 query rows of a request, query head).  Per tile of 128 keys:
+//     S = Q K^T  (tcgen05.mma, M 128 x N 128, accumulator in tensor memory)
+//     softmax    (four warps, one thread per query row: tcgen05.ld of its row of S, running max
+//                 and sum, probabilities rounded to bfloat16 into a 128-byte swizzled tile of
+//                 shared memory)
+//     O_j = P V  (tcgen05.mma with V as the MN-major operand, straight from the page layout)
+//     o = o * 2^(m_old - m_new) + O_j   (in the softmax threads' registers)
+// Roles: warp 0 brings Q once and K/V pages (cp.async.bulk.tensor, one box per page, 128-byte
+// swizzle) into a two-stage ring; one thread of warp 1 issues the products and commits them to
+// mbarriers; warps 2-5 do the softmax and the output.  Two blocks share an SM (112 KB of shared
+// memory and 256 columns of tensor memory each), so one block's products run under the other's
+// softmax.  Keys come from the pages, the portion's own included (they were written before), so a
+// portion may start anywhere in a request; masks: key <= row's position, key > position - window,
+// key < end of the request's computed part.  Scores are scaled in float; softmax by exp2 with
+// log2(e) folded into the scale; sums stay float.
+// Every wait on an mbarrier is bounded; when one runs out the block records it
+// (kvcm_attention_tcgen05_error), stops waiting, frees its tensor memory and leaves.
+// The reference has no prefill kernel (it runs prompt rows through its decode kernel,
+// docs/design.md:113-114).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "pdl.cuh"
+
+namespace kvcm {
+
+constexpr int kFaThreads = 192;
+constexpr int kFaRows = 128;                 // query rows per block
+constexpr int kFaKeys = 128;                 // keys per tile
+constexpr int kFaHD = 64;                    // head_dim
+constexpr int kFaStages = 2;
+constexpr int kFaTileBytes = 128 * 128;      // [128 rows][64 bf16]
+constexpr int kFaTmemCols = 256;             // S: columns 0..127, O_j: columns 128..191
+constexpr unsigned long long kFaWaitLimitNs = 1000000000ull;
+
+__device__ int g_fa_error = 0;
+
+struct PrefillTcParams {
+  bf16* out; int out_stride;
+  const int* block_tables; int max_blocks;
+  const int* tile_seq; const int* tile_q0;                 // tiles of 64 rows; a block takes an even one and its successor
+  const int* seq_q_start; const int* seq_q_len; const int* seq_ctx_len;
+  int nh, nkv, block_size, window;
+  float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t fa_s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ unsigned long long fa_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity) {
+  unsigned long long start = 0;
+  for (unsigned spin = 0;; ++spin) {
+    uint32_t done;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(fa_s32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+    if ((spin & 63) == 63) {
+      const unsigned long long now = fa_now();
+      if (start == 0) start = now;
+      else if (now - start > kFaWaitLimitNs) return false;
+    }
+  }
+}
+__device__ __forceinline__ void fa_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(fa_s32(bar)) : "memory");
+}
+__device__ __forceinline__ void fa_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(fa_s32(bar)) : "memory");
+}
+__device__ __forceinline__ float fa_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Shared-memory descriptor of a tile whose rows are 128 bytes, 128-byte swizzled, 8-row groups 1024
+// bytes apart (the same numbers describe a K-major tile [rows][64 k] and an MN-major tile
+// [k][64 n], whose 8-k groups are 1024 bytes apart); descriptor version 1, swizzle code 2.
+__device__ __forceinline__ uint64_t fa_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr & 0x3FFFF) >> 4);
+  d |= uint64_t(1) << 16;
+  d |= uint64_t(1024 >> 4) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(2) << 61;
+  return d;
+}
+// float accumulator, bfloat16 operands, A K-major; B K-major or MN-major (bit 16).
+__host__ __device__ constexpr uint32_t fa_idesc(int M, int N, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | (uint32_t(N >> 3) << 17) |
+         (uint32_t(M >> 4) << 24);
+}
+__device__ __forceinline__ void fa_mma(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void fa_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+__global__ void __launch_bounds__(kFaThreads)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* q_s = smem_raw;                               // [128 rows][64]            16 KB
+  unsigned char* k_s = q_s + kFaTileBytes;                     // [stages][128 keys][64]    32 KB
+  unsigned char* v_s = k_s + kFaStages * kFaTileBytes;         // [stages][128 keys][64]    32 KB
+  unsigned char* p_s = v_s + kFaStages * kFaTileBytes;         // [2 k-blocks][128 rows][64 keys] 32 KB
+  __shared__ __align__(8) uint64_t q_full, kv_full[kFaStages], kv_empty[kFaStages], s_full, p_full, o_full;
+  __shared__ uint32_t tmem_base;
+  __shared__ volatile int abort_flag;
+
+  pdl_launch_dependents();
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int q0 = p.tile_q0[tile];
+  if (q0 & (kFaRows - 1)) return;                              // the odd tile of 64 rows belongs to the block before
+  if (fa_s32(smem_raw) & 1023) {                               // the swizzled tiles need this alignment
+    if (threadIdx.x == 0) atomicExch(&g_fa_error, (7 << 16) | int(blockIdx.x & 0xffff));
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = p.tile_seq[tile];
+  const int q_start = p.seq_q_start[seq], q_len = p.seq_q_len[seq], ctx = p.seq_ctx_len[seq];
+  const int rows_here = min(kFaRows, q_len - q0);
+  const int pos0 = ctx - q_len + q0;                           // position of the block's first row
+  const int hi = pos0 + rows_here;                             // keys [lo, hi) matter to the block
+  const int lo = (p.window > 0 && pos0 + 1 > p.window) ? pos0 + 1 - p.window : 0;
+  const int j0 = lo / kFaKeys, n_tiles = (hi - 1) / kFaKeys - j0 + 1;
+  const int kvh = head / (p.nh / p.nkv);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    auto init = [](uint64_t* b, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(fa_s32(b)), "r"(count)); };
+    init(&q_full, 1);
+    for (int s = 0; s < kFaStages; ++s) { init(&kv_full[s], 1); init(&kv_empty[s], 1); }
+    init(&s_full, 1);
+    init(&p_full, 4);                                          // the four softmax warps
+    init(&o_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  // The K/V ring starts as zeros: pages beyond the request's last key are not loaded, and what a
+  // slot holds there is multiplied by probability zero, so it must be finite.
+  for (int i = threadIdx.x; i < 2 * kFaStages * kFaTileBytes / 16; i += kFaThreads)
+    reinterpret_cast<uint4*>(k_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(fa_s32(&tmem_base)), "r"(kFaTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem = tmem_base;
+  pdl_wait();                                                  // q and this step's keys come from kernels before
+
+  auto fail = [&](int code) {
+    atomicExch(&g_fa_error, (code << 16) | int(blockIdx.x & 0xffff));
+    abort_flag = 1;
+  };
+
+  if (warp == 0) {
+    // ---- producer: Q once, then a tile of K and V per round, one box per page
+    if (lane == 0) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(fa_s32(&q_full)), "r"(kFaTileBytes) : "memory");
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                   ::"r"(fa_s32(q_s)), "l"(&map_q), "r"(fa_s32(&q_full)), "r"(head * kFaHD), "r"(q_start + q0) : "memory");
+    }
+    const int* table = p.block_tables + size_t(seq) * p.max_blocks;
+    const int B = p.block_size, per_tile = kFaKeys / B;
+    for (int n = 0; n < n_tiles; ++n) {
+      const int s = n % kFaStages;
+      int ok = 1;
+      if (lane == 0) {
+        ok = !abort_flag && fa_wait(&kv_empty[s], ((n / kFaStages) & 1) ^ 1);
+        if (!ok && !abort_flag) fail(1);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const int key0 = (j0 + n) * kFaKeys;
+      const int count = min(per_tile, (hi - key0 + B - 1) / B);                 // pages that hold keys below hi
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
+                     ::"r"(fa_s32(&kv_full[s])), "r"(2 * count * B * 128) : "memory");
+      __syncwarp();
+      for (int i = lane; i < count; i += 32) {
+        const int page = table[key0 / B + i];
+        const int row = (page * p.nkv + kvh) * B;
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                     ::"r"(fa_s32(k_s + s * kFaTileBytes + i * B * 128)), "l"(&map_k), "r"(fa_s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                     ::"r"(fa_s32(v_s + s * kFaTileBytes + i * B * 128)), "l"(&map_v), "r"(fa_s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
+      }
+    }
+  } else if (warp == 1) {
+    // ---- one thread issues the products: S_0; then for every tile O_n = P_n V_n and S_(n+1)
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = fa_idesc(kFaRows, kFaKeys, false);
+      constexpr uint32_t idesc_o = fa_idesc(kFaRows, kFaHD, true);
+      const uint64_t dq = fa_desc(fa_s32(q_s));
+      auto issue_s = [&](int n) {                              // S = Q K_n^T, four steps of 16 along head_dim
+        const uint64_t dk = fa_desc(fa_s32(k_s + (n % kFaStages) * kFaTileBytes));
+#pragma unroll
+        for (int j = 0; j < kFaHD / 16; ++j) fa_mma(tmem, dq + uint64_t(2 * j), dk + uint64_t(2 * j), idesc_s, j > 0);
+        fa_commit(&s_full);
+      };
+      bool ok = fa_wait(&q_full, 0);
+      if (!ok) fail(2);
+      if (ok && !(ok = fa_wait(&kv_full[0], 0))) fail(3);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        issue_s(0);
+      }
+      for (int n = 0; ok && n < n_tiles && !abort_flag; ++n) {
+        if (!fa_wait(&p_full, n & 1)) { fail(4); break; }     // P_n is in shared memory, S is free again
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t v_addr = fa_s32(v_s + (n % kFaStages) * kFaTileBytes);
+#pragma unroll
+        for (int j = 0; j < kFaKeys / 16; ++j) {               // 16 keys per step: 32 bytes along a row of P,
+          const uint64_t dp = fa_desc(fa_s32(p_s + (j / 4) * kFaTileBytes)) + uint64_t(2 * (j % 4));
+          const uint64_t dv = fa_desc(v_addr + j * 16 * 128);  // 16 rows (2,048 bytes) down the tile of V
+          fa_mma(tmem + 128, dp, dv, idesc_o, j > 0);
+        }
+        fa_commit(&o_full);
+        fa_commit(&kv_empty[n % kFaStages]);                   // K_n and V_n have been read
+        if (n + 1 < n_tiles) {
+          if (!fa_wait(&kv_full[(n + 1) % kFaStages], ((n + 1) / kFaStages) & 1)) { fail(3); break; }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          issue_s(n + 1);
+        }
+      }
+    }
+  } else {
+    // ---- softmax and output: this thread owns query row `r` (lane r of tensor memory)
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int pos = pos0 + r;                                  // rows beyond rows_here compute and store nothing
+    const int first = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;   // first key of the row
+    const uint32_t lane_addr = tmem + (uint32_t(quarter * 32) << 16);
+    float m = -INFINITY, l = 0.f;
+    float o[kFaHD];
+#pragma unroll
+    for (int d = 0; d < kFaHD; ++d) o[d] = 0.f;
+    for (int n = 0; n < n_tiles; ++n) {
+      if (abort_flag || !fa_wait(&s_full, n & 1)) {
+        if (!abort_flag && lane == 0) fail(5);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int key0 = (j0 + n) * kFaKeys;
+      // the keys of this tile that the row may see: [a, b) relative to the tile
+      const int a = max(first, lo) - key0, b = min(pos + 1, hi) - key0;
+      uint32_t v[32];
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kFaKeys / 32; ++c) {
+        fa_ld32(lane_addr + uint32_t(c * 32), v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int t = c * 32 + i;
+          mx = (t >= a && t < b) ? fmaxf(mx, __uint_as_float(v[i])) : mx;
+        }
+      }
+      const float m_new = fmaxf(m, mx * p.scale_log2);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // a row that has seen no key yet
+      const float alpha = fa_exp2(m - m_use);
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < kFaKeys / 32; ++c) {
+        fa_ld32(lane_addr + uint32_t(c * 32), v);
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int t = c * 32 + i;
+          const float p0 = (t >= a && t < b) ? fa_exp2(__uint_as_float(v[i]) * p.scale_log2 - m_use) : 0.f;
+          const float p1 = (t + 1 >= a && t + 1 < b) ? fa_exp2(__uint_as_float(v[i + 1]) * p.scale_log2 - m_use) : 0.f;
+          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          // the sum runs over the rounded probabilities, the numbers the product with V sees
+          sum += __bfloat162float(h.x) + __bfloat162float(h.y);
+          packed[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        // 32 keys = four 16-byte chunks of row r in k-block c / 2; chunk index XOR (r % 8): the 128-byte swizzle
+        unsigned char* rowp = p_s + (c / 2) * kFaTileBytes + r * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
+          *reinterpret_cast<uint4*>(rowp + chunk * 16) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      // P is complete and S has been read: the products may go on
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) fa_arrive(&p_full);
+      if (abort_flag || !fa_wait(&o_full, n & 1)) {
+        if (!abort_flag && lane == 0) fail(6);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < kFaHD / 32; ++c) {
+        fa_ld32(lane_addr + uint32_t(128 + c * 32), v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(v[i]);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    }
+    if (!abort_flag && r < rows_here) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = p.out + size_t(q_start + q0 + r) * p.out_stride + size_t(head) * kFaHD;
+#pragma unroll
+      for (int c = 0; c < kFaHD / 8; ++c) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
+        *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(h);
+      }
+    }
+  }
+  // every role ends here; after a wait that ran out, copies still in flight get time to land
+  // before the shared memory is given up; tensor memory goes back
+  if (abort_flag) {
+    const unsigned long long t0 = fa_now();
+    while (fa_now() - t0 < 100000ull) {}
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kFaTmemCols));
+  }
+}
+
+// ---------------------------------------------------------------------------------- host
+
+typedef CUresult (*FaEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static FaEncodeTiledFn fa_encode_tiled() {
+  static FaEncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<FaEncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Row-major [rows, cols] bfloat16 matrix, `ld` elements between rows; boxes of [box_rows x 64 columns].
+static int fa_map(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows) {
+  FaEncodeTiledFn enc = fa_encode_tiled();
+  if (!enc) return KVCM_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
+  cuuint32_t box[2] = {64u, cuuint32_t(box_rows)};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 20000 + int(r);
+}
+
+}  // namespace kvcm
+
+using namespace kvcm;
+
+// 1 if the tcgen05 prefill kernel takes these sizes: head_dim 64, pages of 8..128 keys that divide 128.
+KVCM_API int kvcm_attention_tcgen05_supports(int hd, int block_size) {
+  return hd == kFaHD && block_size >= 8 && block_size <= kFaKeys && (kFaKeys % block_size) == 0 && (block_size % 8) == 0;
+}
+
+// q: [total_rows, >= nh*64] rows `q_stride` elements apart (16-byte aligned, q_stride % 8 == 0); the
+// tiles are those of 64 query rows that the batch builder makes (tile_seq, tile_q0); the cache is
+// [num_pages, nkv, block_size, 64].
+KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, int total_rows, void* out, int out_stride,
+                                                 const void* k_cache, const void* v_cache, int num_pages,
+                                                 const int* block_tables, int max_blocks, const int* tile_seq,
+                                                 const int* tile_q0, const int* seq_q_start, const int* seq_q_len,
+                                                 const int* seq_ctx_len, int tiles, int nh, int nkv, int hd,
+                                                 int block_size, float scale, int window, void* stream) {
+  if (tiles == 0) return 0;
+  if (!kvcm_attention_tcgen05_supports(hd, block_size) || nkv <= 0 || nh % nkv) return KVCM_ERR_UNSUPPORTED;
+  if ((q_stride % 8) || (out_stride % 8) || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) ||
+      (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15))
+    return KVCM_ERR_UNSUPPORTED;
+  CUtensorMap mq, mk, mv;
+  int rc = fa_map(&mq, q, total_rows, nh * hd, q_stride, kFaRows);
+  if (rc) return rc;
+  const long long cache_rows = (long long)num_pages * nkv * block_size;
+  rc = fa_map(&mk, k_cache, cache_rows, hd, hd, block_size);
+  if (rc) return rc;
+  rc = fa_map(&mv, v_cache, cache_rows, hd, hd, block_size);
+  if (rc) return rc;
+  PrefillTcParams p;
+  p.out = (bf16*)out; p.out_stride = out_stride;
+  p.block_tables = block_tables; p.max_blocks = max_blocks; p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
+  p.seq_q_start = seq_q_start; p.seq_q_len = seq_q_len; p.seq_ctx_len = seq_ctx_len;
+  p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const size_t smem = size_t(1 + 2 * kFaStages + 2) * kFaTileBytes;     // two blocks fit an SM exactly
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  return pdl_launch(attn_prefill_tc_kernel, dim3(tiles, nh), dim3(kFaThreads), smem, (cudaStream_t)stream, mq, mk, mv, p);
+}
+
+// Reads and clears the error word of the kernel (0 = no bounded wait ever ran out); else
+// (code << 16) | block: 1 producer waited for a free stage, 2 Q, 3 K/V, 4 P, 5 S, 6 O; 7 shared memory
+// not aligned to 1,024 bytes.
+KVCM_API int kvcm_attention_tcgen05_error(void) {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_fa_error, sizeof v) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_fa_error, &zero, sizeof zero);
+  return v;
+}

@@ -338,7 +338,9 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       block_tables: torch.Tensor, ctx, nh: int, nkv: int, hd: int, scale: float,
                       window: int = 0) -> None:
-    """Rows of portions longer than one token; q/out are the step's full row arrays."""
+    """Rows of portions longer than one token; q/out are the step's full row arrays.
+    ``ctx.options['attn_prefill']``: 'tcgen05' | 'mma' force a kernel; 'auto' takes the tcgen05
+    kernel where it supports the sizes (head_dim 64, pages of 8..128 keys dividing 128)."""
     _cuda(q, out, k_cache, v_cache, block_tables)
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16,
           "attention_prefill: bfloat16 only")
@@ -346,13 +348,33 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
           "attention_prefill: layout")
     _need(q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0, "attention_prefill: q rows must be 16-byte aligned")
     _need(ctx.tile_rows == 64, "attention_prefill: the batch must be tiled in 64 query rows")
+    mode = ctx.options.get("attn_prefill", "auto")
+    B = k_cache.shape[2]
+    if mode != "mma" and (mode == "tcgen05" or prefill_tcgen05_supported(hd, B)):
+        _need(out.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0, "attention_prefill: out rows must be 16-byte aligned")
+        rc = _lib().kvcm_attention_prefill_tcgen05_bf16(
+            _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_cache), _p(v_cache), k_cache.shape[0],
+            _p(block_tables), block_tables.shape[1], _p(ctx.tile_seq), _p(ctx.tile_q0), _p(ctx.seq_q_start),
+            _p(ctx.seq_q_len), _p(ctx.seq_ctx_len), ctx.prefill_tiles, nh, nkv, hd, B, ctypes.c_float(scale),
+            int(window), _stream())
+        _check(rc, "attention_prefill_tcgen05", f"(hd={hd}, nh={nh}, nkv={nkv}, block={B})")
+        return
     rc = _lib().kvcm_attention_prefill_bf16(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), _p(block_tables),
         block_tables.shape[1], _p(ctx.tile_seq), _p(ctx.tile_q0), _p(ctx.seq_q_start), _p(ctx.seq_q_len),
-        _p(ctx.seq_ctx_len), ctx.prefill_tiles, nh, nkv, hd, k_cache.shape[2], ctypes.c_float(scale),
+        _p(ctx.seq_ctx_len), ctx.prefill_tiles, nh, nkv, hd, B, ctypes.c_float(scale),
         int(window), _stream())
     _check(rc, "attention_prefill", f"(hd={hd}, nh={nh}, nkv={nkv})")
 
+
+def prefill_tcgen05_supported(hd: int, block_size: int) -> bool:
+    return bool(_lib().kvcm_attention_tcgen05_supports(int(hd), int(block_size)))
+
+
+def attention_tcgen05_error() -> int:
+    """Error word of the tcgen05 attention kernel: 0, or (code << 16 | block) of a bounded wait that
+    ran out.  Reading clears it.  Synchronises the device."""
+    return int(_lib().kvcm_attention_tcgen05_error())
 
 def skinny_gemm_supported(M: int, N: int, K: int) -> bool:
     """True when the weight-streaming kernel takes this product (M <= 16, K a multiple of 8, X

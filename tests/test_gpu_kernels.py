@@ -434,6 +434,62 @@ def test_attention_kernels_on_a_mixed_batch(nh, nkv, hd, B, window):
             assert torch.equal(got["v2"], got["v2 merge kernel"])
 
 
+@pytest.mark.parametrize("B", [8, 16, 32, 64, 128])
+@pytest.mark.parametrize("window", [0, 150])
+def test_prefill_attention_on_tcgen05(B, window):
+    """The tcgen05 prefill kernel (head_dim 64) against float64 and against the mma.sync kernel:
+    portions that start anywhere, end anywhere, are shorter than a tile, span several key tiles,
+    with pages of every supported size, beside decode rows."""
+    nh, nkv, hd = 8, 2, 64
+    lib = K()
+    assert lib.prefill_tcgen05_supported(hd, B) and not lib.prefill_tcgen05_supported(128, B)
+    seq_lens = [300, 129, 128, 640, 70, 2, 513, 1]
+    q_lens = [300, 129, 1, 131, 64, 2, 257, 1]
+    scale = 1.0 / math.sqrt(hd)
+    case = paged_case(seq_lens, q_lens, nh, nkv, hd, B, "bfloat16", seed=B + window)
+    ref = reference_attention(case, nh, nkv, hd, scale, window)
+    got = {}
+    for mode in ("tcgen05", "mma"):
+        case["ctx"].options = {"attn_prefill": mode}
+        out = torch.zeros(case["ctx"].rows, nh * hd, dtype=torch.bfloat16, device=DEV)
+        lib.paged_attention(case["q"], out, case["kc"], case["vc"], case["tables"], case["ctx"], nh, nkv, hd,
+                            scale, window)
+        assert lib.attention_tcgen05_error() == 0
+        close(out, ref, "bfloat16", f"prefill {mode}, pages of {B}")
+        got[mode] = out
+    close(got["tcgen05"], got["mma"].double(), "bfloat16", "tcgen05 against mma.sync")
+
+
+def test_prefill_attention_on_tcgen05_finds_one_far_key():
+    """Each query row points at one key of its own; a kernel that misses a key (a page's or a
+    tile's edge, the first or the last key of the row) returns an average instead of that value."""
+    nh, nkv, hd, B, n = 2, 1, 64, 16, 700
+    lib = K()
+    case = paged_case([n], [n], nh, nkv, hd, B, "bfloat16", seed=5)
+    kd, vd = case["dense"][0]
+    q = case["q_cpu"].clone()
+    g = torch.Generator().manual_seed(9)
+    needles = [int(torch.randint(0, i + 1, (1,), generator=g)) for i in range(n)]
+    for i in (0, 127, 128, 129, 255, 256, 511, 512, 699):
+        needles[i] = i                                              # the row's own (last) key
+    for i in (130, 300, 600):
+        needles[i] = 0                                              # the first key
+    for i in range(n):
+        unit = kd[needles[i], 0].float() / kd[needles[i], 0].float().norm()
+        for h in range(nh):
+            q[i, h * hd:(h + 1) * hd] = (6.0 * math.sqrt(hd) * unit).to(torch.bfloat16)
+    case["q"], case["q_cpu"] = q.to(DEV), q
+    ref = reference_attention(case, nh, nkv, hd, 1 / math.sqrt(hd), 0)
+    want = torch.stack([torch.cat([vd[needles[i], 0]] * nh) for i in range(n)]).double()
+    assert (ref - want).abs().max() < 0.1                           # the reference itself picks the needles
+    case["ctx"].options = {"attn_prefill": "tcgen05"}
+    out = torch.zeros(n, nh * hd, dtype=torch.bfloat16, device=DEV)
+    lib.paged_attention(case["q"], out, case["kc"], case["vc"], case["tables"], case["ctx"], nh, nkv, hd,
+                        1 / math.sqrt(hd), 0)
+    assert lib.attention_tcgen05_error() == 0
+    close(out, ref, "bfloat16", "needles")
+
+
 def test_decode_attention_long_contexts_and_many_partitions():
     nh, nkv, hd, B = 32, 4, 64, 16
     seq_lens = [2047, 2048, 1, 4097, 513]
