@@ -5,8 +5,13 @@
 //     softmax    (four warps, one thread per query row: tcgen05.ld of its row of S, running max
 //                 and sum, probabilities rounded to bfloat16 into a 128-byte swizzled tile of
 //                 shared memory)
-//     O_j = P V  (tcgen05.mma with V as the MN-major operand, straight from the page layout)
-//     o = o * 2^(m_old - m_new) + O_j   (in the softmax threads' registers)
+//     O += P V   (tcgen05.mma with V as the MN-major operand, straight from the page layout; O stays
+//                 in tensor memory for the whole block)
+// The running maximum a row scales by is only renewed when the true maximum has grown by more than
+// 2^8 since (probabilities then stay below 2^8, harmless in float and bfloat16); only then is the
+// row's O in tensor memory rescaled (tcgen05.ld, multiply, tcgen05.st), which after the first
+// tiles hardly ever happens.  The same reference maximum enters the row's sum, so the quotient at
+// the end is exact softmax.
 // Roles: warp 0 brings Q once and K/V pages (cp.async.bulk.tensor, one box per page, 128-byte
 // swizzle) into a two-stage ring; one thread of warp 1 issues the products and commits them to
 // mbarriers; warps 2-5 do the softmax and the output.  Two blocks share an SM (112 KB of shared
@@ -14,7 +19,8 @@
 // softmax.  Keys come from the pages, the portion's own included (they were written before), so a
 // portion may start anywhere in a request; masks: key <= row's position, key > position - window,
 // key < end of the request's computed part.  Scores are scaled in float; softmax by exp2 with
-// log2(e) folded into the scale; sums stay float.
+// log2(e) folded into the scale; probabilities are rounded to bfloat16 for the product with V,
+// their sums stay float.
 // Every wait on an mbarrier is bounded; when one runs out the block records it
 // (kvcm_attention_tcgen05_error), stops waiting, frees its tensor memory and leaves.
 // The reference has no prefill kernel (it runs prompt rows through its decode kernel,
@@ -32,7 +38,8 @@ constexpr int kFaKeys = 128;                 // keys per tile
 constexpr int kFaHD = 64;                    // head_dim
 constexpr int kFaStages = 2;
 constexpr int kFaTileBytes = 128 * 128;      // [128 rows][64 bf16]
-constexpr int kFaTmemCols = 256;             // S: columns 0..127, O_j: columns 128..191
+constexpr int kFaTmemCols = 256;             // S: columns 0..127, O: columns 128..191
+constexpr float kFaRescaleStep = 8.f;        // in log2 units
 constexpr unsigned long long kFaWaitLimitNs = 1000000000ull;
 
 __device__ int g_fa_error = 0;
@@ -109,10 +116,21 @@ __device__ __forceinline__ void fa_ld32(uint32_t taddr, uint32_t (&v)[32]) {
                  "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
                  "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
                : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
+__device__ __forceinline__ void fa_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void fa_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+               "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                 "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                 "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                 "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+               : "memory");
+}
+__device__ __forceinline__ void fa_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
-__global__ void __launch_bounds__(kFaThreads)
+__global__ void __launch_bounds__(kFaThreads, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -125,11 +143,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __shared__ volatile int abort_flag;
 
   pdl_launch_dependents();
-  const int tile = blockIdx.x, head = blockIdx.y;
+  // Later tiles of a prompt see more keys: the blocks are ordered with the heads fastest and the
+  // last tiles first, so all long blocks start at once and the short ones fill the tail.
+  const int tile = int(gridDim.y) - 1 - int(blockIdx.y), head = blockIdx.x;
   const int q0 = p.tile_q0[tile];
   if (q0 & (kFaRows - 1)) return;                              // the odd tile of 64 rows belongs to the block before
   if (fa_s32(smem_raw) & 1023) {                               // the swizzled tiles need this alignment
-    if (threadIdx.x == 0) atomicExch(&g_fa_error, (7 << 16) | int(blockIdx.x & 0xffff));
+    if (threadIdx.x == 0) atomicExch(&g_fa_error, (7 << 16) | int(blockIdx.y & 0xffff));
     return;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -168,7 +188,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   pdl_wait();                                                  // q and this step's keys come from kernels before
 
   auto fail = [&](int code) {
-    atomicExch(&g_fa_error, (code << 16) | int(blockIdx.x & 0xffff));
+    atomicExch(&g_fa_error, (code << 16) | int(blockIdx.y & 0xffff));
     abort_flag = 1;
   };
 
@@ -232,14 +252,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int j = 0; j < kFaKeys / 16; ++j) {               // 16 keys per step: 32 bytes along a row of P,
           const uint64_t dp = fa_desc(fa_s32(p_s + (j / 4) * kFaTileBytes)) + uint64_t(2 * (j % 4));
           const uint64_t dv = fa_desc(v_addr + j * 16 * 128);  // 16 rows (2,048 bytes) down the tile of V
-          fa_mma(tmem + 128, dp, dv, idesc_o, j > 0);
+          fa_mma(tmem + 128, dp, dv, idesc_o, (n > 0 || j > 0) ? 1u : 0u);
         }
-        fa_commit(&o_full);
         fa_commit(&kv_empty[n % kFaStages]);                   // K_n and V_n have been read
         if (n + 1 < n_tiles) {
           if (!fa_wait(&kv_full[(n + 1) % kFaStages], ((n + 1) / kFaStages) & 1)) { fail(3); break; }
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          issue_s(n + 1);
+          issue_s(n + 1);        // its commit also covers O += P_n V_n: whoever sees S_(n+1) may touch O
+        } else {
+          fa_commit(&o_full);                                  // the last product: O is final
         }
       }
     }
@@ -250,12 +271,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int pos = pos0 + r;                                  // rows beyond rows_here compute and store nothing
     const int first = (p.window > 0 && pos + 1 > p.window) ? pos + 1 - p.window : 0;   // first key of the row
     const uint32_t lane_addr = tmem + (uint32_t(quarter * 32) << 16);
-    float m = -INFINITY, l = 0.f;
-    float o[kFaHD];
-#pragma unroll
-    for (int d = 0; d < kFaHD; ++d) o[d] = 0.f;
+    float m = -INFINITY, l = 0.f;                              // m: the maximum the row currently scales by
     for (int n = 0; n < n_tiles; ++n) {
-      if (abort_flag || !fa_wait(&s_full, n & 1)) {
+      const bool got_s = !abort_flag && fa_wait(&s_full, n & 1);
+      if (!__all_sync(0xffffffffu, got_s)) {                     // the warp stays together whatever a lane saw
         if (!abort_flag && lane == 0) fail(5);
         break;
       }
@@ -263,34 +282,76 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int key0 = (j0 + n) * kFaKeys;
       // the keys of this tile that the row may see: [a, b) relative to the tile
       const int a = max(first, lo) - key0, b = min(pos + 1, hi) - key0;
-      uint32_t v[32];
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kFaKeys / 32; ++c) {
-        fa_ld32(lane_addr + uint32_t(c * 32), v);
+      // Masks are needed only where the tile touches the diagonal, the window's edge or the end of
+      // the keys; for every other tile (most of a long prompt) there is none.
+      const bool full = key0 + kFaKeys - 1 <= pos0 && (p.window <= 0 || key0 >= pos0 + kFaRows - p.window);
+      uint32_t v[4][32];                                       // the row's 128 scores, one wait for all loads
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int t = c * 32 + i;
-          mx = (t >= a && t < b) ? fmaxf(mx, __uint_as_float(v[i])) : mx;
-        }
+      for (int c = 0; c < 4; ++c) fa_ld32(lane_addr + uint32_t(c * 32), v[c]);
+      fa_ld_wait();
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (full) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx[c] = fmaxf(mx[c], __uint_as_float(v[c][i]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int t = c * 32 + i;
+            mx[c] = (t >= a && t < b) ? fmaxf(mx[c], __uint_as_float(v[c][i])) : mx[c];
+          }
       }
-      const float m_new = fmaxf(m, mx * p.scale_log2);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // a row that has seen no key yet
-      const float alpha = fa_exp2(m - m_use);
-      float sum = 0.f;
+      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+      // renew the reference maximum only when it is far behind; O and l then move with it
+      float alpha = 1.f;
+      bool rescale = false;
+      if (m == -INFINITY) {
+        m = m_tile;                                            // nothing was added yet: no rescaling
+      } else if (m_tile > m + kFaRescaleStep) {
+        alpha = fa_exp2(m - m_tile);
+        m = m_tile;
+        rescale = true;
+      }
+      if (__any_sync(0xffffffffu, rescale)) {                  // (S_n is here, so O += P_(n-1) V_(n-1) is complete)
+        uint32_t ov[32];
 #pragma unroll 1
-      for (int c = 0; c < kFaKeys / 32; ++c) {
-        fa_ld32(lane_addr + uint32_t(c * 32), v);
-        uint32_t packed[16];
+        for (int c = 0; c < kFaHD / 32; ++c) {
+          fa_ld32(lane_addr + uint32_t(128 + c * 32), ov);
+          fa_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int t = c * 32 + i;
-          const float p0 = (t >= a && t < b) ? fa_exp2(__uint_as_float(v[i]) * p.scale_log2 - m_use) : 0.f;
-          const float p1 = (t + 1 >= a && t + 1 < b) ? fa_exp2(__uint_as_float(v[i + 1]) * p.scale_log2 - m_use) : 0.f;
-          const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          // the sum runs over the rounded probabilities, the numbers the product with V sees
-          sum += __bfloat162float(h.x) + __bfloat162float(h.y);
-          packed[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          fa_st32(lane_addr + uint32_t(128 + c * 32), ov);
+        }
+        fa_st_wait();
+        l *= alpha;
+      }
+      const float m_use = (m == -INFINITY) ? 0.f : m;           // a row that has seen no key yet
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t packed[16];
+        if (full) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fa_exp2(__uint_as_float(v[c][i]) * p.scale_log2 - m_use);
+            const float p1 = fa_exp2(__uint_as_float(v[c][i + 1]) * p.scale_log2 - m_use);
+            sum[c] += p0 + p1;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            packed[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int t = c * 32 + i;
+            const float p0 = (t >= a && t < b) ? fa_exp2(__uint_as_float(v[c][i]) * p.scale_log2 - m_use) : 0.f;
+            const float p1 = (t + 1 >= a && t + 1 < b) ? fa_exp2(__uint_as_float(v[c][i + 1]) * p.scale_log2 - m_use) : 0.f;
+            sum[c] += p0 + p1;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            packed[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
+          }
         }
         // 32 keys = four 16-byte chunks of row r in k-block c / 2; chunk index XOR (r % 8): the 128-byte swizzle
         unsigned char* rowp = p_s + (c / 2) * kFaTileBytes + r * 128;
@@ -301,37 +362,38 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
         }
       }
-      l = l * alpha + sum;
-      m = m_new;
-      // P is complete and S has been read: the products may go on
+      l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+      // P is complete, S has been read and O is rescaled: the products may go on
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) fa_arrive(&p_full);
-      if (abort_flag || !fa_wait(&o_full, n & 1)) {
-        if (!abort_flag && lane == 0) fail(6);
-        break;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-      for (int c = 0; c < kFaHD / 32; ++c) {
-        fa_ld32(lane_addr + uint32_t(128 + c * 32), v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(v[i]);
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     }
-    if (!abort_flag && r < rows_here) {
+    const bool got_o = !abort_flag && fa_wait(&o_full, 0);
+    const bool all_o = __all_sync(0xffffffffu, got_o);
+    if (!all_o && !abort_flag && lane == 0) fail(6);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    if (all_o) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = p.out + size_t(q_start + q0 + r) * p.out_stride + size_t(head) * kFaHD;
+#pragma unroll 1
+      for (int c = 0; c < kFaHD / 32; ++c) {
+        uint32_t ov[32];
+        fa_ld32(lane_addr + uint32_t(128 + c * 32), ov);       // (all lanes of the warp take part in the load)
+        fa_ld_wait();
+        if (r < rows_here) {
 #pragma unroll
-      for (int c = 0; c < kFaHD / 8; ++c) {
-        __nv_bfloat162 h[4];
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 h[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
-        *reinterpret_cast<uint4*>(dst + c * 8) = *reinterpret_cast<const uint4*>(h);
+            for (int i = 0; i < 4; ++i)
+              h[i] = __floats2bfloat162_rn(__uint_as_float(ov[e * 8 + 2 * i]) * inv, __uint_as_float(ov[e * 8 + 2 * i + 1]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + e * 8) = *reinterpret_cast<const uint4*>(h);
+          }
+        }
       }
     }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   }
   // every role ends here; after a wait that ran out, copies still in flight get time to land
   // before the shared memory is given up; tensor memory goes back
@@ -423,7 +485,7 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  return pdl_launch(attn_prefill_tc_kernel, dim3(tiles, nh), dim3(kFaThreads), smem, (cudaStream_t)stream, mq, mk, mv, p);
+  return pdl_launch(attn_prefill_tc_kernel, dim3(nh, tiles), dim3(kFaThreads), smem, (cudaStream_t)stream, mq, mk, mv, p);
 }
 
 // Reads and clears the error word of the kernel (0 = no bounded wait ever ran out); else
