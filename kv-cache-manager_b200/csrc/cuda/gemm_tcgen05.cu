@@ -51,6 +51,17 @@ __device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+               : "r"(taddr));
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
 // start address / 16, stride between 8-row groups = 1024 bytes, descriptor version 1, swizzle code 2.
 __device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
@@ -68,10 +79,16 @@ __host__ __device__ constexpr uint32_t tc_idesc(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
 }
 
-template <typename OutT, int BN>
+// GATED: W is [2N, K], gate rows first; a tile's 256 accumulator columns are 128 gate columns
+// n0..n0+127 and the 128 up columns N+n0.., and the epilogue stores
+// y[m][n] = round(round(silu(round(gate))) * round(up)) -- the roundings of the separate product
+// and activation kernels -- so the [M, 2N] intermediate never goes to memory.
+template <typename OutT, int BN, bool GATED>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     OutT* __restrict__ Y, int M, int N, int K, int ldy) {
+  static_assert(!GATED || BN == 256, "the gated tile is 128 + 128 columns");
+  constexpr int BNOUT = GATED ? BN / 2 : BN;                   // output columns per tile
   constexpr int kBBytes = BN * kTcBK * 2;
   constexpr int kStageBytes = kTcABytes + kBBytes;
   constexpr int kStages = BN == 256 ? 4 : 6;
@@ -82,7 +99,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __shared__ volatile int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tiles = (M + kTcBM - 1) / kTcBM, n_tiles = (N + BN - 1) / BN;
+  const int m_tiles = (M + kTcBM - 1) / kTcBM, n_tiles = (N + BNOUT - 1) / BNOUT;
   const int tiles = m_tiles * n_tiles;
   const int nk = (K + kTcBK - 1) / kTcBK;
   // Persistent block: tiles blockIdx.x, + gridDim.x, ...  Neighbouring blocks take different column
@@ -116,7 +133,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       int it = 0;                                  // running stage counter across tiles
       for (int tl = 0; tl < my_tiles && !abort_flag; ++tl) {
         const int t = int(blockIdx.x) + tl * int(gridDim.x);
-        const int m0 = (t / n_tiles) * kTcBM, n0 = (t % n_tiles) * BN;
+        const int m0 = (t / n_tiles) * kTcBM, n0 = (t % n_tiles) * BNOUT;
         for (int k = 0; k < nk; ++k, ++it) {
           const int s = it % kStages;
           if (!tc_wait(&empty[s], ((it / kStages) & 1) ^ 1)) {
@@ -131,6 +148,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                        ::"r"(tc_s32(a)), "l"(&map_x), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(m0) : "memory");
           asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                        ::"r"(tc_s32(b)), "l"(&map_w), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(n0) : "memory");
+          if constexpr (GATED)                                   // the map's box is 128 rows: the up rows follow
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                         ::"r"(tc_s32(b + kBBytes / 2)), "l"(&map_w), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(N + n0) : "memory");
         }
       }
     }
@@ -180,7 +200,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     for (int tl = 0; tl < my_tiles; ++tl) {
       const int acc = tl & 1;
       const int t = int(blockIdx.x) + tl * int(gridDim.x);
-      const int m0 = (t / n_tiles) * kTcBM, n0 = (t % n_tiles) * BN;
+      const int m0 = (t / n_tiles) * kTcBM, n0 = (t % n_tiles) * BNOUT;
       if (abort_flag || !tc_wait(&acc_full[acc], (tl >> 1) & 1)) {
         if (!abort_flag && lane == 0) atomicExch(&g_tcgen05_error, (3 << 16) | int(blockIdx.x & 0xffff));
         abort_flag = 1;
@@ -188,6 +208,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const int row = m0 + quarter * 32 + lane;
+      if constexpr (GATED) {
+#pragma unroll 1
+        for (int c = 0; c < BNOUT / 32; ++c) {
+          uint32_t g[32], u[32];
+          const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(acc * BN + c * 32);
+          tc_ld32(taddr, g);
+          tc_ld32(taddr + BNOUT, u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+          if (row < M) {
+            const int col0 = n0 + c * 32;
+            bf16* dst = reinterpret_cast<bf16*>(Y) + size_t(row) * ldy + col0;
+            __nv_bfloat162 h2[16];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float xa = Store<bf16>::round(__uint_as_float(g[i])), xb = Store<bf16>::round(__uint_as_float(u[i]));
+              const float sl = Store<bf16>::round(xa / (1.f + expf(-xa)));
+              const bf16 y = __float2bfloat16_rn(sl * xb);
+              if (i & 1) h2[i / 2].y = y; else h2[i / 2].x = y;
+            }
+            if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(h2)[i];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < N) dst[i] = (i & 1) ? h2[i / 2].y : h2[i / 2].x;
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
@@ -223,6 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
               if (col0 + i < N) stf(dst + i, __uint_as_float(v[i]));
           }
         }
+      }
       }
       // this warp has read its lanes of the accumulator: hand it back to the tensor core
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -271,15 +322,16 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
   return r == CUDA_SUCCESS ? 0 : 20000 + int(r);
 }
 
-template <typename OutT, int BN>
+// GATED: N is the number of output columns; W has 2N rows.
+template <typename OutT, int BN, bool GATED = false>
 int launch_tcgen05_bn(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
                       int sm_count, cudaStream_t s) {
   CUtensorMap mx, mw;
   int rc = make_map(&mx, X, M, K, ldx, kTcBM);
   if (rc) return rc;
-  rc = make_map(&mw, W, N, K, ldw, BN);
+  rc = GATED ? make_map(&mw, W, 2 * N, K, ldw, BN / 2) : make_map(&mw, W, N, K, ldw, BN);
   if (rc) return rc;
-  auto kernel = gemm_tcgen05_kernel<OutT, BN>;
+  auto kernel = gemm_tcgen05_kernel<OutT, BN, GATED>;
   const size_t smem = size_t(BN == 256 ? 4 : 6) * (kTcABytes + BN * kTcBK * 2) + 1024;
   static bool configured = false;
   if (!configured) {
@@ -287,7 +339,8 @@ int launch_tcgen05_bn(const void* X, const void* W, void* Y, int M, int N, int K
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  const int tiles = ((N + BN - 1) / BN) * ((M + kTcBM - 1) / kTcBM);
+  constexpr int BNOUT = GATED ? BN / 2 : BN;
+  const int tiles = ((N + BNOUT - 1) / BNOUT) * ((M + kTcBM - 1) / kTcBM);
   kernel<<<dim3(tiles < sm_count ? tiles : sm_count), kTcThreads, smem, s>>>(mx, mw, reinterpret_cast<OutT*>(Y), M, N, K, ldy);
   return KVCM_LAUNCH_RESULT();
 }
@@ -313,6 +366,20 @@ int launch_tcgen05(const void* X, const void* W, void* Y, int M, int N, int K, i
 }  // namespace kvcm
 
 using namespace kvcm;
+
+// act[M, I] = silu(X Wg^T) * (X Wu^T) with Wg, Wu the halves of W [2I, K] (gate rows first), the
+// roundings of the separate product and activation kernels; bfloat16.
+KVCM_API int kvcm_gate_up_silu_tcgen05_bf16(const void* X, const void* W, void* Y, int M, int I, int K, int ldx,
+                                            int ldw, int ldy, void* stream) {
+  if (M == 0 || I == 0) return 0;
+  if (M < 1 || I < 1 || K < 8 || (K % 8) || (ldx % 8) || (ldw % 8)) return KVCM_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return KVCM_ERR_UNSUPPORTED;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  return launch_tcgen05_bn<bf16, 256, true>(X, W, Y, M, I, K, ldx, ldw, ldy, sms, (cudaStream_t)stream);
+}
 
 KVCM_API int kvcm_gemm_tcgen05_supports(int M, int N, int K, int ldx, int ldw) {
   return M >= 1 && N >= 1 && K >= 8 && (K % 8) == 0 && (ldx % 8) == 0 && (ldw % 8) == 0;

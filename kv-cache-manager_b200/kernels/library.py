@@ -470,6 +470,21 @@ def gate_up_silu_supported(M: int, I: int, K: int) -> bool:
     return I % 8 == 0 and bool(_lib().kvcm_gemm_stream_fused_supports(int(M), int(2 * I), int(K)))
 
 
+def gate_up_silu_tcgen05(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> None:
+    """act[M, I] = silu(x Wg^T) * (x Wu^T) for many rows: the tcgen05 product with the activation in
+    its epilogue (the roundings of the separate product and activation kernels); the [M, 2I]
+    intermediate never goes to memory."""
+    _cuda(x, w_gate_up, act)
+    M, K = x.shape
+    I = act.shape[1]
+    _need(w_gate_up.shape == (2 * I, K) and act.shape[0] == M, "gate_up_silu_tcgen05: shapes")
+    _need(x.dtype == w_gate_up.dtype == act.dtype == torch.bfloat16, "gate_up_silu_tcgen05: bfloat16 only")
+    _need(x.stride(1) == 1 and w_gate_up.stride(1) == 1 and act.stride(1) == 1, "gate_up_silu_tcgen05: rows must be dense")
+    rc = _lib().kvcm_gate_up_silu_tcgen05_bf16(_p(x), _p(w_gate_up), _p(act), M, I, K, x.stride(0),
+                                               w_gate_up.stride(0), act.stride(0), _stream())
+    _check(rc, "gate_up_silu_tcgen05", f"(M={M}, I={I}, K={K})")
+
+
 def tcgen05_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     """True when the tcgen05 kernel takes this product (bfloat16, K and row strides multiples of 8)."""
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1

@@ -65,7 +65,7 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, options:
         return y
     # Many rows (prefill): this engine's tcgen05 kernel where its 128 x 256 tiles fill the SMs well
     # (within about a tenth of the library's speed there), or always with options['gemm'] == 'tcgen05'.
-    if mode == "tcgen05" or (mode == "auto" and M >= TCGEN05_MIN_ROWS and _tiles_fill_well(M, N, x.device)):
+    if mode == "tcgen05" or (mode == "auto" and M >= TCGEN05_MIN_ROWS and tiles_fill_well(M, N, x.device)):
         if K.tcgen05_gemm_supported(x, w):
             y = torch.empty((M, N), dtype=out_dtype, device=x.device)
             K.gemm_tcgen05(x, w, y)
@@ -75,7 +75,7 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, options:
     return torch.mm(x, w.t(), out_dtype=out_dtype)
 
 
-def _tiles_fill_well(M: int, N: int, device) -> bool:
+def tiles_fill_well(M: int, N: int, device) -> bool:
     sms = K.sm_count(device)
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
     rounds = (tiles + sms - 1) // sms

@@ -8,7 +8,7 @@ import torch
 
 from ..kernels import library as K
 from .base import FEED_FORWARDS, FeedForward, StepContext
-from .linear import Linear
+from .linear import Linear, TCGEN05_MIN_ROWS, tiles_fill_well
 
 
 @FEED_FORWARDS.register("gated_mlp")
@@ -30,6 +30,11 @@ class GatedMLP(FeedForward):
                 and ctx.options.get("fuse", True) and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
                 and K.gate_up_silu_supported(h.shape[0], self.intermediate, h.shape[1])):
             K.gate_up_silu(h, w, act)
+        elif (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ctx.options.get("fuse", True)
+              and ctx.options.get("gemm", "auto") in ("auto", "tcgen05") and h.shape[0] >= TCGEN05_MIN_ROWS
+              and tiles_fill_well(h.shape[0], 2 * self.intermediate, h.device) and K.tcgen05_gemm_supported(h, w)):
+            # Many rows (prefill): the tcgen05 product applies the activation in its epilogue.
+            K.gate_up_silu_tcgen05(h, w, act)
         else:
             K.silu_mul(self.gate_up.forward(h, ctx), act)
         return self.down.forward(act, ctx)

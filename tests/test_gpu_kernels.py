@@ -250,6 +250,25 @@ def test_fused_gate_up_silu_gives_the_bits_of_the_separate_kernels(M, H, I):
     close(a2, gg[:, :I] * torch.sigmoid(gg[:, :I]) * gg[:, I:], "bfloat16", "against float64")
 
 
+@pytest.mark.parametrize("M,H,I", [(2048, 2048, 5632), (300, 96, 1000), (129, 64, 24), (640, 256, 128)])
+def test_tcgen05_gate_up_with_the_activation_in_its_epilogue(M, H, I):
+    """Bit for bit the tcgen05 product followed by the activation kernel, and close to float64."""
+    lib = K()
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
+    lib.gemm_tcgen05(x, w, gu)
+    a1 = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    lib.silu_mul(gu, a1)
+    a2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lib.gate_up_silu_tcgen05(x, w, a2)
+    assert lib.tcgen05_error() == 0
+    assert torch.equal(a1, a2)
+    gg = (x.double().cpu() @ w.double().cpu().T)
+    close(a2, gg[:, :I] * torch.sigmoid(gg[:, :I]) * gg[:, I:], "bfloat16", "against float64")
+
+
 @pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (1, 8, 8), (100, 300, 136), (257, 129, 1000), (2048, 2560, 2048),
                                     (640, 11264, 2048), (300, 2048, 5632), (17, 32003, 96)])
 def test_tcgen05_gemm(M, N, Kd):
