@@ -1,26 +1,27 @@
 // Causal prefill attention over the paged cache on the fifth-generation tensor cores (head_dim 64).
 //
-// One block per (128 query rows of a request, query head).  Per tile of 128 keys:
-//     S = Q K^T  (tcgen05.mma, M 128 x N 128, accumulator in tensor memory)
+// One block per (128 query rows of a request, query head).  Per tile of 64 keys:
+//     S = Q K^T  (tcgen05.mma, M 128 x N 64, accumulator in tensor memory, two buffers)
 //     softmax    (four warps, one thread per query row: tcgen05.ld of its row of S, running max
 //                 and sum, probabilities rounded to bfloat16 into a 128-byte swizzled tile of
-//                 shared memory)
+//                 shared memory, two buffers)
 //     O += P V   (tcgen05.mma with V as the MN-major operand, straight from the page layout; O stays
 //                 in tensor memory for the whole block)
+// The products run one tile ahead of the softmax (S_(n+1) is computed while the softmax works on
+// S_n, O += P_(n-1) V_(n-1) while it writes P_n), so the softmax threads hardly ever wait.
 // The running maximum a row scales by is only renewed when the true maximum has grown by more than
 // 2^8 since (probabilities then stay below 2^8, harmless in float and bfloat16); only then is the
 // row's O in tensor memory rescaled (tcgen05.ld, multiply, tcgen05.st), which after the first
 // tiles hardly ever happens.  The same reference maximum enters the row's sum, so the quotient at
 // the end is exact softmax.
 // Roles: warp 0 brings Q once and K/V pages (cp.async.bulk.tensor, one box per page, 128-byte
-// swizzle) into a two-stage ring; one thread of warp 1 issues the products and commits them to
+// swizzle) into a four-stage ring; one thread of warp 1 issues the products and commits them to
 // mbarriers; warps 2-5 do the softmax and the output.  Two blocks share an SM (112 KB of shared
-// memory and 256 columns of tensor memory each), so one block's products run under the other's
-// softmax.  Keys come from the pages, the portion's own included (they were written before), so a
-// portion may start anywhere in a request; masks: key <= row's position, key > position - window,
-// key < end of the request's computed part.  Scores are scaled in float; softmax by exp2 with
-// log2(e) folded into the scale; probabilities are rounded to bfloat16 for the product with V,
-// their sums stay float.
+// memory and 256 columns of tensor memory each).  Keys come from the pages, the portion's own
+// included (they were written before), so a portion may start anywhere in a request; masks: key <=
+// row's position, key > position - window, key < end of the request's computed part.  Scores are
+// scaled in float; softmax by exp2 with log2(e) folded into the scale; probabilities are rounded
+// to bfloat16 for the product with V, their sums stay float.
 // Every wait on an mbarrier is bounded; when one runs out the block records it
 // (kvcm_attention_tcgen05_error), stops waiting, frees its tensor memory and leaves.
 // The reference has no prefill kernel (it runs prompt rows through its decode kernel,
@@ -34,11 +35,12 @@ namespace kvcm {
 
 constexpr int kFaThreads = 192;
 constexpr int kFaRows = 128;                 // query rows per block
-constexpr int kFaKeys = 128;                 // keys per tile
+constexpr int kFaKeys = 64;                  // keys per tile
 constexpr int kFaHD = 64;                    // head_dim
-constexpr int kFaStages = 2;
-constexpr int kFaTileBytes = 128 * 128;      // [128 rows][64 bf16]
-constexpr int kFaTmemCols = 256;             // S: columns 0..127, O: columns 128..191
+constexpr int kFaStages = 4;                 // K/V tiles in flight
+constexpr int kFaTileBytes = 128 * 128;      // [128 rows][64 bf16]: Q, a buffer of P
+constexpr int kFaKvBytes = kFaKeys * 128;    // [64 keys][64 bf16]: a stage of K or of V
+constexpr int kFaTmemCols = 256;             // S: two buffers, columns 0..63 and 64..127; O: columns 128..191
 constexpr float kFaRescaleStep = 8.f;        // in log2 units
 constexpr unsigned long long kFaWaitLimitNs = 1000000000ull;
 
@@ -134,11 +136,12 @@ __global__ void __launch_bounds__(kFaThreads, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* q_s = smem_raw;                               // [128 rows][64]            16 KB
-  unsigned char* k_s = q_s + kFaTileBytes;                     // [stages][128 keys][64]    32 KB
-  unsigned char* v_s = k_s + kFaStages * kFaTileBytes;         // [stages][128 keys][64]    32 KB
-  unsigned char* p_s = v_s + kFaStages * kFaTileBytes;         // [2 k-blocks][128 rows][64 keys] 32 KB
-  __shared__ __align__(8) uint64_t q_full, kv_full[kFaStages], kv_empty[kFaStages], s_full, p_full, o_full;
+  unsigned char* q_s = smem_raw;                               // [128 rows][64]                 16 KB
+  unsigned char* k_s = q_s + kFaTileBytes;                     // [stages][64 keys][64]          32 KB
+  unsigned char* v_s = k_s + kFaStages * kFaKvBytes;           // [stages][64 keys][64]          32 KB
+  unsigned char* p_s = v_s + kFaStages * kFaKvBytes;           // [2][128 rows][64 keys]         32 KB
+  __shared__ __align__(8) uint64_t q_full, kv_full[kFaStages], kv_empty[kFaStages], s_full[2], s_free[2], p_full[2],
+      p_free[2], o_full;
   __shared__ uint32_t tmem_base;
   __shared__ volatile int abort_flag;
 
@@ -167,14 +170,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     auto init = [](uint64_t* b, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(fa_s32(b)), "r"(count)); };
     init(&q_full, 1);
     for (int s = 0; s < kFaStages; ++s) { init(&kv_full[s], 1); init(&kv_empty[s], 1); }
-    init(&s_full, 1);
-    init(&p_full, 4);                                          // the four softmax warps
+    for (int i = 0; i < 2; ++i) {
+      init(&s_full[i], 1);
+      init(&s_free[i], 4);                                     // the four softmax warps
+      init(&p_full[i], 4);
+      init(&p_free[i], 1);
+    }
     init(&o_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   // The K/V ring starts as zeros: pages beyond the request's last key are not loaded, and what a
   // slot holds there is multiplied by probability zero, so it must be finite.
-  for (int i = threadIdx.x; i < 2 * kFaStages * kFaTileBytes / 16; i += kFaThreads)
+  for (int i = threadIdx.x; i < 2 * kFaStages * kFaKvBytes / 16; i += kFaThreads)
     reinterpret_cast<uint4*>(k_s)[i] = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   if (warp == 1) {
@@ -193,14 +200,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   };
 
   if (warp == 0) {
-    // ---- producer: Q once, then a tile of K and V per round, one box per page
+    // ---- producer: Q once, then a tile of K and V per round, one box per page (or per half page)
     if (lane == 0) {
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(fa_s32(&q_full)), "r"(kFaTileBytes) : "memory");
       asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                    ::"r"(fa_s32(q_s)), "l"(&map_q), "r"(fa_s32(&q_full)), "r"(head * kFaHD), "r"(q_start + q0) : "memory");
     }
     const int* table = p.block_tables + size_t(seq) * p.max_blocks;
-    const int B = p.block_size, per_tile = kFaKeys / B;
+    const int B = p.block_size;
+    const int box = min(B, kFaKeys), per_tile = kFaKeys / box;                 // rows of a box; boxes of a tile
     for (int n = 0; n < n_tiles; ++n) {
       const int s = n % kFaStages;
       int ok = 1;
@@ -211,58 +219,55 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       const int key0 = (j0 + n) * kFaKeys;
-      const int count = min(per_tile, (hi - key0 + B - 1) / B);                 // pages that hold keys below hi
+      const int count = min(per_tile, (hi - key0 + box - 1) / box);             // boxes that hold keys below hi
       if (lane == 0)
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
-                     ::"r"(fa_s32(&kv_full[s])), "r"(2 * count * B * 128) : "memory");
+                     ::"r"(fa_s32(&kv_full[s])), "r"(2 * count * box * 128) : "memory");
       __syncwarp();
       for (int i = lane; i < count; i += 32) {
-        const int page = table[key0 / B + i];
-        const int row = (page * p.nkv + kvh) * B;
+        const int key = key0 + i * box;
+        const int page = table[key / B];
+        const int row = (page * p.nkv + kvh) * B + key % B;
         asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                     ::"r"(fa_s32(k_s + s * kFaTileBytes + i * B * 128)), "l"(&map_k), "r"(fa_s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
+                     ::"r"(fa_s32(k_s + s * kFaKvBytes + i * box * 128)), "l"(&map_k), "r"(fa_s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
         asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                     ::"r"(fa_s32(v_s + s * kFaTileBytes + i * B * 128)), "l"(&map_v), "r"(fa_s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
+                     ::"r"(fa_s32(v_s + s * kFaKvBytes + i * box * 128)), "l"(&map_v), "r"(fa_s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
       }
     }
   } else if (warp == 1) {
-    // ---- one thread issues the products: S_0; then for every tile O_n = P_n V_n and S_(n+1)
+    // ---- one thread issues the products, S one tile ahead of O:  S_0, S_1, O+=P_0 V_0, S_2, O+=P_1 V_1, ...
     if (lane == 0) {
       constexpr uint32_t idesc_s = fa_idesc(kFaRows, kFaKeys, false);
       constexpr uint32_t idesc_o = fa_idesc(kFaRows, kFaHD, true);
       const uint64_t dq = fa_desc(fa_s32(q_s));
-      auto issue_s = [&](int n) {                              // S = Q K_n^T, four steps of 16 along head_dim
-        const uint64_t dk = fa_desc(fa_s32(k_s + (n % kFaStages) * kFaTileBytes));
-#pragma unroll
-        for (int j = 0; j < kFaHD / 16; ++j) fa_mma(tmem, dq + uint64_t(2 * j), dk + uint64_t(2 * j), idesc_s, j > 0);
-        fa_commit(&s_full);
-      };
       bool ok = fa_wait(&q_full, 0);
       if (!ok) fail(2);
-      if (ok && !(ok = fa_wait(&kv_full[0], 0))) fail(3);
-      if (ok) {
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        issue_s(0);
-      }
-      for (int n = 0; ok && n < n_tiles && !abort_flag; ++n) {
-        if (!fa_wait(&p_full, n & 1)) { fail(4); break; }     // P_n is in shared memory, S is free again
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const uint32_t v_addr = fa_s32(v_s + (n % kFaStages) * kFaTileBytes);
-#pragma unroll
-        for (int j = 0; j < kFaKeys / 16; ++j) {               // 16 keys per step: 32 bytes along a row of P,
-          const uint64_t dp = fa_desc(fa_s32(p_s + (j / 4) * kFaTileBytes)) + uint64_t(2 * (j % 4));
-          const uint64_t dv = fa_desc(v_addr + j * 16 * 128);  // 16 rows (2,048 bytes) down the tile of V
-          fa_mma(tmem + 128, dp, dv, idesc_o, (n > 0 || j > 0) ? 1u : 0u);
-        }
-        fa_commit(&kv_empty[n % kFaStages]);                   // K_n and V_n have been read
-        if (n + 1 < n_tiles) {
-          if (!fa_wait(&kv_full[(n + 1) % kFaStages], ((n + 1) / kFaStages) & 1)) { fail(3); break; }
+      for (int n = 0; ok && n <= n_tiles && !abort_flag; ++n) {
+        if (n < n_tiles) {                                     // S_n = Q K_n^T into buffer n % 2
+          if (!fa_wait(&kv_full[n % kFaStages], (n / kFaStages) & 1)) { fail(3); break; }
+          if (!fa_wait(&s_free[n & 1], ((n >> 1) & 1) ^ 1)) { fail(8); break; }     // the softmax has read S_(n-2)
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          issue_s(n + 1);        // its commit also covers O += P_n V_n: whoever sees S_(n+1) may touch O
-        } else {
-          fa_commit(&o_full);                                  // the last product: O is final
+          const uint64_t dk = fa_desc(fa_s32(k_s + (n % kFaStages) * kFaKvBytes));
+#pragma unroll
+          for (int j = 0; j < kFaHD / 16; ++j)
+            fa_mma(tmem + uint32_t((n & 1) * kFaKeys), dq + uint64_t(2 * j), dk + uint64_t(2 * j), idesc_s, j > 0);
+          fa_commit(&s_full[n & 1]);
+        }
+        if (n >= 1) {                                          // O += P_m V_m
+          const int m = n - 1;
+          if (!fa_wait(&p_full[m & 1], (m >> 1) & 1)) { fail(4); break; }
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint64_t dp = fa_desc(fa_s32(p_s + (m & 1) * kFaTileBytes));
+          const uint32_t v_addr = fa_s32(v_s + (m % kFaStages) * kFaKvBytes);
+#pragma unroll
+          for (int j = 0; j < kFaKeys / 16; ++j)               // 16 keys per step: 32 bytes along a row of P,
+            fa_mma(tmem + 128, dp + uint64_t(2 * j), fa_desc(v_addr + j * 16 * 128), idesc_o,   // 16 rows down V
+                   (m > 0 || j > 0) ? 1u : 0u);
+          fa_commit(&p_free[m & 1]);                           // P_m has been read, O holds tile m
+          fa_commit(&kv_empty[m % kFaStages]);                 // K_m and V_m have been read
         }
       }
+      fa_commit(&o_full);                                      // everything issued is complete: O is final
     }
   } else {
     // ---- softmax and output: this thread owns query row `r` (lane r of tensor memory)
@@ -273,38 +278,41 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t lane_addr = tmem + (uint32_t(quarter * 32) << 16);
     float m = -INFINITY, l = 0.f;                              // m: the maximum the row currently scales by
     for (int n = 0; n < n_tiles; ++n) {
-      const bool got_s = !abort_flag && fa_wait(&s_full, n & 1);
+      const bool got_s = !abort_flag && fa_wait(&s_full[n & 1], (n >> 1) & 1);
       if (!__all_sync(0xffffffffu, got_s)) {                     // the warp stays together whatever a lane saw
         if (!abort_flag && lane == 0) fail(5);
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      uint32_t v[2][32];                                       // the row's 64 scores
+#pragma unroll
+      for (int c = 0; c < 2; ++c) fa_ld32(lane_addr + uint32_t((n & 1) * kFaKeys + c * 32), v[c]);
+      fa_ld_wait();
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) fa_arrive(&s_free[n & 1]);                // S_(n+2) may be written
       const int key0 = (j0 + n) * kFaKeys;
       // the keys of this tile that the row may see: [a, b) relative to the tile
       const int a = max(first, lo) - key0, b = min(pos + 1, hi) - key0;
       // Masks are needed only where the tile touches the diagonal, the window's edge or the end of
       // the keys; for every other tile (most of a long prompt) there is none.
       const bool full = key0 + kFaKeys - 1 <= pos0 && (p.window <= 0 || key0 >= pos0 + kFaRows - p.window);
-      uint32_t v[4][32];                                       // the row's 128 scores, one wait for all loads
-#pragma unroll
-      for (int c = 0; c < 4; ++c) fa_ld32(lane_addr + uint32_t(c * 32), v[c]);
-      fa_ld_wait();
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      float mx[2] = {-INFINITY, -INFINITY};
       if (full) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) mx[c] = fmaxf(mx[c], __uint_as_float(v[c][i]));
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int t = c * 32 + i;
             mx[c] = (t >= a && t < b) ? fmaxf(mx[c], __uint_as_float(v[c][i])) : mx[c];
           }
       }
-      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+      const float m_tile = fmaxf(mx[0], mx[1]) * p.scale_log2;
       // renew the reference maximum only when it is far behind; O and l then move with it
       float alpha = 1.f;
       bool rescale = false;
@@ -315,7 +323,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         m = m_tile;
         rescale = true;
       }
-      if (__any_sync(0xffffffffu, rescale)) {                  // (S_n is here, so O += P_(n-1) V_(n-1) is complete)
+      if (__any_sync(0xffffffffu, rescale)) {
+        // O must hold tile n - 1 completely and nothing newer: the first is waited for here, the
+        // second holds because O += P_n V_n is only issued after this warp has delivered P_n
+        const bool got = n == 0 || (!abort_flag && fa_wait(&p_free[(n - 1) & 1], ((n - 1) >> 1) & 1));
+        if (!__all_sync(0xffffffffu, got)) {
+          if (!abort_flag && lane == 0) fail(9);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         uint32_t ov[32];
 #pragma unroll 1
         for (int c = 0; c < kFaHD / 32; ++c) {
@@ -328,10 +344,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         fa_st_wait();
         l *= alpha;
       }
+      // the buffer of P_n was last read by O += P_(n-2) V_(n-2)
+      const bool got_p = !abort_flag && fa_wait(&p_free[n & 1], ((n >> 1) & 1) ^ 1);
+      if (!__all_sync(0xffffffffu, got_p)) {
+        if (!abort_flag && lane == 0) fail(9);
+        break;
+      }
       const float m_use = (m == -INFINITY) ? 0.f : m;           // a row that has seen no key yet
-      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      float sum[2] = {0.f, 0.f};
+      unsigned char* rowp = p_s + (n & 1) * kFaTileBytes + r * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t packed[16];
         if (full) {
 #pragma unroll
@@ -353,21 +376,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             packed[i / 2] = *reinterpret_cast<const uint32_t*>(&h);
           }
         }
-        // 32 keys = four 16-byte chunks of row r in k-block c / 2; chunk index XOR (r % 8): the 128-byte swizzle
-        unsigned char* rowp = p_s + (c / 2) * kFaTileBytes + r * 128;
+        // 32 keys = four 16-byte chunks of row r; chunk index XOR (r % 8): the 128-byte swizzle
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
+          const int chunk = (c * 4 + q) ^ (r & 7);
           *reinterpret_cast<uint4*>(rowp + chunk * 16) =
               make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
         }
       }
-      l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-      // P is complete, S has been read and O is rescaled: the products may go on
+      l += sum[0] + sum[1];
+      // P_n is complete and O is rescaled: O += P_n V_n may go
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       __syncwarp();
-      if (lane == 0) fa_arrive(&p_full);
+      if (lane == 0) fa_arrive(&p_full[n & 1]);
     }
     const bool got_o = !abort_flag && fa_wait(&o_full, 0);
     const bool all_o = __all_sync(0xffffffffu, got_o);
@@ -445,9 +467,11 @@ static int fa_map(CUtensorMap* map, const void* base, long long rows, int cols, 
 
 using namespace kvcm;
 
-// 1 if the tcgen05 prefill kernel takes these sizes: head_dim 64, pages of 8..128 keys that divide 128.
+// 1 if the tcgen05 prefill kernel takes these sizes: head_dim 64; pages of 8, 16, 32 or 64 keys, or a
+// multiple of 64 (up to 256, the largest box).
 KVCM_API int kvcm_attention_tcgen05_supports(int hd, int block_size) {
-  return hd == kFaHD && block_size >= 8 && block_size <= kFaKeys && (kFaKeys % block_size) == 0 && (block_size % 8) == 0;
+  if (hd != kFaHD || block_size < 8 || block_size > 256) return 0;
+  return block_size <= kFaKeys ? (kFaKeys % block_size) == 0 && (block_size % 8) == 0 : (block_size % kFaKeys) == 0;
 }
 
 // q: [total_rows, >= nh*64] rows `q_stride` elements apart (16-byte aligned, q_stride % 8 == 0); the
@@ -468,9 +492,10 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
   int rc = fa_map(&mq, q, total_rows, nh * hd, q_stride, kFaRows);
   if (rc) return rc;
   const long long cache_rows = (long long)num_pages * nkv * block_size;
-  rc = fa_map(&mk, k_cache, cache_rows, hd, hd, block_size);
+  const int box_rows = block_size < kFaKeys ? block_size : kFaKeys;
+  rc = fa_map(&mk, k_cache, cache_rows, hd, hd, box_rows);
   if (rc) return rc;
-  rc = fa_map(&mv, v_cache, cache_rows, hd, hd, block_size);
+  rc = fa_map(&mv, v_cache, cache_rows, hd, hd, box_rows);
   if (rc) return rc;
   PrefillTcParams p;
   p.out = (bf16*)out; p.out_stride = out_stride;
@@ -478,7 +503,7 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
   p.seq_q_start = seq_q_start; p.seq_q_len = seq_q_len; p.seq_ctx_len = seq_ctx_len;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
-  const size_t smem = size_t(1 + 2 * kFaStages + 2) * kFaTileBytes;     // two blocks fit an SM exactly
+  const size_t smem = size_t(3) * kFaTileBytes + size_t(2) * kFaStages * kFaKvBytes;     // 112 KB: two blocks fit an SM exactly
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -490,7 +515,7 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
 
 // Reads and clears the error word of the kernel (0 = no bounded wait ever ran out); else
 // (code << 16) | block: 1 producer waited for a free stage, 2 Q, 3 K/V, 4 P, 5 S, 6 O; 7 shared memory
-// not aligned to 1,024 bytes.
+// not aligned to 1,024 bytes; 8 a free buffer of S, 9 a free buffer of P.
 KVCM_API int kvcm_attention_tcgen05_error(void) {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, g_fa_error, sizeof v) != cudaSuccess) return -1;
