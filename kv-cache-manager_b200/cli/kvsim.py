@@ -37,7 +37,7 @@ def simulate(policy: str, a, wl, num_blocks: int, block_size: int, max_seq_len: 
             step += 1
             continue
         sched.schedule(float(step))
-        _, _, wants, _, _ = sched.plan_summary()
+        _, _, wants, _, _, _ = sched.plan_summary()
         sched.update([42] * wants, float(step))
         for f in sched.take_finished():
             if f.rejected:

@@ -312,14 +312,17 @@ PYBIND11_MODULE(kvcm_core, m) {
       .def("plan", &Scheduler::plan, py::return_value_policy::reference_internal)
       // (rows, entries, entries that sample, prompt tokens, single-row entries) of the current plan
       .def("plan_summary", [](const Scheduler& s) {
-        int rows = 0, wants = 0, prefill = 0, singles = 0;
+        int rows = 0, wants = 0, prefill = 0, singles = 0, tempered = 0;
         for (const auto& p : s.plan()) {
           rows += p.num_tokens;
           wants += p.wants_logits;
           if (p.is_prefill) prefill += p.num_tokens;
           singles += p.num_tokens == 1;
+          tempered += p.wants_logits && p.seq->sampling.temperature > 0.f;
         }
-        return py::make_tuple(rows, static_cast<int>(s.plan().size()), wants, prefill, singles);
+        // rows, entries, entries that sample, prompt tokens, single-row entries, entries that sample
+        // with a temperature (0 = the whole step is greedy)
+        return py::make_tuple(rows, static_cast<int>(s.plan().size()), wants, prefill, singles, tempered);
       })
       // Per plan entry that samples: (request id, position of the drawn token, temperature, seed)
       .def("plan_sampling", [](const Scheduler& s) {

@@ -142,17 +142,16 @@ class Engine:
         info = StepInfo()
         t_start = self.now()
         self.sched.schedule(t_start)
-        rows, entries, wants, prefill, singles = self.sched.plan_summary()
+        rows, entries, wants, prefill, singles, tempered = self.sched.plan_summary()
         if entries == 0:
             return info
         if self._has_state:
             for p in self.sched.plan():
                 if p.start == 0:
                     self.runner.pools.reset_slot(p.seq.state_slot)
-        greedy_only = True
-        if wants:
+        greedy_only = tempered == 0
+        if wants and not greedy_only:
             ids, pos, temps, seeds = self.sched.plan_sampling()
-            greedy_only = not any(t > 0 for t in temps)
         timed = self.device_timer is not None
         if self.graphs is not None and singles == entries and wants == entries and greedy_only:
             sampled_dev = self.graphs.run(self.sched, entries, self.device_timer)
