@@ -1,12 +1,14 @@
 """CUDA graphs for decode-only steps.
 
 A decode step of a small model is a few hundred short kernels; launched one by one their launch
-cost exceeds their run time.  A step in which every request brings exactly one token and samples
-greedily is therefore captured once per shape and replayed.  The shape of a captured step is
-(batch bucket, context bucket): the batch is padded to the bucket with rows that read and write
-nothing, and the bucket of the longest context fixes how the decode attention kernel splits the
-keys.  The integer arrays of the batch live in a buffer owned by the graph; a replay is one
-host-to-device copy into that buffer plus one graph launch.
+cost exceeds their run time.  A step in which every request brings exactly one token is therefore
+captured once per shape and replayed.  The shape of a captured step is (batch bucket, context
+bucket, greedy or not): the batch is padded to the bucket with rows that read and write nothing,
+the bucket of the longest context fixes how the decode attention kernel splits the keys, and a
+step in which some request samples with a temperature ends in the sampling kernel (fed from the
+sampler's device buffers) instead of the argmax.  The integer arrays of the batch live in a
+buffer owned by the graph; a replay is one host-to-device copy into that buffer (plus the
+sampling parameters where there are any) and one graph launch.
 """
 from __future__ import annotations
 
@@ -50,13 +52,16 @@ class DecodeGraphs:
         self.replays = 0
         self.kernels_last = 0
 
-    def run(self, sched, n: int, timer=None) -> torch.Tensor:
-        """Runs the scheduler's current plan (n single-row entries that all sample greedily).
+    def run(self, sched, n: int, timer=None, sampling=None) -> torch.Tensor:
+        """Runs the scheduler's current plan (n single-row entries).  ``sampling``: None when every
+        entry samples greedily, else (request ids, positions, temperatures, seeds) of the entries.
         Returns the sampled tokens on the device; the first n are real."""
         r = self.runner
         b = min(batch_bucket(n), max(r.max_seqs, n))
         layout = r.build_from_scheduler(sched, pad_rows=b, pad_seqs=b, pad_logit_rows=b)
-        key = (b, ctx_bucket(layout.max_decode_ctx))
+        key = (b, ctx_bucket(layout.max_decode_ctx), sampling is not None)
+        if sampling is not None:
+            self.sampler.stage(*sampling, rows=b)            # before a first capture too: its eager run reads them
         cap = self.captured.get(key)
         if cap is None:
             cap = self._capture(layout, key)
@@ -85,7 +90,10 @@ class DecodeGraphs:
 
         def body():
             logits = r.forward(ctx)
-            K.argmax(logits, sampled)
+            if key[2]:
+                self.sampler.sample_staged(logits, sampled)    # temperatures, seeds ... in the sampler's buffers
+            else:
+                K.argmax(logits, sampled)
 
         # One eager run on a side stream first: lazy initialisation (library handles, kernel
         # attributes) must not happen inside a capture.

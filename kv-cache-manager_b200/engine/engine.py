@@ -153,8 +153,9 @@ class Engine:
         if wants and not greedy_only:
             ids, pos, temps, seeds = self.sched.plan_sampling()
         timed = self.device_timer is not None
-        if self.graphs is not None and singles == entries and wants == entries and greedy_only:
-            sampled_dev = self.graphs.run(self.sched, entries, self.device_timer)
+        if self.graphs is not None and singles == entries and wants == entries:
+            sampled_dev = self.graphs.run(self.sched, entries, self.device_timer,
+                                          None if greedy_only else (ids, pos, temps, seeds))
             info.graph = True
         else:
             layout = self.runner.build_from_scheduler(self.sched)

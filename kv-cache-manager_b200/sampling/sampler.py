@@ -56,17 +56,31 @@ class Sampler:
         """One token per row of ``logits`` (int32, on the device).  Rows with temperature 0 are
         greedy.  ``positions``: index the drawn token will have in its request."""
         n = logits.shape[0]
-        if n > self.max_rows:
-            raise RuntimeError(f"sampler sized for {self.max_rows} rows, got {n}")
         if not any(t > 0 for t in temperatures):
             return self.greedy(logits)
+        self.stage(request_ids, positions, temperatures, seeds)
+        self.sample_staged(logits, self.out)
+        return self.out[:n]
+
+    def stage(self, request_ids: Sequence[int], positions: Sequence[int], temperatures: Sequence[float],
+              seeds: Sequence[int], rows: int = 0) -> None:
+        """Copies the per-row sampling parameters to the device buffers that ``sample_staged`` (and
+        a captured graph) reads.  ``rows`` > len(...): the rows beyond get temperature 0."""
+        n = len(temperatures)
+        rows = max(rows, n)
+        if rows > self.max_rows:
+            raise RuntimeError(f"sampler sized for {self.max_rows} rows, got {rows}")
         self.h_f[:n] = torch.tensor(list(temperatures), dtype=torch.float32)
+        self.h_f[n:rows] = 0.0
         self.h_i[:n] = torch.tensor(list(positions), dtype=torch.int32)
         self.h_l[:n] = torch.tensor([_signed64(s) for s in seeds], dtype=torch.int64)
-        self.h_l[n:2 * n] = torch.tensor([_signed64(r) for r in request_ids], dtype=torch.int64)
-        self.d_f[:n].copy_(self.h_f[:n], non_blocking=True)
+        self.h_l[self.max_rows:self.max_rows + n] = torch.tensor([_signed64(r) for r in request_ids], dtype=torch.int64)
+        self.d_f[:rows].copy_(self.h_f[:rows], non_blocking=True)
         self.d_i[:n].copy_(self.h_i[:n], non_blocking=True)
-        self.d_l[:2 * n].copy_(self.h_l[:2 * n], non_blocking=True)
-        self.h2d_bytes_last = n * (4 + 4 + 16)
-        K.sample(logits, self.d_f, self.d_l[:n], self.d_l[n:2 * n], self.d_i, self.out)
-        return self.out[:n]
+        self.d_l[:n].copy_(self.h_l[:n], non_blocking=True)
+        self.d_l[self.max_rows:self.max_rows + n].copy_(self.h_l[self.max_rows:self.max_rows + n], non_blocking=True)
+        self.h2d_bytes_last = n * (4 + 4 + 16) + (rows - n) * 4
+
+    def sample_staged(self, logits: torch.Tensor, out: torch.Tensor) -> None:
+        """The sampling kernel on the staged parameters; only enqueues device work."""
+        K.sample(logits, self.d_f, self.d_l[:self.max_rows], self.d_l[self.max_rows:], self.d_i, out)
