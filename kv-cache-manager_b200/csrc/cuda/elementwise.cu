@@ -165,6 +165,55 @@ rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ p
   }
 }
 
+// The same for bfloat16 rows whose heads are rotated over their whole width in rotate-half pairs
+// (rotary_dim == hd, hd a multiple of 16, 16-byte aligned rows): a thread takes 8 neighbouring
+// pairs of a head, i.e. one 16-byte piece of each half, so every access to qkv and to the cache
+// page is a 16-byte vector.  One block per row; the same values as the kernel above.
+__global__ void __launch_bounds__(256)
+rope_cache_vec_kernel(bf16* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                      const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping,
+                      bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int nh, int nkv, int hd,
+                      int block_size, int write_cache) {
+  extern __shared__ float cs_table[];    // [hd/2] cos, then [hd/2] sin: once per row
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int half = hd / 2, per_head = half / 8;                // pieces of 8 pairs per head
+  const float pos = float(positions[t]);
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &cs_table[half + j], &cs_table[j]);
+  __syncthreads();
+  const int heads = write_cache ? nh + 2 * nkv : nh;
+  const int slot = write_cache ? slot_mapping[t] : -1;
+  const int page = slot >= 0 ? slot / block_size : 0, off = slot >= 0 ? slot - page * block_size : 0;
+  bf16* row = qkv + size_t(t) * row_stride;
+  for (int w = threadIdx.x; w < heads * per_head; w += blockDim.x) {
+    const int head = w / per_head, j0 = (w - head * per_head) * 8;
+    bf16* base = row + size_t(head) * hd;
+    uint4 va = *reinterpret_cast<const uint4*>(base + j0);
+    uint4 vb = *reinterpret_cast<const uint4*>(base + half + j0);
+    if (head < nh + nkv) {
+      __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&va);
+      __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&vb);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float r0a, r0b, r1a, r1b;
+        rotate_pair(__bfloat162float(a2[i].x), __bfloat162float(b2[i].x), cs_table[j0 + 2 * i], cs_table[half + j0 + 2 * i], r0a, r0b);
+        rotate_pair(__bfloat162float(a2[i].y), __bfloat162float(b2[i].y), cs_table[j0 + 2 * i + 1], cs_table[half + j0 + 2 * i + 1], r1a, r1b);
+        a2[i] = __floats2bfloat162_rn(r0a, r1a);
+        b2[i] = __floats2bfloat162_rn(r0b, r1b);
+      }
+      *reinterpret_cast<uint4*>(base + j0) = va;
+      *reinterpret_cast<uint4*>(base + half + j0) = vb;
+    }
+    if (head < nh || slot < 0) continue;
+    const bool is_k = head < nh + nkv;
+    const int kvh = is_k ? head - nh : head - nh - nkv;
+    bf16* dst = (is_k ? k_cache : v_cache) + ((size_t(page) * nkv + kvh) * block_size + off) * hd;
+    *reinterpret_cast<uint4*>(dst + j0) = va;
+    *reinterpret_cast<uint4*>(dst + half + j0) = vb;
+  }
+}
+
 // --------------------------------------------------------------------------- SiLU(g) * u
 // gate = columns [0, I) of the fused product, up = columns [I, 2I).  silu is rounded to the
 // storage type before the product (src/cuda/kernels.cu:72-82).
@@ -253,6 +302,14 @@ int launch_rmsnorm(float* x, const T* delta, const void* weight, int weight_is_f
   return launch_rmsnorm_w<T, T>(x, delta, static_cast<const T*>(weight), out, rows, n_rows, hidden, eps, s);
 }
 
+// Whether the vector form of the rotary kernel applies.
+template <typename T>
+bool rope_cache_vec_ok(const void* qkv, int row_stride, const float* inv_freq, int rotary_dim, int interleaved,
+                       const void* k_cache, const void* v_cache, int hd) {
+  if (sizeof(T) != 2 || inv_freq == nullptr || interleaved || rotary_dim != hd || (hd % 16) || (row_stride % 8)) return false;
+  return ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
+}
+
 }  // namespace kvcm
 
 using namespace kvcm;
@@ -283,6 +340,11 @@ using namespace kvcm;
                                         int write_cache, void* stream) {                              \
     if (rows == 0) return 0;                                                                          \
     if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return KVCM_ERR_UNSUPPORTED;           \
+    if (rope_cache_vec_ok<T>(qkv, row_stride, inv_freq, rotary_dim, interleaved, k_cache, v_cache, hd)) \
+      return pdl_launch(rope_cache_vec_kernel, dim3(rows), dim3(256), size_t(hd) * sizeof(float),     \
+                        (cudaStream_t)stream, (bf16*)qkv, row_stride, positions, inv_freq,            \
+                        slot_mapping, (bf16*)k_cache, (bf16*)v_cache, nh, nkv, hd, block_size,        \
+                        write_cache);                                                                 \
     return pdl_launch(rope_cache_kernel<T>, dim3(rows), dim3(256), size_t(rotary_dim) * sizeof(float),\
                       (cudaStream_t)stream, (T*)qkv, row_stride, positions, inv_freq, rotary_dim,     \
                       interleaved, slot_mapping, (T*)k_cache, (T*)v_cache, nh, nkv, hd, block_size,   \
