@@ -223,6 +223,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--gemm", default="auto", choices=["auto", "native", "library"],
+                    help="bfloat16 products: 'auto' the fastest measured (this engine's kernels or the library), "
+                         "'native' this engine's kernels only, 'library' the library wherever it can stand")
     ap.add_argument("--only", default="all", choices=["all", "prefill"],
                     help="'prefill': run only the 2,048-token prefill step and print its numbers (for profiling)")
     args = ap.parse_args()
@@ -251,6 +254,7 @@ def main() -> int:
 
     cfg, spec, ec = build_engine(layers, max(args.batch, 64 if not args.no_points else args.batch),
                                  max_len, graphs=not args.no_graphs)
+    ec.gemm = args.gemm
     vocab = cfg.vocab_size
     m = model_bytes_and_flops(cfg, layers)
     if args.only == "prefill":
@@ -281,7 +285,7 @@ def main() -> int:
                    "head_dim": cfg.head_dim, "ffn": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": B, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
                    "mean_context": round(main_run["mean_ctx"], 1), "kv_block": BLOCK_SIZE,
-                   "parallelism": "single GPU", "cuda_graphs": not args.no_graphs,
+                   "parallelism": "single GPU", "cuda_graphs": not args.no_graphs, "gemm": args.gemm,
                    "l2": "inputs larger than L2 (2.2 GB of weights read per step)",
                    "peaks": pk["source"]},
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",

@@ -16,7 +16,7 @@ def engine_config_from_args(a):
                          prefill_chunk=a.i32("prefill-chunk", 0),
                          chunked_prefill=not a.flag("no-chunked-prefill"))
     return EngineConfig(kv=kv, pool_gb=a.f64("pool-gb", 1.0), sched=sc,
-                        dtype=canonical_dtype(a.str("dtype", "bfloat16")), attn=a.str("attn", "auto"),
+                        dtype=canonical_dtype(a.str("dtype", "bfloat16")), attn=a.str("attn", "auto"), gemm=a.str("gemm", "auto"),
                         sampling_seed=a.i64("sampling-seed", 0), cuda_graphs=not a.flag("no-graphs"))
 
 

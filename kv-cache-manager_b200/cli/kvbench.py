@@ -10,7 +10,7 @@ paged|contiguous, --block-size, --max-seq-len, --prefix, --num-blocks, --waterma
 --output-sigma --min-prompt --max-prompt --min-output --max-output --shared-frac --shared-len
 --num-prefixes --lengths-csv --seed --prompt-len --output-len).  Added: --model DIR | --preset NAME
 [--random-seed S], --dtype, --temperature, --sampling-seed, --prefill-chunk, --no-chunked-prefill,
---no-graphs.
+--no-graphs, --gemm auto|native|library|plain (native: only this engine's product kernels).
 """
 from __future__ import annotations
 

@@ -104,6 +104,8 @@ def bench_gemm(a, out) -> None:
                 res["stream"] = graph_time_us([(lambda w=w: K.gemm_stream(x, w, y)) for w in ws])
             if K.skinny_gemm_supported(M, N, Kd):
                 res["skinny"] = graph_time_us([(lambda w=w: K.gemm_skinny(x, w, y)) for w in ws])
+            if K.splitk_gemm_supported(x, ws[0]):
+                res["splitk"] = graph_time_us([(lambda w=w: K.gemm_tcgen05_splitk(x, w, y)) for w in ws])
             gb = N * Kd * 2 / 1e9
             print(f"M={M:<3} {name:<8} [{N} x {Kd}] " +
                   "  ".join(f"{k} {v:.1f} us ({gb / (v * 1e-6) / 1e3:.2f} TB/s)" for k, v in res.items()))
@@ -111,9 +113,9 @@ def bench_gemm(a, out) -> None:
                 for k, v in res.items():
                     out.write(f"{M},{name},{N},{Kd},{k},{v:.3f},{gb / (v * 1e-6):.1f}\n")
             del ws
-    err = K.stream_error()
-    if err:
-        raise RuntimeError(f"a bounded wait of the streaming kernel ran out (code {err >> 16}, block {err & 0xffff})")
+    for what, err in (("streaming", K.stream_error()), ("split-K tcgen05", K.splitk_error())):
+        if err:
+            raise RuntimeError(f"a bounded wait of the {what} kernel ran out (code {err >> 16}, block {err & 0xffff})")
 
 
 def bench_gemm_large(a, out) -> None:

@@ -48,6 +48,8 @@ class EngineConfig:
     sched: SchedulerConfig = field(default_factory=SchedulerConfig)
     dtype: str = "bfloat16"
     attn: str = "auto"               # decode attention: "v1" (whole context) | "v2" (split) | "auto"
+    gemm: str = "auto"               # bfloat16 products: "auto" (fastest measured: this engine's kernels or the
+                                     # library) | "native" (this engine's kernels only) | "library" | "plain"
     max_logit_rows: int = 0          # 0: max(max_num_seqs, 512)
     sampling_seed: int = 0
     eos_token_id: int = -1           # < 0: no end-of-sequence stop (the reference has none)

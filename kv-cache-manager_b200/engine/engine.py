@@ -87,7 +87,7 @@ class Engine:
             max_seq_len=kv.max_seq_len, num_slots=sc.max_num_seqs,
             max_rows=max(max_rows, kv.max_seq_len), max_seqs=sc.max_num_seqs,
             max_logit_rows=max(self.max_logit_rows, kv.max_seq_len),
-            options={"attn_version": cfg.attn})
+            options={"attn_version": cfg.attn, "gemm": cfg.gemm})
         self.kv = manager_from_config(kv, self.runner.windows)
         s = core.SchedulerConfig()
         s.max_num_seqs, s.max_batched_tokens = sc.max_num_seqs, sc.max_batched_tokens

@@ -509,6 +509,37 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
     _check(rc, "gemm_tcgen05", f"(M={M}, N={N}, K={K})")
 
 
+def splitk_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """True when the split-K tcgen05 kernel takes this product (up to 256 rows, bfloat16, K and row
+    strides multiples of 8)."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and bool(_lib().kvcm_gemm_tcgen05_splitk_supports(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0))))
+
+
+def gemm_tcgen05_splitk(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
+    """y[M,N] = x[M,K] @ w[N,K]^T for M <= 256 on the fifth-generation tensor cores with the operands
+    swapped (128 weight rows are the tall operand) and K split over a thread-block cluster whose
+    blocks add their partial sums through distributed shared memory.  bfloat16 operands; bfloat16 or
+    float32 result."""
+    _cuda(x, w, y)
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape[1] == K and y.shape == (M, N), "gemm_tcgen05_splitk: shapes")
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and y.dtype in (torch.bfloat16, torch.float32),
+          "gemm_tcgen05_splitk: bfloat16 operands, bfloat16 or float32 result")
+    _need(x.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1, "gemm_tcgen05_splitk: rows must be dense")
+    rc = _lib().kvcm_gemm_tcgen05_splitk_bf16(_p(x), _p(w), _p(y), M, N, K, x.stride(0), w.stride(0), y.stride(0),
+                                              int(y.dtype == torch.float32), _stream())
+    _check(rc, "gemm_tcgen05_splitk", f"(M={M}, N={N}, K={K})")
+
+
+def splitk_error() -> int:
+    """Error word of the split-K tcgen05 kernel: 0, or (code << 16 | block) of a bounded wait that
+    ran out.  Reading clears it.  Synchronises the device."""
+    return int(_lib().kvcm_gemm_tcgen05_splitk_error())
+
+
 def tcgen05_error() -> int:
     """Error word of the tcgen05 kernel: 0, or (code << 16 | block) of a bounded wait that ran out
     (1: the TMA thread waited for a free stage, 2: the MMA thread waited for data, 3: the epilogue

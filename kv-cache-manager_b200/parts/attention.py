@@ -44,7 +44,7 @@ class PagedAttention(Mixer):
         # A handful of rows (decode): one kernel does the product, the rotary encoding and the
         # cache write; it gives the same bits as the three separate kernels below.
         if (site.writes and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-                and ctx.options.get("gemm", "auto") == "auto" and ctx.options.get("fuse", True)
+                and ctx.options.get("gemm", "auto") in ("auto", "native") and ctx.options.get("fuse", True)
                 and pos.inv_freq is not None and pos.rotary_dim == self.hd and not pos.interleaved
                 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
                 and K.qkv_rope_cache_supported(M, h.shape[1], self.nh, self.nkv, self.hd)):

@@ -7,7 +7,9 @@ Which kernel runs is decided by the weight's dtype, never by the model:
   tcgen05 kernel for many rows where the tiles fill the GPU (prefill), else the library GEMM
   (cuBLAS through ``torch.mm``, the same place where the reference calls cuBLAS);
   ``options['gemm']``: 'plain' forces the plain twin, 'library' cuBLAS, 'tcgen05' and 'skinny' the
-  respective kernels.
+  respective kernels; 'native' never calls the library: the streaming kernel up to 16 rows, the
+  split-K tcgen05 kernel up to 255, the tiled tcgen05 kernel from 256 (slower than 'auto' where
+  'auto' takes the library: 17 to 255 rows, and tile counts that fill the SMs badly).
 """
 from __future__ import annotations
 
@@ -55,21 +57,28 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, options:
         y = torch.empty((M, N), dtype=out_dtype, device=x.device)
         K.gemm_skinny(x, w, y)
         return y
-    # A handful of rows (decode): this engine's weight-streaming kernel, for matrices up to
-    # STREAM_MAX_BYTES; measured on B200 it beats the library there (5-10 us against 7-15 us at
-    # 8-23 MB) while the library's kernels stream the largest matrices (46-131 MB) faster.
-    if mode != "library" and w.numel() * 2 <= STREAM_MAX_BYTES and K.stream_gemm_supported(M, N, w.shape[1]) \
+    # A handful of rows (decode): this engine's weight-streaming kernel.  Measured on B200 at 8 rows
+    # it beats the library (4-7 us against 7-16 us at 8-23 MB) or ties it (46 and 131 MB); from 9
+    # to 16 rows the library streams matrices beyond STREAM_MAX_BYTES faster.
+    native = mode == "native"
+    if mode != "library" and (native or M <= 8 or w.numel() * 2 <= STREAM_MAX_BYTES) and K.stream_gemm_supported(M, N, w.shape[1]) \
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
         y = torch.empty((M, N), dtype=out_dtype, device=x.device)
         K.gemm_stream(x, w, y)
         return y
     # Many rows (prefill): this engine's tcgen05 kernel where its 128 x 256 tiles fill the SMs well,
     # or always with options['gemm'] == 'tcgen05'.
-    if mode == "tcgen05" or (mode == "auto" and M >= TCGEN05_MIN_ROWS and tiles_fill_well(M, N, x.device)):
+    if mode == "tcgen05" or (M >= TCGEN05_MIN_ROWS and (native or (mode == "auto" and tiles_fill_well(M, N, x.device)))):
         if K.tcgen05_gemm_supported(x, w):
             y = torch.empty((M, N), dtype=out_dtype, device=x.device)
             K.gemm_tcgen05(x, w, y)
             return y
+    # In between: the library, unless the caller wants this engine's kernels only (the split-K
+    # tcgen05 kernel: correct and reproducible, about half the library's speed at these sizes).
+    if (native or mode == "splitk") and K.splitk_gemm_supported(x, w):
+        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        K.gemm_tcgen05_splitk(x, w, y)
+        return y
     if out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)

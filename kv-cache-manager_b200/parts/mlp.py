@@ -26,13 +26,14 @@ class GatedMLP(FeedForward):
         w = self.gate_up.param("weight")
         # A handful of rows (decode): the gate/up product and the activation in one kernel (the
         # same roundings as the two separate kernels).
-        if (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ctx.options.get("gemm", "auto") == "auto"
+        if (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ctx.options.get("gemm", "auto") in ("auto", "native")
                 and ctx.options.get("fuse", True) and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
                 and K.gate_up_silu_supported(h.shape[0], self.intermediate, h.shape[1])):
             K.gate_up_silu(h, w, act)
         elif (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ctx.options.get("fuse", True)
-              and ctx.options.get("gemm", "auto") in ("auto", "tcgen05") and h.shape[0] >= TCGEN05_MIN_ROWS
-              and tiles_fill_well(h.shape[0], 2 * self.intermediate, h.device) and K.tcgen05_gemm_supported(h, w)):
+              and ctx.options.get("gemm", "auto") in ("auto", "native", "tcgen05") and h.shape[0] >= TCGEN05_MIN_ROWS
+              and (ctx.options.get("gemm", "auto") != "auto" or tiles_fill_well(h.shape[0], 2 * self.intermediate, h.device))
+              and K.tcgen05_gemm_supported(h, w)):
             # Many rows (prefill): the tcgen05 product applies the activation in its epilogue.
             K.gate_up_silu_tcgen05(h, w, act)
         else:

@@ -174,6 +174,33 @@ def test_score_returns_every_position(dtype, model_folders):
         make_engine(folder, dtype, name, prefix=True).score(toks)
 
 
+def test_native_products_only(model_folders):
+    """``gemm='native'``: no library product anywhere (streaming kernel up to 16 rows, split-K
+    tcgen05 up to 255, tiled tcgen05 from 256): whole-sequence logits and greedy generation with
+    portions of every size class."""
+    name, dtype = "tiny-b", "bfloat16"
+    folder = model_folders(name, dtype)
+    import kvcm.parts.linear as L
+    calls = []
+    real_mm = torch.mm
+    try:
+        torch.mm = lambda *a, **k: calls.append(1) or real_mm(*a, **k)
+        eng = make_engine(folder, dtype, name, gemm="native", max_seq_len=512, num_blocks=256,
+                          max_batched_tokens=512)
+        toks = helpers.random_tokens(300, helpers.TINY[name]["cfg"]["vocab_size"], 4)     # 300 rows: tiled tcgen05
+        cfg, w = P.read_model_folder(folder)
+        ref = P.llama_forward(cfg, w, toks, torch.bfloat16)
+        helpers.assert_logits_close(eng.score(toks), ref, dtype, "score, native products")
+        ps = prompts(name, [1, 7, 40, 100, 150])                                         # split-K and streaming sizes
+        outs = run(eng, ps, 12)
+        check_greedy(folder, dtype, ps, outs)
+    finally:
+        torch.mm = real_mm
+    assert not calls, "a library product ran in native mode"
+    from kvcm.kernels import library as K
+    assert K.splitk_error() == 0 and K.tcgen05_error() == 0 and K.stream_error() == 0
+
+
 def test_rejects_bad_requests_and_cpu_device(model_folders):
     folder = model_folders("tiny-a", "bfloat16")
     eng = make_engine(folder, "bfloat16", "tiny-a", max_seq_len=64)

@@ -250,6 +250,29 @@ def test_fused_gate_up_silu_gives_the_bits_of_the_separate_kernels(M, H, I):
     close(a2, gg[:, :I] * torch.sigmoid(gg[:, :I]) * gg[:, I:], "bfloat16", "against float64")
 
 
+@pytest.mark.parametrize("M,N,Kd", [(64, 2560, 2048), (64, 2048, 5632), (17, 100, 136), (256, 515, 96), (33, 32003, 256),
+                                    (100, 11264, 2048), (1, 8, 8), (48, 2048, 2048), (200, 130, 4104), (24, 129, 72)])
+def test_tcgen05_splitk_gemm(M, N, Kd):
+    """Swap-AB tcgen05 product with K split over a cluster, against float64; ragged edges in every
+    dimension; the same bits on a second run (the partial sums are added in a fixed order)."""
+    lib = K()
+    g = torch.Generator().manual_seed(M * 3 + N)
+    x = torch.randn(M, Kd + 8, generator=g).to(torch.bfloat16).to(DEV)[:, :Kd]        # strided rows
+    w = (torch.randn(N, Kd, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    assert lib.splitk_gemm_supported(x, w)
+    ref = x.double().cpu() @ w.double().cpu().T
+    for out_dt in (torch.bfloat16, torch.float32):
+        y = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
+        lib.gemm_tcgen05_splitk(x, w, y)
+        assert lib.splitk_error() == 0
+        d = (y.double().cpu() - ref).abs().max().item()
+        bound = (0.02 if out_dt == torch.bfloat16 else 2e-3) * ref.abs().max().item()
+        assert d <= bound, f"{out_dt}: {d} > {bound}"
+    y2 = torch.empty_like(y)
+    lib.gemm_tcgen05_splitk(x, w, y2)
+    assert torch.equal(y, y2)
+
+
 @pytest.mark.parametrize("M,H,I", [(2048, 2048, 5632), (300, 96, 1000), (129, 64, 24), (640, 256, 128)])
 def test_tcgen05_gate_up_with_the_activation_in_its_epilogue(M, H, I):
     """Bit for bit the tcgen05 product followed by the activation kernel, and close to float64."""
