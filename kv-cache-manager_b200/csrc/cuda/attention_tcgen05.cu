@@ -26,10 +26,8 @@
 // (kvcm_attention_tcgen05_error), stops waiting, frees its tensor memory and leaves.
 // The reference has no prefill kernel (it runs prompt rows through its decode kernel,
 // docs/design.md:113-114).
-#include <cuda.h>
-
-#include "common.cuh"
 #include "pdl.cuh"
+#include "tcgen05_common.cuh"
 
 namespace kvcm {
 
@@ -42,7 +40,6 @@ constexpr int kFaTileBytes = 128 * 128;      // [128 rows][64 bf16]: Q, a buffer
 constexpr int kFaKvBytes = kFaKeys * 128;    // [64 keys][64 bf16]: a stage of K or of V
 constexpr int kFaTmemCols = 256;             // S: two buffers, columns 0..63 and 64..127; O: columns 128..191
 constexpr float kFaRescaleStep = 8.f;        // in log2 units
-constexpr unsigned long long kFaWaitLimitNs = 1000000000ull;
 
 __device__ int g_fa_error = 0;
 
@@ -55,82 +52,11 @@ struct PrefillTcParams {
   float scale_log2;
 };
 
-__device__ __forceinline__ uint32_t fa_s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ unsigned long long fa_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity) {
-  unsigned long long start = 0;
-  for (unsigned spin = 0;; ++spin) {
-    uint32_t done;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(done) : "r"(fa_s32(bar)), "r"(parity) : "memory");
-    if (done) return true;
-    if ((spin & 63) == 63) {
-      const unsigned long long now = fa_now();
-      if (start == 0) start = now;
-      else if (now - start > kFaWaitLimitNs) return false;
-    }
-  }
-}
-__device__ __forceinline__ void fa_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(fa_s32(bar)) : "memory");
-}
-__device__ __forceinline__ void fa_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(fa_s32(bar)) : "memory");
-}
 __device__ __forceinline__ float fa_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
-
-// Shared-memory descriptor of a tile whose rows are 128 bytes, 128-byte swizzled, 8-row groups 1024
-// bytes apart (the same numbers describe a K-major tile [rows][64 k] and an MN-major tile
-// [k][64 n], whose 8-k groups are 1024 bytes apart); descriptor version 1, swizzle code 2.
-__device__ __forceinline__ uint64_t fa_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= uint64_t((smem_addr & 0x3FFFF) >> 4);
-  d |= uint64_t(1) << 16;
-  d |= uint64_t(1024 >> 4) << 32;
-  d |= uint64_t(1) << 46;
-  d |= uint64_t(2) << 61;
-  return d;
-}
-// float accumulator, bfloat16 operands, A K-major; B K-major or MN-major (bit 16).
-__host__ __device__ constexpr uint32_t fa_idesc(int M, int N, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | (uint32_t(N >> 3) << 17) |
-         (uint32_t(M >> 4) << 24);
-}
-__device__ __forceinline__ void fa_mma(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-               ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void fa_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-               : "r"(taddr));
-}
-__device__ __forceinline__ void fa_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void fa_st32(uint32_t taddr, const uint32_t (&v)[32]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-               "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
-                 "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
-                 "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
-                 "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-               : "memory");
-}
-__device__ __forceinline__ void fa_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 __global__ void __launch_bounds__(kFaThreads, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -151,7 +77,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int tile = int(gridDim.y) - 1 - int(blockIdx.y), head = blockIdx.x;
   const int q0 = p.tile_q0[tile];
   if (q0 & (kFaRows - 1)) return;                              // the odd tile of 64 rows belongs to the block before
-  if (fa_s32(smem_raw) & 1023) {                               // the swizzled tiles need this alignment
+  if (tc5::s32(smem_raw) & 1023) {                               // the swizzled tiles need this alignment
     if (threadIdx.x == 0) atomicExch(&g_fa_error, (7 << 16) | int(blockIdx.y & 0xffff));
     return;
   }
@@ -167,7 +93,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    auto init = [](uint64_t* b, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(fa_s32(b)), "r"(count)); };
+    auto init = [](uint64_t* b, int count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(tc5::s32(b)), "r"(count)); };
     init(&q_full, 1);
     for (int s = 0; s < kFaStages; ++s) { init(&kv_full[s], 1); init(&kv_empty[s], 1); }
     for (int i = 0; i < 2; ++i) {
@@ -185,7 +111,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     reinterpret_cast<uint4*>(k_s)[i] = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(fa_s32(&tmem_base)), "r"(kFaTmemCols));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5::s32(&tmem_base)), "r"(kFaTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -202,9 +128,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (warp == 0) {
     // ---- producer: Q once, then a tile of K and V per round, one box per page (or per half page)
     if (lane == 0) {
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(fa_s32(&q_full)), "r"(kFaTileBytes) : "memory");
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc5::s32(&q_full)), "r"(kFaTileBytes) : "memory");
       asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                   ::"r"(fa_s32(q_s)), "l"(&map_q), "r"(fa_s32(&q_full)), "r"(head * kFaHD), "r"(q_start + q0) : "memory");
+                   ::"r"(tc5::s32(q_s)), "l"(&map_q), "r"(tc5::s32(&q_full)), "r"(head * kFaHD), "r"(q_start + q0) : "memory");
     }
     const int* table = p.block_tables + size_t(seq) * p.max_blocks;
     const int B = p.block_size;
@@ -213,7 +139,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int s = n % kFaStages;
       int ok = 1;
       if (lane == 0) {
-        ok = !abort_flag && fa_wait(&kv_empty[s], ((n / kFaStages) & 1) ^ 1);
+        ok = !abort_flag && tc5::mbar_wait(&kv_empty[s], ((n / kFaStages) & 1) ^ 1);
         if (!ok && !abort_flag) fail(1);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -222,52 +148,52 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int count = min(per_tile, (hi - key0 + box - 1) / box);             // boxes that hold keys below hi
       if (lane == 0)
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
-                     ::"r"(fa_s32(&kv_full[s])), "r"(2 * count * box * 128) : "memory");
+                     ::"r"(tc5::s32(&kv_full[s])), "r"(2 * count * box * 128) : "memory");
       __syncwarp();
       for (int i = lane; i < count; i += 32) {
         const int key = key0 + i * box;
         const int page = table[key / B];
         const int row = (page * p.nkv + kvh) * B + key % B;
         asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                     ::"r"(fa_s32(k_s + s * kFaKvBytes + i * box * 128)), "l"(&map_k), "r"(fa_s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
+                     ::"r"(tc5::s32(k_s + s * kFaKvBytes + i * box * 128)), "l"(&map_k), "r"(tc5::s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
         asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                     ::"r"(fa_s32(v_s + s * kFaKvBytes + i * box * 128)), "l"(&map_v), "r"(fa_s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
+                     ::"r"(tc5::s32(v_s + s * kFaKvBytes + i * box * 128)), "l"(&map_v), "r"(tc5::s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
       }
     }
   } else if (warp == 1) {
     // ---- one thread issues the products, S one tile ahead of O:  S_0, S_1, O+=P_0 V_0, S_2, O+=P_1 V_1, ...
     if (lane == 0) {
-      constexpr uint32_t idesc_s = fa_idesc(kFaRows, kFaKeys, false);
-      constexpr uint32_t idesc_o = fa_idesc(kFaRows, kFaHD, true);
-      const uint64_t dq = fa_desc(fa_s32(q_s));
-      bool ok = fa_wait(&q_full, 0);
+      constexpr uint32_t idesc_s = tc5::idesc(kFaRows, kFaKeys, false);
+      constexpr uint32_t idesc_o = tc5::idesc(kFaRows, kFaHD, true);
+      const uint64_t dq = tc5::smem_desc(tc5::s32(q_s));
+      bool ok = tc5::mbar_wait(&q_full, 0);
       if (!ok) fail(2);
       for (int n = 0; ok && n <= n_tiles && !abort_flag; ++n) {
         if (n < n_tiles) {                                     // S_n = Q K_n^T into buffer n % 2
-          if (!fa_wait(&kv_full[n % kFaStages], (n / kFaStages) & 1)) { fail(3); break; }
-          if (!fa_wait(&s_free[n & 1], ((n >> 1) & 1) ^ 1)) { fail(8); break; }     // the softmax has read S_(n-2)
+          if (!tc5::mbar_wait(&kv_full[n % kFaStages], (n / kFaStages) & 1)) { fail(3); break; }
+          if (!tc5::mbar_wait(&s_free[n & 1], ((n >> 1) & 1) ^ 1)) { fail(8); break; }     // the softmax has read S_(n-2)
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          const uint64_t dk = fa_desc(fa_s32(k_s + (n % kFaStages) * kFaKvBytes));
+          const uint64_t dk = tc5::smem_desc(tc5::s32(k_s + (n % kFaStages) * kFaKvBytes));
 #pragma unroll
           for (int j = 0; j < kFaHD / 16; ++j)
-            fa_mma(tmem + uint32_t((n & 1) * kFaKeys), dq + uint64_t(2 * j), dk + uint64_t(2 * j), idesc_s, j > 0);
-          fa_commit(&s_full[n & 1]);
+            tc5::mma(tmem + uint32_t((n & 1) * kFaKeys), dq + uint64_t(2 * j), dk + uint64_t(2 * j), idesc_s, j > 0);
+          tc5::commit(&s_full[n & 1]);
         }
         if (n >= 1) {                                          // O += P_m V_m
           const int m = n - 1;
-          if (!fa_wait(&p_full[m & 1], (m >> 1) & 1)) { fail(4); break; }
+          if (!tc5::mbar_wait(&p_full[m & 1], (m >> 1) & 1)) { fail(4); break; }
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          const uint64_t dp = fa_desc(fa_s32(p_s + (m & 1) * kFaTileBytes));
-          const uint32_t v_addr = fa_s32(v_s + (m % kFaStages) * kFaKvBytes);
+          const uint64_t dp = tc5::smem_desc(tc5::s32(p_s + (m & 1) * kFaTileBytes));
+          const uint32_t v_addr = tc5::s32(v_s + (m % kFaStages) * kFaKvBytes);
 #pragma unroll
           for (int j = 0; j < kFaKeys / 16; ++j)               // 16 keys per step: 32 bytes along a row of P,
-            fa_mma(tmem + 128, dp + uint64_t(2 * j), fa_desc(v_addr + j * 16 * 128), idesc_o,   // 16 rows down V
+            tc5::mma(tmem + 128, dp + uint64_t(2 * j), tc5::smem_desc(v_addr + j * 16 * 128), idesc_o,   // 16 rows down V
                    (m > 0 || j > 0) ? 1u : 0u);
-          fa_commit(&p_free[m & 1]);                           // P_m has been read, O holds tile m
-          fa_commit(&kv_empty[m % kFaStages]);                 // K_m and V_m have been read
+          tc5::commit(&p_free[m & 1]);                           // P_m has been read, O holds tile m
+          tc5::commit(&kv_empty[m % kFaStages]);                 // K_m and V_m have been read
         }
       }
-      fa_commit(&o_full);                                      // everything issued is complete: O is final
+      tc5::commit(&o_full);                                      // everything issued is complete: O is final
     }
   } else {
     // ---- softmax and output: this thread owns query row `r` (lane r of tensor memory)
@@ -278,7 +204,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t lane_addr = tmem + (uint32_t(quarter * 32) << 16);
     float m = -INFINITY, l = 0.f;                              // m: the maximum the row currently scales by
     for (int n = 0; n < n_tiles; ++n) {
-      const bool got_s = !abort_flag && fa_wait(&s_full[n & 1], (n >> 1) & 1);
+      const bool got_s = !abort_flag && tc5::mbar_wait(&s_full[n & 1], (n >> 1) & 1);
       if (!__all_sync(0xffffffffu, got_s)) {                     // the warp stays together whatever a lane saw
         if (!abort_flag && lane == 0) fail(5);
         break;
@@ -286,11 +212,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       uint32_t v[2][32];                                       // the row's 64 scores
 #pragma unroll
-      for (int c = 0; c < 2; ++c) fa_ld32(lane_addr + uint32_t((n & 1) * kFaKeys + c * 32), v[c]);
-      fa_ld_wait();
+      for (int c = 0; c < 2; ++c) tc5::ld32(lane_addr + uint32_t((n & 1) * kFaKeys + c * 32), v[c]);
+      tc5::ld_wait();
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       __syncwarp();
-      if (lane == 0) fa_arrive(&s_free[n & 1]);                // S_(n+2) may be written
+      if (lane == 0) tc5::mbar_arrive(&s_free[n & 1]);                // S_(n+2) may be written
       const int key0 = (j0 + n) * kFaKeys;
       // the keys of this tile that the row may see: [a, b) relative to the tile
       const int a = max(first, lo) - key0, b = min(pos + 1, hi) - key0;
@@ -326,7 +252,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (__any_sync(0xffffffffu, rescale)) {
         // O must hold tile n - 1 completely and nothing newer: the first is waited for here, the
         // second holds because O += P_n V_n is only issued after this warp has delivered P_n
-        const bool got = n == 0 || (!abort_flag && fa_wait(&p_free[(n - 1) & 1], ((n - 1) >> 1) & 1));
+        const bool got = n == 0 || (!abort_flag && tc5::mbar_wait(&p_free[(n - 1) & 1], ((n - 1) >> 1) & 1));
         if (!__all_sync(0xffffffffu, got)) {
           if (!abort_flag && lane == 0) fail(9);
           break;
@@ -335,17 +261,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         uint32_t ov[32];
 #pragma unroll 1
         for (int c = 0; c < kFaHD / 32; ++c) {
-          fa_ld32(lane_addr + uint32_t(128 + c * 32), ov);
-          fa_ld_wait();
+          tc5::ld32(lane_addr + uint32_t(128 + c * 32), ov);
+          tc5::ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-          fa_st32(lane_addr + uint32_t(128 + c * 32), ov);
+          tc5::st32(lane_addr + uint32_t(128 + c * 32), ov);
         }
-        fa_st_wait();
+        tc5::st_wait();
         l *= alpha;
       }
       // the buffer of P_n was last read by O += P_(n-2) V_(n-2)
-      const bool got_p = !abort_flag && fa_wait(&p_free[n & 1], ((n >> 1) & 1) ^ 1);
+      const bool got_p = !abort_flag && tc5::mbar_wait(&p_free[n & 1], ((n >> 1) & 1) ^ 1);
       if (!__all_sync(0xffffffffu, got_p)) {
         if (!abort_flag && lane == 0) fail(9);
         break;
@@ -389,9 +315,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       __syncwarp();
-      if (lane == 0) fa_arrive(&p_full[n & 1]);
+      if (lane == 0) tc5::mbar_arrive(&p_full[n & 1]);
     }
-    const bool got_o = !abort_flag && fa_wait(&o_full, 0);
+    const bool got_o = !abort_flag && tc5::mbar_wait(&o_full, 0);
     const bool all_o = __all_sync(0xffffffffu, got_o);
     if (!all_o && !abort_flag && lane == 0) fail(6);
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -401,8 +327,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll 1
       for (int c = 0; c < kFaHD / 32; ++c) {
         uint32_t ov[32];
-        fa_ld32(lane_addr + uint32_t(128 + c * 32), ov);       // (all lanes of the warp take part in the load)
-        fa_ld_wait();
+        tc5::ld32(lane_addr + uint32_t(128 + c * 32), ov);       // (all lanes of the warp take part in the load)
+        tc5::ld_wait();
         if (r < rows_here) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -420,8 +346,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   // every role ends here; after a wait that ran out, copies still in flight get time to land
   // before the shared memory is given up; tensor memory goes back
   if (abort_flag) {
-    const unsigned long long t0 = fa_now();
-    while (fa_now() - t0 < 100000ull) {}
+    const unsigned long long t0 = tc5::now_ns();
+    while (tc5::now_ns() - t0 < 100000ull) {}
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
@@ -432,36 +358,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 // ---------------------------------------------------------------------------------- host
-
-typedef CUresult (*FaEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static FaEncodeTiledFn fa_encode_tiled() {
-  static FaEncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<FaEncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// Row-major [rows, cols] bfloat16 matrix, `ld` elements between rows; boxes of [box_rows x 64 columns].
-static int fa_map(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_rows) {
-  FaEncodeTiledFn enc = fa_encode_tiled();
-  if (!enc) return KVCM_ERR_UNSUPPORTED;
-  cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
-  cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
-  cuuint32_t box[2] = {64u, cuuint32_t(box_rows)};
-  cuuint32_t elem[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : 20000 + int(r);
-}
 
 }  // namespace kvcm
 
@@ -489,13 +385,13 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
       (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15))
     return KVCM_ERR_UNSUPPORTED;
   CUtensorMap mq, mk, mv;
-  int rc = fa_map(&mq, q, total_rows, nh * hd, q_stride, kFaRows);
+  int rc = tc5::make_map(&mq, q, total_rows, nh * hd, q_stride, kFaRows);
   if (rc) return rc;
   const long long cache_rows = (long long)num_pages * nkv * block_size;
   const int box_rows = block_size < kFaKeys ? block_size : kFaKeys;
-  rc = fa_map(&mk, k_cache, cache_rows, hd, hd, box_rows);
+  rc = tc5::make_map(&mk, k_cache, cache_rows, hd, hd, box_rows);
   if (rc) return rc;
-  rc = fa_map(&mv, v_cache, cache_rows, hd, hd, box_rows);
+  rc = tc5::make_map(&mv, v_cache, cache_rows, hd, hd, box_rows);
   if (rc) return rc;
   PrefillTcParams p;
   p.out = (bf16*)out; p.out_stride = out_stride;

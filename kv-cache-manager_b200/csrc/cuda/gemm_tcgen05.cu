@@ -17,67 +17,15 @@
 // is a multiple of 8 work.  Every wait on an mbarrier is bounded; when one runs out the block
 // records it (kvcm_tcgen05_error), stops waiting, frees its tensor memory and leaves.
 // The reference calls cuBLAS for these products (src/model/llama.cpp:45-52).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05_common.cuh"
 
 namespace kvcm {
 
 constexpr int kTcBM = 128, kTcBK = 64;
 constexpr int kTcThreads = 192;
 constexpr int kTcABytes = kTcBM * kTcBK * 2;
-constexpr unsigned long long kTcWaitLimitNs = 1000000000ull;   // every wait gives up after a second
 
 __device__ int g_tcgen05_error = 0;
-
-__device__ __forceinline__ uint32_t tc_s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ unsigned long long tc_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ bool tc_wait(uint64_t* bar, uint32_t parity) {
-  unsigned long long start = 0;
-  for (unsigned spin = 0;; ++spin) {
-    uint32_t done;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(done) : "r"(tc_s32(bar)), "r"(parity) : "memory");
-    if (done) return true;
-    if ((spin & 63) == 63) {
-      const unsigned long long now = tc_now();
-      if (start == 0) start = now;
-      else if (now - start > kTcWaitLimitNs) return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                 "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                 "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-               : "r"(taddr));
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
-// start address / 16, stride between 8-row groups = 1024 bytes, descriptor version 1, swizzle code 2.
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= uint64_t((smem_addr & 0x3FFFF) >> 4);
-  d |= uint64_t(1) << 16;                       // leading byte offset (unused with this swizzle)
-  d |= uint64_t(1024 >> 4) << 32;               // stride byte offset
-  d |= uint64_t(1) << 46;                       // descriptor version
-  d |= uint64_t(2) << 61;                       // SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N and M of the product.
-__host__ __device__ constexpr uint32_t tc_idesc(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
-}
 
 // GATED: W is [2N, K], gate rows first; a tile's 256 accumulator columns are 128 gate columns
 // n0..n0+127 and the 128 up columns N+n0.., and the epilogue stores
@@ -110,17 +58,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc_s32(&full[s])));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc_s32(&empty[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5::s32(&full[s])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5::s32(&empty[s])));
     }
     for (int a = 0; a < 2; ++a) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc_s32(&acc_full[a])));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;\n" ::"r"(tc_s32(&acc_empty[a])));   // four epilogue warps
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tc5::s32(&acc_full[a])));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;\n" ::"r"(tc5::s32(&acc_empty[a])));   // four epilogue warps
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {                                // one warp allocates two accumulators of BN columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_s32(&tmem_base)), "r"(2 * BN));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc5::s32(&tmem_base)), "r"(2 * BN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -136,32 +84,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const int m0 = (t / n_tiles) * kTcBM, n0 = (t % n_tiles) * BNOUT;
         for (int k = 0; k < nk; ++k, ++it) {
           const int s = it % kStages;
-          if (!tc_wait(&empty[s], ((it / kStages) & 1) ^ 1)) {
+          if (!tc5::mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1)) {
             atomicExch(&g_tcgen05_error, (1 << 16) | int(blockIdx.x & 0xffff));
             abort_flag = 1;
             break;
           }
-          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc_s32(&full[s])), "r"(kStageBytes) : "memory");
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc5::s32(&full[s])), "r"(kStageBytes) : "memory");
           unsigned char* a = ring + s * kStageBytes;
           unsigned char* b = a + kTcABytes;
           asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                       ::"r"(tc_s32(a)), "l"(&map_x), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(m0) : "memory");
+                       ::"r"(tc5::s32(a)), "l"(&map_x), "r"(tc5::s32(&full[s])), "r"(k * kTcBK), "r"(m0) : "memory");
           asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                       ::"r"(tc_s32(b)), "l"(&map_w), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(n0) : "memory");
+                       ::"r"(tc5::s32(b)), "l"(&map_w), "r"(tc5::s32(&full[s])), "r"(k * kTcBK), "r"(n0) : "memory");
           if constexpr (GATED)                                   // the map's box is 128 rows: the up rows follow
             asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                         ::"r"(tc_s32(b + kBBytes / 2)), "l"(&map_w), "r"(tc_s32(&full[s])), "r"(k * kTcBK), "r"(N + n0) : "memory");
+                         ::"r"(tc5::s32(b + kBBytes / 2)), "l"(&map_w), "r"(tc5::s32(&full[s])), "r"(k * kTcBK), "r"(N + n0) : "memory");
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = tc_idesc(kTcBM, BN);
+      constexpr uint32_t idesc = tc5::idesc(kTcBM, BN);
       int it = 0;
       for (int tl = 0; tl < my_tiles && !abort_flag; ++tl) {
         const int acc = tl & 1;
         // the epilogue must have drained this accumulator (two tiles ago)
-        if (!tc_wait(&acc_empty[acc], ((tl >> 1) & 1) ^ 1)) {
+        if (!tc5::mbar_wait(&acc_empty[acc], ((tl >> 1) & 1) ^ 1)) {
           atomicExch(&g_tcgen05_error, (4 << 16) | int(blockIdx.x & 0xffff));
           abort_flag = 1;
           break;
@@ -170,14 +118,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const uint32_t d_tmem = tmem + uint32_t(acc * BN);
         for (int k = 0; k < nk; ++k, ++it) {
           const int s = it % kStages;
-          if (!tc_wait(&full[s], (it / kStages) & 1)) {
+          if (!tc5::mbar_wait(&full[s], (it / kStages) & 1)) {
             atomicExch(&g_tcgen05_error, (2 << 16) | int(blockIdx.x & 0xffff));
             abort_flag = 1;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          const uint32_t a_addr = tc_s32(ring + s * kStageBytes);
-          const uint64_t da = tc_smem_desc(a_addr), db = tc_smem_desc(a_addr + kTcABytes);
+          const uint32_t a_addr = tc5::s32(ring + s * kStageBytes);
+          const uint64_t da = tc5::smem_desc(a_addr), db = tc5::smem_desc(a_addr + kTcABytes);
 #pragma unroll
           for (int j = 0; j < kTcBK / 16; ++j) {
             const uint32_t accumulate = (k > 0 || j > 0) ? 1u : 0u;
@@ -187,10 +135,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                          ::"r"(d_tmem), "l"(da + uint64_t(2 * j)), "l"(db + uint64_t(2 * j)), "r"(idesc), "r"(accumulate) : "memory");
           }
           // the ring slot is free once these products have read it
-          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_s32(&empty[s])) : "memory");
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc5::s32(&empty[s])) : "memory");
         }
         if (abort_flag) break;
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc_s32(&acc_full[acc])) : "memory");
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tc5::s32(&acc_full[acc])) : "memory");
       }
     }
   } else {
@@ -201,7 +149,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       const int acc = tl & 1;
       const int t = int(blockIdx.x) + tl * int(gridDim.x);
       const int m0 = (t / n_tiles) * kTcBM, n0 = (t % n_tiles) * BNOUT;
-      if (abort_flag || !tc_wait(&acc_full[acc], (tl >> 1) & 1)) {
+      if (abort_flag || !tc5::mbar_wait(&acc_full[acc], (tl >> 1) & 1)) {
         if (!abort_flag && lane == 0) atomicExch(&g_tcgen05_error, (3 << 16) | int(blockIdx.x & 0xffff));
         abort_flag = 1;
         break;
@@ -213,8 +161,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         for (int c = 0; c < BNOUT / 32; ++c) {
           uint32_t g[32], u[32];
           const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(acc * BN + c * 32);
-          tc_ld32(taddr, g);
-          tc_ld32(taddr + BNOUT, u);
+          tc5::ld32(taddr, g);
+          tc5::ld32(taddr + BNOUT, u);
           asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
           if (row < M) {
             const int col0 = n0 + c * 32;
@@ -278,7 +226,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       // this warp has read its lanes of the accumulator: hand it back to the tensor core
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc_s32(&acc_empty[acc])) : "memory");
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(tc5::s32(&acc_empty[acc])) : "memory");
     }
   }
   // every role ends here; tensor memory goes back before the block leaves
@@ -292,44 +240,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
 // ---------------------------------------------------------------------------------- host
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// Row-major [rows, cols] bfloat16 matrix with `ld` elements between rows; boxes of [box_rows x 64].
-static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
-  EncodeTiledFn enc = encode_tiled();
-  if (!enc) return KVCM_ERR_UNSUPPORTED;
-  cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
-  cuuint64_t strides[1] = {cuuint64_t(ld) * 2};
-  cuuint32_t box[2] = {cuuint32_t(kTcBK), cuuint32_t(box_rows)};
-  cuuint32_t elem[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : 20000 + int(r);
-}
-
 // GATED: N is the number of output columns; W has 2N rows.
 template <typename OutT, int BN, bool GATED = false>
 int launch_tcgen05_bn(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy,
                       int sm_count, cudaStream_t s) {
   CUtensorMap mx, mw;
-  int rc = make_map(&mx, X, M, K, ldx, kTcBM);
+  int rc = tc5::make_map(&mx, X, M, K, ldx, kTcBM);
   if (rc) return rc;
-  rc = GATED ? make_map(&mw, W, 2 * N, K, ldw, BN / 2) : make_map(&mw, W, N, K, ldw, BN);
+  rc = GATED ? tc5::make_map(&mw, W, 2 * N, K, ldw, BN / 2) : tc5::make_map(&mw, W, N, K, ldw, BN);
   if (rc) return rc;
   auto kernel = gemm_tcgen05_kernel<OutT, BN, GATED>;
   const size_t smem = size_t(BN == 256 ? 4 : 6) * (kTcABytes + BN * kTcBK * 2) + 1024;

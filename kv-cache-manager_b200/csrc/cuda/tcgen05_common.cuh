@@ -62,9 +62,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr) {
   d |= uint64_t(2) << 61;                       // SWIZZLE_128B
   return d;
 }
-// Instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N and M of the product.
-__host__ __device__ constexpr uint32_t idesc(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+// Instruction descriptor: float accumulator, bfloat16 A and B, A K-major, B K-major or MN-major
+// (bit 16; the same shared-memory descriptor then describes a tile [k][64 n] whose 8-k groups are
+// 1024 bytes apart), N and M of the product.
+__host__ __device__ constexpr uint32_t idesc(int M, int N, bool b_mn_major = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | (uint32_t(N >> 3) << 17) |
+         (uint32_t(M >> 4) << 24);
 }
 __device__ __forceinline__ void mma(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t instr, uint32_t accumulate) {
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
@@ -89,6 +92,18 @@ __device__ __forceinline__ void ld32(uint32_t taddr, uint32_t (&v)[32]) {
                : "r"(taddr));
 }
 __device__ __forceinline__ void ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+// 32 consecutive columns of this thread's lane of tensor memory, written (no wait).
+__device__ __forceinline__ void st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+               "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                 "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                 "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                 "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+               : "memory");
+}
+__device__ __forceinline__ void st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 // ---- host
 
