@@ -67,7 +67,7 @@ class DecodeGraphs:
             cap = self._capture(layout, key)
         if int(layout.total_ints) != cap.total_ints:
             raise RuntimeError("decode graph: batch layout changed for a captured shape")
-        r.upload(layout, into=cap.ints)
+        r.upload(layout, into=cap.ints, sync_follows=True)    # the engine reads the sampled tokens back
         if timer is not None:
             timer.start()
         cap.graph.replay()

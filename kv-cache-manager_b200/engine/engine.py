@@ -159,7 +159,7 @@ class Engine:
             info.graph = True
         else:
             layout = self.runner.build_from_scheduler(self.sched)
-            self.runner.upload(layout)
+            self.runner.upload(layout, sync_follows=wants > 0)
             if timed:
                 self.device_timer.start()
             logits = self.runner.forward(self.runner.context(layout))

@@ -46,6 +46,7 @@ class ModelRunner:
         self.dev_ints = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._copied = torch.cuda.Event()
         self._copy_pending = False
+        self._views = {}                  # (buffer, length) -> (device view, pinned view) of an upload
         self.h2d_bytes_last = 0
 
     # ------------------------------------------------------------------ batch -> device
@@ -79,12 +80,24 @@ class ModelRunner:
             self._copied.synchronize()      # the pinned buffer is free again
             self._copy_pending = False
 
-    def upload(self, layout, into: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def upload(self, layout, into: Optional[torch.Tensor] = None, sync_follows: bool = False) -> torch.Tensor:
+        """One host-to-device copy of the step's packed integer arrays.  ``sync_follows``: the caller
+        synchronises with the device before the next batch is built (a step that reads its sampled
+        tokens back does), so the pinned buffer needs no event of its own."""
         n = int(layout.total_ints)
         dst = self.dev_ints if into is None else into
-        dst[:n].copy_(self.host_ints[:n], non_blocking=True)
-        self._copied.record()
-        self._copy_pending = True
+        key = (dst.data_ptr(), n)
+        views = self._views.get(key)
+        if views is None:
+            if len(self._views) > 64:
+                self._views.clear()
+            views = self._views[key] = (dst[:n], self.host_ints[:n])
+        views[0].copy_(views[1], non_blocking=True)
+        if sync_follows:
+            self._copy_pending = False
+        else:
+            self._copied.record()
+            self._copy_pending = True
         self.h2d_bytes_last = 4 * n
         return dst
 
