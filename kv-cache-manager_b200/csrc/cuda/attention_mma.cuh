@@ -237,4 +237,10 @@ __device__ __forceinline__ void softmax_step(float (&s)[2][4], float (&m)[2], fl
   pa[3] = pack_bf16(p[1][2], p[1][3]);
 }
 
+// Head sizes the tensor-core kernels are instantiated for.
+#define KVCM_FOR_HEAD_DIMS(X) \
+  X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128) X(160) X(192) X(224) X(256)
+
+constexpr int kAttnThreads = 128;     // 4 warps
+
 }  // namespace kvcm
