@@ -28,6 +28,9 @@ PRESETS = {
     "tiny-b": (dict(vocab_size=384, hidden_size=96, intermediate_size=256, num_hidden_layers=3,
                     num_attention_heads=3, num_key_value_heads=1, head_dim=32, max_position_embeddings=256,
                     rope_theta=500000.0, rms_norm_eps=1e-6, tie_word_embeddings=True), 1, 0.1),
+    "tiny-c": (dict(vocab_size=320, hidden_size=136, intermediate_size=344, num_hidden_layers=2,
+                    num_attention_heads=3, num_key_value_heads=1, head_dim=64, max_position_embeddings=512,
+                    rope_theta=250000.0, rms_norm_eps=2e-6, tie_word_embeddings=False), 2, 0.05),
     "tinyllama-1.1b": (dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=22,
                             num_attention_heads=32, num_key_value_heads=4, head_dim=64,
                             max_position_embeddings=2048, rope_theta=10000.0, rms_norm_eps=1e-5,

@@ -29,6 +29,13 @@ TINY = {
                             max_position_embeddings=256, rope_theta=500000.0, rms_norm_eps=1e-6,
                             tie_word_embeddings=True),
                    block_size=8, seed=1, norm_jitter=0.1),
+    # heads of 64 (the width the tcgen05 attention kernel takes), three query heads on one KV head,
+    # a width that is no multiple of the head size
+    "tiny-c": dict(cfg=dict(vocab_size=320, hidden_size=136, intermediate_size=344, num_hidden_layers=2,
+                            num_attention_heads=3, num_key_value_heads=1, head_dim=64,
+                            max_position_embeddings=512, rope_theta=250000.0, rms_norm_eps=2e-6,
+                            tie_word_embeddings=False),
+                   block_size=16, seed=2, norm_jitter=0.05),
 }
 
 TORCH_DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
