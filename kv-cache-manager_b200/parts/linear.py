@@ -3,9 +3,9 @@ layout of every matrix of the reference (``src/model/llama.cpp:45-52``).
 
 Which kernel runs is decided by the weight's dtype, never by the model:
 * float32 weight  -> this engine's plain float kernel (true 32-bit, fixed summation order);
-* bfloat16 weight -> this engine's weight-streaming kernel for a handful of rows (decode), its
-  tcgen05 kernel for many rows where the tiles fill the GPU (prefill), else the library GEMM
-  (cuBLAS through ``torch.mm``, the same place where the reference calls cuBLAS);
+* bfloat16 weight -> this engine's weight-streaming kernel for a handful of rows (decode), else
+  the library GEMM (cuBLAS through ``torch.mm``, the same place where the reference calls cuBLAS);
+  this engine's tcgen05 kernels for many rows on request, and for the fused gate/up product;
   ``options['gemm']``: 'plain' forces the plain twin, 'library' cuBLAS, 'tcgen05' and 'skinny' the
   respective kernels; 'native' never calls the library: the streaming kernel up to 16 rows, the
   split-K tcgen05 kernel up to 255, the tiled tcgen05 kernel from 256 (slower than 'auto' where
@@ -23,6 +23,7 @@ from .base import Part, StepContext
 
 STREAM_MAX_BYTES = 32 << 20
 TCGEN05_MIN_ROWS = 256
+TCGEN05_GATED_MAX_HIDDEN = 3072    # beyond, the library product plus the activation kernel is faster
 
 
 class Linear(Part):
@@ -66,9 +67,12 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, options:
         y = torch.empty((M, N), dtype=out_dtype, device=x.device)
         K.gemm_stream(x, w, y)
         return y
-    # Many rows (prefill): this engine's tcgen05 kernel where its 128 x 256 tiles fill the SMs well,
-    # or always with options['gemm'] == 'tcgen05'.
-    if mode == "tcgen05" or (M >= TCGEN05_MIN_ROWS and (native or (mode == "auto" and tiles_fill_well(M, N, x.device)))):
+    # Many rows (prefill): this engine's tiled tcgen05 kernel with 'tcgen05' or 'native'.  'auto'
+    # takes the library here: measured at 2,048 rows its kernels are 10-25 % faster for a plain
+    # product (2048 x 2048: 16.4 against 18.8 us, 2048 x 5632: 35.4 against 40.6 us; a Llama-3-8B
+    # shaped prefill: 27 against 34 ms); the tcgen05 kernel earns its place in 'auto' where it
+    # saves a kernel: the gate/up product with the activation in its epilogue (parts/mlp.py).
+    if mode == "tcgen05" or (native and M >= TCGEN05_MIN_ROWS):
         if K.tcgen05_gemm_supported(x, w):
             y = torch.empty((M, N), dtype=out_dtype, device=x.device)
             K.gemm_tcgen05(x, w, y)
@@ -85,11 +89,9 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, options:
 
 
 def tiles_fill_well(M: int, N: int, device) -> bool:
-    """The tcgen05 kernel's 128 x 256 tiles keep most SMs busy in every round.  (At 2,048 rows the
-    library's kernels for 2048 x 2048 and 2048 x 5632 are a little faster one by one, 16.4 against
-    18.8 us and 35.4 against 40.6 us, but a whole prefill step through them took 6.9 ms against
-    5.7 ms: the step is launched eagerly and their host-side cost shows.)"""
+    """The tcgen05 kernel's 128 x 256 tiles give every SM work in every round but (at most a fifth
+    of) the last."""
     sms = K.sm_count(device)
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
     rounds = (tiles + sms - 1) // sms
-    return tiles >= 96 and tiles >= 0.8 * rounds * sms
+    return tiles >= sms and tiles >= 0.8 * rounds * sms

@@ -8,7 +8,7 @@ import torch
 
 from ..kernels import library as K
 from .base import FEED_FORWARDS, FeedForward, StepContext
-from .linear import Linear, TCGEN05_MIN_ROWS, tiles_fill_well
+from .linear import Linear, TCGEN05_GATED_MAX_HIDDEN, TCGEN05_MIN_ROWS, tiles_fill_well
 
 
 @FEED_FORWARDS.register("gated_mlp")
@@ -32,9 +32,14 @@ class GatedMLP(FeedForward):
             K.gate_up_silu(h, w, act)
         elif (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ctx.options.get("fuse", True)
               and ctx.options.get("gemm", "auto") in ("auto", "native", "tcgen05") and h.shape[0] >= TCGEN05_MIN_ROWS
-              and (ctx.options.get("gemm", "auto") != "auto" or tiles_fill_well(h.shape[0], 2 * self.intermediate, h.device))
+              and (ctx.options.get("gemm", "auto") != "auto"
+                   or (tiles_fill_well(h.shape[0], 2 * self.intermediate, h.device)
+                       and h.shape[1] <= TCGEN05_GATED_MAX_HIDDEN))
               and K.tcgen05_gemm_supported(h, w)):
-            # Many rows (prefill): the tcgen05 product applies the activation in its epilogue.
+            # Many rows (prefill): the tcgen05 product applies the activation in its epilogue.  It
+            # saves the activation kernel (time ~ rows x I) and loses about a tenth of the product
+            # against the library (time ~ rows x I x hidden): a win up to a hidden size of ~3,000
+            # (TinyLlama shape: 84 us against 76 + 15; Llama-3-8B shape: the library wins).
             K.gate_up_silu_tcgen05(h, w, act)
         else:
             K.silu_mul(self.gate_up.forward(h, ctx), act)
