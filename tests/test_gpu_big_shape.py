@@ -1,0 +1,148 @@
+"""The kernels at the sizes they are tuned for, inside the engine: two layers of the TinyLlama-1.1B
+shape (hidden 2048, 32 query heads on 4 KV heads of 64, feed-forward 5632; a vocabulary that is no
+power of two) with random weights.  The bfloat16 engine (tcgen05 attention and gated product for
+long portions, the streaming products with fused epilogues and the clustered decode attention for
+single tokens) against this engine's own true 32-bit path on the same (bfloat16-rounded) weights,
+which the small-configuration tests pin to the plain implementation: whole, in portions, token by
+token, and mixed."""
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def engines():
+    import kvcm
+    from kvcm.config import LlamaConfig
+    from kvcm.engine import model_from_tensors
+    from kvcm.weights import random_tensors
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", vocab_size=4100, hidden_size=2048, intermediate_size=5632,
+                      num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=4, head_dim=64,
+                      max_position_embeddings=4096, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    t16 = dict(random_tensors(cfg, 7, torch.bfloat16, device="cuda:0", norm_jitter=0.1))
+    t32 = {k: v.float() for k, v in t16.items()}
+    out = {}
+    for dtype, t in (("bfloat16", t16), ("float32", t32)):
+        spec = model_from_tensors(cfg, dict(t), dtype, "cuda:0")
+        out[dtype] = lambda spec=spec, dtype=dtype: helpers.Replayer(None, dtype, 4096, 16, spec=spec, max_live=4)
+    return cfg, out
+
+
+def same_cut(got, ref, what):
+    """Two ways of cutting the same work in bfloat16: what differs are roundings the paths do not
+    share (other kernels, other orders of summation), so the difference stays below one path's own
+    distance from float32 (~1 % of the logits' standard deviation in the root mean square).  For the
+    worst element the bound of the small-configuration tests (4 % at ~10^4 elements) grows with
+    the number of elements as the maximum of that many Gaussians does, by sqrt(ln N / ln 10^4)."""
+    import math
+    got, ref = got.double(), ref.double()
+    assert torch.isfinite(got).all(), what
+    std = ref.std().item()
+    d = got - ref
+    rms, worst = d.pow(2).mean().sqrt().item(), d.abs().max().item()
+    bound = 0.04 * math.sqrt(max(1.0, math.log(d.numel()) / math.log(1e4)))
+    assert rms <= 0.01 * std and worst <= bound * std, \
+        f"{what}: rms {rms / std:.4f}, max {worst / std:.4f} of std (bounds 0.01, {bound:.4f})"
+
+
+def near_float32(got, ref, what):
+    """bfloat16 against the true 32-bit path, which rounds no activation: about twenty tensors on the
+    way to a logit are rounded with a relative error of 2^-9 / sqrt(3) each, which the attention's
+    rounded probabilities and two residual layers roughly double: about 1 % of the logits' standard
+    deviation in the root mean square, five times that at the worst of ~10^5 elements.  A real fault
+    (a missed or wrong key, a stale page, a wrong tile) moves whole rows by the order of that
+    deviation itself."""
+    got, ref = got.double(), ref.double()
+    assert torch.isfinite(got).all(), what
+    std = ref.std().item()
+    d = got - ref
+    rms, worst = d.pow(2).mean().sqrt().item(), d.abs().max().item()
+    assert rms <= 0.02 * std and worst <= 0.1 * std, f"{what}: rms {rms / std:.4f}, max {worst / std:.4f} of std"
+
+
+def test_whole_portions_and_token_by_token(engines):
+    cfg, make = engines
+    toks = helpers.random_tokens(1500, cfg.vocab_size, 3)
+    want = [0, 1, 63, 64, 127, 128, 129, 700, 1023, 1024] + list(range(1436, 1500))
+    ref = make["float32"]().step([dict(id="a", tokens=toks, want=want)])
+    whole = make["bfloat16"]().step([dict(id="a", tokens=toks, want=want)])
+    near_float32(whole, ref, "whole prompt")
+    r = make["bfloat16"]()
+    got, at = [], 0
+    for k in (700, 2, 300, 466):                                   # 1468 tokens in portions ...
+        w = [p - at for p in want if at <= p < at + k]
+        o = r.step([dict(id="a", tokens=toks[at:at + k], want=w)])
+        if w:
+            got.append(o)
+        at += k
+    for t in range(at, 1500):                                        # ... the last 32 one by one
+        got.append(r.step([dict(id="a", tokens=toks[t:t + 1], want=[0])]))
+    near_float32(torch.cat(got), ref, "portions, then token by token")
+    same_cut(torch.cat(got), whole, "portions, then token by token, against the whole prompt")
+    from kvcm.kernels import library as K
+    assert K.attention_tcgen05_error() == 0 and K.tcgen05_error() == 0 and K.stream_error() == 0
+
+
+def test_mixed_batch(engines):
+    """Three requests: portions of one beside single tokens of the others, in one step each."""
+    cfg, make = engines
+    seqs = [helpers.random_tokens(n, cfg.vocab_size, 10 + i) for i, n in enumerate((400, 333, 150))]
+    refs, alone = [], []
+    for s in seqs:
+        w = list(range(len(s) - 20, len(s)))
+        refs.append(make["float32"]().step([dict(id="x", tokens=s, want=w)]))
+        alone.append(make["bfloat16"]().step([dict(id="x", tokens=s, want=w)]))
+    r = make["bfloat16"]()
+    # everything but the last 20 tokens of each request first, in two steps
+    r.step([dict(id=f"r{i}", tokens=s[:len(s) - 20 - 7 * i], want=[]) for i, s in enumerate(seqs)])
+    fed = [len(s) - 20 - 7 * i for i, s in enumerate(seqs)]
+    got = [[] for _ in seqs]
+    while any(f < len(s) for f, s in zip(fed, seqs)):
+        entries = []
+        for i, s in enumerate(seqs):
+            if fed[i] >= len(s):
+                continue
+            k = 1 if i != 1 else min(5, len(s) - fed[i])           # request 1 goes on in portions of five
+            k = min(k, len(s) - fed[i])
+            w = [p - fed[i] for p in range(len(s) - 20, len(s)) if fed[i] <= p < fed[i] + k]
+            entries.append((i, dict(id=f"r{i}", tokens=s[fed[i]:fed[i] + k], want=w)))
+            fed[i] += k
+        out = r.step([e for _, e in entries])
+        at = 0
+        for i, e in entries:
+            n = len(e["want"])
+            if n:
+                got[i].append(out[at:at + n])
+            at += n
+    for i in range(3):
+        near_float32(torch.cat(got[i]), refs[i], f"mixed, request {i}")
+        same_cut(torch.cat(got[i]), alone[i], f"mixed, request {i}, against the request alone")
+
+
+def test_decode_graphs_give_the_tokens_of_eager_steps(engines):
+    """Greedy generation through the engine at this shape with CUDA graphs (padded batch buckets,
+    context buckets, dependent launches inside the graph) and without: the same tokens."""
+    import kvcm
+    from kvcm.config import EngineConfig, KVManagerConfig, SchedulerConfig
+    from kvcm.engine import model_from_tensors
+    from kvcm.weights import random_tensors
+    cfg, _ = engines
+    spec = model_from_tensors(cfg, dict(random_tensors(cfg, 7, torch.bfloat16, device="cuda:0", norm_jitter=0.1)),
+                              "bfloat16", "cuda:0")
+    prompts = [helpers.random_tokens(n, cfg.vocab_size, 20 + i) for i, n in enumerate((300, 150, 700))]
+    outs = {}
+    for graphs in (True, False):
+        ec = EngineConfig(kv=KVManagerConfig(num_blocks=160, block_size=16, max_seq_len=1024, watermark_blocks=0),
+                          sched=SchedulerConfig(max_num_seqs=4, max_batched_tokens=1024), dtype="bfloat16",
+                          cuda_graphs=graphs)
+        eng = kvcm.Engine(spec, ec)
+        outs[graphs] = kvcm.generate(eng, prompts, 24)
+        assert (eng.graphs is not None) == graphs
+        if graphs:
+            assert eng.graphs.replays > 0
+        assert eng.kv.blocks_in_use() == 0
+    assert outs[True] == outs[False]
+    assert all(len(o) == 24 for o in outs[True])
