@@ -1,4 +1,5 @@
-// Causal prefill attention over the paged cache on the fifth-generation tensor cores (head_dim 64).
+// Causal prefill attention over the paged cache on the fifth-generation tensor cores (head_dim 64
+// or 128).
 //
 // One block per (128 query rows of a request, query head).  Per tile of 64 keys:
 //     S = Q K^T  (tcgen05.mma, M 128 x N 64, accumulator in tensor memory, two buffers)
@@ -16,8 +17,8 @@
 // the end is exact softmax.
 // Roles: warp 0 brings Q once and K/V pages (cp.async.bulk.tensor, one box per page, 128-byte
 // swizzle) into a four-stage ring; one thread of warp 1 issues the products and commits them to
-// mbarriers; warps 2-5 do the softmax and the output.  Two blocks share an SM (112 KB of shared
-// memory and 256 columns of tensor memory each).  Keys come from the pages, the portion's own
+// mbarriers; warps 2-5 do the softmax and the output.  At head_dim 64 two blocks share an SM (112 KB
+// of shared memory and 256 columns of tensor memory each); at 128 a block takes 192 KB.  Keys come from the pages, the portion's own
 // included (they were written before), so a portion may start anywhere in a request; masks: key <=
 // row's position, key > position - window, key < end of the request's computed part.  Scores are
 // scaled in float; softmax by exp2 with log2(e) folded into the scale; probabilities are rounded
@@ -34,11 +35,13 @@ namespace kvcm {
 constexpr int kFaThreads = 192;
 constexpr int kFaRows = 128;                 // query rows per block
 constexpr int kFaKeys = 64;                  // keys per tile
-constexpr int kFaHD = 64;                    // head_dim
 constexpr int kFaStages = 4;                 // K/V tiles in flight
-constexpr int kFaTileBytes = 128 * 128;      // [128 rows][64 bf16]: Q, a buffer of P
-constexpr int kFaKvBytes = kFaKeys * 128;    // [64 keys][64 bf16]: a stage of K or of V
-constexpr int kFaTmemCols = 256;             // S: two buffers, columns 0..63 and 64..127; O: columns 128..191
+constexpr int kFaTileBytes = 128 * 128;      // [128 rows][64 bf16]: a 64-wide block of Q, a buffer of P
+constexpr int kFaKvBlock = kFaKeys * 128;    // [64 keys][64 bf16]: a 64-wide block of a stage of K or of V
+constexpr int kFaTmemCols = 256;             // S: two buffers, columns 0..63 and 64..127; O: columns 128..(128 + head_dim)
+// head_dim 64 or 128.  Operands wider than 64 elements are kept as blocks of 64 (one 128-byte
+// swizzled row each): Q [HD/64][128 rows][64], a stage of K or V [HD/64][64 keys][64]; the
+// products step through the blocks (S over head_dim) or write 64 columns of O per block of V.
 constexpr float kFaRescaleStep = 8.f;        // in log2 units
 
 __device__ int g_fa_error = 0;
@@ -58,13 +61,16 @@ __device__ __forceinline__ float fa_exp2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kFaThreads, 2)
+template <int HD>
+__global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* q_s = smem_raw;                               // [128 rows][64]                 16 KB
-  unsigned char* k_s = q_s + kFaTileBytes;                     // [stages][64 keys][64]          32 KB
-  unsigned char* v_s = k_s + kFaStages * kFaKvBytes;           // [stages][64 keys][64]          32 KB
+  constexpr int KB = HD / 64;                                  // 64-wide blocks of head_dim
+  constexpr int kFaKvBytes = KB * kFaKvBlock;                  // a stage of K or of V
+  unsigned char* q_s = smem_raw;                               // [KB][128 rows][64]             16 KB x KB
+  unsigned char* k_s = q_s + KB * kFaTileBytes;                // [stages][KB][64 keys][64]      32 KB x KB
+  unsigned char* v_s = k_s + kFaStages * kFaKvBytes;           // [stages][KB][64 keys][64]      32 KB x KB
   unsigned char* p_s = v_s + kFaStages * kFaKvBytes;           // [2][128 rows][64 keys]         32 KB
   __shared__ __align__(8) uint64_t q_full, kv_full[kFaStages], kv_empty[kFaStages], s_full[2], s_free[2], p_full[2],
       p_free[2], o_full;
@@ -128,9 +134,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (warp == 0) {
     // ---- producer: Q once, then a tile of K and V per round, one box per page (or per half page)
     if (lane == 0) {
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(tc5::s32(&q_full)), "r"(kFaTileBytes) : "memory");
-      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                   ::"r"(tc5::s32(q_s)), "l"(&map_q), "r"(tc5::s32(&q_full)), "r"(head * kFaHD), "r"(q_start + q0) : "memory");
+      tc5::mbar_expect_tx(&q_full, KB * kFaTileBytes);
+      for (int kb = 0; kb < KB; ++kb)
+        tc5::tma_load_2d(q_s + kb * kFaTileBytes, &map_q, &q_full, head * HD + kb * 64, q_start + q0);
     }
     const int* table = p.block_tables + size_t(seq) * p.max_blocks;
     const int B = p.block_size;
@@ -148,23 +154,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int count = min(per_tile, (hi - key0 + box - 1) / box);             // boxes that hold keys below hi
       if (lane == 0)
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
-                     ::"r"(tc5::s32(&kv_full[s])), "r"(2 * count * box * 128) : "memory");
+                     ::"r"(tc5::s32(&kv_full[s])), "r"(2 * KB * count * box * 128) : "memory");
       __syncwarp();
       for (int i = lane; i < count; i += 32) {
         const int key = key0 + i * box;
         const int page = table[key / B];
         const int row = (page * p.nkv + kvh) * B + key % B;
-        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                     ::"r"(tc5::s32(k_s + s * kFaKvBytes + i * box * 128)), "l"(&map_k), "r"(tc5::s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
-        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                     ::"r"(tc5::s32(v_s + s * kFaKvBytes + i * box * 128)), "l"(&map_v), "r"(tc5::s32(&kv_full[s])), "r"(0), "r"(row) : "memory");
+        for (int kb = 0; kb < KB; ++kb) {
+          tc5::tma_load_2d(k_s + s * kFaKvBytes + kb * kFaKvBlock + i * box * 128, &map_k, &kv_full[s], kb * 64, row);
+          tc5::tma_load_2d(v_s + s * kFaKvBytes + kb * kFaKvBlock + i * box * 128, &map_v, &kv_full[s], kb * 64, row);
+        }
       }
     }
   } else if (warp == 1) {
     // ---- one thread issues the products, S one tile ahead of O:  S_0, S_1, O+=P_0 V_0, S_2, O+=P_1 V_1, ...
     if (lane == 0) {
       constexpr uint32_t idesc_s = tc5::idesc(kFaRows, kFaKeys, false);
-      constexpr uint32_t idesc_o = tc5::idesc(kFaRows, kFaHD, true);
+      constexpr uint32_t idesc_o = tc5::idesc(kFaRows, 64, true);       // one 64-wide block of V (and of O) per product
       const uint64_t dq = tc5::smem_desc(tc5::s32(q_s));
       bool ok = tc5::mbar_wait(&q_full, 0);
       if (!ok) fail(2);
@@ -175,8 +181,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
           const uint64_t dk = tc5::smem_desc(tc5::s32(k_s + (n % kFaStages) * kFaKvBytes));
 #pragma unroll
-          for (int j = 0; j < kFaHD / 16; ++j)
-            tc5::mma(tmem + uint32_t((n & 1) * kFaKeys), dq + uint64_t(2 * j), dk + uint64_t(2 * j), idesc_s, j > 0);
+          for (int kb = 0; kb < KB; ++kb)                      // (descriptor addresses count units of 16 bytes)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              tc5::mma(tmem + uint32_t((n & 1) * kFaKeys), dq + uint64_t(kb * (kFaTileBytes >> 4) + 2 * j),
+                       dk + uint64_t(kb * (kFaKvBlock >> 4) + 2 * j), idesc_s, (kb > 0 || j > 0) ? 1u : 0u);
           tc5::commit(&s_full[n & 1]);
         }
         if (n >= 1) {                                          // O += P_m V_m
@@ -187,8 +196,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const uint32_t v_addr = tc5::s32(v_s + (m % kFaStages) * kFaKvBytes);
 #pragma unroll
           for (int j = 0; j < kFaKeys / 16; ++j)               // 16 keys per step: 32 bytes along a row of P,
-            tc5::mma(tmem + 128, dp + uint64_t(2 * j), tc5::smem_desc(v_addr + j * 16 * 128), idesc_o,   // 16 rows down V
-                   (m > 0 || j > 0) ? 1u : 0u);
+#pragma unroll
+            for (int nb = 0; nb < KB; ++nb)                    // 16 rows down each 64-wide block of V
+              tc5::mma(tmem + 128 + nb * 64, dp + uint64_t(2 * j), tc5::smem_desc(v_addr + nb * kFaKvBlock + j * 16 * 128),
+                       idesc_o, (m > 0 || j > 0) ? 1u : 0u);
           tc5::commit(&p_free[m & 1]);                           // P_m has been read, O holds tile m
           tc5::commit(&kv_empty[m % kFaStages]);                 // K_m and V_m have been read
         }
@@ -260,7 +271,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         uint32_t ov[32];
 #pragma unroll 1
-        for (int c = 0; c < kFaHD / 32; ++c) {
+        for (int c = 0; c < HD / 32; ++c) {
           tc5::ld32(lane_addr + uint32_t(128 + c * 32), ov);
           tc5::ld_wait();
 #pragma unroll
@@ -323,9 +334,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     if (all_o) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = p.out + size_t(q_start + q0 + r) * p.out_stride + size_t(head) * kFaHD;
+      bf16* dst = p.out + size_t(q_start + q0 + r) * p.out_stride + size_t(head) * HD;
 #pragma unroll 1
-      for (int c = 0; c < kFaHD / 32; ++c) {
+      for (int c = 0; c < HD / 32; ++c) {
         uint32_t ov[32];
         tc5::ld32(lane_addr + uint32_t(128 + c * 32), ov);       // (all lanes of the warp take part in the load)
         tc5::ld_wait();
@@ -363,10 +374,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
 using namespace kvcm;
 
-// 1 if the tcgen05 prefill kernel takes these sizes: head_dim 64; pages of 8, 16, 32 or 64 keys, or a
+// 1 if the tcgen05 prefill kernel takes these sizes: head_dim 64 or 128; pages of 8, 16, 32 or 64 keys, or a
 // multiple of 64 (up to 256, the largest box).
 KVCM_API int kvcm_attention_tcgen05_supports(int hd, int block_size) {
-  if (hd != kFaHD || block_size < 8 || block_size > 256) return 0;
+  if ((hd != 64 && hd != 128) || block_size < 8 || block_size > 256) return 0;
   return block_size <= kFaKeys ? (kFaKeys % block_size) == 0 && (block_size % 8) == 0 : (block_size % kFaKeys) == 0;
 }
 
@@ -399,14 +410,27 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
   p.seq_q_start = seq_q_start; p.seq_q_len = seq_q_len; p.seq_ctx_len = seq_ctx_len;
   p.nh = nh; p.nkv = nkv; p.block_size = block_size; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
-  const size_t smem = size_t(3) * kFaTileBytes + size_t(2) * kFaStages * kFaKvBytes;     // 112 KB: two blocks fit an SM exactly
+  const int KB = hd / 64;
+  // 112 KB at head_dim 64 (two blocks fit an SM exactly), 192 KB at 128
+  const size_t smem = size_t(KB + 2) * kFaTileBytes + size_t(2) * kFaStages * KB * kFaKvBlock;
+  const dim3 grid(nh, tiles), block(kFaThreads);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (hd == 64) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return int(e);
+      configured = true;
+    }
+    return pdl_launch(attn_prefill_tc_kernel<64>, grid, block, smem, s, mq, mk, mv, p);
+  }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  return pdl_launch(attn_prefill_tc_kernel, dim3(nh, tiles), dim3(kFaThreads), smem, (cudaStream_t)stream, mq, mk, mv, p);
+  return pdl_launch(attn_prefill_tc_kernel<128>, grid, block, smem, s, mq, mk, mv, p);
 }
 
 // Reads and clears the error word of the kernel (0 = no bounded wait ever ran out); else

@@ -342,7 +342,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                       window: int = 0) -> None:
     """Rows of portions longer than one token; q/out are the step's full row arrays.
     ``ctx.options['attn_prefill']``: 'tcgen05' | 'mma' force a kernel; 'auto' takes the tcgen05
-    kernel where it supports the sizes (head_dim 64; pages of 8 to 64 keys dividing 64, or multiples of 64)."""
+    kernel where it supports the sizes (head_dim 64 or 128; pages of 8 to 64 keys dividing 64, or multiples of 64)."""
     _cuda(q, out, k_cache, v_cache, block_tables)
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16,
           "attention_prefill: bfloat16 only")

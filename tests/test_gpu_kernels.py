@@ -477,18 +477,18 @@ def test_attention_kernels_on_a_mixed_batch(nh, nkv, hd, B, window):
 
 
 @pytest.mark.parametrize("B", [8, 16, 32, 64, 128])
-@pytest.mark.parametrize("window", [0, 150])
-def test_prefill_attention_on_tcgen05(B, window):
-    """The tcgen05 prefill kernel (head_dim 64) against float64 and against the mma.sync kernel:
-    portions that start anywhere, end anywhere, are shorter than a tile, span several key tiles,
-    with pages of every supported size, beside decode rows."""
-    nh, nkv, hd = 8, 2, 64
+@pytest.mark.parametrize("window,hd", [(0, 64), (150, 64), (0, 128), (90, 128)])
+def test_prefill_attention_on_tcgen05(B, window, hd):
+    """The tcgen05 prefill kernel (head_dim 64 and 128) against float64 and against the mma.sync
+    kernel: portions that start anywhere, end anywhere, are shorter than a tile, span several key
+    tiles, with pages of every supported size, beside decode rows."""
+    nh, nkv = (8, 2) if hd == 64 else (6, 3)
     lib = K()
-    assert lib.prefill_tcgen05_supported(hd, B) and not lib.prefill_tcgen05_supported(128, B)
+    assert lib.prefill_tcgen05_supported(hd, B) and not lib.prefill_tcgen05_supported(96, B)
     seq_lens = [300, 129, 128, 640, 70, 2, 513, 1]
     q_lens = [300, 129, 1, 131, 64, 2, 257, 1]
     scale = 1.0 / math.sqrt(hd)
-    case = paged_case(seq_lens, q_lens, nh, nkv, hd, B, "bfloat16", seed=B + window)
+    case = paged_case(seq_lens, q_lens, nh, nkv, hd, B, "bfloat16", seed=B + window + hd)
     ref = reference_attention(case, nh, nkv, hd, scale, window)
     got = {}
     for mode in ("tcgen05", "mma"):
