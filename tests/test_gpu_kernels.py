@@ -313,6 +313,53 @@ def test_tcgen05_gemm(M, N, Kd):
     assert not lib.tcgen05_gemm_supported(x[:, :Kd - 4], w[:, :Kd - 4])               # K not a multiple of 8
 
 
+@pytest.mark.parametrize("M,N,Kd,bn", [(256, 256, 64, 0), (1, 8, 8, 0), (100, 300, 136, 0), (257, 129, 1000, 0),
+                                       (2048, 2560, 2048, 0), (640, 11264, 2048, 0), (300, 2048, 5632, 0),
+                                       (17, 32003, 96, 0), (513, 700, 264, 32), (513, 700, 264, 96), (900, 2048, 2048, 160),
+                                       (2048, 2048, 2048, 224), (2048, 2560, 2048, 288), (700, 1000, 520, 512),
+                                       (5000, 4100, 264, 352), (2304, 700, 64, 0)])
+def test_tcgen05_pair_gemm(M, N, Kd, bn):
+    """The two-SM kernel (tcgen05.mma.cta_group::2, tiles of 256 x bn over a pair of blocks) against
+    float64 at every tile width; ragged edges in every dimension; many tiles per pair."""
+    lib = K()
+    g = torch.Generator().manual_seed(M + N + bn)
+    x = torch.randn(M, Kd + 8, generator=g).to(torch.bfloat16).to(DEV)[:, :Kd]        # strided rows
+    w = (torch.randn(N, Kd, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    assert lib.pair_gemm_supported(x, w)
+    ref = x.double().cpu() @ w.double().cpu().T
+    for out_dt in (torch.bfloat16, torch.float32):
+        y = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
+        lib.gemm_tcgen05_pair(x, w, y, bn)
+        assert lib.pair_error() == 0
+        d = (y.double().cpu() - ref).abs().max().item()
+        bound = (0.01 if out_dt == torch.bfloat16 else 1e-3) * max(ref.abs().max().item(), 1e-3)
+        assert d <= bound, f"{out_dt}: {d} > {bound}"
+    assert not lib.pair_gemm_supported(x[:, :Kd - 4], w[:, :Kd - 4])                  # K not a multiple of 8
+    with pytest.raises(lib.KernelError):
+        lib.gemm_tcgen05_pair(x, w, y, 48)                                            # no such tile width
+
+
+@pytest.mark.parametrize("M,H,I,bn", [(2048, 2048, 5632, 0), (300, 96, 1000, 0), (129, 64, 24, 0), (640, 256, 128, 64),
+                                      (700, 136, 344, 128), (512, 2048, 1000, 192), (700, 136, 344, 320),
+                                      (1100, 264, 1000, 512)])
+def test_tcgen05_pair_gate_up_with_the_activation_in_its_epilogue(M, H, I, bn):
+    """Bit for bit the two-SM product followed by the activation kernel, and close to float64."""
+    lib = K()
+    g = torch.Generator().manual_seed(M + I + bn)
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
+    lib.gemm_tcgen05_pair(x, w, gu)
+    a1 = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    lib.silu_mul(gu, a1)
+    a2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lib.gate_up_silu_tcgen05_pair(x, w, a2, bn)
+    assert lib.pair_error() == 0
+    assert torch.equal(a1, a2)
+    gg = (x.double().cpu() @ w.double().cpu().T)
+    close(a2, gg[:, :I] * torch.sigmoid(gg[:, :I]) * gg[:, I:], "bfloat16", "against float64")
+
+
 def test_skinny_gemm_refuses_what_it_cannot_run():
     lib = K()
     assert not lib.skinny_gemm_supported(17, 64, 64)                # too many rows
