@@ -21,7 +21,10 @@
 // products side by side into one accumulator, in a four-stage ring) chosen on the host for
 // the least estimated time: wide enough for L2, narrow enough that the last round of pairs is full.
 // Tiles are walked row-major, or in bands of eight row tiles when W is too large to stay in L2
-// (pair_tile).  Rows, columns and k beyond the matrices are
+// (pair_tile).  When the tiles do not fill the last round of pairs, the pairs instead take equal
+// shares of all (tile, k-step) units (PairWalk): a pair that starts in the middle of a tile's k
+// range leaves float partial sums in a workspace, the pair that began the tile adds them in a
+// fixed order in its epilogue, so the result does not depend on timing.  Rows, columns and k beyond the matrices are
 // zero-filled by the TMA unit: any M, N and any K that is a multiple of 8 work.  Every wait on an
 // mbarrier is bounded; when one runs out the block records it (kvcm_gemm_tcgen05_pair_error),
 // stops waiting, and both blocks meet at the cluster barrier, free their tensor memory and leave.
@@ -109,10 +112,48 @@ __device__ __forceinline__ void pair_tile(int t, int m_tiles, int n_tiles, int b
   nt = rem / rows;
 }
 
+// The pieces of work of one pair, in order.  Tile by tile (pair, pair + pairs, ... of the walk), or
+// with `split` an equal share of all (tile, k-step) units: the pair's first piece may then start in
+// the middle of a tile's k range (it leaves partial sums in a workspace) and its last may end in
+// the middle of one (it collects the partial sums of the pairs after it, who made them first).
+struct PairWalk {
+  int nk, tiles, pairs, pair_id, tl;
+  bool split;
+  long long u, u1;
+  __device__ PairWalk(int nk_, int tiles_, int pairs_, int pair_id_, bool split_)
+      : nk(nk_), tiles(tiles_), pairs(pairs_), pair_id(pair_id_), tl(0), split(split_) {
+    const long long total = (long long)tiles * nk;
+    u = total * pair_id / pairs;
+    u1 = total * (pair_id + 1) / pairs;
+  }
+  // First unit of pair q's share.
+  __device__ long long first_unit(int q) const { return (long long)tiles * nk * q / pairs; }
+  __device__ bool next(int& t, int& kb, int& ke) {
+    if (!split) {
+      t = pair_id + tl * pairs;
+      if (t >= tiles) return false;
+      ++tl;
+      kb = 0;
+      ke = nk;
+      return true;
+    }
+    if (u >= u1) return false;
+    t = int(u / nk);
+    kb = int(u - (long long)t * nk);
+    const long long left = u1 - u;
+    ke = (nk - kb) <= left ? nk : kb + int(left);
+    u += ke - kb;
+    return true;
+  }
+};
+
+constexpr int kPairPartFloats = 128 * kPairAccCols;      // one block's rows of one accumulator
+
 template <typename OutT, bool GATED, bool WIDE>
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                         OutT* __restrict__ Y, int M, int N, int K, int ldy, int BN, int band_rows) {
+                         OutT* __restrict__ Y, int M, int N, int K, int ldy, int BN, int band_rows,
+                         float* __restrict__ part, int* __restrict__ part_flag) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ __align__(8) uint64_t full[kPairStages], empty[kPairStages], acc_full[2], acc_empty[2];
@@ -132,7 +173,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   const int m_tiles = (M + 2 * kPairBM - 1) / (2 * kPairBM), n_tiles = (N + bnout - 1) / bnout;
   const int tiles = m_tiles * n_tiles;
   const int nk = (K + kPairBK - 1) / kPairBK;
-  const int my_tiles = pair_id < tiles ? (tiles - 1 - pair_id) / pairs + 1 : 0;
+  const bool split = part != nullptr;                          // equal shares of (tile, k-step) units
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -164,9 +205,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       const uint32_t full0 = pair::map_to_rank(tc5::s32(&full[0]), 0);
       const uint32_t stage_tx = 2u * uint32_t(kPairABytes + nmma * b_rows * kPairBK * 2);   // both blocks' bytes
       int s = 0, round = 0;                        // stage, and how often the ring has been walked
-      for (int tl = 0; tl < my_tiles && !abort_flag; ++tl) {
+      PairWalk walk(nk, tiles, pairs, pair_id, split);
+      int t, kb, ke;
+      while (!abort_flag && walk.next(t, kb, ke)) {
         int mt, nt;
-        pair_tile(pair_id + tl * pairs, m_tiles, n_tiles, band_rows, mt, nt);
+        pair_tile(t, m_tiles, n_tiles, band_rows, mt, nt);
         const int m0 = mt * 2 * kPairBM + int(rank) * kPairBM;
         const int n0 = nt * bnout;
         // rows of W for product j: with one product the leading block holds the left half of its
@@ -179,7 +222,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           w_row[0] = n0 + int(rank) * b_rows;
           w_row[1] = n0 + n_mma + int(rank) * b_rows;
         }
-        for (int k = 0; k < nk; ++k) {
+        for (int k = kb; k < ke; ++k) {
           if (!tc5::mbar_wait(&empty[s], (round & 1) ^ 1)) {
             atomicExch(&g_pair_error, (1 << 16) | int(blockIdx.x & 0xffff));
             abort_flag = 1;
@@ -200,7 +243,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = tc5::idesc(2 * kPairBM, n_mma);
       int s = 0, round = 0;
-      for (int tl = 0; tl < my_tiles && !abort_flag; ++tl) {
+      PairWalk walk(nk, tiles, pairs, pair_id, split);
+      int t, kb, ke;
+      for (int tl = 0; !abort_flag && walk.next(t, kb, ke); ++tl) {
         const int acc = tl % nacc;
         // both epilogues must have drained this accumulator (the tile that used it before)
         if (!pair::wait_cluster(&acc_empty[acc], ((tl / nacc) & 1) ^ 1)) {
@@ -210,7 +255,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         }
         tc5::fence_after();
         const uint32_t d_tmem = tmem + uint32_t(acc * kPairAccCols);
-        for (int k = 0; k < nk; ++k) {
+        for (int k = kb; k < ke; ++k) {
           if (!tc5::mbar_wait(&full[s], round & 1)) {
             atomicExch(&g_pair_error, (2 << 16) | int(blockIdx.x & 0xffff));
             abort_flag = 1;
@@ -225,7 +270,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #pragma unroll
             for (int j = 0; j < kPairBK / 16; ++j)
               pair::mma(d_tmem + uint32_t(h * n_mma), da + uint64_t(2 * j), dbh + uint64_t(2 * j), idesc,
-                        (k > 0 || j > 0) ? 1u : 0u);
+                        (k > kb || j > 0) ? 1u : 0u);
           }
           pair::commit_both(&empty[s]);           // the slot is free in both blocks once these have read it
           if (++s == stages) s = 0, ++round;
@@ -238,10 +283,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     // ---- epilogue: this warp reads lanes 32*(warp % 4) .. +31 of this block's accumulator
     const int quarter = warp & 3;
     const uint32_t acc_empty0 = pair::map_to_rank(tc5::s32(&acc_empty[0]), 0);
-    for (int tl = 0; tl < my_tiles; ++tl) {
+    // Partial sums of a piece that does not start its tile's k range: slot (pair, block), laid out
+    // [chunk of 32 columns][quarter][column in chunk][lane] so that a warp writes and reads whole
+    // lines; one flag per (pair, block, quarter): 1 = written, put back to 0 by the reader.
+    const size_t part_slot = (size_t(pair_id) * 2 + rank) * kPairPartFloats;
+    PairWalk walk(nk, tiles, pairs, pair_id, split);
+    int t, kb, ke;
+    for (int tl = 0; walk.next(t, kb, ke); ++tl) {
       const int acc = tl % nacc;
       int mt, nt;
-      pair_tile(pair_id + tl * pairs, m_tiles, n_tiles, band_rows, mt, nt);
+      pair_tile(t, m_tiles, n_tiles, band_rows, mt, nt);
       const int m0 = mt * 2 * kPairBM + int(rank) * kPairBM, n0 = nt * bnout;
       if (abort_flag || !tc5::mbar_wait(&acc_full[acc], (tl / nacc) & 1)) {
         if (!abort_flag && lane == 0) atomicExch(&g_pair_error, (3 << 16) | int(blockIdx.x & 0xffff));
@@ -251,59 +302,152 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       tc5::fence_after();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t tbase = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(acc * kPairAccCols);
+      if (kb > 0) {
+        // the later part of a tile's k range: leave the sums for the pair that began the tile
+        float* dst = part + part_slot + size_t(quarter) * 1024 + lane;
 #pragma unroll 1
-      for (int c = 0; c < bnout / 32; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= N) break;                                  // warp-uniform
-        if constexpr (GATED) {
-          uint32_t g[32], u[32];
-          tc5::ld32(tbase + uint32_t(c * 32), g);
-          tc5::ld32(tbase + uint32_t(bnout + c * 32), u);
-          tc5::ld_wait();
-          if (row < M) {
-            bf16* dst = reinterpret_cast<bf16*>(Y) + size_t(row) * ldy + col0;
-            __nv_bfloat162 h2[16];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float xa = Store<bf16>::round(__uint_as_float(g[i])), xb = Store<bf16>::round(__uint_as_float(u[i]));
-              const float sl = Store<bf16>::round(xa / (1.f + expf(-xa)));
-              const bf16 y = __float2bfloat16_rn(sl * xb);
-              if (i & 1) h2[i / 2].y = y; else h2[i / 2].x = y;
-            }
-            if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(h2)[i];
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col0 + i < N) dst[i] = (i & 1) ? h2[i / 2].y : h2[i / 2].x;
-            }
-          }
-        } else {
+        for (int c = 0; c < BN / 32; ++c) {
           uint32_t v[32];
           tc5::ld32(tbase + uint32_t(c * 32), v);
           tc5::ld_wait();
-          if (row < M) {
-            OutT* dst = Y + size_t(row) * ldy + col0;
-            if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-              if constexpr (sizeof(OutT) == 2) {
-                uint4 packed[4];
-                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(packed);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) h2[i] = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-#pragma unroll
-                for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(dst)[i] = packed[i];
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          for (int i = 0; i < 32; ++i) dst[size_t(c) * 4096 + i * 32] = __uint_as_float(v[i]);
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          int* flag = part_flag + (pair_id * 2 + int(rank)) * 4 + quarter;
+          asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(flag), "r"(1) : "memory");
+        }
+      } else {
+        // which pairs hold the rest of this tile's k range (none unless this piece ends early)
+        int q_end = pair_id + 1;
+        if (ke < nk)
+          while (q_end < pairs && walk.first_unit(q_end) < (long long)(t + 1) * nk) ++q_end;
+        int have_parts = 1;
+        if (lane == 0) {
+          for (int q = pair_id + 1; q < q_end && have_parts; ++q) {
+            const int* flag = part_flag + (q * 2 + int(rank)) * 4 + quarter;
+            unsigned long long start = 0;
+            for (unsigned spin = 0;; ++spin) {
+              int f;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(f) : "l"(flag) : "memory");
+              if (f == 1) break;
+              if ((spin & 63) == 63) {
+                const unsigned long long now = tc5::now_ns();
+                if (start == 0) start = now;
+                else if (now - start > tc5::kWaitLimitNs) { have_parts = 0; break; }
               }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col0 + i < N) stf(dst + i, __uint_as_float(v[i]));
             }
           }
+        }
+        have_parts = __shfl_sync(0xffffffffu, have_parts, 0);
+        if (!have_parts) {
+          if (lane == 0) atomicExch(&g_pair_error, (5 << 16) | int(blockIdx.x & 0xffff));
+          abort_flag = 1;
+          break;
+        }
+        // The partial sums of a chunk of 32 columns are fetched one chunk ahead (a round trip to
+        // L2 takes about as long as a chunk's other work) and added in the order of the pairs.
+        const bool parts = q_end > pair_id + 1;
+        constexpr int kFetch = GATED ? 2 : 1;                  // chunks of the accumulator per chunk of output
+        float pnext[kFetch][32];
+        auto fetch = [&](int c) {
+          if (!parts || c >= bnout / 32) return;
+#pragma unroll
+          for (int h = 0; h < kFetch; ++h) {
+            const int chunk = c + h * (bnout >> 5);
+            const float* src = part + (size_t(pair_id + 1) * 2 + rank) * kPairPartFloats + size_t(chunk) * 4096 +
+                               size_t(quarter) * 1024 + lane;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pnext[h][i] = __ldcg(src + i * 32);
+            for (int q = pair_id + 2; q < q_end; ++q) {
+              src += 2 * kPairPartFloats;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) pnext[h][i] += __ldcg(src + i * 32);
+            }
+          }
+        };
+        fetch(0);
+#pragma unroll 1
+        for (int c = 0; c < bnout / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= N) break;                                  // warp-uniform
+          float pcur[kFetch][32];
+          if (parts) {
+#pragma unroll
+            for (int h = 0; h < kFetch; ++h)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) pcur[h][i] = pnext[h][i];
+            fetch(c + 1);
+          }
+          if constexpr (GATED) {
+            uint32_t g[32], u[32];
+            tc5::ld32(tbase + uint32_t(c * 32), g);
+            tc5::ld32(tbase + uint32_t(bnout + c * 32), u);
+            tc5::ld_wait();
+            if (parts) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                g[i] = __float_as_uint(__uint_as_float(g[i]) + pcur[0][i]);
+                u[i] = __float_as_uint(__uint_as_float(u[i]) + pcur[kFetch - 1][i]);
+              }
+            }
+            if (row < M) {
+              bf16* dst = reinterpret_cast<bf16*>(Y) + size_t(row) * ldy + col0;
+              __nv_bfloat162 h2[16];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float xa = Store<bf16>::round(__uint_as_float(g[i])), xb = Store<bf16>::round(__uint_as_float(u[i]));
+                const float sl = Store<bf16>::round(xa / (1.f + expf(-xa)));
+                const bf16 y = __float2bfloat16_rn(sl * xb);
+                if (i & 1) h2[i / 2].y = y; else h2[i / 2].x = y;
+              }
+              if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(h2)[i];
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < N) dst[i] = (i & 1) ? h2[i / 2].y : h2[i / 2].x;
+              }
+            }
+          } else {
+            uint32_t v[32];
+            tc5::ld32(tbase + uint32_t(c * 32), v);
+            tc5::ld_wait();
+            if (parts) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + pcur[0][i]);
+            }
+            if (row < M) {
+              OutT* dst = Y + size_t(row) * ldy + col0;
+              if (col0 + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                if constexpr (sizeof(OutT) == 2) {
+                  uint4 packed[4];
+                  __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(packed);
+#pragma unroll
+                  for (int i = 0; i < 16; ++i) h2[i] = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(dst)[i] = packed[i];
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i)
+                    reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < N) stf(dst + i, __uint_as_float(v[i]));
+              }
+            }
+          }
+        }
+        // the partial sums have been read: their slots are free for the next launch
+        if (parts) {
+          __syncwarp();
+          if (lane == 0)
+            for (int q = pair_id + 1; q < q_end; ++q) part_flag[(q * 2 + int(rank)) * 4 + quarter] = 0;
         }
       }
       // this warp has read its lanes of the accumulator: tell the leading block's tensor-core thread
@@ -350,18 +494,23 @@ int pair_capacity(Kernel kernel) {
   return n;
 }
 
-// The tile width (accumulator columns) with the least estimated time, among widths whose products
-// are multiples of 64 columns (the tensor cores take a narrower one in the same time).  Per k-step
-// a tile costs the larger of the tensor cores' time (2 clocks per column) and the time to bring its
-// operands from L2 (measured: about a clock per row and half-column, at least 420); tiles wider
-// than 256 columns fill tensor memory, so their epilogue (about 12 clocks per column) is not hidden
-// behind the next tile.
-inline int pair_choose_bn(int M, int N, int K, int pairs, bool gated) {
+// The tile width (accumulator columns) and the kind of walk with the least estimated time, among
+// widths whose products are multiples of 64 columns (the tensor cores take a narrower one in the
+// same time).  Per k-step a tile costs the larger of the tensor cores' time (2 clocks per column)
+// and the time to bring its operands from L2 (measured: about a clock per row and half-column, at
+// least 420); tiles wider than 256 columns fill tensor memory, so their epilogue (about 12 clocks
+// per column) is not hidden behind the next tile.  Equal shares of (tile, k-step) units of 256-wide
+// tiles cost their k-steps, the epilogue, and the partial sums written and read.
+struct PairPlan {
+  int bn;
+  bool split;
+};
+inline PairPlan pair_plan(int M, int N, int K, int pairs, bool gated, bool may_split) {
   const long long m_tiles = (M + 2 * kPairBM - 1) / (2 * kPairBM);
   const long long nk = (K + kPairBK - 1) / kPairBK;
   const int widths[5] = {256, 512, 384, 192, 128};
   double best_cost = -1;
-  int best = 256;
+  PairPlan best = {256, false};
   for (int bn : widths) {
     const int bnout = gated ? bn / 2 : bn;
     const long long tiles = m_tiles * ((N + bnout - 1) / bnout);
@@ -372,7 +521,15 @@ inline int pair_choose_bn(int M, int N, int K, int pairs, bool gated) {
     const double per_k = bn > 256 ? tc : (tc > l2 ? tc : l2);
     const double epi = 12.0 * bn;
     const double cost = rounds * nk * per_k + (bn > 256 ? rounds * epi : epi);
-    if (best_cost < 0 || cost < best_cost * 0.98) best_cost = cost, best = bn;
+    if (best_cost < 0 || cost < best_cost * 0.98) best_cost = cost, best = {bn, false};
+    if (bn == 256 && may_split && tiles * nk >= pairs) {
+      // a pair's share of k-steps, its epilogue, one partial sum written (about 4,000 clocks at an
+      // SM's bandwidth to L2) and those of the tile's other pairs read
+      const double share = double((tiles * nk + pairs - 1) / pairs);
+      const double others = share >= nk ? 1.0 : double(nk) / share;
+      const double cost_split = share * per_k + epi + 4000.0 * (1.0 + others);
+      if (cost_split < best_cost * 0.95) best_cost = cost_split, best = {bn, true};
+    }
   }
   return best;
 }
@@ -380,7 +537,7 @@ inline int pair_choose_bn(int M, int N, int K, int pairs, bool gated) {
 // GATED: N is the number of output columns; W has 2N rows.  bn: 0 = choose.
 template <typename OutT, bool GATED, bool WIDE>
 int launch_pair_as(const CUtensorMap& mx, const CUtensorMap& mw, void* Y, int M, int N, int K, int ldy, int bn, int band,
-                   int grid_pairs, cudaStream_t s) {
+                   int grid_pairs, float* part, int* part_flag, cudaStream_t s) {
   auto kernel = gemm_tcgen05_pair_kernel<OutT, GATED, WIDE>;
   static bool configured = false;
   if (!configured) {
@@ -389,22 +546,46 @@ int launch_pair_as(const CUtensorMap& mx, const CUtensorMap& mw, void* Y, int M,
     configured = true;
   }
   return pdl_launch_cluster(kernel, dim3(2 * grid_pairs), dim3(kPairThreads), kPairSmem, s, 2, mx, mw,
-                            reinterpret_cast<OutT*>(Y), M, N, K, ldy, bn, band);
+                            reinterpret_cast<OutT*>(Y), M, N, K, ldy, bn, band, part, part_flag);
 }
 
+// The workspace of the split walk: partial sums and flags of `slots` pairs (see the kernel).
+struct PairWorkspace {
+  float* part;
+  int* flag;
+  int slots;
+};
+
 template <typename OutT, bool GATED>
-int launch_pair(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy, int bn,
-                int band, cudaStream_t s) {
+int pair_capacity_of() {
   static int pairs = -1;
   if (pairs < 0) {
     auto kernel = gemm_tcgen05_pair_kernel<OutT, GATED, false>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPairSmem));
-    if (e != cudaSuccess) return int(e);
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPairSmem)) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
     pairs = pair_capacity(kernel);
   }
+  return pairs;
+}
+
+// bn, band: 0 = chosen here.  split: -1 = chosen here, 0 = tile by tile, 1 = equal shares of k-steps.
+template <typename OutT, bool GATED>
+int launch_pair(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy, int bn,
+                int band, int split, PairWorkspace ws, cudaStream_t s) {
+  const int pairs = pair_capacity_of<OutT, GATED>();
   if (pairs <= 0) return KVCM_ERR_UNSUPPORTED;
-  if (bn == 0) bn = pair_choose_bn(M, N, K, pairs, GATED);
-  if (bn < 32 || bn > 512 || bn % (GATED ? 64 : 32)) return KVCM_ERR_UNSUPPORTED;
+  const bool have_ws = ws.part != nullptr && ws.flag != nullptr && ws.slots >= pairs;
+  if (split == 1 && (!have_ws || bn > 256)) return KVCM_ERR_UNSUPPORTED;
+  if (bn == 0) {
+    const PairPlan plan = pair_plan(M, N, K, pairs, GATED, have_ws && split != 0);
+    bn = plan.bn;
+    if (split < 0) split = plan.split;
+    else if (split == 1) bn = 256;
+  }
+  if (split < 0) split = 0;
+  if (bn < 32 || bn > 512 || bn % (GATED ? 64 : 32) || (split && bn > 256)) return KVCM_ERR_UNSUPPORTED;
   if (band == 0) band = (long long)(GATED ? 2 * N : N) * K * 2 > kPairWInL2 ? 8 : 1;
   if (band < 1) return KVCM_ERR_UNSUPPORTED;
   CUtensorMap mx, mw;
@@ -414,9 +595,12 @@ int launch_pair(const void* X, const void* W, void* Y, int M, int N, int K, int 
   if (rc) return rc;
   const int bnout = GATED ? bn / 2 : bn;
   const long long tiles = (long long)((M + 2 * kPairBM - 1) / (2 * kPairBM)) * ((N + bnout - 1) / bnout);
-  const int grid_pairs = int(tiles < pairs ? tiles : pairs);
-  return bn > 256 ? launch_pair_as<OutT, GATED, true>(mx, mw, Y, M, N, K, ldy, bn, band, grid_pairs, s)
-                  : launch_pair_as<OutT, GATED, false>(mx, mw, Y, M, N, K, ldy, bn, band, grid_pairs, s);
+  const long long units = split ? tiles * ((K + kPairBK - 1) / kPairBK) : tiles;   // every pair gets at least one
+  const int grid_pairs = int(units < pairs ? units : pairs);
+  float* part = split ? ws.part : nullptr;
+  int* flag = split ? ws.flag : nullptr;
+  return bn > 256 ? launch_pair_as<OutT, GATED, true>(mx, mw, Y, M, N, K, ldy, bn, band, grid_pairs, part, flag, s)
+                  : launch_pair_as<OutT, GATED, false>(mx, mw, Y, M, N, K, ldy, bn, band, grid_pairs, part, flag, s);
 }
 
 inline bool pair_operands_ok(const void* X, const void* W, int M, int N, int K, int ldx, int ldw) {
@@ -432,25 +616,38 @@ KVCM_API int kvcm_gemm_tcgen05_pair_supports(int M, int N, int K, int ldx, int l
   return M >= 1 && N >= 1 && K >= 8 && (K % 8) == 0 && (ldx % 8) == 0 && (ldw % 8) == 0;
 }
 
+// How many pairs of blocks run at a time (the workspace of the split walk holds as many slots), and
+// the sizes of a slot: floats of partial sums, flags.
+KVCM_API int kvcm_gemm_tcgen05_pair_capacity(void) { return pair_capacity_of<bf16, false>(); }
+KVCM_API int kvcm_gemm_tcgen05_pair_slot_floats(void) { return 2 * kPairPartFloats; }
+KVCM_API int kvcm_gemm_tcgen05_pair_slot_flags(void) { return 8; }
+
 // out_f32: 0 = bfloat16 result, 1 = float result.  bn: tile width (multiple of 32 up to 512),
-// 0 = chosen here.  band: row tiles walked together (1 = row-major walk), 0 = chosen here.
+// band: row tiles walked together (1 = row-major walk); 0 = chosen here.  split: 1 = the pairs take
+// equal shares of all (tile, k-step) units and add partial sums through the workspace (`part`:
+// slots x slot_floats floats, `part_flag`: slots x slot_flags zeroed ints, both private to the
+// stream), 0 = tile by tile, -1 = chosen here.
 KVCM_API int kvcm_gemm_tcgen05_pair_bf16(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw,
-                                         int ldy, int out_f32, int bn, int band, void* stream) {
+                                         int ldy, int out_f32, int bn, int band, int split, void* part,
+                                         void* part_flag, int slots, void* stream) {
   if (M == 0 || N == 0) return 0;
   if (!pair_operands_ok(X, W, M, N, K, ldx, ldw)) return KVCM_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
-  return out_f32 ? launch_pair<float, false>(X, W, Y, M, N, K, ldx, ldw, ldy, bn, band, s)
-                 : launch_pair<bf16, false>(X, W, Y, M, N, K, ldx, ldw, ldy, bn, band, s);
+  const PairWorkspace ws = {static_cast<float*>(part), static_cast<int*>(part_flag), slots};
+  return out_f32 ? launch_pair<float, false>(X, W, Y, M, N, K, ldx, ldw, ldy, bn, band, split, ws, s)
+                 : launch_pair<bf16, false>(X, W, Y, M, N, K, ldx, ldw, ldy, bn, band, split, ws, s);
 }
 
 // act[M, I] = silu(X Wg^T) * (X Wu^T) with Wg, Wu the halves of W [2I, K] (gate rows first), the
 // roundings of the separate product and activation kernels; bfloat16.  bn: accumulator columns per
-// tile (multiple of 64 up to 512: half of them gate, half up), 0 = chosen here.
+// tile (multiple of 64 up to 512: half of them gate, half up); the other arguments as above.
 KVCM_API int kvcm_gate_up_silu_tcgen05_pair_bf16(const void* X, const void* W, void* Y, int M, int I, int K, int ldx,
-                                                 int ldw, int ldy, int bn, int band, void* stream) {
+                                                 int ldw, int ldy, int bn, int band, int split, void* part,
+                                                 void* part_flag, int slots, void* stream) {
   if (M == 0 || I == 0) return 0;
   if (!pair_operands_ok(X, W, M, I, K, ldx, ldw)) return KVCM_ERR_UNSUPPORTED;
-  return launch_pair<bf16, true>(X, W, Y, M, I, K, ldx, ldw, ldy, bn, band, (cudaStream_t)stream);
+  const PairWorkspace ws = {static_cast<float*>(part), static_cast<int*>(part_flag), slots};
+  return launch_pair<bf16, true>(X, W, Y, M, I, K, ldx, ldw, ldy, bn, band, split, ws, (cudaStream_t)stream);
 }
 
 // Reads and clears the error word (0 = no bounded wait ever ran out).  Synchronises the device.

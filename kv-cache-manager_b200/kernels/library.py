@@ -547,10 +547,35 @@ def pair_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and bool(_lib().kvcm_gemm_tcgen05_pair_supports(x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0))))
 
 
-def gemm_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, bn: int = 0, band: int = 0) -> None:
+_pair_workspaces: dict = {}
+
+
+def _pair_workspace(device: torch.device, split: int):
+    """Partial sums and flags of the two-SM kernel's split walk, one set per device (the kernel's
+    launches on a device are expected on one stream at a time).  (None, None, 0) without it."""
+    if split == 0:
+        return None, None, 0
+    key = torch.device(device).index or 0
+    ws = _pair_workspaces.get(key)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None, None, 0
+        slots = int(_lib().kvcm_gemm_tcgen05_pair_capacity())
+        if slots <= 0:
+            return None, None, 0
+        part = torch.empty(slots * int(_lib().kvcm_gemm_tcgen05_pair_slot_floats()), dtype=torch.float32, device=device)
+        flag = torch.zeros(slots * int(_lib().kvcm_gemm_tcgen05_pair_slot_flags()), dtype=torch.int32, device=device)
+        ws = _pair_workspaces[key] = (part, flag, slots)
+    return ws
+
+
+def gemm_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, bn: int = 0, band: int = 0,
+                      split: int = -1) -> None:
     """y[M,N] = x[M,K] @ w[N,K]^T with 256 x bn tiles computed by pairs of SMs (tcgen05.mma.cta_group::2:
     each block of a pair loads half of the tile's rows of w).  bn: tile width, band: row tiles walked
-    together; 0 = chosen by the kernel's host side.  bfloat16 operands; bfloat16 or float32 result."""
+    together; 0 = chosen by the kernel's host side.  split: 1 = equal shares of k-steps for every
+    pair (partial sums through a workspace), 0 = whole tiles, -1 = chosen by the host side.
+    bfloat16 operands; bfloat16 or float32 result."""
     _cuda(x, w, y)
     M, K = x.shape
     N = w.shape[0]
@@ -558,13 +583,16 @@ def gemm_tcgen05_pair(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, bn: int
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and y.dtype in (torch.bfloat16, torch.float32),
           "gemm_tcgen05_pair: bfloat16 operands, bfloat16 or float32 result")
     _need(x.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1, "gemm_tcgen05_pair: rows must be dense")
+    part, flag, slots = _pair_workspace(x.device, split)
     rc = _lib().kvcm_gemm_tcgen05_pair_bf16(_p(x), _p(w), _p(y), M, N, K, x.stride(0), w.stride(0), y.stride(0),
-                                            int(y.dtype == torch.float32), int(bn), int(band), _stream())
-    _check(rc, "gemm_tcgen05_pair", f"(M={M}, N={N}, K={K}, bn={bn})")
+                                            int(y.dtype == torch.float32), int(bn), int(band), int(split),
+                                            _p(part) if part is not None else None,
+                                            _p(flag) if flag is not None else None, slots, _stream())
+    _check(rc, "gemm_tcgen05_pair", f"(M={M}, N={N}, K={K}, bn={bn}, split={split})")
 
 
 def gate_up_silu_tcgen05_pair(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, bn: int = 0,
-                              band: int = 0) -> None:
+                              band: int = 0, split: int = -1) -> None:
     """act[M, I] = silu(x Wg^T) * (x Wu^T) on pairs of SMs: one block of a pair loads the tile's gate
     rows, the other its up rows, and the epilogue applies the activation (the roundings of the
     separate product and activation kernels)."""
@@ -574,15 +602,19 @@ def gate_up_silu_tcgen05_pair(x: torch.Tensor, w_gate_up: torch.Tensor, act: tor
     _need(w_gate_up.shape == (2 * I, K) and act.shape[0] == M, "gate_up_silu_tcgen05_pair: shapes")
     _need(x.dtype == w_gate_up.dtype == act.dtype == torch.bfloat16, "gate_up_silu_tcgen05_pair: bfloat16 only")
     _need(x.stride(1) == 1 and w_gate_up.stride(1) == 1 and act.stride(1) == 1, "gate_up_silu_tcgen05_pair: rows must be dense")
+    part, flag, slots = _pair_workspace(x.device, split)
     rc = _lib().kvcm_gate_up_silu_tcgen05_pair_bf16(_p(x), _p(w_gate_up), _p(act), M, I, K, x.stride(0),
-                                                    w_gate_up.stride(0), act.stride(0), int(bn), int(band), _stream())
-    _check(rc, "gate_up_silu_tcgen05_pair", f"(M={M}, I={I}, K={K}, bn={bn})")
+                                                    w_gate_up.stride(0), act.stride(0), int(bn), int(band), int(split),
+                                                    _p(part) if part is not None else None,
+                                                    _p(flag) if flag is not None else None, slots, _stream())
+    _check(rc, "gate_up_silu_tcgen05_pair", f"(M={M}, I={I}, K={K}, bn={bn}, split={split})")
 
 
 def pair_error() -> int:
     """Error word of the two-SM tcgen05 kernel: 0, or (code << 16 | block) of a bounded wait that ran
     out (1: a TMA thread waited for a free stage, 2: the MMA thread waited for data, 3: an epilogue
-    waited for the accumulator, 4: the MMA thread waited for the epilogues).  Reading clears it.
+    waited for the accumulator, 4: the MMA thread waited for the epilogues, 5: an epilogue waited for
+    another pair's partial sums).  Reading clears it.
     Synchronises the device."""
     return int(_lib().kvcm_gemm_tcgen05_pair_error())
 

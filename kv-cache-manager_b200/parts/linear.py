@@ -6,10 +6,11 @@ Which kernel runs is decided by the weight's dtype, never by the model:
 * bfloat16 weight -> this engine's weight-streaming kernel for a handful of rows (decode), else
   the library GEMM (cuBLAS through ``torch.mm``, the same place where the reference calls cuBLAS);
   this engine's tcgen05 kernels for many rows on request, and for the fused gate/up product;
-  ``options['gemm']``: 'plain' forces the plain twin, 'library' cuBLAS, 'tcgen05' and 'skinny' the
-  respective kernels; 'native' never calls the library: the streaming kernel up to 16 rows, the
-  split-K tcgen05 kernel up to 255, the tiled tcgen05 kernel from 256 (slower than 'auto' where
-  'auto' takes the library: 17 to 255 rows, and tile counts that fill the SMs badly).
+  ``options['gemm']``: 'plain' forces the plain twin, 'library' cuBLAS, 'tcgen05', 'pair' and 'skinny'
+  the respective kernels; 'native' never calls the library: the streaming kernel up to 16 rows, the
+  split-K tcgen05 kernel up to 255, from 256 the tiled tcgen05 kernel (one SM per tile) or, for wide
+  outputs, its two-SM form (slower than 'auto' where 'auto' takes the library: 17 to 255 rows, and
+  tile counts that fill the SMs badly).
 """
 from __future__ import annotations
 
@@ -24,6 +25,7 @@ from .base import Part, StepContext
 STREAM_MAX_BYTES = 32 << 20
 TCGEN05_MIN_ROWS = 256
 TCGEN05_GATED_MAX_HIDDEN = 3072    # beyond, the library product plus the activation kernel is faster
+PAIR_MIN_COLS = 8192               # from here the two-SM tcgen05 kernel is faster than the one-SM kernel
 
 
 class Linear(Part):
@@ -72,6 +74,11 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, options:
     # product (2048 x 2048: 16.4 against 18.8 us, 2048 x 5632: 35.4 against 40.6 us; a Llama-3-8B
     # shaped prefill: 27 against 34 ms); the tcgen05 kernel earns its place in 'auto' where it
     # saves a kernel: the gate/up product with the activation in its epilogue (parts/mlp.py).
+    if mode == "pair" or (native and M >= TCGEN05_MIN_ROWS and N >= PAIR_MIN_COLS):
+        if K.pair_gemm_supported(x, w):
+            y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+            K.gemm_tcgen05_pair(x, w, y)
+            return y
     if mode == "tcgen05" or (native and M >= TCGEN05_MIN_ROWS):
         if K.tcgen05_gemm_supported(x, w):
             y = torch.empty((M, N), dtype=out_dtype, device=x.device)

@@ -31,7 +31,7 @@ class GatedMLP(FeedForward):
                 and K.gate_up_silu_supported(h.shape[0], self.intermediate, h.shape[1])):
             K.gate_up_silu(h, w, act)
         elif (h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ctx.options.get("fuse", True)
-              and ctx.options.get("gemm", "auto") in ("auto", "native", "tcgen05") and h.shape[0] >= TCGEN05_MIN_ROWS
+              and ctx.options.get("gemm", "auto") in ("auto", "native", "tcgen05", "pair") and h.shape[0] >= TCGEN05_MIN_ROWS
               and (ctx.options.get("gemm", "auto") != "auto"
                    or (tiles_fill_well(h.shape[0], 2 * self.intermediate, h.device)
                        and h.shape[1] <= TCGEN05_GATED_MAX_HIDDEN))
@@ -40,7 +40,12 @@ class GatedMLP(FeedForward):
             # saves the activation kernel (time ~ rows x I) and loses about a tenth of the product
             # against the library (time ~ rows x I x hidden): a win up to a hidden size of ~3,000
             # (TinyLlama shape: 84 us against 76 + 15; Llama-3-8B shape: the library wins).
-            K.gate_up_silu_tcgen05(h, w, act)
+            # Beyond that size the two-SM form of the kernel is the faster of this engine's two
+            # (Llama-3-8B shape: about 0.4 against 0.58 ms).
+            if ctx.options.get("gemm", "auto") == "pair" or h.shape[1] > TCGEN05_GATED_MAX_HIDDEN:
+                K.gate_up_silu_tcgen05_pair(h, w, act)
+            else:
+                K.gate_up_silu_tcgen05(h, w, act)
         else:
             K.silu_mul(self.gate_up.forward(h, ctx), act)
         return self.down.forward(act, ctx)

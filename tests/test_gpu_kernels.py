@@ -349,7 +349,7 @@ def test_tcgen05_pair_gate_up_with_the_activation_in_its_epilogue(M, H, I, bn):
     x = torch.randn(M, H, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
     gu = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
-    lib.gemm_tcgen05_pair(x, w, gu)
+    lib.gemm_tcgen05_pair(x, w, gu, 0, 0, 0)           # whole tiles: the same order of sums
     a1 = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
     lib.silu_mul(gu, a1)
     a2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
@@ -358,6 +358,48 @@ def test_tcgen05_pair_gate_up_with_the_activation_in_its_epilogue(M, H, I, bn):
     assert torch.equal(a1, a2)
     gg = (x.double().cpu() @ w.double().cpu().T)
     close(a2, gg[:, :I] * torch.sigmoid(gg[:, :I]) * gg[:, I:], "bfloat16", "against float64")
+
+
+@pytest.mark.parametrize("M,N,Kd", [(2048, 2560, 2048), (2048, 2048, 2048), (300, 700, 136), (256, 256, 64), (1, 8, 8),
+                                    (5000, 4100, 264), (700, 515, 4104), (257, 129, 1000), (640, 11264, 2048)])
+def test_tcgen05_pair_gemm_with_split_k_ranges(M, N, Kd):
+    """The pairs take equal shares of all (tile, k-step) units; a tile whose k range is cut is summed
+    from partial sums in a fixed order: against float64, the same bits on every run (the flags are
+    put back by their readers), and again after a launch without the split."""
+    lib = K()
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, Kd + 8, generator=g).to(torch.bfloat16).to(DEV)[:, :Kd]
+    w = (torch.randn(N, Kd, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    ref = x.double().cpu() @ w.double().cpu().T
+    for out_dt in (torch.bfloat16, torch.float32):
+        runs = []
+        for i in range(3):
+            y = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
+            lib.gemm_tcgen05_pair(x, w, y, 0, 0, 1)
+            runs.append(y)
+            if i == 1:
+                lib.gemm_tcgen05_pair(x, w, torch.empty_like(y), 0, 0, 0)
+        assert lib.pair_error() == 0
+        d = (runs[0].double().cpu() - ref).abs().max().item()
+        bound = (0.01 if out_dt == torch.bfloat16 else 1e-3) * max(ref.abs().max().item(), 1e-3)
+        assert d <= bound, f"{out_dt}: {d} > {bound}"
+        assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])
+
+
+@pytest.mark.parametrize("M,H,I", [(2048, 2048, 5632), (300, 96, 1000), (700, 4104, 344)])
+def test_tcgen05_pair_gate_up_with_split_k_ranges(M, H, I):
+    lib = K()
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    a1 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    a2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lib.gate_up_silu_tcgen05_pair(x, w, a1, 0, 0, 1)
+    lib.gate_up_silu_tcgen05_pair(x, w, a2, 0, 0, 1)
+    assert lib.pair_error() == 0
+    assert torch.equal(a1, a2)
+    gg = (x.double().cpu() @ w.double().cpu().T)
+    close(a1, gg[:, :I] * torch.sigmoid(gg[:, :I]) * gg[:, I:], "bfloat16", "against float64")
 
 
 def test_skinny_gemm_refuses_what_it_cannot_run():
