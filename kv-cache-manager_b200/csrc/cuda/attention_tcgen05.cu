@@ -61,8 +61,12 @@ __device__ __forceinline__ float fa_exp2(float x) {
   return y;
 }
 
+// Two blocks of six warps share an SM at head_dim 64.  Registers are handed out per scheduler, a
+// block's warps in fours, so two blocks of six warps need room for sixteen: at most 128 registers
+// a thread, which the bound of 256 threads asks the compiler for (with 132 registers about half of
+// the SMs took a single block).
 template <int HD>
-__global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1)
+__global__ void __launch_bounds__(HD == 64 ? 256 : kFaThreads, HD == 64 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
