@@ -1,6 +1,6 @@
 """Test helpers: the two tiny configurations, model folders, replay drivers, tolerances.
 
-tiny-A and tiny-B differ in every size and option: layers 2/3, hidden 64/96, query heads 4/3,
+tiny-A and tiny-B (and tiny-C, tiny-D for the head sizes of the tcgen05 attention kernel) differ in every size and option: layers 2/3, hidden 64/96, query heads 4/3,
 KV heads 2/1 (group 2/3), head_dim 16/32, FFN 172/256 (172 is no multiple of 16), vocabulary
 256/384, rope_theta 1e4/5e5, rms_norm_eps 1e-5/1e-6, max positions 128/256, untied/tied output
 head, page size 16/8, norm weights 1 / 1+N(0,0.1), seeds 0/1.
@@ -36,6 +36,13 @@ TINY = {
                             max_position_embeddings=512, rope_theta=250000.0, rms_norm_eps=2e-6,
                             tie_word_embeddings=False),
                    block_size=16, seed=2, norm_jitter=0.05),
+    # heads of 128 (the other width of the tcgen05 attention kernel: operands as two 64-wide blocks),
+    # pages of 32
+    "tiny-d": dict(cfg=dict(vocab_size=288, hidden_size=264, intermediate_size=520, num_hidden_layers=2,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                            max_position_embeddings=512, rope_theta=1000000.0, rms_norm_eps=3e-6,
+                            tie_word_embeddings=True),
+                   block_size=32, seed=3, norm_jitter=0.05),
 }
 
 TORCH_DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}

@@ -13,8 +13,9 @@ import plain_llama as P
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"tiny-a": [5, 17, 33, 64, 100], "tiny-b": [1, 7, 40, 100, 150, 200], "tiny-c": [3, 70, 130, 250, 193]}
-CASES = [(n, d) for n in ("tiny-a", "tiny-b") for d in ("float32", "bfloat16")] + [("tiny-c", "bfloat16")]
+LENGTHS = {"tiny-a": [5, 17, 33, 64, 100], "tiny-b": [1, 7, 40, 100, 150, 200], "tiny-c": [3, 70, 130, 250, 193],
+           "tiny-d": [2, 65, 129, 255, 200]}
+CASES = [(n, d) for n in ("tiny-a", "tiny-b") for d in ("float32", "bfloat16")] + [("tiny-c", "bfloat16"), ("tiny-d", "bfloat16")]
 
 
 @pytest.fixture(scope="module")
