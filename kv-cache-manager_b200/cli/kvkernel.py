@@ -119,7 +119,8 @@ def bench_gemm(a, out) -> None:
 
 
 def bench_gemm_large(a, out) -> None:
-    """Prefill products (many rows): this engine's tcgen05 kernel against the library product."""
+    """Prefill products (many rows): this engine's tcgen05 kernels (one SM or a pair of SMs to a
+    tile) against the library product."""
     import torch
     from ..kernels import library as K
     H, I, V = a.i32("hidden", 2048), a.i32("ffn", 5632), a.i32("vocab", 32000)
@@ -136,16 +137,21 @@ def bench_gemm_large(a, out) -> None:
             x = torch.randn(M, Kd, device=dev).to(torch.bfloat16)
             y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
             res = {"library": graph_time_us([lambda: torch.mm(x, w.t(), out=y)] * 10),
-                   "tcgen05": graph_time_us([lambda: K.gemm_tcgen05(x, w, y)] * 10)}
+                   "tcgen05": graph_time_us([lambda: K.gemm_tcgen05(x, w, y)] * 10),
+                   "pair": graph_time_us([lambda: K.gemm_tcgen05_pair(x, w, y)] * 10)}
+            if name == "gate_up":                # the same product with the activation in its epilogue
+                act = torch.empty(M, N // 2, dtype=torch.bfloat16, device=dev)
+                res["tcgen05+silu"] = graph_time_us([lambda: K.gate_up_silu_tcgen05(x, w, act)] * 10)
+                res["pair+silu"] = graph_time_us([lambda: K.gate_up_silu_tcgen05_pair(x, w, act)] * 10)
             fl = 2.0 * M * N * Kd
             print(f"M={M:<5} {name:<8} [{N} x {Kd}] " +
                   "  ".join(f"{k} {v:.1f} us ({fl / (v * 1e-6) / 1e12:.0f} TFLOP/s)" for k, v in res.items()))
             if out:
                 for k, v in res.items():
                     out.write(f"{M},{name},{N},{Kd},{k},{v:.3f},{fl / (v * 1e-6) / 1e12:.1f}\n")
-    err = K.tcgen05_error()
-    if err:
-        raise RuntimeError(f"a bounded wait of the tcgen05 kernel ran out (code {err >> 16}, block {err & 0xffff})")
+    for what, err in (("tcgen05", K.tcgen05_error()), ("two-SM tcgen05", K.pair_error())):
+        if err:
+            raise RuntimeError(f"a bounded wait of the {what} kernel ran out (code {err >> 16}, block {err & 0xffff})")
 
 
 def main(argv=None) -> int:
