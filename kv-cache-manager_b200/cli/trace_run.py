@@ -85,6 +85,10 @@ def main(argv=None) -> int:
             bad = [t for t in toks if t < 0 or t >= vocab]
             if bad:
                 raise SystemExit(f"trace_run: step {tag}: token {bad[0]} outside the vocabulary of {vocab}")
+            bad = [w for w in want if w < 0 or w >= len(toks)]
+            if bad:
+                raise SystemExit(f"trace_run: step {tag}: request {rid!r} wants place {bad[0]} of a portion of "
+                                 f"{len(toks)} tokens")
             seq = live.get(rid)
             if seq is None:
                 seq = core.Sequence()

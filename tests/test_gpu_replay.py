@@ -225,3 +225,27 @@ def test_tcgen05_products_inside_the_engine(name, model_folders, oracle):
         helpers.assert_logits_close(got, oracle(name, dtype, i), dtype, f"{name} request {i} through tcgen05")
     from kvcm.kernels import library as K
     assert K.tcgen05_error() == 0
+
+
+def test_trace_tool_refuses_with_one_line(model_folders, tmp_path):
+    """What the tool cannot run ends it with a message that names the step and the request, not
+    with a stack trace: a portion beyond the pool, a wanted place outside the portion, no tokens, a
+    token beyond the vocabulary."""
+    import json
+    import os
+    import subprocess
+    import sys
+    folder = model_folders("tiny-a", "bfloat16")
+    toks = tokens_of("tiny-a", 4)
+    cases = [([dict(step=3, entries=[dict(id="a", tokens=toks[:100], want=[99])], end=[])], "out of cache pages"),
+             ([dict(step=3, entries=[dict(id="a", tokens=toks[:10], want=[10])], end=[])], "wants place 10"),
+             ([dict(step=3, entries=[dict(id="a", tokens=[], want=[])], end=[])], "brings no tokens"),
+             ([dict(step=3, entries=[dict(id="a", tokens=[256], want=[0])], end=[])], "outside the vocabulary")]
+    for steps, message in cases:
+        p = subprocess.run([sys.executable, os.path.join(helpers.ROOT, "bin", "trace_run"), "--model", folder,
+                            "--dtype", "bfloat16", "--out", str(tmp_path), "--max-tokens", "64"],
+                           input="".join(json.dumps(s) + "\n" for s in steps), text=True,
+                           stdout=subprocess.PIPE, stderr=subprocess.PIPE, timeout=600)
+        assert p.returncode != 0 and "done 3" not in p.stdout
+        last = [l for l in p.stderr.splitlines() if l.strip()][-1]
+        assert last.startswith("trace_run: step 3:") and message in last, p.stderr[-1500:]
