@@ -65,6 +65,13 @@ __device__ __forceinline__ float fa_exp2(float x) {
 // block's warps in fours, so two blocks of six warps need room for sixteen: at most 128 registers
 // a thread, which the bound of 256 threads asks the compiler for (with 132 registers about half of
 // the SMs took a single block).
+// Blackwell's three-input maximum.
+__device__ __forceinline__ float fa_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(HD == 64 ? 256 : kFaThreads, HD == 64 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -240,10 +247,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const bool full = key0 + kFaKeys - 1 <= pos0 && (p.window <= 0 || key0 >= pos0 + kFaRows - p.window);
       float mx[2] = {-INFINITY, -INFINITY};
       if (full) {
+        // eight chains of three-input maxima, four steps deep, instead of two chains of 32
+        float part[8];
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx[c] = fmaxf(mx[c], __uint_as_float(v[c][i]));
+          for (int g = 0; g < 4; ++g) {
+            float t = fa_max3(__uint_as_float(v[c][8 * g]), __uint_as_float(v[c][8 * g + 1]), __uint_as_float(v[c][8 * g + 2]));
+            t = fa_max3(t, __uint_as_float(v[c][8 * g + 3]), __uint_as_float(v[c][8 * g + 4]));
+            t = fa_max3(t, __uint_as_float(v[c][8 * g + 5]), __uint_as_float(v[c][8 * g + 6]));
+            part[c * 4 + g] = fmaxf(t, __uint_as_float(v[c][8 * g + 7]));
+          }
+        mx[0] = fmaxf(fa_max3(part[0], part[1], part[2]), part[3]);
+        mx[1] = fmaxf(fa_max3(part[4], part[5], part[6]), part[7]);
       } else {
 #pragma unroll
         for (int c = 0; c < 2; ++c)
@@ -285,12 +301,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tc5::st_wait();
         l *= alpha;
       }
-      // the buffer of P_n was last read by O += P_(n-2) V_(n-2)
-      const bool got_p = !abort_flag && tc5::mbar_wait(&p_free[n & 1], ((n >> 1) & 1) ^ 1);
-      if (!__all_sync(0xffffffffu, got_p)) {
-        if (!abort_flag && lane == 0) fail(9);
-        break;
-      }
+      // The buffer of P_n was last read by O += P_(n-2) V_(n-2).  That product was issued before
+      // S_n, and the commit that announced S_n completes only after everything issued before it:
+      // having seen S_n, this thread may write P_n without another wait.
       const float m_use = (m == -INFINITY) ? 0.f : m;           // a row that has seen no key yet
       float sum[2] = {0.f, 0.f};
       unsigned char* rowp = p_s + (n & 1) * kFaTileBytes + r * 128;
