@@ -32,7 +32,7 @@ _PKG = os.path.dirname(_HERE)
 
 CORE_SOURCES = ["core/block_allocator.cpp", "core/prefix_cache.cpp", "core/kv_manager.cpp",
                 "core/paged_manager.cpp", "core/scheduler.cpp", "core/batch.cpp",
-                "core/bindings.cpp"]
+                "core/safetensors.cpp", "core/bindings.cpp"]
 CUDA_ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

@@ -9,6 +9,7 @@
 #include "kv_manager.h"
 #include "paged_manager.h"
 #include "prefix_cache.h"
+#include "safetensors.h"
 #include "scheduler.h"
 #include "sequence.h"
 
@@ -43,6 +44,24 @@ PYBIND11_MODULE(kvcm_core, m) {
   m.def("page_hash", [](uint64_t parent, const std::vector<int32_t>& tokens) {
     return page_hash(parent, tokens.data(), static_cast<int>(tokens.size()));
   });
+
+  // One memory-mapped .safetensors file.  Faults of the file raise RuntimeError with the message.
+  py::class_<SafetensorsReader>(m, "SafetensorsReader")
+      .def(py::init<const std::string&>())
+      .def_property_readonly("path", &SafetensorsReader::path)
+      .def("names", &SafetensorsReader::names)
+      .def("has", &SafetensorsReader::has)
+      .def("metadata", [](const SafetensorsReader& r) {
+        py::dict d;
+        for (const auto& kv : r.metadata()) d[py::str(kv.first)] = py::str(kv.second);
+        return d;
+      })
+      .def("info", [](const SafetensorsReader& r, const std::string& name) {
+        const SafetensorsEntry& e = r.entry(name);
+        return py::make_tuple(e.dtype, e.shape, e.end - e.begin);
+      }, "(dtype name, shape, bytes) of a tensor")
+      .def("address", &SafetensorsReader::address, "address of the tensor's bytes inside the map")
+      .def("data_bytes", &SafetensorsReader::data_bytes);
 
   py::class_<SamplingParams>(m, "SamplingParams")
       .def(py::init<>())

@@ -11,8 +11,8 @@ the public container by tensor name replaces its Python export step
 """
 from __future__ import annotations
 
+import ctypes
 import json
-import mmap
 import os
 import struct
 from typing import Dict, Iterable, Iterator, List, Tuple
@@ -34,74 +34,44 @@ _NAMES = {v[0]: k for k, v in _DTYPES.items()}
 
 
 class SafetensorsFile:
-    """Memory-maps one ``.safetensors`` file; tensors are views into the map until copied."""
+    """One ``.safetensors`` file, opened, checked and memory-mapped by the C++ core
+    (``csrc/core/safetensors.cpp``); tensors are views into the map until copied."""
 
     def __init__(self, path: str):
+        from ..csrc.build import load_core
         self.path = path
         try:
-            self._f = open(path, "rb")
-        except OSError as e:
-            raise SafetensorsError(f"cannot open '{path}': {e.strerror}") from None
-        size = os.fstat(self._f.fileno()).st_size
-        if size < 8:
-            raise SafetensorsError(f"{path}: truncated (no header length)")
-        (n,) = struct.unpack("<Q", self._f.read(8))
-        if n > size - 8 or n > (100 << 20):
-            raise SafetensorsError(f"{path}: header length {n} does not fit the file ({size} bytes)")
-        try:
-            header = json.loads(self._f.read(n).decode("utf-8"))
-        except (UnicodeDecodeError, json.JSONDecodeError) as e:
-            raise SafetensorsError(f"{path}: header is not valid JSON ({e})") from None
-        if not isinstance(header, dict):
-            raise SafetensorsError(f"{path}: header must be a JSON object")
-        self.metadata = header.pop("__metadata__", {}) or {}
-        self._data_start = 8 + n
-        data_len = size - self._data_start
-        self.entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...], int, int]] = {}
-        for name, e in header.items():
-            try:
-                dt, isz = _DTYPES[e["dtype"]]
-                shape = tuple(int(x) for x in e["shape"])
-                b, en = (int(x) for x in e["data_offsets"])
-            except (KeyError, TypeError, ValueError):
-                raise SafetensorsError(f"{path}: bad header entry for '{name}': {e!r}") from None
-            numel = 1
-            for s in shape:
-                numel *= s
-            if b < 0 or en < b or en > data_len:
-                raise SafetensorsError(
-                    f"{path}: tensor '{name}' data_offsets [{b}, {en}) lie outside the data "
-                    f"section of {data_len} bytes (file truncated?)")
-            if en - b != numel * isz:
-                raise SafetensorsError(
-                    f"{path}: tensor '{name}' has {en - b} bytes but shape {list(shape)} of "
-                    f"{e['dtype']} needs {numel * isz}")
-            self.entries[name] = (dt, shape, b, en)
-        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if size else None
+            self._reader = load_core().SafetensorsReader(path)
+        except RuntimeError as e:
+            raise SafetensorsError(str(e)) from None
+        self.metadata = dict(self._reader.metadata())
+        self.entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...], int]] = {}
+        for name in self._reader.names():
+            dtype_name, shape, nbytes = self._reader.info(name)
+            if dtype_name not in _DTYPES:
+                raise SafetensorsError(f"{path}: tensor '{name}' has dtype {dtype_name}, which this engine does not read")
+            self.entries[name] = (_DTYPES[dtype_name][0], tuple(int(x) for x in shape), int(nbytes))
 
     def names(self) -> List[str]:
         return list(self.entries)
 
     def info(self, name: str) -> Tuple[torch.dtype, Tuple[int, ...]]:
-        dt, shape, _, _ = self.entries[name]
+        dt, shape, _ = self.entries[name]
         return dt, shape
 
     def tensor(self, name: str) -> torch.Tensor:
-        """A CPU tensor that aliases the memory map (read-only; copy before changing it)."""
-        dt, shape, b, e = self.entries[name]
-        if e == b:
+        """A CPU tensor that aliases the memory map (read-only; copy before changing it).  The
+        tensor keeps the map alive."""
+        dt, shape, nbytes = self.entries[name]
+        if nbytes == 0:
             return torch.empty(shape, dtype=dt)
-        buf = memoryview(self._mm)[self._data_start + b:self._data_start + e]
-        import warnings
-        with warnings.catch_warnings():
-            warnings.simplefilter("ignore")       # torch warns that the buffer is not writable
-            t = torch.frombuffer(buf, dtype=dt)
-        return t.reshape(shape)
+        buf = (ctypes.c_char * nbytes).from_address(self._reader.address(name))
+        buf._map_owner = self._reader                 # the map lives as long as any view of it
+        return torch.frombuffer(buf, dtype=dt).reshape(shape)
 
     def close(self) -> None:
-        # Tensors handed out keep the map alive through their buffer; drop only our handles.
-        self._mm = None
-        self._f.close()
+        # Tensors handed out keep the map alive through their buffer; drop only our handle.
+        self._reader = None
 
 
 def open_model_files(folder: str) -> List[SafetensorsFile]:

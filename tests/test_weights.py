@@ -134,3 +134,38 @@ def test_random_weights_depend_on_seed_and_name_only():
     assert abs(w.std().item() - 0.02) < 0.002 and abs(w.mean().item()) < 0.002
     j = dict(random_tensors(cfg, 3, torch.float32, norm_jitter=0.1))["model.norm.weight"]
     assert 0.03 < (j - 1).std().item() < 0.2
+
+
+def test_reader_in_the_core_keeps_the_map_alive_and_reports_header_faults(tmp_path):
+    """The C++ reader: metadata, header order, a tensor view that outlives its file object, escapes
+    in names, and one message per kind of header fault."""
+    import gc
+    p = str(tmp_path / "m.safetensors")
+    a, b = torch.randn(5, 3), torch.arange(4, dtype=torch.int32)
+    write_safetensors(p, [("layer \"0\".wé", a), ("b", b), ("empty", torch.empty(0, 7))], {"format": "pt"})
+    f = SafetensorsFile(p)
+    assert f.names() == ["layer \"0\".wé", "b", "empty"] and f.metadata == {"format": "pt"}
+    view = f.tensor("layer \"0\".wé")
+    assert f.tensor("empty").shape == (0, 7) and f.info("b") == (torch.int32, (4,))
+    f.close()
+    del f
+    gc.collect()
+    assert torch.equal(view, a)                               # the map lives while a view of it does
+
+    def header_file(header: str, data: bytes = b"") -> str:
+        q = str(tmp_path / "h.safetensors")
+        blob = header.encode()
+        open(q, "wb").write(struct.pack("<Q", len(blob)) + blob + data)
+        return q
+    for header, data, message in [
+            ('{"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}', b"\0" * 4, "outside the data section"),
+            ('{"a": {"dtype": "F32", "shape": [3], "data_offsets": [0, 8]}}', b"\0" * 8, "needs 12"),
+            ('{"a": {"dtype": "Q4", "shape": [2], "data_offsets": [0, 8]}}', b"\0" * 8, "bad header entry"),
+            ('{"a": {"dtype": "F32", "shape": [2]}}', b"\0" * 8, "bad header entry"),
+            ('{"a": {"dtype": "F32", "shape": [-2], "data_offsets": [0, 8]}}', b"\0" * 8, "bad header entry"),
+            ('[1, 2]', b"", "JSON object"),
+            ('{"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]},}', b"\0" * 8, "not valid JSON")]:
+        with pytest.raises(SafetensorsError, match=message):
+            SafetensorsFile(header_file(header, data))
+    with pytest.raises(SafetensorsError, match="cannot open"):
+        SafetensorsFile(str(tmp_path / "absent.safetensors"))
