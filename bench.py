@@ -17,9 +17,14 @@ reference's benchmark model (TinyLlama 1.1B: 22 layers, hidden 2048, 32 query / 
                 requests) over its time, against the HBM copy bandwidth;
 * ``points``    decode tokens/s at batch 1 and 64.
 
+The timed decode window is centred on a context of 1,536 tokens (the middle of 1,024 -> 2,048)
+whatever K is: prompts have ``1536 - W - K/2`` tokens, which is 1,020 for the default K = 1,000.
+
 This engine is single-GPU: for ``--gpus N`` with N > 1 it says so and exits with 2.  The
-reference arm (``--impl reference``) is unavailable: the reference is a CMake C++ project that
-``pip install`` cannot install, so there is nothing under ``baseline/_ref`` to run.
+reference arm (``--impl reference``) runs the unmodified reference, built by its own CMake project
+under ``baseline/_ref``, through its serving benchmark ``kvbench`` on a random weight file of the
+same shape, with the same prompts lengths, batch and steps (``baseline/reference_arm.py``); it
+prints the same JSON line with ``"impl": "reference"``, or one ``unavailable`` line.
 """
 from __future__ import annotations
 
@@ -40,7 +45,8 @@ MODEL = dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hid
              num_attention_heads=32, num_key_value_heads=4, head_dim=64,
              max_position_embeddings=2048, rope_theta=10000.0, rms_norm_eps=1e-5,
              tie_word_embeddings=False)
-PROMPT_LEN = 1024
+PROMPT_LEN = 1024          # of the metric; the run's own prompt length centres the timed window
+MID_CONTEXT = 1536         # middle of 1,024 -> 2,048
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 BLOCK_SIZE = 16
@@ -130,18 +136,23 @@ def build_engine(layers, batch, max_len, graphs=True, max_batched=4096):
     return cfg, spec, ec
 
 
-def decode_run(spec, ec, vocab, batch, steps, warmup, sample_clocks=False):
-    """Prefills `batch` prompts of PROMPT_LEN tokens, runs `warmup` untimed and `steps` timed decode
+def window_prompt_len(steps, warmup):
+    """Prompt length that puts the middle of the timed steps at a context of MID_CONTEXT tokens."""
+    return max(16, MID_CONTEXT - warmup - steps // 2)
+
+
+def decode_run(spec, ec, vocab, batch, steps, warmup, prompt_len, sample_clocks=False):
+    """Prefills `batch` prompts of `prompt_len` tokens, runs `warmup` untimed and `steps` timed decode
     steps through Engine.step().  Returns device ms, wall ms, copies per step, launches per step."""
     import torch
     from kvcm.engine.engine import DeviceTimer, Engine
     from kvcm.kernels import launch_count
     eng = Engine(spec, ec)
     g = torch.Generator().manual_seed(1)
-    prompts = torch.randint(3, vocab, (batch, PROMPT_LEN), generator=g).tolist()
+    prompts = torch.randint(3, vocab, (batch, prompt_len), generator=g).tolist()
     for p in prompts:
         eng.add_request(p, max_new_tokens=1 << 30)   # ends only at max_seq_len, sized with headroom
-    while eng.sched.num_waiting() or eng.sched.counters().prefill_tokens < batch * PROMPT_LEN:
+    while eng.sched.num_waiting() or eng.sched.counters().prefill_tokens < batch * prompt_len:
         eng.step()                                   # prompt portions (and the first tokens)
     for _ in range(warmup):
         info = eng.step()
@@ -213,6 +224,89 @@ def prefill_run(spec, ec, vocab, cfg, layers, reps=5):
     return ms, gemm_flops + attn_flops
 
 
+def reference_main(args) -> int:
+    """The same metric and shape through the unmodified reference (fp16, its own kvbench)."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ra
+    if args.gpus != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is a single-GPU engine"}))
+        return 0
+    steps, warmup, B = args.steps, max(args.warmup, 3), args.batch
+    layers = MODEL["num_hidden_layers"]
+    prompt_len = window_prompt_len(steps, warmup)
+    kv_per_token = 2 * 2 * layers * MODEL["num_key_value_heads"] * MODEL["head_dim"]
+    max_len = max(CONTEXT, prompt_len + warmup + steps + 64 + 16)
+    pk = peaks()
+    work = None
+    try:
+        ra.ensure_built()
+        work = ra.make_workdir()
+        wfile = os.path.join(work, "weights.bin")
+        ra.write_weight_file(wfile, MODEL, seed=0)
+        clocks = ClockSampler()
+        clocks.start()
+        main_run = ra.decode_run(wfile, B, prompt_len, steps, warmup, kv_per_token, max_len, work)
+        clk = clocks.stop()
+        pts, prefill = {}, None
+        if not args.no_points:
+            for b in (1, 64):
+                r = ra.decode_run(wfile, b, prompt_len, steps, warmup, kv_per_token, max_len, work)
+                pts[f"decode_b{b}"] = round(b * 1e3 / r["ms_per_step"], 1)
+            prefill = ra.prefill_run(wfile, PREFILL_TOKENS, 7, work)
+    except ra.ReferenceUnavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e)}))
+        return 0
+    except subprocess.TimeoutExpired:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's kvbench did not end in time"}))
+        return 0
+    finally:
+        if work:
+            import shutil
+            shutil.rmtree(work, ignore_errors=True)
+    H, I, V = MODEL["hidden_size"], MODEL["intermediate_size"], MODEL["vocab_size"]
+    qkv = (MODEL["num_attention_heads"] + 2 * MODEL["num_key_value_heads"]) * MODEL["head_dim"]
+    per_layer = qkv * H + H * H + 2 * I * H + H * I
+    weight_bytes = 2 * (per_layer * layers + V * H + (2 * layers + 1) * H)
+    ms = main_run["ms_per_step"]
+    value = B * 1e3 / ms
+    achieved = (weight_bytes + B * main_run["mean_ctx"] * kv_per_token) / (ms * 1e-3) / 1e9
+    out = {
+        "metric": "decode tokens/s (TinyLlama-1.1B shape, batch 8, 1,024-token prompts decoded towards 2,048)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(value / PUBLISHED[B], 2) if B in PUBLISHED else None,
+        "dtype": "fp16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
+        "impl": "reference",
+        "config": {"model": "TinyLlama-1.1B shape (Llama dense decoder)", "layers": layers,
+                   "layers_full": layers, "hidden": H, "heads": MODEL["num_attention_heads"],
+                   "kv_heads": MODEL["num_key_value_heads"], "head_dim": MODEL["head_dim"], "ffn": I,
+                   "vocab": V, "global_batch": B, "seq_len": CONTEXT, "prompt_len": prompt_len,
+                   "mean_context": round(main_run["mean_ctx"], 1), "kv_block": BLOCK_SIZE,
+                   "parallelism": "single GPU", "cuda_graphs": False, "gemm": "cuBLAS",
+                   "l2": "inputs larger than L2 (2.2 GB of weights read per step)",
+                   "peaks": pk["source"],
+                   "timing": "host clock of the reference's own step log (schedule, copies, forward, synchronize)"},
+        # The reference has one clock, around its whole step on the host: both figures are that one.
+        "e2e": {"value": round(value, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": int(4 * (6 * B + B * ((max_len + BLOCK_SIZE - 1) // BLOCK_SIZE))),
+                "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": 13 * layers + 4 + 2 * layers,   # src/model/llama.cpp:104-129, attention v2 adds its merge
+        "clocks": clk,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"]},
+    }
+    if pts:
+        out["points"] = pts
+    if prefill:
+        flops = 2.0 * per_layer * layers * PREFILL_TOKENS + 2.0 * V * H \
+            + 4.0 * MODEL["head_dim"] * MODEL["num_attention_heads"] * (PREFILL_TOKENS * (PREFILL_TOKENS + 1) / 2) * layers
+        out["prefill"] = {"value": round(PREFILL_TOKENS * 1e3 / prefill, 1), "tokens": PREFILL_TOKENS,
+                          "ms": round(prefill, 3),
+                          "frac": round(flops / (prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -231,10 +325,7 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a CMake C++/CUDA project without setup.py or pyproject.toml: "
-                          "pip cannot install it into baseline/_ref offline"}))
-        return 0
+        return reference_main(args)
     if args.gpus != 1:
         print(f"bench.py: this engine is single-GPU by design; --gpus {args.gpus} is not supported "
               f"(run with --gpus 1)")
@@ -248,8 +339,9 @@ def main() -> int:
         return 1
     steps, warmup, layers = args.steps, args.warmup, args.layers
     # Requests admitted first already decode while later prompts are still being prefilled.
-    head = 64 * PROMPT_LEN // 4096 + 32
-    max_len = max(CONTEXT, PROMPT_LEN + warmup + steps + head)
+    prompt_len = window_prompt_len(steps, warmup)
+    head = 64 * prompt_len // 4096 + 32
+    max_len = max(CONTEXT, prompt_len + warmup + steps + head)
     pk = peaks()
 
     cfg, spec, ec = build_engine(layers, max(args.batch, 64 if not args.no_points else args.batch),
@@ -264,7 +356,7 @@ def main() -> int:
                                       "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}}))
         return 0
 
-    main_run = decode_run(spec, ec, vocab, args.batch, steps, warmup, sample_clocks=True)
+    main_run = decode_run(spec, ec, vocab, args.batch, steps, warmup, prompt_len, sample_clocks=True)
     B = args.batch
     ms_per_step = main_run["dev_ms"] / steps
     value = B * 1e3 / ms_per_step
@@ -283,7 +375,7 @@ def main() -> int:
                    "layers_full": MODEL["num_hidden_layers"], "hidden": cfg.hidden_size,
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "ffn": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "global_batch": B, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+                   "global_batch": B, "seq_len": CONTEXT, "prompt_len": prompt_len,
                    "mean_context": round(main_run["mean_ctx"], 1), "kv_block": BLOCK_SIZE,
                    "parallelism": "single GPU", "cuda_graphs": not args.no_graphs, "gemm": args.gemm,
                    "l2": "inputs larger than L2 (2.2 GB of weights read per step)",
@@ -299,7 +391,7 @@ def main() -> int:
     if not args.no_points:
         pts = {}
         for b in (1, 64):
-            r = decode_run(spec, ec, vocab, b, steps, warmup)
+            r = decode_run(spec, ec, vocab, b, steps, warmup, prompt_len)
             pts[f"decode_b{b}"] = round(b * steps * 1e3 / r["dev_ms"], 1)
         out["points"] = pts
         ms, flops = prefill_run(spec, ec, vocab, cfg, layers)
