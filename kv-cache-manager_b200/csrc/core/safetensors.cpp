@@ -97,17 +97,28 @@ SafetensorsReader::SafetensorsReader(const std::string& path) : path_(path) {
     if (!ok) throw std::runtime_error(path + ": bad header entry for '" + name + "'");
     out.begin = off->items[0].integer;
     out.end = off->items[1].integer;
+    // Products are checked: a header like [2^32, 2^32, k] must not wrap round to a size that fits.
     long long numel = 1;
-    for (long long d : out.shape) numel *= d;
+    bool overflow = false;
+    for (long long d : out.shape) {
+      if (d < 0 || __builtin_mul_overflow(numel, d, &numel)) overflow = true;
+    }
+    long long need = 0;
+    if (!overflow && __builtin_mul_overflow(numel, static_cast<long long>(isz), &need)) overflow = true;
+    if (overflow)
+      throw std::runtime_error(path + ": tensor '" + name + "' has a shape " + shape_text(out.shape) +
+                               " whose size does not fit 63 bits");
     if (out.begin < 0 || out.end < out.begin || out.end > data_len_)
       throw std::runtime_error(path + ": tensor '" + name + "' data_offsets [" + std::to_string(out.begin) + ", " +
                                std::to_string(out.end) + ") lie outside the data section of " +
                                std::to_string(data_len_) + " bytes (file truncated?)");
-    if (out.end - out.begin != numel * isz)
+    if (out.end - out.begin != need)
       throw std::runtime_error(path + ": tensor '" + name + "' has " + std::to_string(out.end - out.begin) +
                                " bytes but shape " + shape_text(out.shape) + " of " + out.dtype + " needs " +
-                               std::to_string(numel * isz));
-    if (!entries_.count(name)) names_.push_back(name);
+                               std::to_string(need));
+    if (entries_.count(name))
+      throw std::runtime_error(path + ": tensor name '" + name + "' appears twice in the header");
+    names_.push_back(name);
     entries_[name] = std::move(out);
   }
 }

@@ -23,7 +23,10 @@ namespace {
 static __device__ __align__(256) float noalloc_scratch[KVCM_NOALLOC_SCRATCH_FLOATS];
 
 constexpr int kMaxDevices = 64;
-float* scratch_address[kMaxDevices] = {};        // device address of the array, per device
+// Device address of the array, per device.  A plain global written without a lock: two threads that
+// make their first call on a device at the same moment both look the address up and both store the
+// same value, which is harmless.
+float* scratch_address[kMaxDevices] = {};
 thread_local char last_error[512] = "";
 
 // Once per device, with that device current: the address kernels can use.

@@ -452,6 +452,12 @@ KVCM_API int kvcm_attention_prefill_tcgen05_bf16(const void* q, int q_stride, in
 
 // Reads and clears the error word of the kernel (0 = no bounded wait ever ran out); else
 // (code << 16) | block: 1 producer waited for a free stage, 2 Q, 3 K/V, 4 P, 5 S, 6 O; 7 shared memory
+// Device address of the error word (the sampling kernels copy it out with the step's tokens).
+KVCM_API const int* kvcm_attention_tcgen05_error_address(void) {
+  int* p = nullptr;
+  return cudaGetSymbolAddress((void**)&p, g_fa_error) == cudaSuccess ? p : nullptr;
+}
+
 // not aligned to 1,024 bytes; 8 a free buffer of S, 9 a free buffer of P.
 KVCM_API int kvcm_attention_tcgen05_error(void) {
   int v = 0, zero = 0;

@@ -43,6 +43,10 @@ constexpr int kXPad = 32;                              // the same for the stage
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // every wait gives up after two seconds
 
 __device__ int g_stream_error = 0;                     // 0 = ok; else (code << 16) | block
+// For tests of the failure path only: the wait limit in force, and a stage (index in a block's
+// sequence of copies) whose copy is left out, so that its consumers wait for bytes that never come.
+__device__ unsigned long long g_stream_wait_limit_ns = kWaitLimitNs;
+__device__ int g_stream_skip_stage = -1;
 
 // What happens to a finished tile of 16 output columns x M rows.
 //  kStore    : y[m][n] = sum.
@@ -88,7 +92,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 // Bounded wait for the phase with the given parity.  False = gave up after kWaitLimitNs.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns = kWaitLimitNs) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
   unsigned long long start = 0;
   for (unsigned spin = 0;; ++spin) {
     uint32_t done;
@@ -166,7 +170,10 @@ gemm_stream_kernel(StreamParams p) {
 
   // Producer warp: lane 0 announces the bytes of a stage, lanes 0..15 each copy one row of it
   // (sixteen copies issued side by side).  Stage i holds rows of tile (i / Kc) at k-chunk (i % Kc).
+  const unsigned long long wait_limit = g_stream_wait_limit_ns;
+  const int skip_stage = g_stream_skip_stage;
   auto issue = [&](int i) {
+    if (i == skip_stage) return;                              // (tests: the bytes of this stage never arrive)
     const int s = i % kStages;
     const int tile = blockIdx.x + (i / Kc) * gridDim.x;
     const int k0 = (i % Kc) * kChunk;
@@ -189,7 +196,7 @@ gemm_stream_kernel(StreamParams p) {
       const int s = issued % kStages;
       int ok = 1;
       if (lane == 0) {
-        ok = !abort_flag && mbar_wait(&empty[s], ((issued / kStages) - 1) & 1);   // consumers freed the slot?
+        ok = !abort_flag && mbar_wait(&empty[s], ((issued / kStages) - 1) & 1, wait_limit);   // consumers freed the slot?
         if (!ok && !abort_flag) {
           atomicExch(&g_stream_error, (1 << 16) | int(blockIdx.x));
           abort_flag = 1;
@@ -205,7 +212,7 @@ gemm_stream_kernel(StreamParams p) {
     if (lane == 0)
       for (int s = 0; s < kStages; ++s) {
         const int fills = issued > s ? (issued - s - 1) / kStages + 1 : 0;
-        if (fills > 0) mbar_wait(&full[s], (fills - 1) & 1, kWaitLimitNs / 4);
+        if (fills > 0) mbar_wait(&full[s], (fills - 1) & 1, wait_limit / 4);
       }
     return;
   }
@@ -255,7 +262,7 @@ gemm_stream_kernel(StreamParams p) {
         asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
       }
       const int s = i % kStages;
-      if (!abort_flag && !mbar_wait(&full[s], (i / kStages) & 1)) {
+      if (!abort_flag && !mbar_wait(&full[s], (i / kStages) & 1, wait_limit)) {
         if (lane == 0) atomicExch(&g_stream_error, (2 << 16) | int(blockIdx.x));
         abort_flag = 1;                                        // everyone stops waiting, nobody leaves a barrier alone
       }
@@ -497,6 +504,21 @@ KVCM_API int kvcm_gate_up_silu_bf16(const void* X, const void* W, void* Y, int M
 
 // The fused products (rotary/cache and gate/up epilogues) of these sizes: X is always staged there.
 KVCM_API int kvcm_gemm_stream_fused_supports(int M, int N, int K) { return stream_ok(M, N, K, current_sm_count(), false); }
+
+// Device address of the error word (the sampling kernels copy it out with the step's tokens).
+KVCM_API const int* kvcm_stream_error_address(void) {
+  int* p = nullptr;
+  return cudaGetSymbolAddress((void**)&p, g_stream_error) == cudaSuccess ? p : nullptr;
+}
+
+// Test hooks of the failure path: the wait limit (0 = the default of two seconds) and the stage
+// whose copy is left out (-1 = none).  Not for production use.
+KVCM_API int kvcm_stream_test_hooks(unsigned long long wait_limit_ns, int skip_stage) {
+  const unsigned long long limit = wait_limit_ns ? wait_limit_ns : kWaitLimitNs;
+  if (cudaMemcpyToSymbol(g_stream_wait_limit_ns, &limit, sizeof limit) != cudaSuccess) return -1;
+  if (cudaMemcpyToSymbol(g_stream_skip_stage, &skip_stage, sizeof skip_stage) != cudaSuccess) return -1;
+  return 0;
+}
 
 // Reads and clears the error word of the streaming kernels (0 = no bounded wait ever ran out).
 KVCM_API int kvcm_stream_error(void) {

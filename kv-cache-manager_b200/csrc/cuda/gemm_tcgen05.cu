@@ -314,6 +314,12 @@ KVCM_API int kvcm_gemm_tcgen05_bf16(const void* X, const void* W, void* Y, int M
                  : launch_tcgen05<bf16>(X, W, Y, M, N, K, ldx, ldw, ldy, s);
 }
 
+// Device address of the error word (the sampling kernels copy it out with the step's tokens).
+KVCM_API const int* kvcm_tcgen05_error_address(void) {
+  int* p = nullptr;
+  return cudaGetSymbolAddress((void**)&p, g_tcgen05_error) == cudaSuccess ? p : nullptr;
+}
+
 // Reads and clears the error word (0 = no bounded wait ever ran out).  Synchronises the device.
 KVCM_API int kvcm_tcgen05_error(void) {
   int v = 0, zero = 0;

@@ -650,6 +650,12 @@ KVCM_API int kvcm_gate_up_silu_tcgen05_pair_bf16(const void* X, const void* W, v
   return launch_pair<bf16, true>(X, W, Y, M, I, K, ldx, ldw, ldy, bn, band, split, ws, (cudaStream_t)stream);
 }
 
+// Device address of the error word (the sampling kernels copy it out with the step's tokens).
+KVCM_API const int* kvcm_gemm_tcgen05_pair_error_address(void) {
+  int* p = nullptr;
+  return cudaGetSymbolAddress((void**)&p, g_pair_error) == cudaSuccess ? p : nullptr;
+}
+
 // Reads and clears the error word (0 = no bounded wait ever ran out).  Synchronises the device.
 KVCM_API int kvcm_gemm_tcgen05_pair_error(void) {
   int v = 0, zero = 0;

@@ -260,6 +260,12 @@ KVCM_API int kvcm_gemm_tcgen05_splitk_bf16(const void* X, const void* W, void* Y
 
 // Reads and clears the error word of the kernel (0 = no bounded wait ever ran out); else
 // (code << 16) | block: 1 the producer waited for a free stage, 2 the products for data, 3 the
+// Device address of the error word (the sampling kernels copy it out with the step's tokens).
+KVCM_API const int* kvcm_gemm_tcgen05_splitk_error_address(void) {
+  int* p = nullptr;
+  return cudaGetSymbolAddress((void**)&p, g_splitk_error) == cudaSuccess ? p : nullptr;
+}
+
 // epilogue for the accumulator, 7 shared memory not aligned to 1,024 bytes.
 KVCM_API int kvcm_gemm_tcgen05_splitk_error(void) {
   int v = 0, zero = 0;

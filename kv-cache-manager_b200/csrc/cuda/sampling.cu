@@ -15,6 +15,25 @@
 namespace kvcm {
 
 constexpr int kSampleThreads = 1024;
+constexpr int kStatusWords = 5;
+
+// The error words of the kernel families whose waits are bounded (0 = healthy).  The sampling
+// kernels read them at the end of a step and write the first that is set beside the sampled
+// tokens, so the host learns of a wait that ran out from the copy it makes anyway.
+struct StatusWords {
+  const int* word[kStatusWords];
+};
+// status[0] = 1 + index of the first family whose word is set (0 = none), status[1] = that word.
+__device__ __forceinline__ void gather_status(const StatusWords& sw, int* status) {
+  int first = 0, value = 0;
+#pragma unroll
+  for (int i = 0; i < kStatusWords; ++i) {
+    const int v = sw.word[i] ? *reinterpret_cast<const volatile int*>(sw.word[i]) : 0;
+    if (v != 0 && first == 0) { first = i + 1; value = v; }
+  }
+  status[0] = first;
+  status[1] = value;
+}
 
 __device__ __forceinline__ void argmax_merge(float& bv, int& bi, float ov, int oi) {
   if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
@@ -61,11 +80,12 @@ __device__ void block_argmax(const float* __restrict__ row, int vocab, float& be
 }
 
 __global__ void __launch_bounds__(kSampleThreads)
-argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, StatusWords sw, int* status) {
   __shared__ float sv[32];
   __shared__ int si[32];
   pdl_launch_dependents();
   pdl_wait();
+  if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) gather_status(sw, status);
   float best;
   int index;
   block_argmax(logits + size_t(blockIdx.x) * vocab, vocab, best, index, sv, si);
@@ -85,7 +105,8 @@ __device__ __forceinline__ float sampling_uniform(unsigned long long seed, long 
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const unsigned long long* __restrict__ seed, const long long* __restrict__ request_id,
-              const int* __restrict__ position, int* __restrict__ out, int vocab) {
+              const int* __restrict__ position, int* __restrict__ out, int vocab, StatusWords sw, int* status) {
+  if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) gather_status(sw, status);
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ float part[kSampleThreads];
@@ -145,16 +166,52 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 
 using namespace kvcm;
 
-KVCM_API int kvcm_argmax_f32(const float* logits, int* out, int rows, int vocab, void* stream) {
+extern "C" {
+const int* kvcm_stream_error_address(void);
+const int* kvcm_tcgen05_error_address(void);
+const int* kvcm_gemm_tcgen05_pair_error_address(void);
+const int* kvcm_gemm_tcgen05_splitk_error_address(void);
+const int* kvcm_attention_tcgen05_error_address(void);
+}
+
+// The families in the order of the status index (1-based in status[0]): streaming product,
+// tiled tcgen05 product, two-SM product, split-K product, tcgen05 prefill attention.
+static StatusWords status_words() {
+  StatusWords sw;
+  sw.word[0] = kvcm_stream_error_address();
+  sw.word[1] = kvcm_tcgen05_error_address();
+  sw.word[2] = kvcm_gemm_tcgen05_pair_error_address();
+  sw.word[3] = kvcm_gemm_tcgen05_splitk_error_address();
+  sw.word[4] = kvcm_attention_tcgen05_error_address();
+  return sw;
+}
+
+// `status` (optional): two ints that receive the first error word that is set, see gather_status.
+KVCM_API int kvcm_argmax_status_f32(const float* logits, int* out, int rows, int vocab, int* status, void* stream) {
   if (rows == 0) return 0;
-  return pdl_launch(argmax_kernel, dim3(rows), dim3(kSampleThreads), 0, (cudaStream_t)stream, logits, out, vocab);
+  return pdl_launch(argmax_kernel, dim3(rows), dim3(kSampleThreads), 0, (cudaStream_t)stream, logits, out, vocab,
+                    status ? status_words() : StatusWords{}, status);
+}
+
+KVCM_API int kvcm_argmax_f32(const float* logits, int* out, int rows, int vocab, void* stream) {
+  return kvcm_argmax_status_f32(logits, out, rows, vocab, nullptr, stream);
+}
+
+KVCM_API int kvcm_sample_status_f32(const float* logits, const float* temperature, const unsigned long long* seed,
+                                    const long long* request_id, const int* position, int* out, int rows,
+                                    int vocab, int* status, void* stream) {
+  if (rows == 0) return 0;
+  sample_kernel<<<rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits, temperature, seed, request_id, position,
+                                                                   out, vocab, status ? status_words() : StatusWords{},
+                                                                   status);
+  return KVCM_LAUNCH_RESULT();
 }
 
 KVCM_API int kvcm_sample_f32(const float* logits, const float* temperature,
                              const unsigned long long* seed, const long long* request_id,
                              const int* position, int* out, int rows, int vocab, void* stream) {
-  if (rows == 0) return 0;
-  sample_kernel<<<rows, kSampleThreads, 0, (cudaStream_t)stream>>>(logits, temperature, seed,
-                                                                   request_id, position, out, vocab);
-  return KVCM_LAUNCH_RESULT();
+  return kvcm_sample_status_f32(logits, temperature, seed, request_id, position, out, rows, vocab, nullptr, stream);
 }
+
+// How many kernel families report through the status words, for the host's table of names.
+KVCM_API int kvcm_status_families(void) { return kStatusWords; }

@@ -39,7 +39,7 @@ def ctx_bucket(n: int) -> int:
 class _Captured:
     graph: torch.cuda.CUDAGraph
     ints: torch.Tensor
-    sampled: torch.Tensor
+    sampled: torch.Tensor     # [status pair | one token per row of the bucket]
     total_ints: int
     kernels: int = 0          # launches of this engine's kernels inside one replay
 
@@ -55,7 +55,7 @@ class DecodeGraphs:
     def run(self, sched, n: int, timer=None, sampling=None) -> torch.Tensor:
         """Runs the scheduler's current plan (n single-row entries).  ``sampling``: None when every
         entry samples greedily, else (request ids, positions, temperatures, seeds) of the entries.
-        Returns the sampled tokens on the device; the first n are real."""
+        Returns [status pair | sampled tokens] on the device; the first n tokens are real."""
         r = self.runner
         b = min(batch_bucket(n), max(r.max_seqs, n))
         layout = r.build_from_scheduler(sched, pad_rows=b, pad_seqs=b, pad_logit_rows=b)
@@ -64,7 +64,12 @@ class DecodeGraphs:
             self.sampler.stage(*sampling, rows=b)            # before a first capture too: its eager run reads them
         cap = self.captured.get(key)
         if cap is None:
+            # The capture's warm-up ran THIS step eagerly (a capture itself runs nothing) and left
+            # its tokens in the graph's buffer.  The step must not run a second time: writing a page
+            # twice is harmless, advancing a mixer's per-request state twice is not.
             cap = self._capture(layout, key)
+            self.kernels_last = cap.kernels
+            return cap.sampled
         if int(layout.total_ints) != cap.total_ints:
             raise RuntimeError("decode graph: batch layout changed for a captured shape")
         r.upload(layout, into=cap.ints, sync_follows=True)    # the engine reads the sampled tokens back
@@ -81,7 +86,7 @@ class DecodeGraphs:
         r = self.runner
         n_ints = int(layout.total_ints)
         ints = torch.zeros(n_ints, dtype=torch.int32, device=r.device)
-        sampled = torch.zeros(key[0], dtype=torch.int32, device=r.device)
+        sampled = torch.zeros(2 + key[0], dtype=torch.int32, device=r.device)
         r.upload(layout, into=ints)
         ctx = r.context(layout, ints=ints)
         ctx.max_decode_ctx = key[1]
@@ -91,12 +96,12 @@ class DecodeGraphs:
         def body():
             logits = r.forward(ctx)
             if key[2]:
-                self.sampler.sample_staged(logits, sampled)    # temperatures, seeds ... in the sampler's buffers
+                self.sampler.sample_staged(logits, sampled[2:], sampled[:2])   # temperatures, seeds ... in the sampler's buffers
             else:
-                K.argmax(logits, sampled)
+                K.argmax(logits, sampled[2:], sampled[:2])
 
         # One eager run on a side stream first: lazy initialisation (library handles, kernel
-        # attributes) must not happen inside a capture.
+        # attributes) must not happen inside a capture.  It is the real run of the step at hand.
         side = torch.cuda.Stream(device=r.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):

@@ -18,6 +18,7 @@ from ..cache import core, manager_from_config
 from ..cache.pools import bytes_per_block, plan_cache
 from ..config.engine_config import EngineConfig, canonical_dtype
 from ..models.spec import ModelSpec
+from ..kernels import library as K
 from ..sampling import Sampler
 from .decode_graph import DecodeGraphs
 from .model_io import load_model, torch_dtype
@@ -154,8 +155,8 @@ class Engine:
             ids, pos, temps, seeds = self.sched.plan_sampling()
         timed = self.device_timer is not None
         if self.graphs is not None and singles == entries and wants == entries:
-            sampled_dev = self.graphs.run(self.sched, entries, self.device_timer,
-                                          None if greedy_only else (ids, pos, temps, seeds))
+            packed = self.graphs.run(self.sched, entries, self.device_timer,
+                                     None if greedy_only else (ids, pos, temps, seeds))
             info.graph = True
         else:
             layout = self.runner.build_from_scheduler(self.sched)
@@ -163,15 +164,23 @@ class Engine:
             if timed:
                 self.device_timer.start()
             logits = self.runner.forward(self.runner.context(layout))
-            sampled_dev = None
             if wants:
-                sampled_dev = (self.sampler.greedy(logits) if greedy_only else
-                               self.sampler.sample(logits, ids, pos, temps, seeds))
+                if greedy_only:
+                    self.sampler.greedy(logits)
+                else:
+                    self.sampler.sample(logits, ids, pos, temps, seeds)
+            packed = self.sampler.packed
             if timed:
                 self.device_timer.stop()
         info.h2d_bytes = self.runner.h2d_bytes_last + (self.sampler.h2d_bytes_last if wants else 0)
-        sampled: List[int] = sampled_dev[:wants].tolist() if wants else []   # the step's one sync
-        info.d2h_bytes = 4 * wants
+        sampled: List[int] = []
+        if wants:
+            # The step's one synchronisation: the sampled tokens and, in front of them, the status
+            # pair that the sampling kernel gathered from the kernels' error words.
+            got = packed[:2 + wants].tolist()
+            K.raise_on_status(got[0], got[1])
+            sampled = got[2:]
+        info.d2h_bytes = 4 * (2 + wants) if wants else 0
         t_end = self.now()
         self.sched.update(sampled, t_end)
         info.rows, info.seqs, info.prefill_tokens = rows, entries, prefill
@@ -207,6 +216,7 @@ class Engine:
                 raise RuntimeError("score: models with per-request state are scored through add_request")
             logits = self.runner.step([(s, 0, s.length(), list(range(s.length())))])
             torch.cuda.synchronize()
+            K.check_errors()
         finally:
             self.kv.release(s)
         return logits

@@ -206,18 +206,67 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
               ctypes.c_float(scale), int(window), _stream()), "attention_plain", f"(hd={hd}, nh={nh}, nkv={nkv})")
 
 
-def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+# Kernel families whose bounded waits report through an error word, in the order of the status
+# index that the sampling kernels write (csrc/cuda/sampling.cu: status_words).
+STATUS_FAMILIES = ("gemm_stream", "gemm_tcgen05", "gemm_tcgen05_pair", "gemm_tcgen05_splitk", "attention_tcgen05")
+
+
+def describe_status(first: int, word: int) -> str:
+    """Text for a status pair written by the sampling kernels: ``first`` = 1 + index of the kernel
+    family whose error word was set (0 = none), ``word`` = (code << 16) | block."""
+    name = STATUS_FAMILIES[first - 1] if 1 <= first <= len(STATUS_FAMILIES) else f"family {first}"
+    return (f"{name}: a bounded wait ran out on the device (code {(word >> 16) & 0xffff}, block {word & 0xffff}); "
+            f"the outputs of this step are not valid")
+
+
+def raise_on_status(first: int, word: int) -> None:
+    """Raises ``KernelError`` when the status pair of a step names a kernel family; clears the
+    device's error words first so that the next step starts clean."""
+    if not first:
+        return
+    clear_errors()
+    raise KernelError(describe_status(int(first), int(word)))
+
+
+def clear_errors() -> None:
+    """Reads and clears every family's error word (synchronises with the device)."""
+    for fn in (stream_error, tcgen05_error, pair_error, splitk_error, attention_tcgen05_error):
+        fn()
+
+
+def check_errors() -> None:
+    """Host-side read of every family's error word (synchronises); raises if one is set.  For paths
+    that synchronise anyway (scoring, replay); generation reads the status pair beside its tokens."""
+    for i, fn in enumerate((stream_error, tcgen05_error, pair_error, splitk_error, attention_tcgen05_error)):
+        word = fn()
+        if word:
+            clear_errors()
+            raise KernelError(describe_status(i + 1, word))
+
+
+def _status_ptr(status: Optional[torch.Tensor]):
+    if status is None:
+        return None
+    _cuda(status)
+    _need(status.dtype == _I32 and status.numel() >= 2 and status.is_contiguous(), "status: int32 [2]")
+    return _p(status)
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+    """out[r] = first index of the row's maximum.  ``status`` (int32 [2], optional) receives the
+    first error word that a kernel of this step has set (see ``describe_status``)."""
     _cuda(logits, out)
     R, V = logits.shape
     _need(logits.dtype == torch.float32 and logits.is_contiguous() and out.dtype == _I32
           and out.numel() >= R, "argmax: logits float32 [R,V], out int32 [R]")
-    _check(_lib().kvcm_argmax_f32(_p(logits), _p(out), R, V, _stream()), "argmax")
+    _check(_lib().kvcm_argmax_status_f32(_p(logits), _p(out), R, V, _status_ptr(status), _stream()), "argmax")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor,
-           request_id: torch.Tensor, position: torch.Tensor, out: torch.Tensor) -> None:
+           request_id: torch.Tensor, position: torch.Tensor, out: torch.Tensor,
+           status: Optional[torch.Tensor] = None) -> None:
     """Per row: temperature <= 0 -> argmax; else one draw from softmax(logits / temperature) with a
-    uniform number that depends only on (seed, request id, position)."""
+    uniform number that depends only on (seed, request id, position).  ``status`` as in ``argmax``."""
     _cuda(logits, temperature, seed, request_id, position, out)
     R, V = logits.shape
     _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: logits float32 [R,V]")
@@ -226,8 +275,8 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor,
           "sample: temperature f32, seed/request_id i64, position/out i32")
     _need(min(temperature.numel(), seed.numel(), request_id.numel(), position.numel(),
               out.numel()) >= R, "sample: per-row arrays shorter than the number of rows")
-    _check(_lib().kvcm_sample_f32(_p(logits), _p(temperature), _p(seed), _p(request_id),
-                                  _p(position), _p(out), R, V, _stream()), "sample")
+    _check(_lib().kvcm_sample_status_f32(_p(logits), _p(temperature), _p(seed), _p(request_id),
+                                         _p(position), _p(out), R, V, _status_ptr(status), _stream()), "sample")
 
 
 # ------------------------------------------------------------------ dispatch of attention
@@ -417,6 +466,14 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
     rc = _lib().kvcm_gemm_stream_bf16(_p(x), _p(w), _p(y), M, N, K, x.stride(0), w.stride(0), y.stride(0),
                                       int(y.dtype == torch.float32), sm_count(x.device), _stream())
     _check(rc, "gemm_stream", f"(M={M}, N={N}, K={K})")
+
+
+def stream_test_hooks(wait_limit_ns: int = 0, skip_stage: int = -1) -> None:
+    """For tests of the failure path: the streaming product's wait limit (0 = its default) and a
+    stage of every block whose copy is left out (-1 = none), so that a wait runs out."""
+    rc = _lib().kvcm_stream_test_hooks(ctypes.c_uint64(int(wait_limit_ns)), int(skip_stage))
+    if rc != 0:
+        raise KernelError("stream_test_hooks: could not set the device words")
 
 
 def stream_error() -> int:

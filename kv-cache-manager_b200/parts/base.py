@@ -40,9 +40,14 @@ class ParamSpec:
 class Part:
     """Base of every part: named parameters, named children.
 
-    ``capturable``: the part's forward only enqueues device work (no host synchronisation, no
-    host-side reading of device data), so a step that contains it may be recorded into a CUDA
-    graph.  A part that cannot promise this sets it to False and the engine replays no graphs."""
+    ``capturable``: a step that contains the part may be recorded into a CUDA graph and replayed.
+    That asks three things of ``forward``: it only enqueues device work (no host synchronisation,
+    no host-side reading of device data); everything that changes from step to step reaches it
+    through device memory at fixed addresses (the ``StepContext``'s index tensors, the cache, state
+    slabs), never through Python values or freshly computed shapes; and a replay does exactly what
+    the recorded call did, once -- a part with state of its own may update it in place, the engine
+    runs every step exactly once, the step that is recorded included.  A part that cannot promise
+    this sets it to False and the engine replays no graphs."""
 
     capturable = True
 

@@ -35,7 +35,10 @@ class Sampler:
     def __init__(self, device, max_rows: int) -> None:
         self.device = torch.device(device)
         self.max_rows = max_rows
-        self.out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        # [status pair | sampled tokens]: one buffer, so that the copy that brings the tokens to the
+        # host also brings the word that says whether a kernel of the step gave up a bounded wait
+        self.packed = torch.zeros(2 + max_rows, dtype=torch.int32, device=self.device)
+        self.status, self.out = self.packed[:2], self.packed[2:]
         # [temperature (as float bits) | position] int32 and [seed | request id] int64, pinned
         self.h_f = torch.zeros(max_rows, dtype=torch.float32, pin_memory=True)
         self.h_i = torch.zeros(max_rows, dtype=torch.int32, pin_memory=True)
@@ -47,7 +50,7 @@ class Sampler:
 
     def greedy(self, logits: torch.Tensor) -> torch.Tensor:
         n = logits.shape[0]
-        K.argmax(logits, self.out)
+        K.argmax(logits, self.out, self.status)
         self.h2d_bytes_last = 0
         return self.out[:n]
 
@@ -59,7 +62,7 @@ class Sampler:
         if not any(t > 0 for t in temperatures):
             return self.greedy(logits)
         self.stage(request_ids, positions, temperatures, seeds)
-        self.sample_staged(logits, self.out)
+        self.sample_staged(logits, self.out, self.status)
         return self.out[:n]
 
     def stage(self, request_ids: Sequence[int], positions: Sequence[int], temperatures: Sequence[float],
@@ -81,6 +84,6 @@ class Sampler:
         self.d_l[self.max_rows:self.max_rows + n].copy_(self.h_l[self.max_rows:self.max_rows + n], non_blocking=True)
         self.h2d_bytes_last = n * (4 + 4 + 16) + (rows - n) * 4
 
-    def sample_staged(self, logits: torch.Tensor, out: torch.Tensor) -> None:
+    def sample_staged(self, logits: torch.Tensor, out: torch.Tensor, status=None) -> None:
         """The sampling kernel on the staged parameters; only enqueues device work."""
-        K.sample(logits, self.d_f, self.d_l[:self.max_rows], self.d_l[self.max_rows:], self.d_i, out)
+        K.sample(logits, self.d_f, self.d_l[:self.max_rows], self.d_l[self.max_rows:], self.d_i, out, status)

@@ -723,3 +723,94 @@ def test_unsupported_sizes_are_refused_not_miscomputed():
                             case["ctx"].positions, 5, 2, 24, 0.2, 0)
     with pytest.raises(lib.KernelError):
         lib.rmsnorm(torch.zeros(2, 8), None, torch.ones(8), torch.zeros(2, 8), 1e-5)     # CPU tensors
+
+
+@pytest.mark.parametrize("hd,B,window", [(64, 16, 150), (128, 32, 90), (64, 8, 40)])
+def test_prefill_attention_on_tcgen05_with_pages_given_back(hd, B, window):
+    """A windowed layer group gives pages back once every key on them lies below the window: their
+    table entries are -1 while later portions of the same prompt still run.  The kernel must not
+    read through such an entry (its key tiles start at multiples of 64 keys, below the window's
+    first key).  Entries of pages that no row of the step may see are set to -1 here, as the cache
+    manager leaves them, and the result is compared with float64."""
+    nh, nkv = (8, 2) if hd == 64 else (6, 3)
+    lib = K()
+    seq_lens = [700, 333, 520, 64]
+    q_lens = [131, 70, 257, 2]
+    scale = 1.0 / math.sqrt(hd)
+    case = paged_case(seq_lens, q_lens, nh, nkv, hd, B, "bfloat16", seed=hd + B + window)
+    ref = reference_attention(case, nh, nkv, hd, scale, window)
+    tables = case["tables"].cpu()
+    gone = 0
+    for si, i in enumerate(case["order"]):
+        first_key = max(0, (seq_lens[i] - q_lens[i]) + 1 - window)      # of the portion's first row
+        dead = first_key // B
+        tables[si, :dead] = -1
+        gone += dead
+    assert gone > 20
+    for mode in ("tcgen05", "mma"):
+        case["ctx"].options = {"attn_prefill": mode}
+        out = torch.zeros(case["ctx"].rows, nh * hd, dtype=torch.bfloat16, device=DEV)
+        lib.paged_attention(case["q"], out, case["kc"], case["vc"], tables.to(DEV), case["ctx"], nh, nkv, hd,
+                            scale, window)
+        torch.cuda.synchronize()
+        assert lib.attention_tcgen05_error() == 0
+        close(out, ref, "bfloat16", f"prefill {mode} with pages given back")
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns():
+    """Failure path of the bounded waits, without a fault: a test hook leaves out one copy of the
+    streaming product, so its consumers wait for bytes that never come.  The wait gives up after the
+    (shortened) limit, the kernel returns, the error word is set, the sampling kernel copies it out
+    beside the tokens, and the host turns it into an exception.  Afterwards the same call works."""
+    lib = K()
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(8, 2048, generator=g) * 0.5).bfloat16().to(DEV)
+    w = (torch.randn(2560, 2048, generator=g) * 0.05).bfloat16().to(DEV)
+    ref = x.double().cpu() @ w.double().cpu().T
+    y = torch.zeros(8, 2560, dtype=torch.bfloat16, device=DEV)
+    logits = torch.randn(8, 300, generator=g).to(DEV)
+    packed = torch.zeros(2 + 8, dtype=torch.int32, device=DEV)
+    lib.clear_errors()
+    try:
+        lib.stream_test_hooks(wait_limit_ns=3_000_000, skip_stage=1)
+        lib.gemm_stream(x, w, y)
+        lib.argmax(logits, packed[2:], packed[:2])
+        torch.cuda.synchronize()                                   # returns: nothing spins for ever
+        first, word = packed[:2].tolist()
+        assert first == 1 and (word >> 16) in (1, 2), (first, word)
+        with pytest.raises(lib.KernelError, match="gemm_stream: a bounded wait ran out"):
+            lib.raise_on_status(first, word)
+        assert lib.stream_error() == 0                              # cleared by raise_on_status
+    finally:
+        lib.stream_test_hooks(0, -1)
+        lib.clear_errors()
+    lib.gemm_stream(x, w, y)
+    lib.argmax(logits, packed[2:], packed[:2])
+    torch.cuda.synchronize()
+    assert packed[:2].tolist() == [0, 0]
+    close(y, ref, "bfloat16", "streaming product after the hooks were taken out")
+    assert packed[2:].tolist() == logits.argmax(-1).tolist()
+
+
+def test_the_engine_raises_when_a_kernel_gave_up_a_wait(tmp_path):
+    """The same through generation: the step whose decode products could not finish raises instead
+    of handing out tokens sampled from unfinished logits."""
+    import kvcm
+    import helpers
+    from kvcm.config import EngineConfig, KVManagerConfig, SchedulerConfig
+    lib = K()
+    folder = helpers.write_tiny("tiny-c", "bfloat16", str(tmp_path / "m"))
+    ec = EngineConfig(kv=KVManagerConfig(num_blocks=32, block_size=16, max_seq_len=128, watermark_blocks=0),
+                      sched=SchedulerConfig(max_num_seqs=2, max_batched_tokens=64), dtype="bfloat16", cuda_graphs=False)
+    eng = kvcm.Engine.from_folder(folder, ec)
+    eng.add_request(helpers.random_tokens(20, 320, 1), max_new_tokens=8)
+    eng.step()                                                     # the prompt
+    eng.step()                                                     # a healthy decode step
+    lib.clear_errors()
+    try:
+        lib.stream_test_hooks(wait_limit_ns=3_000_000, skip_stage=0)
+        with pytest.raises(lib.KernelError, match="gemm_stream: a bounded wait ran out"):
+            eng.step()
+    finally:
+        lib.stream_test_hooks(0, -1)
+        lib.clear_errors()

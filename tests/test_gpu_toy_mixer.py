@@ -264,3 +264,149 @@ def test_toy_model_generates_through_the_engine(toy):
     with pytest.raises(ValueError, match="prefix caching"):
         kvcm.Engine.from_folder(folder, EngineConfig(kv=KVManagerConfig(num_blocks=24, block_size=8, max_seq_len=96,
                                                                         prefix_caching=True), dtype="float32"))
+
+
+# ------------------------------------------------------------------------------------------------
+# A second toy: a mixer with state of its own that CAN be recorded into CUDA graphs (device-side
+# tensor operations only, nothing read on the host).  Decode steps are then replayed from graphs,
+# and the step in which a graph is recorded must still advance the state exactly once.
+
+def register_capturable_toy():
+    from kvcm.config import ModelConfig, register_architecture
+    from kvcm.models.spec import ModelSpec, TensorBinding
+    from kvcm.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, LayerCall, Linear, Mixer, StateSpec
+    from kvcm.parts.embedding import Embedding, LMHead
+
+    class RunningMean(Mixer):
+        """y_t = W (s_t / (t + 1)),  s_t = s_{t-1} + h_t.  State per request: s (float32 [hidden])."""
+
+        def __init__(self, hidden: int) -> None:
+            super().__init__()
+            self.hidden = hidden
+            self.proj = self.add_child("proj", Linear(hidden, hidden))
+
+        def state_spec(self):
+            return StateSpec((self.hidden,), torch.float32)
+
+        def forward(self, h, ctx, site):
+            hf = h.float()
+            seq = ctx.row_seq.long()
+            slot = ctx.seq_state_slot.long()
+            valid = slot >= 0                                          # padding entries hold no slot
+            slot_c = slot.clamp(min=0)
+            c = torch.cumsum(hf, 0)
+            start = ctx.seq_q_start.long()[seq]
+            before = torch.where((start > 0)[:, None], c[(start - 1).clamp(min=0)], torch.zeros_like(c))
+            old = site.state[slot_c] * valid[:, None]
+            s = old[seq] + (c - before)                                # the sum up to and including each row
+            out = (s / (ctx.positions.float()[:, None] + 1).clamp(min=1)).to(h.dtype)
+            last = (ctx.seq_q_start + ctx.seq_q_len - 1).long()
+            site.state.index_add_(0, slot_c, (s[last] - old) * valid[:, None])
+            return self.proj.forward(out, ctx)
+
+    if "running_mean" not in MIXERS.names():
+        MIXERS.register("running_mean", RunningMean)
+
+    @dataclass(frozen=True)
+    class CapToyConfig(ModelConfig):
+        vocab: int = 0
+        width: int = 0
+        ffn: int = 0
+        heads: int = 0
+        head_dim: int = 0
+        eps: float = 1e-5
+
+        @classmethod
+        def from_json_dict(cls, d):
+            return cls(architecture="ToyCapturableForTests",
+                       **{k: d[k] for k in ("vocab", "width", "ffn", "heads", "head_dim", "eps")})
+
+        def to_json_dict(self):
+            d = {k: getattr(self, k) for k in ("vocab", "width", "ffn", "heads", "head_dim", "eps")}
+            d["architectures"] = [self.architecture]
+            return d
+
+    def build(cfg):
+        H = cfg.width
+        emb = Embedding(cfg.vocab, H)
+        bind = [TensorBinding(emb, "weight", [("emb.weight", (cfg.vocab, H))])]
+        blocks = []
+        for l, kind in enumerate(["attention", "running_mean"]):
+            if kind == "attention":
+                pos = POSITION_ENCODINGS.build("rope", head_dim=cfg.head_dim, theta=10000.0)
+                mixer = MIXERS.build("attention", hidden=H, num_heads=cfg.heads, num_kv_heads=cfg.heads,
+                                     head_dim=cfg.head_dim, position=pos)
+                q = cfg.heads * cfg.head_dim
+                bind += [TensorBinding(mixer.qkv, "weight", [(f"l{l}.q", (q, H)), (f"l{l}.k", (q, H)), (f"l{l}.v", (q, H))]),
+                         TensorBinding(mixer.o, "weight", [(f"l{l}.o", (H, q))])]
+            else:
+                mixer = MIXERS.build("running_mean", hidden=H)
+                bind.append(TensorBinding(mixer.proj, "weight", [(f"l{l}.proj", (H, H))]))
+            ffn = FEED_FORWARDS.build("gated_mlp", hidden=H, intermediate=cfg.ffn)
+            n1, n2 = NORMS.build("rmsnorm", hidden=H, eps=cfg.eps), NORMS.build("rmsnorm", hidden=H, eps=cfg.eps)
+            blocks.append(BLOCKS.build("pre_norm", norm1=n1, mixer=mixer, norm2=n2, ffn=ffn))
+            bind += [TensorBinding(n1, "weight", [(f"l{l}.n1", (H,))]), TensorBinding(n2, "weight", [(f"l{l}.n2", (H,))]),
+                     TensorBinding(ffn.gate_up, "weight", [(f"l{l}.gate", (cfg.ffn, H)), (f"l{l}.up", (cfg.ffn, H))]),
+                     TensorBinding(ffn.down, "weight", [(f"l{l}.down", (H, cfg.ffn))])]
+        fin = NORMS.build("rmsnorm", hidden=H, eps=cfg.eps)
+        head = LMHead(H, cfg.vocab)
+        bind += [TensorBinding(fin, "weight", [("final.weight", (H,))]),
+                 TensorBinding(head, "weight", [("head.weight", (cfg.vocab, H))], tie_to=bind[0], tied=True)]
+        return ModelSpec(cfg, emb, blocks, [LayerCall(0), LayerCall(1)], fin, head, bind)
+
+    register_architecture("ToyCapturableForTests", CapToyConfig, build, replace=True)
+    return CapToyConfig
+
+
+def plain_capturable_toy(cfg, w, tokens):
+    n = len(tokens)
+    pos = torch.arange(n)
+    c = dict(nh=cfg["heads"], nkv=cfg["heads"], hd=cfg["head_dim"], theta=10000.0)
+    x = P.embedding(w["emb.weight"], tokens)
+
+    def layer(l, x, mix):
+        x = x + mix(P.rmsnorm(x, w[f"l{l}.n1"], cfg["eps"]))
+        return x + P.gated_mlp(P.rmsnorm(x, w[f"l{l}.n2"], cfg["eps"]), w[f"l{l}.gate"], w[f"l{l}.up"], w[f"l{l}.down"])
+
+    x = layer(0, x, lambda h: P.attention_block(h, w["l0.q"], w["l0.k"], w["l0.v"], w["l0.o"], pos, c))
+    x = layer(1, x, lambda h: (torch.cumsum(h, 0) / (pos.double()[:, None] + 1)) @ w["l1.proj"].T)
+    return P.rmsnorm(x, w["final.weight"], cfg["eps"]) @ w["emb.weight"].T
+
+
+def test_stateful_mixer_under_cuda_graphs_advances_once_per_step(tmp_path):
+    """Greedy generation with decode steps replayed from CUDA graphs, against the plain
+    implementation and against the same engine without graphs.  Requests of several lengths make
+    several (batch, context) shapes, so graphs are recorded in the middle of generation: a recorded
+    step that ran twice would add its input to the state twice."""
+    import kvcm
+    from kvcm.config import EngineConfig, KVManagerConfig, SchedulerConfig
+    CapToyConfig = register_capturable_toy()
+    cfg = CapToyConfig(architecture="ToyCapturableForTests", vocab=150, width=40, ffn=64, heads=2, head_dim=16, eps=1e-5)
+    folder = str(tmp_path / "captoy")
+    kvcm.write_random_model(folder, cfg, seed=11, dtype=torch.float32, norm_jitter=0.1)
+    cj = json.load(open(os.path.join(folder, "config.json")))
+    from safetensors import safe_open
+    w = {}
+    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as f:
+        for k in f.keys():
+            w[k] = f.get_tensor(k).double()
+    prompts = [helpers.random_tokens(n, cfg.vocab, 60 + i) for i, n in enumerate([6, 19, 3, 30, 11])]
+
+    def run(graphs):
+        ec = EngineConfig(kv=KVManagerConfig(num_blocks=64, block_size=8, max_seq_len=128, watermark_blocks=0),
+                          sched=SchedulerConfig(max_num_seqs=4, max_batched_tokens=32), dtype="float32",
+                          cuda_graphs=graphs)
+        eng = kvcm.Engine.from_folder(folder, ec)
+        outs = kvcm.generate(eng, prompts, 24)
+        return eng, outs
+
+    eng, outs = run(True)
+    assert eng.graphs is not None and eng.graphs.replays > 20 and len(eng.graphs.captured) >= 3
+    for p, o in zip(prompts, outs):
+        assert len(o) == 24
+        logits = plain_capturable_toy(cj, w, list(p) + list(o))
+        for k, tok in enumerate(o):
+            row = logits[len(p) - 1 + k]
+            assert row.max().item() - row[tok].item() <= 2e-4, (len(p), k, tok, P.greedy_pick(row))
+    eng2, outs2 = run(False)
+    assert eng2.graphs is None and outs2 == outs

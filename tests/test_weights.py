@@ -163,9 +163,55 @@ def test_reader_in_the_core_keeps_the_map_alive_and_reports_header_faults(tmp_pa
             ('{"a": {"dtype": "Q4", "shape": [2], "data_offsets": [0, 8]}}', b"\0" * 8, "bad header entry"),
             ('{"a": {"dtype": "F32", "shape": [2]}}', b"\0" * 8, "bad header entry"),
             ('{"a": {"dtype": "F32", "shape": [-2], "data_offsets": [0, 8]}}', b"\0" * 8, "bad header entry"),
+            ('{"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}, '
+             '"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}', b"\0" * 8, "appears twice"),
+            # 2^32 * 2^32 * 2 wraps round to 0 in 64 bits, and 0 * 4 bytes would "fit" an empty range
+            ('{"a": {"dtype": "F32", "shape": [4294967296, 4294967296, 2], "data_offsets": [0, 0]}}', b"",
+             "does not fit"),
+            # 2^30 * 2^30 * 16 = 2^64 wraps round to 0 as well
+            ('{"a": {"dtype": "F32", "shape": [1073741824, 1073741824, 16], "data_offsets": [0, 0]}}', b"",
+             "does not fit"),
             ('[1, 2]', b"", "JSON object"),
             ('{"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]},}', b"\0" * 8, "not valid JSON")]:
         with pytest.raises(SafetensorsError, match=message):
             SafetensorsFile(header_file(header, data))
     with pytest.raises(SafetensorsError, match="cannot open"):
         SafetensorsFile(str(tmp_path / "absent.safetensors"))
+
+
+def test_model_folder_in_shards_through_the_index_file(tmp_path):
+    """A model folder without model.safetensors but with model.safetensors.index.json and two
+    shards loads like the single file; a tensor that the index promises but no shard holds is
+    reported as missing, by name."""
+    import json
+    import kvcm
+    from kvcm.weights.loader import load_weights
+    cfg = helpers.tiny_config("tiny-a")
+    tensors = list(random_tensors(cfg, 0, torch.float32))
+    folder = tmp_path / "sharded"
+    folder.mkdir()
+    with open(folder / "config.json", "w") as f:
+        json.dump(cfg.to_json_dict(), f)
+    half = len(tensors) // 2
+    shards = {"model-00001-of-00002.safetensors": tensors[:half], "model-00002-of-00002.safetensors": tensors[half:]}
+    weight_map = {}
+    for name, items in shards.items():
+        write_safetensors(str(folder / name), items)
+        weight_map.update({k: name for k, _ in items})
+    with open(folder / "model.safetensors.index.json", "w") as f:
+        json.dump({"metadata": {"total_size": 0}, "weight_map": weight_map}, f)
+    spec = get_architecture(cfg.architecture).build(cfg)
+    load_weights(spec, str(folder), "cpu", torch.float32)
+    want = dict(tensors)
+    assert torch.equal(spec.embedding.param("weight"), want["model.embed_tokens.weight"])
+    assert torch.equal(spec.blocks[1].ffn.down.param("weight"), want["model.layers.1.mlp.down_proj.weight"])
+    assert torch.equal(spec.final_norm.param("weight"), want["model.norm.weight"])
+    # the second shard loses a tensor
+    write_safetensors(str(folder / "model-00002-of-00002.safetensors"),
+                      [(k, v) for k, v in tensors[half:] if k != "model.norm.weight"])
+    spec = get_architecture(cfg.architecture).build(cfg)
+    with pytest.raises(WeightError) as e:
+        load_weights(spec, str(folder), "cpu", torch.float32)
+    assert e.value.missing == ["model.norm.weight"]
+    with pytest.raises(SafetensorsError, match="no model.safetensors"):
+        load_weights(get_architecture(cfg.architecture).build(cfg), str(tmp_path), "cpu", torch.float32)
