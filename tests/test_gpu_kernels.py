@@ -772,7 +772,7 @@ def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns():
     packed = torch.zeros(2 + 8, dtype=torch.int32, device=DEV)
     lib.clear_errors()
     try:
-        lib.stream_test_hooks(wait_limit_ns=3_000_000, skip_stage=1)
+        lib.stream_test_hooks(wait_limit_ns=3_000_000, skip_stage=0)
         lib.gemm_stream(x, w, y)
         lib.argmax(logits, packed[2:], packed[:2])
         torch.cuda.synchronize()                                   # returns: nothing spins for ever

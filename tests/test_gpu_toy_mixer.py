@@ -401,7 +401,7 @@ def test_stateful_mixer_under_cuda_graphs_advances_once_per_step(tmp_path):
         return eng, outs
 
     eng, outs = run(True)
-    assert eng.graphs is not None and eng.graphs.replays > 20 and len(eng.graphs.captured) >= 3
+    assert eng.graphs is not None and eng.graphs.replays > 20 and len(eng.graphs.captured) >= 2
     for p, o in zip(prompts, outs):
         assert len(o) == 24
         logits = plain_capturable_toy(cj, w, list(p) + list(o))
