@@ -10,7 +10,8 @@ paged|contiguous, --block-size, --max-seq-len, --prefix, --num-blocks, --waterma
 --output-sigma --min-prompt --max-prompt --min-output --max-output --shared-frac --shared-len
 --num-prefixes --lengths-csv --seed --prompt-len --output-len).  Added: --model DIR | --preset NAME
 [--random-seed S], --dtype, --temperature, --sampling-seed, --prefill-chunk, --no-chunked-prefill,
---no-graphs, --gemm auto|native|library|plain (native: only this engine's product kernels).
+--no-graphs, --gemm auto|native|library|plain (native: only this engine's product kernels),
+--profile (device time per kernel family, from an event after every launch; runs without CUDA graphs).
 """
 from __future__ import annotations
 
@@ -29,6 +30,9 @@ def main(argv=None) -> int:
         from ..engine.metrics import BenchSummary, MetricsCollector, append_bench_csv, print_summary
         from ..engine.workload import WorkloadConfig, generate_workload, make_prompt_tokens
         ec = engine_config_from_args(a)
+        profile = a.flag("profile")
+        if profile:
+            ec.cuda_graphs = False           # events cannot be recorded into a graph
         wl = WorkloadConfig.from_args(a)
         wl.max_seq_len = ec.kv.max_seq_len
         warmup = a.i32("warmup", 8)
@@ -52,6 +56,9 @@ def main(argv=None) -> int:
             eng.take_finished()
             eng.sched.reset_counters()
         ps0 = eng.kv.prefix_stats()
+        if profile:
+            from ..kernels import library as K
+            K.profile_start()
         reqs = generate_workload(wl)
         log = open(step_log, "w") if step_log else None
         if log:
@@ -101,6 +108,12 @@ def main(argv=None) -> int:
         free_b, total_b = torch.cuda.mem_get_info()
         s.gpu_used_gb = (total_b - free_b) / 2**30
         print_summary(s)
+        if profile:
+            fam = K.profile_stop()
+            total = sum(ms for _, ms in fam.values()) or 1.0
+            print(f"profile: device time per kernel family ({total:.1f} ms in {sum(c for c, _ in fam.values())} launches)")
+            for name, (calls, ms) in sorted(fam.items(), key=lambda kv: -kv[1][1]):
+                print(f"profile: {name or 'other':<28} {calls:>8} launches {ms:>10.2f} ms {100 * ms / total:>6.1f} %")
         if summary_csv:
             append_bench_csv(summary_csv, s)
     except (Exception, SystemExit) as e:

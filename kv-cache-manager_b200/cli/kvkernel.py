@@ -52,8 +52,11 @@ def bench_attention(a, out) -> None:
     blocks = a.ints("block-size", "16")
     nh, nkv, hd, iters = a.i32("heads", 32), a.i32("kv-heads", 4), a.i32("head-dim", 64), a.i32("iters", 100)
     a.warn_unused()
-    peak = 6650.0
-    print(f"{'B':>4} {'batch':>6} {'ctx':>6} {'variant':<16} {'us/call':>9} {'GB/s':>9}")
+    from ..engine.peaks import measured_peaks
+    pk = measured_peaks()
+    peak = pk["hbm_gbs"]
+    print(f"HBM peak {peak:.0f} GB/s ({pk['source']})")
+    print(f"{'B':>4} {'batch':>6} {'ctx':>6} {'variant':<16} {'us/call':>9} {'GB/s':>9} {'of peak':>8}")
     if out:
         out.write("block_size,batch,ctx,variant,us,gbps\n")
     dev = "cuda:0"
@@ -77,7 +80,7 @@ def bench_attention(a, out) -> None:
                     c = types.SimpleNamespace(max_decode_ctx=ctx, seq_ctx_len=lens, options={"attn_version": version})
                     us = graph_time_us([lambda: K.attention_decode(q, o, kc, vc, t, c, nh, nkv, hd, hd ** -0.5)] * iters)
                     gbs = nbytes / (us * 1e-6) / 1e9
-                    print(f"{B:>4} {batch:>6} {ctx:>6} {name:<16} {us:>9.2f} {gbs:>9.1f}")
+                    print(f"{B:>4} {batch:>6} {ctx:>6} {name:<16} {us:>9.2f} {gbs:>9.1f} {gbs / peak:>8.3f}")
                     if out:
                         out.write(f"{B},{batch},{ctx},{name},{us:.3f},{gbs:.2f}\n")
 

@@ -6,6 +6,7 @@ thing in the reference is ``Engine::score`` (``src/engine/engine.cpp:92-108``), 
 whole sequence; here the caller decides step by step which tokens of which request run.
 
     trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+              [--policy paged|contiguous] [--prefix] [--block-size B] [--max-seq-len L]
 
 Steps are read from standard input, one JSON object a line:
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
@@ -31,17 +32,26 @@ def main(argv=None) -> int:
                     help="most tokens live requests hold at any time (sizes the page pool)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--max-live", type=int, default=64, help="most requests live at a time")
+    ap.add_argument("--policy", default="paged", choices=["paged", "contiguous"],
+                    help="cache policy (the reference's two: src/core/kv_manager.h:64-72)")
+    ap.add_argument("--prefix", action="store_true",
+                    help="prefix caching: a new request takes over the cached pages that match its first "
+                         "portion; those tokens are not computed and their places cannot be wanted")
+    ap.add_argument("--max-seq-len", type=int, default=0,
+                    help="longest request (0: the whole pool when paged, a quarter of it when contiguous, "
+                         "where every request reserves this many tokens)")
     ap.add_argument("--attention", default="auto", choices=["auto", "plain"])
-    ap.add_argument("--gemm", default="auto", choices=["auto", "plain", "library", "skinny", "tcgen05"])
+    ap.add_argument("--gemm", default="auto", choices=["auto", "plain", "library", "skinny", "tcgen05", "native"])
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
     print("trace_run: loading (the first call compiles the kernels; lines from [kvcm build] follow)",
           file=sys.stderr, flush=True)
     import torch
-    from ..cache import core, manager_from_config
-    from ..config import KVManagerConfig, canonical_dtype
-    from ..engine import ModelRunner, load_model, torch_dtype
+    from ..config import canonical_dtype
+    from ..engine import load_model
+    from ..engine.replay import ReplayError, ReplaySession
+    from ..kernels import library as K
 
     dtype = canonical_dtype(args.dtype)
     if not torch.cuda.is_available():
@@ -49,76 +59,24 @@ def main(argv=None) -> int:
         return 3
     os.makedirs(args.out, exist_ok=True)
     spec = load_model(args.model, dtype, args.device)
-    B = args.block_size
-    num_blocks = (args.max_tokens + B - 1) // B
-    max_seq_len = num_blocks * B
-    runner = ModelRunner(spec, torch_dtype(dtype), args.device, num_blocks=num_blocks, block_size=B,
-                         max_seq_len=max_seq_len, num_slots=args.max_live, max_rows=max_seq_len,
-                         max_seqs=args.max_live, max_logit_rows=max_seq_len,
-                         options={"attention": args.attention, "gemm": args.gemm})
-    kv = manager_from_config(KVManagerConfig(policy="paged", num_blocks=num_blocks, block_size=B,
-                                             max_seq_len=max_seq_len, prefix_caching=False,
-                                             watermark_blocks=0), runner.windows)
-    slots = core.StateSlots(args.max_live)
-    vocab = spec.lm_head.vocab
-    live = {}
-    next_id = 0
-
-    def release(rid):
-        seq = live.pop(rid)
-        kv.release(seq)
-        if seq.state_slot >= 0:
-            slots.give_back(seq.state_slot)
-
+    session = ReplaySession(spec, dtype, args.max_tokens, block_size=args.block_size, max_live=args.max_live,
+                            policy=args.policy, prefix_caching=args.prefix, max_seq_len=args.max_seq_len,
+                            options={"attention": args.attention, "gemm": args.gemm}, device=args.device)
     for line in sys.stdin:
         line = line.strip()
         if not line:
             continue
         step = json.loads(line)
         tag = step["step"]
-        entries = []
-        for e in step.get("entries", []):
-            rid, toks = e["id"], [int(t) for t in e["tokens"]]
-            want = [int(w) for w in e.get("want", [])]
-            if not toks:
-                raise SystemExit(f"trace_run: step {tag}: request {rid!r} brings no tokens")
-            bad = [t for t in toks if t < 0 or t >= vocab]
-            if bad:
-                raise SystemExit(f"trace_run: step {tag}: token {bad[0]} outside the vocabulary of {vocab}")
-            bad = [w for w in want if w < 0 or w >= len(toks)]
-            if bad:
-                raise SystemExit(f"trace_run: step {tag}: request {rid!r} wants place {bad[0]} of a portion of "
-                                 f"{len(toks)} tokens")
-            seq = live.get(rid)
-            if seq is None:
-                seq = core.Sequence()
-                seq.id = next_id
-                next_id += 1
-                seq.state_slot = slots.take()
-                if seq.state_slot < 0:
-                    raise SystemExit(f"trace_run: step {tag}: more than {args.max_live} live requests")
-                kv.admit(seq)                       # empty token list: starts the page tables
-                runner.pools.reset_slot(seq.state_slot)
-                live[rid] = seq
-            start = seq.length()
-            seq.extend_tokens(toks)
-            if not kv.ensure(seq, seq.length()):
-                raise SystemExit(f"trace_run: step {tag}: out of cache pages for request {rid!r} "
-                                 f"({seq.length()} tokens; pool made for --max-tokens {args.max_tokens})")
-            entries.append((seq, start, len(toks), want))
-        if entries:
-            logits = runner.step(entries)
-            for seq, start, n, _ in entries:
-                seq.num_computed = start + n
-                kv.commit(seq)
-            if logits is not None:
-                logits.detach().to("cpu").contiguous().numpy().astype("<f4", copy=False).tofile(
-                    os.path.join(args.out, f"{tag}.f32"))
-            else:
-                torch.cuda.synchronize()
-        for rid in step.get("end", []):
-            if rid in live:
-                release(rid)
+        try:
+            logits = session.step(step.get("entries", []), step.get("end", []), tag=tag)
+        except ReplayError as e:
+            raise SystemExit(f"trace_run: {e}")
+        torch.cuda.synchronize()
+        K.check_errors()                            # a kernel that gave up a bounded wait: no logits are written
+        if logits is not None:
+            logits.detach().to("cpu").contiguous().numpy().astype("<f4", copy=False).tofile(
+                os.path.join(args.out, f"{tag}.f32"))
         print(f"done {tag}", flush=True)
     return 0
 

@@ -66,9 +66,44 @@ def _cuda(*tensors) -> None:
                               "(this engine has no CPU path)")
 
 
+_profile = None          # while profiling: [(kernel family, event recorded after its launch)]
+
+
+def profile_start() -> None:
+    """Starts per-family timing: from now on an event is recorded after every launch of this
+    library's kernels (and after library products, which call ``profile_mark``).  The stream runs
+    in order, so the time between two consecutive events is the time of the later launch (its
+    launch gap included).  For eager steps only: events cannot be recorded into a CUDA graph."""
+    global _profile
+    first = torch.cuda.Event(enable_timing=True)
+    first.record()
+    _profile = [("", first)]
+
+
+def profile_mark(name: str) -> None:
+    if _profile is not None:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        _profile.append((name, e))
+
+
+def profile_stop() -> dict:
+    """Ends profiling; {family: (launches, device milliseconds)}."""
+    global _profile
+    marks, _profile = _profile or [], None
+    torch.cuda.synchronize()
+    out: dict = {}
+    for (_, before), (name, after) in zip(marks, marks[1:]):
+        calls, ms = out.get(name, (0, 0.0))
+        out[name] = (calls + 1, ms + before.elapsed_time(after))
+    return out
+
+
 def _check(rc: int, name: str, detail: str = "") -> None:
     global _launches
     _launches += 1
+    if _profile is not None:
+        profile_mark(name)
     if rc == 0:
         return
     if rc == _ERR_UNSUPPORTED:

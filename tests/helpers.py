@@ -101,56 +101,36 @@ def first_bad_row(d: torch.Tensor, tol: float) -> int:
 # ------------------------------------------------------------------------- in-process replay
 
 class Replayer:
-    """Drives the engine's step function the way trace replay does, inside the test process."""
+    """The replay driver of ``bin/trace_run`` (``kvcm.engine.replay.ReplaySession``) inside the test
+    process, with a record of which pages every request held."""
 
     def __init__(self, folder: str, dtype: str, max_tokens: int, block_size: int, options=None,
-                 spec=None, max_live: int = 8) -> None:
-        from kvcm.cache import core, manager_from_config
-        from kvcm.config import KVManagerConfig
-        from kvcm.engine import ModelRunner, load_model, torch_dtype
+                 spec=None, max_live: int = 8, policy: str = "paged", prefix_caching: bool = False,
+                 max_seq_len: int = 0) -> None:
+        from kvcm.cache import core
+        from kvcm.engine import load_model
+        from kvcm.engine.replay import ReplaySession
         self.core = core
         self.spec = spec if spec is not None else load_model(folder, dtype, "cuda:0")
-        nb = (max_tokens + block_size - 1) // block_size
-        self.runner = ModelRunner(self.spec, torch_dtype(dtype), "cuda:0", num_blocks=nb,
-                                  block_size=block_size, max_seq_len=nb * block_size, num_slots=max_live,
-                                  max_rows=nb * block_size, max_seqs=max_live,
-                                  max_logit_rows=nb * block_size, options=options or {})
-        self.kv = manager_from_config(KVManagerConfig(policy="paged", num_blocks=nb, block_size=block_size,
-                                                      max_seq_len=nb * block_size, watermark_blocks=0),
-                                      self.runner.windows)
-        self.slots = core.StateSlots(max_live)
-        self.live: Dict[str, object] = {}
+        self.session = ReplaySession(self.spec, dtype, max_tokens, block_size=block_size, max_live=max_live,
+                                     policy=policy, prefix_caching=prefix_caching, max_seq_len=max_seq_len,
+                                     options=options or {})
+        self.runner, self.kv, self.slots, self.live = (self.session.runner, self.session.kv, self.session.slots,
+                                                       self.session.live)
         self.pages_seen: List[int] = []
         self.page_owners: Dict[int, set] = {}
 
     def step(self, entries: Sequence[dict], end: Sequence[str] = ()) -> Optional[torch.Tensor]:
-        batch = []
+        out = self.session.step(entries, ())
         for e in entries:
-            seq = self.live.get(e["id"])
-            if seq is None:
-                seq = self.core.Sequence()
-                seq.id = self._next_id = getattr(self, '_next_id', 999) + 1
-                seq.state_slot = self.slots.take()
-                self.kv.admit(seq)
-                self.runner.pools.reset_slot(seq.state_slot)
-                self.live[e["id"]] = seq
-            start = seq.length()
-            seq.extend_tokens([int(t) for t in e["tokens"]])
-            assert self.kv.ensure(seq, seq.length()), "test pool too small"
-            batch.append((seq, start, len(e["tokens"]), list(e.get("want", []))))
-        out = self.runner.step(batch) if batch else None
-        for seq, start, n, _ in batch:
-            seq.num_computed = start + n
-            self.kv.commit(seq)
+            seq = self.live[e["id"]]
             self.pages_seen.extend(p for p in seq.table(0) if p >= 0)
             for p in seq.table(0):
                 if p >= 0:
                     self.page_owners.setdefault(p, set()).add(seq.id)
         torch.cuda.synchronize()
         for rid in end:
-            seq = self.live.pop(rid)
-            self.kv.release(seq)
-            self.slots.give_back(seq.state_slot)
+            self.session.release(rid)
         return None if out is None else out.float().cpu()
 
 

@@ -2,13 +2,17 @@
 shape (hidden 2048, 32 query heads on 4 KV heads of 64, feed-forward 5632; a vocabulary that is no
 power of two) with random weights.  The bfloat16 engine (tcgen05 attention and gated product for
 long portions, the streaming products with fused epilogues and the clustered decode attention for
-single tokens) against this engine's own true 32-bit path on the same (bfloat16-rounded) weights,
-which the small-configuration tests pin to the plain implementation: whole, in portions, token by
-token, and mixed."""
+single tokens, the library products and unfused kernels of larger decode batches) against the plain
+implementation in float64 on the CPU with the same roundings of stored tensors, and against this
+engine's own true 32-bit path: whole at the full context of 2,048 tokens, in portions, token by
+token, mixed, and in decode batches of 24 and 64."""
+import math
+
 import pytest
 import torch
 
 import helpers
+import plain_llama as P
 
 pytestmark = pytest.mark.gpu
 
@@ -27,8 +31,35 @@ def engines():
     out = {}
     for dtype, t in (("bfloat16", t16), ("float32", t32)):
         spec = model_from_tensors(cfg, dict(t), dtype, "cuda:0")
-        out[dtype] = lambda spec=spec, dtype=dtype: helpers.Replayer(None, dtype, 4096, 16, spec=spec, max_live=4)
+        out[dtype] = lambda spec=spec, dtype=dtype, max_live=4, max_tokens=4096: helpers.Replayer(
+            None, dtype, max_tokens, 16, spec=spec, max_live=max_live)
+    # the plain implementation on the same (bfloat16-rounded) weights, in float64 on the CPU
+    w = {k: v.double().cpu() for k, v in t16.items()}
+    cj = cfg.to_json_dict()
+    memo = {}
+
+    def plain(tokens, storage=torch.bfloat16):
+        key = (tuple(tokens), storage)
+        if key not in memo:
+            memo[key] = P.llama_forward(cj, w, list(tokens), storage)
+        return memo[key]
+    out["plain"] = plain
     return cfg, out
+
+
+def near_plain(got, ref, what):
+    """bfloat16 engine against the plain implementation run with the same roundings of stored
+    tensors: the bound of the small-configuration tests (4 % of the logits' standard deviation at
+    ~10^4 elements) grown with the number of elements as the maximum of that many Gaussians grows,
+    and 1 % in the root mean square."""
+    got, ref = got.double().cpu(), ref.double().cpu()
+    assert got.shape == ref.shape and torch.isfinite(got).all(), what
+    std = ref.std().item()
+    d = got - ref
+    rms, worst = d.pow(2).mean().sqrt().item(), d.abs().max().item()
+    bound = 0.04 * math.sqrt(max(1.0, math.log(d.numel()) / math.log(1e4)))
+    assert rms <= 0.01 * std and worst <= bound * std, \
+        f"{what}: rms {rms / std:.4f}, max {worst / std:.4f} of std (bounds 0.01, {bound:.4f})"
 
 
 def same_cut(got, ref, what):
@@ -65,21 +96,28 @@ def near_float32(got, ref, what):
 
 def test_whole_portions_and_token_by_token(engines):
     cfg, make = engines
-    toks = helpers.random_tokens(1500, cfg.vocab_size, 3)
-    want = [0, 1, 63, 64, 127, 128, 129, 700, 1023, 1024] + list(range(1436, 1500))
+    n = 2048                                                         # the benchmark's full context
+    toks = helpers.random_tokens(n, cfg.vocab_size, 3)
+    want = [0, 1, 63, 64, 127, 128, 129, 700, 1023, 1024, 1535, 1536] + list(range(n - 64, n))
+    plain = make["plain"](toks)[want]
     ref = make["float32"]().step([dict(id="a", tokens=toks, want=want)])
+    helpers.assert_logits_close(ref, make["plain"](toks, None)[want], "float32",
+                                "true 32-bit path, whole prompt of 2,048")
     whole = make["bfloat16"]().step([dict(id="a", tokens=toks, want=want)])
+    near_plain(whole, plain, "whole prompt of 2,048 tokens")
     near_float32(whole, ref, "whole prompt")
     r = make["bfloat16"]()
     got, at = [], 0
-    for k in (700, 2, 300, 466):                                   # 1468 tokens in portions ...
+    for k in (700, 2, 300, 466, 548):                              # 2016 tokens in portions ...
         w = [p - at for p in want if at <= p < at + k]
         o = r.step([dict(id="a", tokens=toks[at:at + k], want=w)])
         if w:
             got.append(o)
         at += k
-    for t in range(at, 1500):                                        # ... the last 32 one by one
+    assert at == n - 32
+    for t in range(at, n):                                           # ... the last 32 one by one
         got.append(r.step([dict(id="a", tokens=toks[t:t + 1], want=[0])]))
+    near_plain(torch.cat(got), plain, "portions, then token by token")
     near_float32(torch.cat(got), ref, "portions, then token by token")
     same_cut(torch.cat(got), whole, "portions, then token by token, against the whole prompt")
     from kvcm.kernels import library as K
@@ -118,8 +156,29 @@ def test_mixed_batch(engines):
                 got[i].append(out[at:at + n])
             at += n
     for i in range(3):
+        near_plain(torch.cat(got[i]), make["plain"](seqs[i])[-20:], f"mixed, request {i}, against the plain implementation")
         near_float32(torch.cat(got[i]), refs[i], f"mixed, request {i}")
         same_cut(torch.cat(got[i]), alone[i], f"mixed, request {i}, against the request alone")
+
+
+@pytest.mark.parametrize("batch", [24, 64])
+def test_decode_batches_beyond_the_streaming_kernels(engines, batch):
+    """Decode steps of 24 and 64 requests: more rows than the weight-streaming products take, so the
+    library products, the separate rotary / cache-write and activation kernels and another plan of
+    context partitions run.  Contexts differ from request to request (pages and tiles end in
+    different places); every request's logits are held against the plain implementation."""
+    cfg, make = engines
+    lens = [33 + (37 * i) % 190 for i in range(batch)]
+    seqs = [helpers.random_tokens(n + 3, cfg.vocab_size, 500 + i) for i, n in enumerate(lens)]
+    r = make["bfloat16"](max_live=batch, max_tokens=batch * 256)
+    for lo in range(0, batch, 8):                                    # the prompts, eight requests a step
+        r.step([dict(id=f"r{i}", tokens=seqs[i][:lens[i]], want=[]) for i in range(lo, min(lo + 8, batch))])
+    outs = []
+    for t in range(3):                                               # three decode steps of the whole batch
+        outs.append(r.step([dict(id=f"r{i}", tokens=[seqs[i][lens[i] + t]], want=[0]) for i in range(batch)]))
+    for t in range(3):
+        ref = torch.stack([make["plain"](seqs[i])[lens[i] + t] for i in range(batch)])
+        near_plain(outs[t], ref, f"decode step {t} of {batch} requests")
 
 
 def test_decode_graphs_give_the_tokens_of_eager_steps(engines):
@@ -146,3 +205,54 @@ def test_decode_graphs_give_the_tokens_of_eager_steps(engines):
         assert eng.kv.blocks_in_use() == 0
     assert outs[True] == outs[False]
     assert all(len(o) == 24 for o in outs[True])
+
+
+def test_graph_buckets_are_crossed_while_portions_are_in_flight(engines):
+    """Eleven requests arrive one after another while earlier ones decode: prompts are cut into
+    portions of at most 96 tokens, so for many steps a portion runs beside the decode rows (those
+    steps run eagerly), and in between the decode-only steps grow from one request to eleven, over
+    the graph buckets 1, 2, 4, 8 and 16.  With graphs and without, every token is the plain
+    implementation's greedy choice unless that choice is a near-tie."""
+    import kvcm
+    from kvcm.config import EngineConfig, KVManagerConfig, SchedulerConfig
+    from kvcm.engine import model_from_tensors
+    from kvcm.weights import random_tensors
+    cfg, make = engines
+    spec = model_from_tensors(cfg, dict(random_tensors(cfg, 7, torch.bfloat16, device="cuda:0", norm_jitter=0.1)),
+                              "bfloat16", "cuda:0")
+    prompts = [helpers.random_tokens(60 + 23 * i, cfg.vocab_size, 700 + i) for i in range(11)]
+    outs, seen = {}, {}
+    for graphs in (True, False):
+        ec = EngineConfig(kv=KVManagerConfig(num_blocks=400, block_size=16, max_seq_len=512, watermark_blocks=0),
+                          sched=SchedulerConfig(max_num_seqs=16, max_batched_tokens=96), dtype="bfloat16",
+                          cuda_graphs=graphs)
+        eng = kvcm.Engine(spec, ec)
+        ids, done, mixed, step = [], {}, 0, 0
+        while len(ids) < len(prompts) or not eng.idle():
+            if step % 3 == 0 and len(ids) < len(prompts):
+                ids.append(eng.add_request(prompts[len(ids)], max_new_tokens=40))
+            info = eng.step()
+            mixed += int(info.prefill_tokens > 0 and info.decode_seqs > 0)
+            for f in eng.take_finished():
+                done[f.id] = f.generated()
+            step += 1
+        outs[graphs] = [done[i] for i in ids]
+        seen[graphs] = (mixed, sorted({k[0] for k in eng.graphs.captured}) if eng.graphs else [])
+    assert seen[True][0] >= 8 and set(seen[True][1]) >= {1, 2, 4, 8, 16}, seen[True]
+    # Every token of both runs is the plain implementation's greedy choice, or within a near-tie of
+    # it.  The two runs need not agree to the bit (a padded batch of 16 and a batch of 11 take
+    # different library kernels and other context partitions), so where they part ways, the plain
+    # logits must show a near-tie at that very place.
+    for p, a, b in zip(prompts, outs[True], outs[False]):
+        assert len(a) == 40 and len(b) == 40
+        for o in ((a,) if a == b else (a, b)):
+            logits = make["plain"](list(p) + list(o))
+            margin = 0.08 * logits.std().item()
+            for k, tok in enumerate(o):
+                row = logits[len(p) - 1 + k]
+                assert row.max().item() - row[tok].item() <= margin, (len(p), k, tok)
+        if a != b:
+            k = next(i for i in range(40) if a[i] != b[i])
+            row = make["plain"](list(p) + list(a))[len(p) - 1 + k]
+            top = row.topk(2).values
+            assert (top[0] - top[1]).item() <= 0.08 * row.std().item(), f"runs part ways at a clear choice (token {k})"

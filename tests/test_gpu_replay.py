@@ -237,7 +237,7 @@ def test_trace_tool_refuses_with_one_line(model_folders, tmp_path):
     import sys
     folder = model_folders("tiny-a", "bfloat16")
     toks = tokens_of("tiny-a", 4)
-    cases = [([dict(step=3, entries=[dict(id="a", tokens=toks[:100], want=[99])], end=[])], "out of cache pages"),
+    cases = [([dict(step=3, entries=[dict(id="a", tokens=toks[:100], want=[99])], end=[])], "does not fit the cache"),
              ([dict(step=3, entries=[dict(id="a", tokens=toks[:10], want=[10])], end=[])], "wants place 10"),
              ([dict(step=3, entries=[dict(id="a", tokens=[], want=[])], end=[])], "brings no tokens"),
              ([dict(step=3, entries=[dict(id="a", tokens=[256], want=[0])], end=[])], "outside the vocabulary")]
@@ -249,3 +249,102 @@ def test_trace_tool_refuses_with_one_line(model_folders, tmp_path):
         assert p.returncode != 0 and "done 3" not in p.stdout
         last = [l for l in p.stderr.splitlines() if l.strip()][-1]
         assert last.startswith("trace_run: step 3:") and message in last, p.stderr[-1500:]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_mixed_batches_under_the_contiguous_policy(name, dtype, model_folders, oracle):
+    """The mixed schedule again with the contiguous policy (every request reserves its longest
+    length as one run of pages): right against the plain implementation, and equal bit for bit to
+    the paged run -- the kernels are the same, only the page numbers differ."""
+    steps, places = mixed_trace(name)
+    block = helpers.TINY[name]["block_size"]
+    longest = helpers.roundup(max(LENGTHS[name]), block)
+    paged = replayer(model_folders, name, dtype, mixed_pool_tokens(name))
+    contiguous = replayer(model_folders, name, dtype, 4 * longest, policy="contiguous", max_seq_len=longest)
+    assert contiguous.kv.name() == "contiguous"
+    for s, where in zip(steps, places):
+        a = paged.step(s["entries"], s["end"])
+        b = contiguous.step(s["entries"], s["end"])
+        ref = torch.stack([oracle(name, dtype, i)[pos] for i, pos in where])
+        helpers.assert_logits_close(b, ref, dtype, f"{name} contiguous, mixed step {s['step']}")
+        assert torch.equal(a, b), f"{name} step {s['step']}: paged and contiguous differ"
+        for e in s["entries"]:
+            if e["id"] in contiguous.live:
+                t = contiguous.live[e["id"]].table(0)
+                assert t == list(range(t[0], t[0] + len(t))) and len(t) == longest // block
+    assert contiguous.kv.blocks_in_use() == 0
+
+
+@pytest.mark.parametrize("name,dtype", [("tiny-b", "float32"), ("tiny-b", "bfloat16"), ("tiny-c", "bfloat16"),
+                                        ("tiny-d", "bfloat16")])
+def test_prefix_cache_hits_at_the_logit_level(name, dtype, model_folders):
+    """With prefix caching a new request takes over the pages of an earlier one that hold the same
+    tokens, and computes only the rest.  Checked on logits, not on greedy tokens: a shared page that
+    is slightly wrong moves them.  Request b shares 67 tokens with a; its first portion ends in the
+    middle of a page, the next ones start there; a is still live meanwhile (the pages are held
+    twice) and goes on afterwards; c arrives after both have ended and hits the parked pages."""
+    block = helpers.TINY[name]["block_size"]
+    vocab = helpers.TINY[name]["cfg"]["vocab_size"]
+    cfg, w = P.read_model_folder(model_folders(name, dtype))
+    storage = None if dtype == "float32" else torch.bfloat16
+    ta = helpers.random_tokens(101, vocab, 7)
+    tb = ta[:67] + helpers.random_tokens(53, vocab, 8)
+    tc = tb[:90] + helpers.random_tokens(20, vocab, 9)
+    ra, rb, rc = (P.llama_forward(cfg, w, t, storage) for t in (ta, tb, tc))
+    r = replayer(model_folders, name, dtype, 512, prefix_caching=True)
+    got = r.step([dict(id="a", tokens=ta[:100], want=list(range(100)))])
+    helpers.assert_logits_close(got, ra[:100], dtype, "request a")
+    # b: its first portion of 70 tokens; the pages of a that match (whole pages, and never the page
+    # with the portion's last token) are taken over
+    hit = min(67 // block, (70 - 1) // block) * block
+    assert hit >= 32
+    with pytest.raises(Exception, match="taken over from the prefix cache"):
+        r.step([dict(id="b", tokens=tb[:70], want=[0])])
+    assert "b" not in r.live                                   # a refused request is not taken
+    got = r.step([dict(id="b", tokens=tb[:70], want=list(range(hit, 70)))])
+    assert r.session.cached_tokens_last == {"b": hit}
+    assert r.live["b"].table(0)[:hit // block] == r.live["a"].table(0)[:hit // block]     # the same pages
+    helpers.assert_logits_close(got, rb[hit:70], dtype, "b after a prefix hit")
+    outs, at = [], 70
+    for k in (2, 13, 1, 1, len(tb) - 87):
+        outs.append(r.step([dict(id="b", tokens=tb[at:at + k], want=list(range(k)))]))
+        at += k
+    assert at == len(tb)
+    helpers.assert_logits_close(torch.cat(outs), rb[70:], dtype, "b in portions that start inside a page")
+    # a goes on: its shared pages are what they were
+    got = r.step([dict(id="a", tokens=ta[100:], want=[0])], end=["a", "b"])
+    helpers.assert_logits_close(got, ra[100:], dtype, "a after b read its pages")
+    assert r.kv.blocks_in_use() == 0 and r.kv.blocks_cached_free() > 0
+    # c: both are gone, their pages are parked; c finds 90 tokens of b among them
+    hit_c = min(90 // block, (len(tc) - 1) // block) * block
+    got = r.step([dict(id="c", tokens=tc, want=list(range(hit_c, len(tc))))], end=["c"])
+    assert r.session.cached_tokens_last == {"c": hit_c} and hit_c >= 64
+    helpers.assert_logits_close(got, rc[hit_c:], dtype, "c after hitting parked pages")
+    st = r.kv.prefix_stats()
+    assert st.hit_blocks >= (hit + hit_c) // block
+
+
+def test_trace_tool_with_policy_and_prefix_flags(model_folders, tmp_path):
+    """``bin/trace_run --policy contiguous`` and ``--prefix`` as a user runs them."""
+    name, dtype = "tiny-b", "bfloat16"
+    block = helpers.TINY[name]["block_size"]
+    vocab = helpers.TINY[name]["cfg"]["vocab_size"]
+    cfg, w = P.read_model_folder(model_folders(name, dtype))
+    ta = helpers.random_tokens(60, vocab, 17)
+    tb = ta[:41] + helpers.random_tokens(30, vocab, 18)
+    ra, rb = (P.llama_forward(cfg, w, t, torch.bfloat16) for t in (ta, tb))
+    hit = (41 // block) * block
+    steps = [dict(step=0, entries=[dict(id="a", tokens=ta, want=[59])], end=[]),
+             dict(step=1, entries=[dict(id="b", tokens=tb[:50], want=list(range(hit, 50)))], end=["a"]),
+             dict(step=2, entries=[dict(id="b", tokens=tb[50:], want=list(range(21)))], end=["b"])]
+    out = helpers.run_trace_tool(model_folders(name, dtype), dtype, steps, 256, str(tmp_path / "p"),
+                                 ["--block-size", str(block), "--prefix"])
+    helpers.assert_logits_close(torch.from_numpy(out[0]), ra[[59]], dtype, "trace_run --prefix, a")
+    helpers.assert_logits_close(torch.from_numpy(out[1]), rb[hit:50], dtype, "trace_run --prefix, b after a hit")
+    helpers.assert_logits_close(torch.from_numpy(out[2]), rb[50:], dtype, "trace_run --prefix, b goes on")
+    steps = [dict(step=0, entries=[dict(id="a", tokens=ta, want=[59])], end=[]),
+             dict(step=1, entries=[dict(id="b", tokens=tb, want=[70])], end=["a", "b"])]
+    out = helpers.run_trace_tool(model_folders(name, dtype), dtype, steps, 256, str(tmp_path / "c"),
+                                 ["--block-size", str(block), "--policy", "contiguous", "--max-seq-len", "96"])
+    helpers.assert_logits_close(torch.from_numpy(out[0]), ra[[59]], dtype, "trace_run --policy contiguous, a")
+    helpers.assert_logits_close(torch.from_numpy(out[1]), rb[[70]], dtype, "trace_run --policy contiguous, b")
