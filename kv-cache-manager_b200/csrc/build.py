@@ -177,7 +177,7 @@ def load_core():
 def build_cuda() -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     flags = NVCC_FLAGS + CUDA_ARCH_FLAGS
-    return _build("libkvcm_cuda.so", cuda_sources(), nvcc, flags, ["-lcudart", "-lcuda"], "cuda")
+    return _build("libkvcm_cuda.so", cuda_sources(), nvcc, flags, ["-lcudart", "-lcuda", "-lcublas"], "cuda")
 
 
 def load_cuda() -> ctypes.CDLL:

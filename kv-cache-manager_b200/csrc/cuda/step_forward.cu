@@ -1,0 +1,283 @@
+// The forward pass of one step, launched from C++: embedding, every call site of the run order
+// (RMSNorm -> paged attention with rotate-half rotary encoding -> RMSNorm -> SiLU-gated
+// feed-forward, pre-norm, float residual stream), final norm on the wanted rows and the output head.
+//
+// This file holds no kernel.  It is the host-side loop that the step function would otherwise run
+// in Python, one ctypes call and a few tensor objects per launch (about 8 us each, 3.7 ms for a
+// prefill step of 22 layers): the same launchers, in the same order, chosen by the same rules, called
+// directly.  The order and the formulas are the reference's forward (src/model/llama.cpp:84-139);
+// which product kernel runs is this engine's own dispatch (parts/linear.py gives the reasons):
+//   float32 storage  -> the plain kernels throughout (the true 32-bit path);
+//   bfloat16 storage -> the weight-streaming kernel for a handful of rows, with the rotary encoding
+//                       and the cache write (qkv) or SiLU*up (gate/up) in its epilogue; the tcgen05
+//                       kernel with the gated epilogue for the gate/up product of many rows; the
+//                       library product (cuBLAS, where the reference calls it too) for the rest.
+// The caller (engine/native_forward.py) checks that the model is made of exactly these parts, owns
+// every buffer, and falls back to the part-by-part path for anything else.
+#include <cublas_v2.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "common.cuh"
+
+extern "C" {
+// launchers of the other files of this library (C ABI; see each file for the contract)
+int kvcm_embed_f32(const int*, const void*, float*, int, int, int, void*);
+int kvcm_embed_bf16(const int*, const void*, float*, int, int, int, void*);
+int kvcm_rmsnorm_f32(float*, const void*, const void*, int, void*, const int*, int, int, float, void*);
+int kvcm_rmsnorm_bf16(float*, const void*, const void*, int, void*, const int*, int, int, float, void*);
+int kvcm_rope_cache_f32(void*, int, const int*, const float*, int, int, const int*, void*, void*, int, int, int, int, int, int, void*);
+int kvcm_rope_cache_bf16(void*, int, const int*, const float*, int, int, const int*, void*, void*, int, int, int, int, int, int, void*);
+int kvcm_silu_mul_f32(const void*, void*, int, int, void*);
+int kvcm_silu_mul_bf16(const void*, void*, int, int, void*);
+int kvcm_gemm_plain_f32(const void*, const void*, void*, int, int, int, int, int, int, void*);
+int kvcm_attention_plain_f32(const void*, int, void*, int, const void*, const void*, const int*, int, const int*, const int*,
+                             int, int, int, int, int, float, int, void*);
+int kvcm_attention_plain_bf16(const void*, int, void*, int, const void*, const void*, const int*, int, const int*, const int*,
+                              int, int, int, int, int, float, int, void*);
+int kvcm_attention_fast_supports(int);
+int kvcm_attention_decode_resident_blocks(int);
+int kvcm_attention_decode_cluster_parts(void);
+int kvcm_attention_decode_bf16(const void*, int, void*, int, const void*, const void*, const int*, int, const int*, int, int,
+                               int, int, int, float, int, int, int, float*, int, void*);
+int kvcm_attention_tcgen05_supports(int, int);
+int kvcm_attention_prefill_tcgen05_bf16(const void*, int, int, void*, int, const void*, const void*, int, const int*, int,
+                                        const int*, const int*, const int*, const int*, const int*, int, int, int, int, int,
+                                        float, int, void*);
+int kvcm_attention_prefill_bf16(const void*, int, void*, int, const void*, const void*, const int*, int, const int*,
+                                const int*, const int*, const int*, const int*, int, int, int, int, int, float, int, void*);
+int kvcm_gemm_stream_supports(int, int, int);
+int kvcm_gemm_stream_fused_supports(int, int, int);
+int kvcm_gemm_stream_bf16(const void*, const void*, void*, int, int, int, int, int, int, int, int, void*);
+int kvcm_qkv_rope_cache_bf16(const void*, const void*, void*, int, int, int, int, int, const int*, const float*, const int*,
+                             void*, void*, int, int, int, int, int, void*);
+int kvcm_gate_up_silu_bf16(const void*, const void*, void*, int, int, int, int, int, int, int, void*);
+int kvcm_gemm_tcgen05_supports(int, int, int, int, int);
+int kvcm_gate_up_silu_tcgen05_bf16(const void*, const void*, void*, int, int, int, int, int, int, void*);
+}
+
+namespace {
+
+constexpr int kMaxGroups = 4;
+constexpr long long kStreamMaxBytes = 32ll << 20;       // parts/linear.py: STREAM_MAX_BYTES
+constexpr int kTcgen05MinRows = 256;                    // TCGEN05_MIN_ROWS
+constexpr int kTcgen05GatedMaxHidden = 3072;            // TCGEN05_GATED_MAX_HIDDEN
+constexpr int kKeyTile = 64;
+
+}  // namespace
+
+// One call site of the run order (host array).
+struct KvcmForwardLayer {
+  const void* w_qkv; const void* w_o; const void* w_gate_up; const void* w_down;
+  const void* norm1; const void* norm2;
+  void* k_cache; void* v_cache;
+  float eps1, eps2;
+  int group, window, writes, num_pages;
+};
+
+struct KvcmForwardArgs {
+  // the model (fixed for an engine)
+  const KvcmForwardLayer* layers;                       // host memory
+  const void* embed; const void* final_norm; const void* lm_head;
+  const float* inv_freq;
+  // the step: the batch's integer arrays on the device
+  const int* tokens; const int* positions; const int* row_seq; const int* seq_q_start; const int* seq_q_len;
+  const int* seq_ctx_len; const int* tile_seq; const int* tile_q0; const int* logit_rows;
+  const int* group_tables[kMaxGroups]; const int* group_slots[kMaxGroups];
+  // buffers of the caller, sized for the step: x [T,H] float; h, proj [T,H]; qkv [T,QKV]; attn [T,nh*hd];
+  // gate_up [T,2I]; act [T,I]; h_last [L,H]; logits [L,V] float; attn_scratch floats; a library workspace
+  float* x; void* h; void* qkv; void* attn; void* proj; void* gate_up; void* act; void* h_last; float* logits;
+  float* attn_scratch; void* lib_workspace;
+  long long attn_scratch_floats, lib_workspace_bytes;
+  int num_layers, f32, H, I, nh, nkv, hd, V, block_size, max_blocks, sm_count;
+  int rows, seqs, decode_seqs, prefill_tiles, tile_rows, max_decode_ctx, num_logits, reserved;
+  float final_eps, scale;
+};
+
+namespace {
+
+struct Library {                                        // one cuBLAS handle per device
+  cublasHandle_t handle[64] = {};
+  std::mutex lock;
+  cublasHandle_t get() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> g(lock);
+    if (handle[dev] == nullptr && cublasCreate(&handle[dev]) != CUBLAS_STATUS_SUCCESS) handle[dev] = nullptr;
+    return handle[dev];
+  }
+};
+Library g_library;
+
+// y[M,N] = x[M,K] w[N,K]^T with the library: bfloat16 operands, float accumulation.
+int library_gemm(const KvcmForwardArgs& a, const void* x, const void* w, void* y, int M, int N, int K, bool out_f32,
+                 cudaStream_t s) {
+  cublasHandle_t h = g_library.get();
+  if (h == nullptr) return KVCM_ERR_UNSUPPORTED;
+  if (cublasSetStream(h, s) != CUBLAS_STATUS_SUCCESS) return KVCM_ERR_UNSUPPORTED;
+  // a workspace of the caller's: the library must not allocate while a CUDA graph is recorded
+  if (a.lib_workspace != nullptr &&
+      cublasSetWorkspace(h, a.lib_workspace, size_t(a.lib_workspace_bytes)) != CUBLAS_STATUS_SUCCESS)
+    return KVCM_ERR_UNSUPPORTED;
+  const float alpha = 1.f, beta = 0.f;
+  // row-major y = x w^T  <=>  column-major y^T[N,M] = w[K,N]^T x^T[K,M]
+  const cublasStatus_t st = cublasGemmEx(h, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, w, CUDA_R_16BF, K, x, CUDA_R_16BF, K,
+                                         &beta, y, out_f32 ? CUDA_R_32F : CUDA_R_16BF, N, CUBLAS_COMPUTE_32F,
+                                         CUBLAS_GEMM_DEFAULT);
+  return st == CUBLAS_STATUS_SUCCESS ? 0 : 20000 + int(st);
+}
+
+// The product of a part: which kernel, by the rules of parts/linear.py ('auto').
+int product(const KvcmForwardArgs& a, const void* x, const void* w, void* y, int M, int N, int K, bool out_f32,
+            cudaStream_t s) {
+  if (M == 0) return 0;
+  if (a.f32) return kvcm_gemm_plain_f32(x, w, y, M, N, K, K, K, N, s);
+  if ((M <= 8 || (long long)N * K * 2 <= kStreamMaxBytes) && kvcm_gemm_stream_supports(M, N, K))
+    return kvcm_gemm_stream_bf16(x, w, y, M, N, K, K, K, N, out_f32 ? 1 : 0, a.sm_count, s);
+  return library_gemm(a, x, w, y, M, N, K, out_f32, s);
+}
+
+bool tiles_fill_well(int M, int N, int sms) {
+  const long long tiles = (long long)((M + 127) / 128) * ((N + 255) / 256);
+  const long long rounds = (tiles + sms - 1) / sms;
+  return tiles >= sms && tiles * 10 >= 8 * rounds * sms;
+}
+
+// How decode attention splits the context (kernels/library.py: decode_partitions, 'auto').
+void decode_partitions(int seqs, int nh, int nkv, int hd, int max_ctx, int* size, int* parts) {
+  max_ctx = std::max(max_ctx, 1);
+  const int G = nh / nkv;
+  const int blocks = std::max(1, seqs * nkv * ((G + 15) / 16));
+  static int resident_hd = -1, resident = 0;
+  if (resident_hd != hd) {
+    resident = kvcm_attention_decode_resident_blocks(hd);
+    resident_hd = hd;
+  }
+  int sms = 0, dev = 0;
+  if (resident <= 0 && cudaGetDevice(&dev) == cudaSuccess)
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int res = resident > 0 ? resident : 3 * std::max(sms, 1);
+  const int cluster = kvcm_attention_decode_cluster_parts();
+  int p = std::max(1, std::min(res / blocks, max_ctx / 128));
+  if (p > cluster) p = std::max(cluster, std::min(p, (max_ctx + 511) / 512));
+  *size = ((max_ctx + p - 1) / p + kKeyTile - 1) / kKeyTile * kKeyTile;
+  *parts = (max_ctx + *size - 1) / *size;
+}
+
+int attention(const KvcmForwardArgs& a, const KvcmForwardLayer& L, const void* q, int q_stride, int& launches,
+              cudaStream_t s) {
+  const int* tables = a.group_tables[L.group];
+  if (a.f32 || !kvcm_attention_fast_supports(a.hd) || a.nh % a.nkv) {
+    ++launches;
+    return (a.f32 ? kvcm_attention_plain_f32 : kvcm_attention_plain_bf16)(
+        q, q_stride, a.attn, a.nh * a.hd, L.k_cache, L.v_cache, tables, a.max_blocks, a.row_seq, a.positions, a.rows, a.nh,
+        a.nkv, a.hd, a.block_size, a.scale, L.window, s);
+  }
+  int rc = 0;
+  const int nd = a.decode_seqs;
+  if (nd > 0) {
+    int size = 0, parts = 1;
+    decode_partitions(nd, a.nh, a.nkv, a.hd, a.max_decode_ctx, &size, &parts);
+    const int cluster = kvcm_attention_decode_cluster_parts();
+    int in_cluster = parts > 1 && parts <= cluster;
+    if (parts > 1 && !in_cluster && (long long)nd * a.nh * parts * (a.hd + 2) > a.attn_scratch_floats)
+      return KVCM_ERR_UNSUPPORTED;                                  // the caller sizes the scratch for its limits
+    rc = kvcm_attention_decode_bf16(q, q_stride, a.attn, a.nh * a.hd, L.k_cache, L.v_cache, tables, a.max_blocks,
+                                    a.seq_ctx_len, nd, a.nh, a.nkv, a.hd, a.block_size, a.scale, L.window, size, parts,
+                                    a.attn_scratch, in_cluster, s);
+    if (rc) return rc;
+    launches += (parts > 1 && !in_cluster) ? 2 : 1;
+  }
+  if (a.rows > nd) {
+    if (a.tile_rows != 64) return KVCM_ERR_UNSUPPORTED;
+    ++launches;
+    if (kvcm_attention_tcgen05_supports(a.hd, a.block_size) && (q_stride % 8) == 0)
+      return kvcm_attention_prefill_tcgen05_bf16(q, q_stride, a.rows, a.attn, a.nh * a.hd, L.k_cache, L.v_cache, L.num_pages,
+                                                 tables, a.max_blocks, a.tile_seq, a.tile_q0, a.seq_q_start, a.seq_q_len,
+                                                 a.seq_ctx_len, a.prefill_tiles, a.nh, a.nkv, a.hd, a.block_size, a.scale,
+                                                 L.window, s);
+    return kvcm_attention_prefill_bf16(q, q_stride, a.attn, a.nh * a.hd, L.k_cache, L.v_cache, tables, a.max_blocks,
+                                       a.tile_seq, a.tile_q0, a.seq_q_start, a.seq_q_len, a.seq_ctx_len, a.prefill_tiles,
+                                       a.nh, a.nkv, a.hd, a.block_size, a.scale, L.window, s);
+  }
+  return rc;
+}
+
+}  // namespace
+
+#define KVCM_TRY(expr)        \
+  do {                        \
+    const int rc_ = (expr);   \
+    if (rc_ != 0) return rc_; \
+  } while (0)
+
+// Runs the step.  Only enqueues device work on `stream`; returns the first non-zero launch result.
+// `launches` (optional) receives the number of launches made.
+KVCM_API int kvcm_forward(const KvcmForwardArgs* ap, int* launches, void* stream) {
+  const KvcmForwardArgs& a = *ap;
+  cudaStream_t s = (cudaStream_t)stream;
+  int n = 0;
+  if (launches) *launches = 0;
+  if (a.rows == 0) return 0;
+  if (a.num_layers < 0 || a.H <= 0 || a.nkv <= 0 || a.nh % a.nkv) return KVCM_ERR_UNSUPPORTED;
+  const int T = a.rows, H = a.H, I = a.I, QK = a.nh * a.hd, QKV = (a.nh + 2 * a.nkv) * a.hd;
+  const auto embed = a.f32 ? kvcm_embed_f32 : kvcm_embed_bf16;
+  const auto rmsnorm = a.f32 ? kvcm_rmsnorm_f32 : kvcm_rmsnorm_bf16;
+  const auto rope_cache = a.f32 ? kvcm_rope_cache_f32 : kvcm_rope_cache_bf16;
+  const auto silu_mul = a.f32 ? kvcm_silu_mul_f32 : kvcm_silu_mul_bf16;
+
+  KVCM_TRY(embed(a.tokens, a.embed, a.x, T, H, a.V, s)); ++n;
+  const void* pending = nullptr;
+  for (int l = 0; l < a.num_layers; ++l) {
+    const KvcmForwardLayer& L = a.layers[l];
+    if (L.group < 0 || L.group >= kMaxGroups) return KVCM_ERR_UNSUPPORTED;
+    KVCM_TRY(rmsnorm(a.x, pending, L.norm1, 0, a.h, nullptr, T, H, L.eps1, s)); ++n;
+    // attention: qkv product, rotary encoding, cache write -- one kernel for a handful of rows
+    const void* q = a.qkv;
+    int q_stride = QKV;
+    if (!a.f32 && L.writes && (a.hd % 16) == 0 && kvcm_gemm_stream_fused_supports(T, QKV, H)) {
+      KVCM_TRY(kvcm_qkv_rope_cache_bf16(a.h, L.w_qkv, a.qkv, T, H, H, H, QK, a.positions, a.inv_freq,
+                                        a.group_slots[L.group], L.k_cache, L.v_cache, a.nh, a.nkv, a.hd, a.block_size,
+                                        a.sm_count, s));
+      ++n;
+      q_stride = QK;
+    } else {
+      KVCM_TRY(product(a, a.h, L.w_qkv, a.qkv, T, QKV, H, false, s)); ++n;
+      KVCM_TRY(rope_cache(a.qkv, QKV, a.positions, a.inv_freq, a.hd, 0, a.group_slots[L.group], L.k_cache, L.v_cache, T, a.nh,
+                          a.nkv, a.hd, a.block_size, L.writes, s));
+      ++n;
+    }
+    KVCM_TRY(attention(a, L, q, q_stride, n, s));
+    KVCM_TRY(product(a, a.attn, L.w_o, a.proj, T, H, QK, false, s)); ++n;
+    KVCM_TRY(rmsnorm(a.x, a.proj, L.norm2, 0, a.h, nullptr, T, H, L.eps2, s)); ++n;
+    // feed-forward: gate/up product and activation -- one kernel where one exists for the shape
+    if (!a.f32 && (I % 8) == 0 && kvcm_gemm_stream_fused_supports(T, 2 * I, H)) {
+      KVCM_TRY(kvcm_gate_up_silu_bf16(a.h, L.w_gate_up, a.act, T, I, H, H, H, I, a.sm_count, s)); ++n;
+    } else if (!a.f32 && T >= kTcgen05MinRows && tiles_fill_well(T, 2 * I, a.sm_count) && H <= kTcgen05GatedMaxHidden &&
+               kvcm_gemm_tcgen05_supports(T, 2 * I, H, H, H)) {
+      KVCM_TRY(kvcm_gate_up_silu_tcgen05_bf16(a.h, L.w_gate_up, a.act, T, I, H, H, H, I, s)); ++n;
+    } else {
+      KVCM_TRY(product(a, a.h, L.w_gate_up, a.gate_up, T, 2 * I, H, false, s)); ++n;
+      KVCM_TRY(silu_mul(a.gate_up, a.act, T, I, s)); ++n;
+    }
+    KVCM_TRY(product(a, a.act, L.w_down, a.proj, T, H, I, false, s)); ++n;
+    pending = a.proj;
+  }
+  if (a.num_logits > 0) {
+    KVCM_TRY(rmsnorm(a.x, pending, a.final_norm, 0, a.h_last, a.logit_rows, a.num_logits, H, a.final_eps, s)); ++n;
+    if (a.f32) {
+      KVCM_TRY(kvcm_gemm_plain_f32(a.h_last, a.lm_head, a.logits, a.num_logits, a.V, H, H, H, a.V, s));
+    } else {
+      KVCM_TRY(product(a, a.h_last, a.lm_head, a.logits, a.num_logits, a.V, H, true, s));
+    }
+    ++n;
+  }
+  if (launches) *launches = n;
+  return 0;
+}
+
+KVCM_API int kvcm_forward_args_bytes(void) { return int(sizeof(KvcmForwardArgs)); }
+KVCM_API int kvcm_forward_layer_bytes(void) { return int(sizeof(KvcmForwardLayer)); }

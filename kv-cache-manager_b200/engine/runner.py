@@ -48,6 +48,9 @@ class ModelRunner:
         self._copy_pending = False
         self._views = {}                  # (buffer, length) -> (device view, pinned view) of an upload
         self.h2d_bytes_last = 0
+        # The standard arrangement of parts runs its layer loop in C++ (engine/native_forward.py).
+        from .native_forward import NativeForward
+        self.native = NativeForward.plan(spec, self) if self.options.get("native_forward", True) else None
 
     # ------------------------------------------------------------------ batch -> device
     def build(self, entries: Seq[Tuple[object, int, int, Seq[int]]], pad_rows: int = 0,
@@ -132,6 +135,8 @@ class ModelRunner:
         """Hidden states through every layer; float32 logits [wanted rows, vocab] (None when no
         row is wanted: the step then only fills the cache)."""
         spec = self.spec
+        if self.native is not None and self.native.takes(ctx):
+            return self.native.run(ctx)
         x = spec.embedding.forward(ctx)
         pending = None
         for k, call in enumerate(spec.order):

@@ -716,3 +716,66 @@ def tcgen05_error() -> int:
     (1: the TMA thread waited for a free stage, 2: the MMA thread waited for data, 3: the epilogue
     waited for the accumulator).  Reading clears it.  Synchronises the device."""
     return int(_lib().kvcm_tcgen05_error())
+
+
+# ------------------------------------------------------------------ the step's forward pass from C++
+
+FORWARD_MAX_GROUPS = 4
+
+
+class ForwardLayer(ctypes.Structure):
+    """One call site of the run order (csrc/cuda/step_forward.cu: KvcmForwardLayer)."""
+    _fields_ = [("w_qkv", ctypes.c_void_p), ("w_o", ctypes.c_void_p), ("w_gate_up", ctypes.c_void_p),
+                ("w_down", ctypes.c_void_p), ("norm1", ctypes.c_void_p), ("norm2", ctypes.c_void_p),
+                ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
+                ("eps1", ctypes.c_float), ("eps2", ctypes.c_float),
+                ("group", ctypes.c_int), ("window", ctypes.c_int), ("writes", ctypes.c_int), ("num_pages", ctypes.c_int)]
+
+
+class ForwardArgs(ctypes.Structure):
+    """The argument block of ``kvcm_forward`` (csrc/cuda/step_forward.cu: KvcmForwardArgs)."""
+    _fields_ = [
+        ("layers", ctypes.c_void_p), ("embed", ctypes.c_void_p), ("final_norm", ctypes.c_void_p),
+        ("lm_head", ctypes.c_void_p), ("inv_freq", ctypes.c_void_p),
+        ("tokens", ctypes.c_void_p), ("positions", ctypes.c_void_p), ("row_seq", ctypes.c_void_p),
+        ("seq_q_start", ctypes.c_void_p), ("seq_q_len", ctypes.c_void_p), ("seq_ctx_len", ctypes.c_void_p),
+        ("tile_seq", ctypes.c_void_p), ("tile_q0", ctypes.c_void_p), ("logit_rows", ctypes.c_void_p),
+        ("group_tables", ctypes.c_void_p * FORWARD_MAX_GROUPS), ("group_slots", ctypes.c_void_p * FORWARD_MAX_GROUPS),
+        ("x", ctypes.c_void_p), ("h", ctypes.c_void_p), ("qkv", ctypes.c_void_p), ("attn", ctypes.c_void_p),
+        ("proj", ctypes.c_void_p), ("gate_up", ctypes.c_void_p), ("act", ctypes.c_void_p), ("h_last", ctypes.c_void_p),
+        ("logits", ctypes.c_void_p), ("attn_scratch", ctypes.c_void_p), ("lib_workspace", ctypes.c_void_p),
+        ("attn_scratch_floats", ctypes.c_longlong), ("lib_workspace_bytes", ctypes.c_longlong),
+        ("num_layers", ctypes.c_int), ("f32", ctypes.c_int), ("H", ctypes.c_int), ("I", ctypes.c_int),
+        ("nh", ctypes.c_int), ("nkv", ctypes.c_int), ("hd", ctypes.c_int), ("V", ctypes.c_int),
+        ("block_size", ctypes.c_int), ("max_blocks", ctypes.c_int), ("sm_count", ctypes.c_int),
+        ("rows", ctypes.c_int), ("seqs", ctypes.c_int), ("decode_seqs", ctypes.c_int), ("prefill_tiles", ctypes.c_int),
+        ("tile_rows", ctypes.c_int), ("max_decode_ctx", ctypes.c_int), ("num_logits", ctypes.c_int),
+        ("reserved", ctypes.c_int),
+        ("final_eps", ctypes.c_float), ("scale", ctypes.c_float),
+    ]
+
+
+def forward_layouts_match() -> bool:
+    lib = _lib()
+    return (ctypes.sizeof(ForwardArgs) == int(lib.kvcm_forward_args_bytes())
+            and ctypes.sizeof(ForwardLayer) == int(lib.kvcm_forward_layer_bytes()))
+
+
+_forward_launches = ctypes.c_int(0)
+
+
+def forward(args: ForwardArgs) -> int:
+    """The whole forward pass of a step launched from C++ (csrc/cuda/step_forward.cu); returns the
+    number of kernel launches it made.  The caller owns every buffer the block names."""
+    global _launches
+    rc = _lib().kvcm_forward(ctypes.byref(args), ctypes.byref(_forward_launches), _stream())
+    n = int(_forward_launches.value)
+    _launches += n
+    if _profile is not None:
+        profile_mark("forward (whole step)")
+    if rc == 0:
+        return n
+    if rc == _ERR_UNSUPPORTED:
+        raise KernelError(f"forward: sizes not supported (rows {args.rows}, hidden {args.H}, heads {args.nh}/{args.nkv} "
+                          f"of {args.hd})")
+    raise KernelError(f"forward: error {rc} at a launch (rows {args.rows})")
