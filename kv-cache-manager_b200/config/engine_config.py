@@ -54,4 +54,5 @@ class EngineConfig:
     sampling_seed: int = 0
     eos_token_id: int = -1           # < 0: no end-of-sequence stop (the reference has none)
     cuda_graphs: bool = True         # capture decode-only steps per batch-size bucket
+    native_loop: bool = True         # run the request loop and the layer loop in C++ where the model allows it
     device: str = "cuda:0"

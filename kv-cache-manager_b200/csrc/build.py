@@ -32,7 +32,7 @@ _PKG = os.path.dirname(_HERE)
 
 CORE_SOURCES = ["core/block_allocator.cpp", "core/prefix_cache.cpp", "core/kv_manager.cpp",
                 "core/paged_manager.cpp", "core/scheduler.cpp", "core/batch.cpp",
-                "core/safetensors.cpp", "core/bindings.cpp"]
+                "core/safetensors.cpp", "core/native_engine.cpp", "core/bindings.cpp"]
 CUDA_ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
@@ -74,7 +74,7 @@ def cuda_sources() -> List[str]:
 def _digest(paths: List[str], flags: List[str]) -> str:
     h = hashlib.sha256()
     h.update("\0".join(flags).encode())
-    dirs = sorted({os.path.dirname(os.path.join(_HERE, p)) for p in paths})
+    dirs = sorted({os.path.dirname(os.path.join(_HERE, p)) for p in paths} | {os.path.join(_HERE, "include")})
     files = set(os.path.join(_HERE, p) for p in paths)
     for d in dirs:                                  # headers count too
         for f in os.listdir(d):

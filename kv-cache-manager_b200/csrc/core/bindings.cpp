@@ -7,6 +7,7 @@
 #include "block_allocator.h"
 #include "hash.h"
 #include "kv_manager.h"
+#include "native_engine.h"
 #include "paged_manager.h"
 #include "prefix_cache.h"
 #include "safetensors.h"
@@ -381,4 +382,79 @@ PYBIND11_MODULE(kvcm_core, m) {
       .def("reset_counters", &Scheduler::reset_counters)
       .def("slots_taken", [](const Scheduler& s) { return s.slots().num_taken(); })
       .def("kv_stats", [](Scheduler& s) { return s.kv().stats(s.live()); });
+
+  // ---- the request loop in C++ (native_engine.h)
+  py::class_<NativeStepInfo>(m, "NativeStepInfo")
+      .def_readonly("rows", &NativeStepInfo::rows)
+      .def_readonly("seqs", &NativeStepInfo::seqs)
+      .def_readonly("prefill_tokens", &NativeStepInfo::prefill_tokens)
+      .def_readonly("decode_seqs", &NativeStepInfo::decode_seqs)
+      .def_readonly("sampled", &NativeStepInfo::sampled)
+      .def_readonly("launches", &NativeStepInfo::launches)
+      .def_readonly("h2d_bytes", &NativeStepInfo::h2d_bytes)
+      .def_readonly("d2h_bytes", &NativeStepInfo::d2h_bytes)
+      .def_readonly("graph", &NativeStepInfo::graph)
+      .def_readonly("ms", &NativeStepInfo::ms)
+      .def_readonly("device_ms", &NativeStepInfo::device_ms);
+
+  m.def("device_backend_bytes", []() { return sizeof(KvcmDeviceBackend); });
+  m.def("forward_args_bytes", []() { return py::make_tuple(sizeof(KvcmForwardArgs), sizeof(KvcmForwardLayer)); });
+  m.def("fake_next_token", &fake_next_token);
+  m.def("fake_backend_forward_calls", &fake_backend_forward_calls);
+
+  py::class_<NativeEngine>(m, "NativeEngine")
+      // model: dict with the sizes, the device addresses of embed / final_norm / lm_head / inv_freq and
+      // `layers`: a list of dicts (addresses w_qkv, w_o, w_gate_up, w_down, norm1, norm2, k_cache, v_cache;
+      // eps1, eps2, group, window, writes, num_pages).  config: dict of NativeEngineConfig fields.
+      // backend_address: address of a KvcmDeviceBackend filled by the kernel library, 0 = the stand-in
+      // device that runs on the CPU (tests).
+      .def(py::init([](KVManager& kv, Scheduler& sched, const py::dict& model, const py::dict& config,
+                       uintptr_t backend_address) {
+             NativeModel mm;
+             auto geti = [](const py::dict& d, const char* k) { return d[k].cast<long long>(); };
+             auto getf = [](const py::dict& d, const char* k) { return d[k].cast<double>(); };
+             mm.embed = geti(model, "embed"); mm.final_norm = geti(model, "final_norm");
+             mm.lm_head = geti(model, "lm_head"); mm.inv_freq = geti(model, "inv_freq");
+             mm.f32 = int(geti(model, "f32")); mm.H = int(geti(model, "H")); mm.I = int(geti(model, "I"));
+             mm.nh = int(geti(model, "nh")); mm.nkv = int(geti(model, "nkv")); mm.hd = int(geti(model, "hd"));
+             mm.V = int(geti(model, "V")); mm.sm_count = int(geti(model, "sm_count"));
+             mm.final_eps = float(getf(model, "final_eps")); mm.scale = float(getf(model, "scale"));
+             for (const py::handle& item : model["layers"].cast<py::list>()) {
+               const py::dict d = item.cast<py::dict>();
+               KvcmForwardLayer L{};
+               L.w_qkv = reinterpret_cast<const void*>(geti(d, "w_qkv")); L.w_o = reinterpret_cast<const void*>(geti(d, "w_o"));
+               L.w_gate_up = reinterpret_cast<const void*>(geti(d, "w_gate_up"));
+               L.w_down = reinterpret_cast<const void*>(geti(d, "w_down"));
+               L.norm1 = reinterpret_cast<const void*>(geti(d, "norm1")); L.norm2 = reinterpret_cast<const void*>(geti(d, "norm2"));
+               L.k_cache = reinterpret_cast<void*>(geti(d, "k_cache")); L.v_cache = reinterpret_cast<void*>(geti(d, "v_cache"));
+               L.eps1 = float(getf(d, "eps1")); L.eps2 = float(getf(d, "eps2"));
+               L.group = int(geti(d, "group")); L.window = int(geti(d, "window")); L.writes = int(geti(d, "writes"));
+               L.num_pages = int(geti(d, "num_pages"));
+               mm.layers.push_back(L);
+             }
+             NativeEngineConfig c;
+             c.block_size = int(geti(config, "block_size")); c.max_seq_len = int(geti(config, "max_seq_len"));
+             c.num_groups = int(geti(config, "num_groups")); c.max_rows = int(geti(config, "max_rows"));
+             c.max_seqs = int(geti(config, "max_seqs")); c.graphs = config["graphs"].cast<bool>();
+             if (config.contains("tile_rows")) c.tile_rows = int(geti(config, "tile_rows"));
+             if (config.contains("attn_scratch_floats")) c.attn_scratch_floats = geti(config, "attn_scratch_floats");
+             if (config.contains("lib_workspace_bytes")) c.lib_workspace_bytes = geti(config, "lib_workspace_bytes");
+             const KvcmDeviceBackend backend = backend_address
+                 ? *reinterpret_cast<const KvcmDeviceBackend*>(backend_address) : make_fake_backend();
+             return std::make_unique<NativeEngine>(kv, sched, std::move(mm), c, backend);
+           }), py::keep_alive<1, 2>(), py::keep_alive<1, 3>(), py::arg("kv"), py::arg("scheduler"), py::arg("model"),
+           py::arg("config"), py::arg("backend_address") = 0)
+      // (the step waits for the device: other Python threads may run meanwhile)
+      .def("step", &NativeEngine::step, py::call_guard<py::gil_scoped_release>())
+      .def("now", &NativeEngine::now)
+      .def("reset_clock", &NativeEngine::reset_clock)
+      .def("set_timing", &NativeEngine::set_timing)
+      .def("device_ms_total", &NativeEngine::device_ms_total)
+      .def("reset_device_ms", &NativeEngine::reset_device_ms)
+      .def("graphs_captured", &NativeEngine::graphs_captured)
+      .def("graph_replays", &NativeEngine::graph_replays)
+      .def("graph_shapes", &NativeEngine::graph_shapes)
+      .def("stream", [](const NativeEngine& e) { return reinterpret_cast<uintptr_t>(e.stream()); })
+      .def_static("batch_bucket", &NativeEngine::batch_bucket)
+      .def_static("ctx_bucket", &NativeEngine::ctx_bucket);
 }

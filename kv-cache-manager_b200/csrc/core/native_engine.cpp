@@ -1,0 +1,418 @@
+#include "native_engine.h"
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <stdexcept>
+
+namespace kvcm {
+
+namespace {
+constexpr int kBatchBuckets[] = {1, 2, 4, 8, 16, 32, 64, 128, 256, 512};
+constexpr int kMinCtxBucket = 256;
+const char* const kFamilies[] = {"gemm_stream", "gemm_tcgen05", "gemm_tcgen05_pair", "gemm_tcgen05_splitk",
+                                 "attention_tcgen05"};
+}  // namespace
+
+int NativeEngine::batch_bucket(int n) {
+  for (int b : kBatchBuckets)
+    if (n <= b) return b;
+  return (n + 255) / 256 * 256;
+}
+
+int NativeEngine::ctx_bucket(int n) {
+  int b = kMinCtxBucket;
+  while (b < n) b *= 2;
+  return b;
+}
+
+void NativeEngine::check(int rc, const char* what) const {
+  if (rc != 0) throw std::runtime_error(std::string("engine: ") + what + " failed with code " + std::to_string(rc));
+}
+
+NativeEngine::NativeEngine(KVManager& kv, Scheduler& sched, NativeModel model, NativeEngineConfig cfg,
+                           const KvcmDeviceBackend& backend)
+    : kv_(kv), sched_(sched), model_(std::move(model)), cfg_(cfg), dev_(backend),
+      builder_(cfg.block_size, (cfg.max_seq_len + cfg.block_size - 1) / cfg.block_size, cfg.num_groups, cfg.tile_rows) {
+  if (model_.layers.empty() || model_.H <= 0 || model_.V <= 0 || model_.nkv <= 0 || model_.nh % model_.nkv)
+    throw std::invalid_argument("NativeEngine: the model's sizes are incomplete");
+  if (cfg_.num_groups < 1 || cfg_.num_groups > KVCM_FORWARD_MAX_GROUPS)
+    throw std::invalid_argument("NativeEngine: between 1 and " + std::to_string(KVCM_FORWARD_MAX_GROUPS) + " layer groups");
+  if (cfg_.max_rows < cfg_.max_seqs) cfg_.max_rows = cfg_.max_seqs;
+  max_logits_ = std::max(cfg_.max_seqs, batch_bucket(cfg_.max_seqs));
+  const int pad_rows = std::max(cfg_.max_rows, max_logits_);
+  capacity_ = builder_.capacity_for(pad_rows, max_logits_, max_logits_);
+  check(dev_.stream_create(&stream_), "creating the stream");
+  check(dev_.event_create(&ev0_), "creating an event");
+  check(dev_.event_create(&ev1_), "creating an event");
+
+  auto device = [&](size_t bytes) {
+    void* p = nullptr;
+    check(dev_.device_alloc(&p, bytes), "device allocation");
+    device_allocs_.push_back(p);
+    return p;
+  };
+  auto host = [&](size_t bytes) {
+    void* p = nullptr;
+    check(dev_.host_alloc(&p, bytes), "pinned host allocation");
+    return p;
+  };
+  const size_t esz = model_.f32 ? 4 : 2;
+  const size_t T = size_t(pad_rows), H = size_t(model_.H), I = size_t(model_.I);
+  const size_t QK = size_t(model_.nh) * model_.hd, QKV = size_t(model_.nh + 2 * model_.nkv) * model_.hd;
+  h_ints_ = static_cast<int32_t*>(host(size_t(capacity_) * 4));
+  d_ints_ = static_cast<int32_t*>(device(size_t(capacity_) * 4));
+  h_packed_ = static_cast<int32_t*>(host(size_t(2 + max_logits_) * 4));
+  d_packed_ = static_cast<int32_t*>(device(size_t(2 + max_logits_) * 4));
+  sampling_bytes_ = size_t(max_logits_) * (4 + 4 + 8 + 8);
+  h_sampling_ = static_cast<unsigned char*>(host(sampling_bytes_));
+  d_sampling_ = static_cast<unsigned char*>(device(sampling_bytes_));
+  x_ = device(T * H * 4);
+  h_ = device(T * H * esz);
+  proj_ = device(T * H * esz);
+  qkv_ = device(T * QKV * esz);
+  attn_ = device(T * QK * esz);
+  gate_up_ = device(T * 2 * I * esz);
+  act_ = device(T * I * esz);
+  h_last_ = device(size_t(max_logits_) * H * esz);
+  logits_ = device(size_t(max_logits_) * model_.V * 4);
+  if (cfg_.attn_scratch_floats > 0) attn_scratch_ = device(size_t(cfg_.attn_scratch_floats) * 4);
+  if (!model_.f32 && cfg_.lib_workspace_bytes > 0) lib_ws_ = device(size_t(cfg_.lib_workspace_bytes));
+}
+
+NativeEngine::~NativeEngine() {
+  if (stream_) dev_.stream_sync(stream_);
+  for (auto& g : graphs_) {
+    if (g.second.exec) dev_.graph_destroy(g.second.exec);
+    if (g.second.ints) dev_.device_free(g.second.ints);
+  }
+  for (void* p : device_allocs_) dev_.device_free(p);
+  if (h_ints_) dev_.host_free(h_ints_);
+  if (h_packed_) dev_.host_free(h_packed_);
+  if (h_sampling_) dev_.host_free(h_sampling_);
+  if (ev0_) dev_.event_destroy(ev0_);
+  if (ev1_) dev_.event_destroy(ev1_);
+  if (stream_) dev_.stream_destroy(stream_);
+}
+
+std::vector<std::tuple<int, int, int>> NativeEngine::graph_shapes() const {
+  std::vector<std::tuple<int, int, int>> v;
+  for (const auto& g : graphs_) v.push_back(g.first);
+  return v;
+}
+
+void NativeEngine::fill_args(KvcmForwardArgs& a, const BatchLayout& L, const int32_t* base, int max_decode_ctx) const {
+  std::memset(&a, 0, sizeof a);
+  a.layers = model_.layers.data();
+  a.embed = reinterpret_cast<const void*>(model_.embed);
+  a.final_norm = reinterpret_cast<const void*>(model_.final_norm);
+  a.lm_head = reinterpret_cast<const void*>(model_.lm_head);
+  a.inv_freq = reinterpret_cast<const float*>(model_.inv_freq);
+  a.tokens = base + L.off_tokens;
+  a.positions = base + L.off_positions;
+  a.row_seq = base + L.off_row_seq;
+  a.seq_q_start = base + L.off_seq_q_start;
+  a.seq_q_len = base + L.off_seq_q_len;
+  a.seq_ctx_len = base + L.off_seq_ctx_len;
+  a.tile_seq = base + L.off_tile_seq;
+  a.tile_q0 = base + L.off_tile_q0;
+  a.logit_rows = base + L.off_logit_rows;
+  for (int g = 0; g < L.groups; ++g) {
+    a.group_tables[g] = base + L.off_block_tables + int64_t(g) * L.seqs * L.max_blocks;
+    a.group_slots[g] = base + L.off_slot_mapping + int64_t(g) * L.rows;
+  }
+  a.x = static_cast<float*>(x_);
+  a.h = h_; a.qkv = qkv_; a.attn = attn_; a.proj = proj_; a.gate_up = gate_up_; a.act = act_; a.h_last = h_last_;
+  a.logits = static_cast<float*>(logits_);
+  a.attn_scratch = static_cast<float*>(attn_scratch_);
+  a.attn_scratch_floats = attn_scratch_ ? cfg_.attn_scratch_floats : 0;
+  a.lib_workspace = lib_ws_;
+  a.lib_workspace_bytes = lib_ws_ ? cfg_.lib_workspace_bytes : 0;
+  a.num_layers = static_cast<int>(model_.layers.size());
+  a.f32 = model_.f32;
+  a.H = model_.H; a.I = model_.I; a.nh = model_.nh; a.nkv = model_.nkv; a.hd = model_.hd; a.V = model_.V;
+  a.block_size = cfg_.block_size;
+  a.max_blocks = L.max_blocks;
+  a.sm_count = model_.sm_count;
+  a.rows = L.rows;
+  a.seqs = L.seqs;
+  a.decode_seqs = L.decode_seqs + (L.seqs - L.real_seqs);      // padding entries are single rows too
+  a.prefill_tiles = L.prefill_tiles;
+  a.tile_rows = L.tile_rows;
+  a.max_decode_ctx = max_decode_ctx;
+  a.num_logits = L.logit_rows;
+  a.final_eps = model_.final_eps;
+  a.scale = model_.scale;
+}
+
+// Per-row sampling parameters of the plan's entries that sample, rows beyond them greedy.
+void NativeEngine::stage_sampling(const std::vector<ScheduledSeq>& plan, int rows) {
+  const size_t R = size_t(max_logits_);
+  float* temps = reinterpret_cast<float*>(h_sampling_);
+  int32_t* pos = reinterpret_cast<int32_t*>(h_sampling_ + 4 * R);
+  uint64_t* seeds = reinterpret_cast<uint64_t*>(h_sampling_ + 8 * R);
+  int64_t* ids = reinterpret_cast<int64_t*>(h_sampling_ + 16 * R);
+  int n = 0;
+  for (const ScheduledSeq& p : plan) {
+    if (!p.wants_logits) continue;
+    temps[n] = p.seq->sampling.temperature;
+    pos[n] = p.start + p.num_tokens;
+    seeds[n] = p.seq->sampling.seed;
+    ids[n] = p.seq->id;
+    ++n;
+  }
+  for (; n < rows; ++n) { temps[n] = 0.f; pos[n] = 0; seeds[n] = 0; ids[n] = 0; }
+  check(dev_.copy_to_device(d_sampling_, h_sampling_, sampling_bytes_, stream_), "copying the sampling parameters");
+}
+
+int NativeEngine::run_device(const KvcmForwardArgs& a, int logit_rows, bool tempered) {
+  int launches = 0;
+  check(dev_.forward(&a, &launches, stream_), "the forward pass");
+  if (logit_rows > 0) {
+    const size_t R = size_t(max_logits_);
+    if (tempered)
+      check(dev_.sample(static_cast<const float*>(logits_), reinterpret_cast<const float*>(d_sampling_),
+                        reinterpret_cast<const unsigned long long*>(d_sampling_ + 8 * R),
+                        reinterpret_cast<const long long*>(d_sampling_ + 16 * R),
+                        reinterpret_cast<const int*>(d_sampling_ + 4 * R), d_packed_ + 2, logit_rows, model_.V, d_packed_,
+                        stream_),
+            "the sampling kernel");
+    else
+      check(dev_.argmax(static_cast<const float*>(logits_), d_packed_ + 2, logit_rows, model_.V, d_packed_, stream_),
+            "the argmax kernel");
+    ++launches;
+  }
+  return launches;
+}
+
+void NativeEngine::raise_status(int first, int word) {
+  dev_.clear_errors();
+  const int n = int(sizeof(kFamilies) / sizeof(kFamilies[0]));
+  const std::string name = (first >= 1 && first <= n) ? kFamilies[first - 1] : "family " + std::to_string(first);
+  throw std::runtime_error(name + ": a bounded wait ran out on the device (code " + std::to_string((word >> 16) & 0xffff) +
+                           ", block " + std::to_string(word & 0xffff) + "); the outputs of this step are not valid");
+}
+
+NativeStepInfo NativeEngine::step() {
+  NativeStepInfo info;
+  const double t_start = now();
+  const std::vector<ScheduledSeq>& plan = sched_.schedule(t_start);
+  if (plan.empty()) return info;
+  int rows = 0, wants = 0, prefill = 0, singles = 0, tempered = 0;
+  entries_.clear();
+  for (const ScheduledSeq& p : plan) {
+    rows += p.num_tokens;
+    wants += p.wants_logits;
+    if (p.is_prefill) prefill += p.num_tokens;
+    singles += p.num_tokens == 1;
+    tempered += p.wants_logits && p.seq->sampling.temperature > 0.f;
+    BatchEntry e;
+    e.seq = p.seq.get();
+    e.start = p.start;
+    e.num_tokens = p.num_tokens;
+    if (p.wants_logits) e.want.push_back(p.num_tokens - 1);
+    entries_.push_back(std::move(e));
+  }
+  const int n = static_cast<int>(plan.size());
+  if (rows > cfg_.max_rows || n > cfg_.max_seqs)
+    throw std::runtime_error("engine: a step of " + std::to_string(rows) + " rows / " + std::to_string(n) +
+                             " requests exceeds the limits " + std::to_string(cfg_.max_rows) + " / " +
+                             std::to_string(cfg_.max_seqs));
+  const bool decode_only = cfg_.graphs && singles == n && wants == n;
+  KvcmForwardArgs args;
+  if (decode_only) {
+    const int b = std::min(batch_bucket(n), std::max(max_logits_, n));
+    const BatchLayout L = builder_.build(entries_, h_ints_, capacity_, b, b, b);
+    const auto key = std::make_tuple(b, ctx_bucket(L.max_decode_ctx), tempered > 0 ? 1 : 0);
+    if (tempered > 0) stage_sampling(plan, b);
+    auto it = graphs_.find(key);
+    if (it == graphs_.end()) {
+      // Record this shape.  The step at hand runs eagerly first (lazy set-up of kernels and of the
+      // library must not fall into a recording, and a recording runs nothing): it is the real run.
+      Captured c;
+      void* ints = nullptr;
+      check(dev_.device_alloc(&ints, size_t(L.total_ints) * 4), "device allocation for a graph");
+      c.ints = static_cast<int32_t*>(ints);
+      c.total_ints = L.total_ints;
+      check(dev_.copy_to_device(c.ints, h_ints_, size_t(L.total_ints) * 4, stream_), "copying the batch");
+      fill_args(args, L, c.ints, std::get<1>(key));
+      if (timing_) check(dev_.event_record(ev0_, stream_), "recording an event");
+      c.launches = run_device(args, b, tempered > 0);
+      if (timing_) check(dev_.event_record(ev1_, stream_), "recording an event");
+      check(dev_.copy_to_host(h_packed_, d_packed_, size_t(2 + n) * 4, stream_), "reading the tokens back");
+      check(dev_.stream_sync(stream_), "waiting for the step");
+      int rc = dev_.graph_begin(stream_);
+      if (rc == 0) {
+        try {
+          run_device(args, b, tempered > 0);
+        } catch (...) {
+          void* dead = nullptr;
+          dev_.graph_end(stream_, &dead);
+          if (dead) dev_.graph_destroy(dead);
+          dev_.device_free(c.ints);
+          throw;
+        }
+        rc = dev_.graph_end(stream_, &c.exec);
+      }
+      if (rc != 0) {
+        dev_.device_free(c.ints);
+        check(rc, "recording a CUDA graph");
+      }
+      graphs_[key] = c;
+      info.launches = c.launches;
+    } else {
+      Captured& c = it->second;
+      if (c.total_ints != L.total_ints) throw std::runtime_error("engine: batch layout changed for a recorded shape");
+      check(dev_.copy_to_device(c.ints, h_ints_, size_t(L.total_ints) * 4, stream_), "copying the batch");
+      if (timing_) check(dev_.event_record(ev0_, stream_), "recording an event");
+      check(dev_.graph_launch(c.exec, stream_), "launching a CUDA graph");
+      if (timing_) check(dev_.event_record(ev1_, stream_), "recording an event");
+      check(dev_.copy_to_host(h_packed_, d_packed_, size_t(2 + n) * 4, stream_), "reading the tokens back");
+      check(dev_.stream_sync(stream_), "waiting for the step");
+      ++replays_;
+      info.launches = c.launches;
+      info.graph = true;
+    }
+    info.h2d_bytes = L.total_ints * 4 + (tempered > 0 ? static_cast<long long>(sampling_bytes_) : 0);
+  } else {
+    const BatchLayout L = builder_.build(entries_, h_ints_, capacity_);
+    check(dev_.copy_to_device(d_ints_, h_ints_, size_t(L.total_ints) * 4, stream_), "copying the batch");
+    if (wants > 0 && tempered > 0) stage_sampling(plan, wants);
+    fill_args(args, L, d_ints_, L.max_decode_ctx);
+    if (timing_) check(dev_.event_record(ev0_, stream_), "recording an event");
+    info.launches = run_device(args, wants, tempered > 0);
+    if (timing_) check(dev_.event_record(ev1_, stream_), "recording an event");
+    if (wants > 0) check(dev_.copy_to_host(h_packed_, d_packed_, size_t(2 + wants) * 4, stream_), "reading the tokens back");
+    check(dev_.stream_sync(stream_), "waiting for the step");
+    info.h2d_bytes = L.total_ints * 4 + (wants > 0 && tempered > 0 ? static_cast<long long>(sampling_bytes_) : 0);
+  }
+  if (timing_) {
+    float ms = 0.f;
+    check(dev_.event_elapsed_ms(ev0_, ev1_, &ms), "reading the events");
+    info.device_ms = ms;
+    device_ms_total_ += ms;
+  }
+  sampled_.clear();
+  if (wants > 0) {
+    if (h_packed_[0] != 0) raise_status(h_packed_[0], h_packed_[1]);
+    sampled_.assign(h_packed_ + 2, h_packed_ + 2 + wants);
+    info.d2h_bytes = 4ll * (2 + wants);
+  }
+  const double t_end = now();
+  sched_.update(sampled_, t_end);
+  info.rows = rows;
+  info.seqs = n;
+  info.prefill_tokens = prefill;
+  info.decode_seqs = singles;
+  info.sampled = wants;
+  info.ms = (t_end - t_start) * 1e3;
+  return info;
+}
+
+// ------------------------------------------------------------------------ the stand-in device
+namespace {
+
+struct FakeGraph {
+  std::vector<std::function<void()>> calls;
+};
+struct FakeState {
+  bool recording = false;
+  FakeGraph* open = nullptr;
+  long long forward_calls = 0;
+};
+FakeState g_fake;
+
+void fake_forward_now(KvcmForwardArgs a) {
+  ++g_fake.forward_calls;
+  // logits[r][v] = 1 at v = next_token(token, position) of the wanted row, 0 elsewhere
+  for (int r = 0; r < a.num_logits; ++r) {
+    const int row = a.logit_rows[r];
+    float* out = a.logits + size_t(r) * a.V;
+    std::fill(out, out + a.V, 0.f);
+    const int pos = a.positions[row];
+    if (pos >= 0) out[fake_next_token(a.tokens[row], pos, a.V)] = 1.f;
+  }
+}
+int fake_forward(const KvcmForwardArgs* a, int* launches, void*) {
+  if (launches) *launches = 1;
+  if (g_fake.recording) g_fake.open->calls.push_back([args = *a] { fake_forward_now(args); });
+  else fake_forward_now(*a);
+  return 0;
+}
+void fake_argmax_now(const float* logits, int* out, int rows, int vocab, int* status) {
+  for (int r = 0; r < rows; ++r) {
+    const float* l = logits + size_t(r) * vocab;
+    out[r] = static_cast<int>(std::max_element(l, l + vocab) - l);
+  }
+  if (status) status[0] = status[1] = 0;
+}
+int fake_argmax(const float* logits, int* out, int rows, int vocab, int* status, void*) {
+  if (g_fake.recording) g_fake.open->calls.push_back([=] { fake_argmax_now(logits, out, rows, vocab, status); });
+  else fake_argmax_now(logits, out, rows, vocab, status);
+  return 0;
+}
+int fake_sample(const float* logits, const float*, const unsigned long long*, const long long*, const int*, int* out,
+                int rows, int vocab, int* status, void* s) {
+  return fake_argmax(logits, out, rows, vocab, status, s);
+}
+int fake_copy(void* dst, const void* src, size_t bytes, void*) { std::memcpy(dst, src, bytes); return 0; }
+int fake_stream_create(void** s) { *s = reinterpret_cast<void*>(0x1); return 0; }
+int fake_ok_ptr(void*) { return 0; }
+int fake_alloc(void** p, size_t bytes) { *p = std::calloc(bytes ? bytes : 1, 1); return *p ? 0 : 2; }
+int fake_free(void* p) { std::free(p); return 0; }
+int fake_event_create(void** e) { *e = reinterpret_cast<void*>(0x2); return 0; }
+int fake_event_record(void*, void*) { return 0; }
+int fake_event_elapsed(void*, void*, float* ms) { *ms = 0.f; return 0; }
+int fake_graph_begin(void*) {
+  g_fake.recording = true;
+  g_fake.open = new FakeGraph();
+  return 0;
+}
+int fake_graph_end(void*, void** exec) {
+  g_fake.recording = false;
+  *exec = g_fake.open;
+  g_fake.open = nullptr;
+  return 0;
+}
+int fake_graph_launch(void* exec, void*) {
+  for (auto& f : static_cast<FakeGraph*>(exec)->calls) f();
+  return 0;
+}
+int fake_graph_destroy(void* exec) { delete static_cast<FakeGraph*>(exec); return 0; }
+int fake_clear() { return 0; }
+
+}  // namespace
+
+int32_t fake_next_token(int32_t token, int32_t position, int vocab) {
+  return static_cast<int32_t>((int64_t(token) * 31 + int64_t(position) * 7 + 1) % vocab);
+}
+long long fake_backend_forward_calls() { return g_fake.forward_calls; }
+
+KvcmDeviceBackend make_fake_backend() {
+  KvcmDeviceBackend b{};
+  b.forward = fake_forward;
+  b.argmax = fake_argmax;
+  b.sample = fake_sample;
+  b.copy_to_device = fake_copy;
+  b.copy_to_host = fake_copy;
+  b.stream_create = fake_stream_create;
+  b.stream_destroy = fake_ok_ptr;
+  b.stream_sync = fake_ok_ptr;
+  b.device_alloc = fake_alloc;
+  b.device_free = fake_free;
+  b.host_alloc = fake_alloc;
+  b.host_free = fake_free;
+  b.event_create = fake_event_create;
+  b.event_destroy = fake_ok_ptr;
+  b.event_record = fake_event_record;
+  b.event_elapsed_ms = fake_event_elapsed;
+  b.graph_begin = fake_graph_begin;
+  b.graph_end = fake_graph_end;
+  b.graph_launch = fake_graph_launch;
+  b.graph_destroy = fake_graph_destroy;
+  b.clear_errors = fake_clear;
+  return b;
+}
+
+}  // namespace kvcm

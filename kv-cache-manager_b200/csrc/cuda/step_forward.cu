@@ -21,6 +21,7 @@
 #include <algorithm>
 #include <mutex>
 
+#include "../include/forward_args.h"
 #include "common.cuh"
 
 extern "C" {
@@ -61,41 +62,13 @@ int kvcm_gate_up_silu_tcgen05_bf16(const void*, const void*, void*, int, int, in
 
 namespace {
 
-constexpr int kMaxGroups = 4;
+constexpr int kMaxGroups = KVCM_FORWARD_MAX_GROUPS;
 constexpr long long kStreamMaxBytes = 32ll << 20;       // parts/linear.py: STREAM_MAX_BYTES
 constexpr int kTcgen05MinRows = 256;                    // TCGEN05_MIN_ROWS
 constexpr int kTcgen05GatedMaxHidden = 3072;            // TCGEN05_GATED_MAX_HIDDEN
 constexpr int kKeyTile = 64;
 
 }  // namespace
-
-// One call site of the run order (host array).
-struct KvcmForwardLayer {
-  const void* w_qkv; const void* w_o; const void* w_gate_up; const void* w_down;
-  const void* norm1; const void* norm2;
-  void* k_cache; void* v_cache;
-  float eps1, eps2;
-  int group, window, writes, num_pages;
-};
-
-struct KvcmForwardArgs {
-  // the model (fixed for an engine)
-  const KvcmForwardLayer* layers;                       // host memory
-  const void* embed; const void* final_norm; const void* lm_head;
-  const float* inv_freq;
-  // the step: the batch's integer arrays on the device
-  const int* tokens; const int* positions; const int* row_seq; const int* seq_q_start; const int* seq_q_len;
-  const int* seq_ctx_len; const int* tile_seq; const int* tile_q0; const int* logit_rows;
-  const int* group_tables[kMaxGroups]; const int* group_slots[kMaxGroups];
-  // buffers of the caller, sized for the step: x [T,H] float; h, proj [T,H]; qkv [T,QKV]; attn [T,nh*hd];
-  // gate_up [T,2I]; act [T,I]; h_last [L,H]; logits [L,V] float; attn_scratch floats; a library workspace
-  float* x; void* h; void* qkv; void* attn; void* proj; void* gate_up; void* act; void* h_last; float* logits;
-  float* attn_scratch; void* lib_workspace;
-  long long attn_scratch_floats, lib_workspace_bytes;
-  int num_layers, f32, H, I, nh, nkv, hd, V, block_size, max_blocks, sm_count;
-  int rows, seqs, decode_seqs, prefill_tiles, tile_rows, max_decode_ctx, num_logits, reserved;
-  float final_eps, scale;
-};
 
 namespace {
 

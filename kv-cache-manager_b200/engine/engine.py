@@ -57,10 +57,27 @@ class DeviceTimer:
 
     def total_ms(self) -> float:
         torch.cuda.synchronize()
-        return sum(a.elapsed_time(b) for a, b in self.pairs)
+        own = sum(a.elapsed_time(b) for a, b in self.pairs)
+        return own + (self.native.device_ms_total() if getattr(self, "native", None) is not None else 0.0)
 
     def reset(self) -> None:
         self.pairs = []
+
+
+class _NativeGraphs:
+    """What callers read of the decode graphs when the C++ loop owns them."""
+
+    def __init__(self, native) -> None:
+        self._native = native
+        self.kernels_last = 0
+
+    @property
+    def replays(self) -> int:
+        return int(self._native.graph_replays())
+
+    @property
+    def captured(self) -> dict:
+        return {(b, c, bool(t)): None for b, c, t in self._native.graph_shapes()}
 
 
 class Engine:
@@ -101,7 +118,21 @@ class Engine:
         self._next_id = 0
         self._t0 = time.perf_counter()
         self._has_state = plan.has_state
-        self.device_timer = None          # a DeviceTimer brackets the device work of every step
+        self._device_timer = None         # a DeviceTimer brackets the device work of every step
+        # The standard arrangement of parts with default options: the whole request loop runs in C++
+        # (csrc/core/native_engine.cpp) over the same scheduler, cache manager and pools.
+        self.native = None
+        nf = self.runner.native
+        if cfg.native_loop and nf is not None and cfg.gemm == "auto" and cfg.attn == "auto" and not plan.has_state:
+            torch.cuda.synchronize(self.runner.device)         # weights and pools are in place
+            scratch = 0 if nf.f32 else min(sc.max_num_seqs, 1024) * nf.nh * 64 * (nf.hd + 2)
+            self.native = core.NativeEngine(
+                self.kv, self.sched, nf.model_for_core(),
+                dict(block_size=kv.block_size, max_seq_len=kv.max_seq_len, num_groups=self.runner.num_groups,
+                     max_rows=max(max_rows, kv.max_seq_len), max_seqs=sc.max_num_seqs, graphs=bool(cfg.cuda_graphs),
+                     attn_scratch_floats=scratch),
+                K.device_backend_address())
+            self.graphs = _NativeGraphs(self.native) if cfg.cuda_graphs else None
 
     @classmethod
     def from_folder(cls, folder: str, cfg: Optional[EngineConfig] = None) -> "Engine":
@@ -110,10 +141,27 @@ class Engine:
 
     # -------------------------------------------------------------------------- clock
     def now(self) -> float:
-        return time.perf_counter() - self._t0
+        return self.native.now() if self.native is not None else time.perf_counter() - self._t0
 
     def reset_clock(self) -> None:
         self._t0 = time.perf_counter()
+        if self.native is not None:
+            self.native.reset_clock()
+
+    @property
+    def device_timer(self):
+        return self._device_timer
+
+    @device_timer.setter
+    def device_timer(self, timer) -> None:
+        """A ``DeviceTimer`` (or None): device time of every step from now on.  With the C++ loop the
+        events are its own and the timer is handed their sum."""
+        self._device_timer = timer
+        if self.native is not None:
+            self.native.set_timing(timer is not None)
+            self.native.reset_device_ms()
+            if timer is not None:
+                timer.native = self.native
 
     # ----------------------------------------------------------------------- requests
     def add_request(self, tokens: Sequence[int], max_new_tokens: int, temperature: float = 0.0,
@@ -140,6 +188,8 @@ class Engine:
 
     # --------------------------------------------------------------------------- step
     def step(self) -> StepInfo:
+        if self.native is not None and not K.profiling():
+            return self._native_step()
         info = StepInfo()
         t_start = self.now()
         self.sched.schedule(t_start)
@@ -188,6 +238,19 @@ class Engine:
         info.ms = (t_end - t_start) * 1e3
         return info
 
+    def _native_step(self) -> StepInfo:
+        try:
+            n = self.native.step()
+        except RuntimeError as e:
+            if "a bounded wait ran out" in str(e):
+                raise K.KernelError(str(e)) from None
+            raise
+        K.add_launches(n.launches)
+        if self.graphs is not None:
+            self.graphs.kernels_last = n.launches
+        return StepInfo(rows=n.rows, seqs=n.seqs, prefill_tokens=n.prefill_tokens, decode_seqs=n.decode_seqs,
+                        sampled=n.sampled, ms=n.ms, h2d_bytes=n.h2d_bytes, d2h_bytes=n.d2h_bytes, graph=n.graph)
+
     def run_until_idle(self, max_steps: int = 1 << 30) -> int:
         n = 0
         while not self.idle() and n < max_steps:
@@ -202,6 +265,7 @@ class Engine:
         every position again would write pages that other requests share."""
         if self.cfg.kv.prefix_caching:
             raise RuntimeError("score: disable prefix caching")
+        torch.cuda.synchronize()              # the C++ loop runs on a stream of its own
         s = core.Sequence()
         s.id = -1
         s.tokens = [int(t) for t in tokens]

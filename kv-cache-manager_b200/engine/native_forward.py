@@ -101,6 +101,21 @@ class NativeForward:
             return None                             # rows of the buffers must stay 16-byte aligned
         return cls(spec, runner, sizes, layers, inv_freq, scale)
 
+    def model_for_core(self) -> dict:
+        """The model as the C++ request loop wants it (csrc/core/native_engine.h: NativeModel)."""
+        names = ("w_qkv", "w_o", "w_gate_up", "w_down", "norm1", "norm2", "k_cache", "v_cache")
+        layers = []
+        for L in self.layers:
+            d = {k: int(getattr(L, k) or 0) for k in names}
+            d.update(eps1=float(L.eps1), eps2=float(L.eps2), group=int(L.group), window=int(L.window),
+                     writes=int(L.writes), num_pages=int(L.num_pages))
+            layers.append(d)
+        return dict(embed=self.spec.embedding.param("weight").data_ptr(),
+                    final_norm=self.spec.final_norm.param("weight").data_ptr(),
+                    lm_head=self.spec.lm_head.param("weight").data_ptr(), inv_freq=self.inv_freq.data_ptr(),
+                    f32=int(self.f32), H=self.H, I=self.I, nh=self.nh, nkv=self.nkv, hd=self.hd, V=self.vocab,
+                    sm_count=self.sms, final_eps=float(self.spec.final_norm.eps), scale=float(self.scale), layers=layers)
+
     # ------------------------------------------------------------------------- one step
     def takes(self, ctx: StepContext) -> bool:
         o = ctx.options

@@ -33,6 +33,37 @@ def reset_launch_count() -> None:
     _launches = 0
 
 
+def add_launches(n: int) -> None:
+    """Launches made by the C++ request loop, which calls the launchers without passing here."""
+    global _launches
+    _launches += int(n)
+
+
+def profiling() -> bool:
+    return _profile is not None
+
+
+class DeviceBackend(ctypes.Structure):
+    """Opaque room for the table of device functions that the kernel library fills for the C++
+    request loop (csrc/include/device_backend.h): 21 function pointers."""
+    _fields_ = [("slots", ctypes.c_void_p * 21)]
+
+
+_backend = None
+
+
+def device_backend_address() -> int:
+    """Address of the filled table (kept alive for the life of the process)."""
+    global _backend
+    if _backend is None:
+        b = DeviceBackend()
+        size = int(_lib().kvcm_device_backend(ctypes.byref(b)))
+        if size != ctypes.sizeof(DeviceBackend):
+            raise KernelError("device backend: the table of the library has another layout")
+        _backend = b
+    return ctypes.addressof(_backend)
+
+
 def _lib():
     return load_cuda()
 
