@@ -65,8 +65,10 @@ def ensure_built() -> str:
     return KVBENCH
 
 
-def write_weight_file(path: str, m: dict, seed: int = 0) -> int:
-    """Random weights in the reference's file format; returns the bytes written."""
+def write_weight_file(path: str, m: dict, seed: int = 0, repeat_block: bool = False) -> int:
+    """Random weights in the reference's file format; returns the bytes written.  ``repeat_block``:
+    draw 16 Mi values once and write them over and over (for the 7B and 8B shapes, whose 13-16 GB of
+    distinct normals would take minutes to draw; speed does not depend on the values)."""
     import numpy as np
     V, H, I, L = m["vocab_size"], m["hidden_size"], m["intermediate_size"], m["num_hidden_layers"]
     nh, nkv, hd = m["num_attention_heads"], m["num_key_value_heads"], m["head_dim"]
@@ -76,12 +78,16 @@ def write_weight_file(path: str, m: dict, seed: int = 0) -> int:
         + struct.pack("<2f", m["rope_theta"], m["rms_norm_eps"])
     hdr += b"\0" * (64 - len(hdr))
     rng = np.random.default_rng(seed)
+    block = (rng.standard_normal(1 << 24, dtype=np.float32) * 0.02).astype(np.float16) if repeat_block else None
 
     def matrix(f, rows, cols):
         left = rows * cols
         while left:
             n = min(left, 1 << 24)
-            f.write((rng.standard_normal(n, dtype=np.float32) * 0.02).astype(np.float16).tobytes())
+            if block is not None:
+                f.write(block[:n].tobytes())
+            else:
+                f.write((rng.standard_normal(n, dtype=np.float32) * 0.02).astype(np.float16).tobytes())
             left -= n
 
     ones = np.ones(H, dtype=np.float16).tobytes()
