@@ -105,8 +105,6 @@ def bench_gemm(a, out) -> None:
             res = {"library": graph_time_us([(lambda w=w: torch.mm(x, w.t(), out=y)) for w in ws])}
             if K.stream_gemm_supported(M, N, Kd):
                 res["stream"] = graph_time_us([(lambda w=w: K.gemm_stream(x, w, y)) for w in ws])
-            if K.skinny_gemm_supported(M, N, Kd):
-                res["skinny"] = graph_time_us([(lambda w=w: K.gemm_skinny(x, w, y)) for w in ws])
             if K.splitk_gemm_supported(x, ws[0]):
                 res["splitk"] = graph_time_us([(lambda w=w: K.gemm_tcgen05_splitk(x, w, y)) for w in ws])
             gb = N * Kd * 2 / 1e9

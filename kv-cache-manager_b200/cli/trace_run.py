@@ -41,7 +41,7 @@ def main(argv=None) -> int:
                     help="longest request (0: the whole pool when paged, a quarter of it when contiguous, "
                          "where every request reserves this many tokens)")
     ap.add_argument("--attention", default="auto", choices=["auto", "plain"])
-    ap.add_argument("--gemm", default="auto", choices=["auto", "plain", "library", "skinny", "tcgen05", "native"])
+    ap.add_argument("--gemm", default="auto", choices=["auto", "plain", "library", "tcgen05", "native"])
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 

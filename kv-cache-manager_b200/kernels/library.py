@@ -493,27 +493,6 @@ def attention_tcgen05_error() -> int:
     ran out.  Reading clears it.  Synchronises the device."""
     return int(_lib().kvcm_attention_tcgen05_error())
 
-def skinny_gemm_supported(M: int, N: int, K: int) -> bool:
-    """True when the weight-streaming kernel takes this product (M <= 16, K a multiple of 8, X
-    fits shared memory)."""
-    return bool(_lib().kvcm_gemm_skinny_supports(int(M), int(N), int(K)))
-
-
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, kw: int = 0) -> None:
-    """y[M,N] = x[M,K] @ w[N,K]^T for M <= 16 (bfloat16 operands, float accumulation, bfloat16 or
-    float result).  ``kw``: warps that share a 16-row tile of w along K (0: chosen from the sizes)."""
-    _cuda(x, w, y)
-    M, K = x.shape
-    N = w.shape[0]
-    _need(w.shape[1] == K and y.shape == (M, N), "gemm_skinny: shapes")
-    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and y.dtype in (torch.bfloat16, torch.float32),
-          "gemm_skinny: bfloat16 operands, bfloat16 or float32 result")
-    _need(x.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1, "gemm_skinny: rows must be dense")
-    rc = _lib().kvcm_gemm_skinny_bf16(_p(x), _p(w), _p(y), M, N, K, x.stride(0), w.stride(0), y.stride(0),
-                                      int(y.dtype == torch.float32), int(kw), sm_count(x.device), _stream())
-    _check(rc, "gemm_skinny", f"(M={M}, N={N}, K={K})")
-
-
 def stream_gemm_supported(M: int, N: int, K: int) -> bool:
     """True when the TMA-pipelined weight-streaming kernel takes this product."""
     return bool(_lib().kvcm_gemm_stream_supports(int(M), int(N), int(K)))

@@ -6,7 +6,7 @@ Which kernel runs is decided by the weight's dtype, never by the model:
 * bfloat16 weight -> this engine's weight-streaming kernel for a handful of rows (decode), else
   the library GEMM (cuBLAS through ``torch.mm``, the same place where the reference calls cuBLAS);
   this engine's tcgen05 kernels for many rows on request, and for the fused gate/up product;
-  ``options['gemm']``: 'plain' forces the plain twin, 'library' cuBLAS, 'tcgen05', 'pair' and 'skinny'
+  ``options['gemm']``: 'plain' forces the plain twin, 'library' cuBLAS, 'tcgen05' and 'pair'
   the respective kernels; 'native' never calls the library: the streaming kernel up to 16 rows, the
   split-K tcgen05 kernel up to 255, from 256 the tiled tcgen05 kernel (one SM per tile) or, for wide
   outputs, its two-SM form (slower than 'auto' where 'auto' takes the library: 17 to 255 rows, and
@@ -55,10 +55,6 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, options:
     if mode == "plain":
         y = torch.empty((M, N), dtype=out_dtype, device=x.device)
         K.gemm_plain(x, w, y)
-        return y
-    if mode == "skinny" and K.skinny_gemm_supported(M, N, w.shape[1]):
-        y = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        K.gemm_skinny(x, w, y)
         return y
     # A handful of rows (decode): this engine's weight-streaming kernel.  Measured on B200 at 8 rows
     # it beats the library (4-7 us against 7-16 us at 8-23 MB) or ties it (46 and 131 MB); from 9

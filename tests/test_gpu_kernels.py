@@ -154,26 +154,6 @@ def test_plain_gemm_rows_do_not_depend_on_the_batch():
     assert torch.equal(full[20:21], one)
 
 
-@pytest.mark.parametrize("M,N,Kd", [(1, 2048, 2048), (8, 2560, 2048), (3, 100, 176), (16, 37, 5632),
-                                    (9, 515, 96), (8, 32003, 256), (5, 16, 8)])
-@pytest.mark.parametrize("kw", [0, 1, 2, 4, 8])
-def test_skinny_gemm(M, N, Kd, kw):
-    lib = K()
-    assert lib.skinny_gemm_supported(M, N, Kd)
-    x = torch.randn(M, Kd + 8).to(torch.bfloat16)[:, :Kd]           # strided rows
-    w = torch.randn(N, Kd).to(torch.bfloat16)
-    ref = x.double() @ w.double().T
-    for out_dt in (torch.bfloat16, torch.float32):
-        y = torch.full((M, N), float("nan"), dtype=out_dt, device=DEV)
-        lib.gemm_skinny(x.to(DEV), w.to(DEV), y, kw)
-        d = (y.double().cpu() - ref).abs().max().item()
-        bound = (0.02 if out_dt == torch.bfloat16 else 2e-3) * ref.abs().max().item()
-        assert d <= bound, f"{out_dt}: {d} > {bound}"
-    y2 = torch.empty_like(y)
-    lib.gemm_skinny(x.to(DEV), w.to(DEV), y2, kw)
-    assert torch.equal(y, y2)                                       # fixed summation order
-
-
 @pytest.mark.parametrize("M,N,Kd", [(1, 2048, 2048), (8, 2560, 2048), (3, 100, 176), (16, 37, 2048), (8, 37, 5632),
                                     (9, 515, 96), (8, 32003, 256), (5, 16, 8), (8, 11264, 2048),
                                     (7, 4096, 1032), (2, 33, 520),
@@ -402,15 +382,14 @@ def test_tcgen05_pair_gate_up_with_split_k_ranges(M, H, I):
     close(a1, gg[:, :I] * torch.sigmoid(gg[:, :I]) * gg[:, I:], "bfloat16", "against float64")
 
 
-def test_skinny_gemm_refuses_what_it_cannot_run():
+def test_streaming_gemm_refuses_what_it_cannot_run():
     lib = K()
-    assert not lib.skinny_gemm_supported(17, 64, 64)                # too many rows
-    assert not lib.skinny_gemm_supported(4, 64, 60)                 # K not a multiple of 8
-    assert not lib.skinny_gemm_supported(16, 64, 16384)             # X does not fit shared memory
+    assert not lib.stream_gemm_supported(17, 64, 64)                # too many rows
+    assert not lib.stream_gemm_supported(4, 64, 60)                 # K not a multiple of 8
     x = torch.zeros(4, 60, dtype=torch.bfloat16, device=DEV)
     w = torch.zeros(64, 60, dtype=torch.bfloat16, device=DEV)
-    with pytest.raises(lib.KernelError):
-        lib.gemm_skinny(x, w, torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(lib.KernelError, match="not supported"):
+        lib.gemm_stream(x, w, torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV))
 
 
 def test_argmax_ties_and_edges():
