@@ -177,9 +177,11 @@ def decode_run(spec, ec, vocab, batch, steps, warmup, prompt_len, sample_clocks=
         if info.graph and eng.native is None:
             graph_kernels += eng.graphs.kernels_last       # (the C++ loop reports its launches itself)
         ctx_sum += eng.sched.cached_tokens_total()
+    wall_ms = (time.perf_counter() - t0) * 1e3     # the host holds the tokens of `steps` steps
+    dev_ms = timer.total_ms()                      # device time of exactly these steps
+    if eng.native is not None:
+        eng.native.drain()                         # (a step enqueued ahead ends outside the timed region)
     torch.cuda.synchronize()
-    wall_ms = (time.perf_counter() - t0) * 1e3
-    dev_ms = timer.total_ms()
     eager_kernels = launch_count() - launches0
     eng.device_timer = None
     clk = clocks.stop() if sample_clocks else None

@@ -437,6 +437,7 @@ PYBIND11_MODULE(kvcm_core, m) {
              c.num_groups = int(geti(config, "num_groups")); c.max_rows = int(geti(config, "max_rows"));
              c.max_seqs = int(geti(config, "max_seqs")); c.graphs = config["graphs"].cast<bool>();
              if (config.contains("tile_rows")) c.tile_rows = int(geti(config, "tile_rows"));
+             if (config.contains("lookahead")) c.lookahead = config["lookahead"].cast<bool>();
              if (config.contains("attn_scratch_floats")) c.attn_scratch_floats = geti(config, "attn_scratch_floats");
              if (config.contains("lib_workspace_bytes")) c.lib_workspace_bytes = geti(config, "lib_workspace_bytes");
              const KvcmDeviceBackend backend = backend_address
@@ -446,6 +447,9 @@ PYBIND11_MODULE(kvcm_core, m) {
            py::arg("config"), py::arg("backend_address") = 0)
       // (the step waits for the device: other Python threads may run meanwhile)
       .def("step", &NativeEngine::step, py::call_guard<py::gil_scoped_release>())
+      .def("drain", &NativeEngine::drain, py::call_guard<py::gil_scoped_release>())
+      .def("in_flight", &NativeEngine::in_flight)
+      .def("lookahead_steps", &NativeEngine::lookahead_steps)
       .def("now", &NativeEngine::now)
       .def("reset_clock", &NativeEngine::reset_clock)
       .def("set_timing", &NativeEngine::set_timing)
@@ -455,6 +459,16 @@ PYBIND11_MODULE(kvcm_core, m) {
       .def("graph_replays", &NativeEngine::graph_replays)
       .def("graph_shapes", &NativeEngine::graph_shapes)
       .def("stream", [](const NativeEngine& e) { return reinterpret_cast<uintptr_t>(e.stream()); })
+      // host microseconds per step, by phase, averaged over the steps since the last reset
+      .def("host_times_us", [](const NativeEngine& e) {
+        const auto& t = e.host_times();
+        const double n = t.steps ? double(t.steps) : 1.0;
+        py::dict d;
+        d["schedule"] = 1e6 * t.schedule / n; d["build"] = 1e6 * t.build / n; d["enqueue"] = 1e6 * t.enqueue / n;
+        d["wait"] = 1e6 * t.wait / n; d["update"] = 1e6 * t.update / n; d["steps"] = t.steps;
+        return d;
+      })
+      .def("reset_host_times", &NativeEngine::reset_host_times)
       .def_static("batch_bucket", &NativeEngine::batch_bucket)
       .def_static("ctx_bucket", &NativeEngine::ctx_bucket);
 }

@@ -44,8 +44,11 @@ NativeEngine::NativeEngine(KVManager& kv, Scheduler& sched, NativeModel model, N
   const int pad_rows = std::max(cfg_.max_rows, max_logits_);
   capacity_ = builder_.capacity_for(pad_rows, max_logits_, max_logits_);
   check(dev_.stream_create(&stream_), "creating the stream");
-  check(dev_.event_create(&ev0_), "creating an event");
-  check(dev_.event_create(&ev1_), "creating an event");
+  for (int i = 0; i < 2; ++i) {
+    check(dev_.event_create(&ev0_[i]), "creating an event");
+    check(dev_.event_create(&ev1_[i]), "creating an event");
+    check(dev_.event_create(&done_[i]), "creating an event");
+  }
 
   auto device = [&](size_t bytes) {
     void* p = nullptr;
@@ -61,9 +64,11 @@ NativeEngine::NativeEngine(KVManager& kv, Scheduler& sched, NativeModel model, N
   const size_t esz = model_.f32 ? 4 : 2;
   const size_t T = size_t(pad_rows), H = size_t(model_.H), I = size_t(model_.I);
   const size_t QK = size_t(model_.nh) * model_.hd, QKV = size_t(model_.nh + 2 * model_.nkv) * model_.hd;
-  h_ints_ = static_cast<int32_t*>(host(size_t(capacity_) * 4));
+  for (int i = 0; i < 2; ++i) {
+    h_ints_[i] = static_cast<int32_t*>(host(size_t(capacity_) * 4));
+    h_packed_[i] = static_cast<int32_t*>(host(size_t(2 + max_logits_) * 4));
+  }
   d_ints_ = static_cast<int32_t*>(device(size_t(capacity_) * 4));
-  h_packed_ = static_cast<int32_t*>(host(size_t(2 + max_logits_) * 4));
   d_packed_ = static_cast<int32_t*>(device(size_t(2 + max_logits_) * 4));
   sampling_bytes_ = size_t(max_logits_) * (4 + 4 + 8 + 8);
   h_sampling_ = static_cast<unsigned char*>(host(sampling_bytes_));
@@ -85,14 +90,18 @@ NativeEngine::~NativeEngine() {
   if (stream_) dev_.stream_sync(stream_);
   for (auto& g : graphs_) {
     if (g.second.exec) dev_.graph_destroy(g.second.exec);
+    if (g.second.exec_chained) dev_.graph_destroy(g.second.exec_chained);
     if (g.second.ints) dev_.device_free(g.second.ints);
   }
   for (void* p : device_allocs_) dev_.device_free(p);
-  if (h_ints_) dev_.host_free(h_ints_);
-  if (h_packed_) dev_.host_free(h_packed_);
+  for (int i = 0; i < 2; ++i) {
+    if (h_ints_[i]) dev_.host_free(h_ints_[i]);
+    if (h_packed_[i]) dev_.host_free(h_packed_[i]);
+    if (ev0_[i]) dev_.event_destroy(ev0_[i]);
+    if (ev1_[i]) dev_.event_destroy(ev1_[i]);
+    if (done_[i]) dev_.event_destroy(done_[i]);
+  }
   if (h_sampling_) dev_.host_free(h_sampling_);
-  if (ev0_) dev_.event_destroy(ev0_);
-  if (ev1_) dev_.event_destroy(ev1_);
   if (stream_) dev_.stream_destroy(stream_);
 }
 
@@ -194,38 +203,70 @@ void NativeEngine::raise_status(int first, int word) {
                            ", block " + std::to_string(word & 0xffff) + "); the outputs of this step are not valid");
 }
 
-NativeStepInfo NativeEngine::step() {
-  NativeStepInfo info;
-  const double t_start = now();
-  const std::vector<ScheduledSeq>& plan = sched_.schedule(t_start);
-  if (plan.empty()) return info;
-  int rows = 0, wants = 0, prefill = 0, singles = 0, tempered = 0;
+NativeEngine::Planned NativeEngine::summarise() {
+  Planned p;
   entries_.clear();
-  for (const ScheduledSeq& p : plan) {
-    rows += p.num_tokens;
-    wants += p.wants_logits;
-    if (p.is_prefill) prefill += p.num_tokens;
-    singles += p.num_tokens == 1;
-    tempered += p.wants_logits && p.seq->sampling.temperature > 0.f;
+  for (const ScheduledSeq& q : sched_.plan()) {
+    p.rows += q.num_tokens;
+    p.wants += q.wants_logits;
+    if (q.is_prefill) p.prefill += q.num_tokens;
+    p.singles += q.num_tokens == 1;
+    p.tempered += q.wants_logits && q.seq->sampling.temperature > 0.f;
     BatchEntry e;
-    e.seq = p.seq.get();
-    e.start = p.start;
-    e.num_tokens = p.num_tokens;
-    if (p.wants_logits) e.want.push_back(p.num_tokens - 1);
+    e.seq = q.seq.get();
+    e.start = q.start;
+    e.num_tokens = q.num_tokens;
+    if (q.wants_logits) e.want.push_back(q.num_tokens - 1);
     entries_.push_back(std::move(e));
   }
-  const int n = static_cast<int>(plan.size());
-  if (rows > cfg_.max_rows || n > cfg_.max_seqs)
-    throw std::runtime_error("engine: a step of " + std::to_string(rows) + " rows / " + std::to_string(n) +
+  p.n = static_cast<int>(sched_.plan().size());
+  if (p.rows > cfg_.max_rows || p.n > cfg_.max_seqs)
+    throw std::runtime_error("engine: a step of " + std::to_string(p.rows) + " rows / " + std::to_string(p.n) +
                              " requests exceeds the limits " + std::to_string(cfg_.max_rows) + " / " +
                              std::to_string(cfg_.max_seqs));
-  const bool decode_only = cfg_.graphs && singles == n && wants == n;
+  return p;
+}
+
+// Records both forms of a decode shape: token ids from the batch arrays, and from the sampled
+// tokens of the step before (the chained form of the lookahead).
+void NativeEngine::record_shape(Captured& c, const KvcmForwardArgs& args, int b, bool tempered) {
+  for (int form = 0; form < 2; ++form) {
+    KvcmForwardArgs a = args;
+    if (form == 1) a.tokens = d_packed_ + 2;
+    void** exec = form == 0 ? &c.exec : &c.exec_chained;
+    int rc = dev_.graph_begin(stream_);
+    if (rc == 0) {
+      try {
+        run_device(a, b, tempered);
+      } catch (...) {
+        void* dead = nullptr;
+        dev_.graph_end(stream_, &dead);
+        if (dead) dev_.graph_destroy(dead);
+        throw;
+      }
+      rc = dev_.graph_end(stream_, exec);
+    }
+    check(rc, "recording a CUDA graph");
+    if (tempered || !cfg_.lookahead) break;               // the chained form serves greedy steps only
+  }
+}
+
+// The plan as schedule() made it, run to its end before this returns.
+NativeStepInfo NativeEngine::run_planned(const Planned& p, double t_start) {
+  NativeStepInfo info;
+  const std::vector<ScheduledSeq>& plan = sched_.plan();
+  const int par = int(step_no_++ & 1);
+  const double t_scheduled = now();
+  double t_built = t_scheduled, t_enqueued = t_scheduled;
+  const int n = p.n, wants = p.wants;
+  const bool decode_only = cfg_.graphs && p.singles == n && wants == n;
   KvcmForwardArgs args;
   if (decode_only) {
     const int b = std::min(batch_bucket(n), std::max(max_logits_, n));
-    const BatchLayout L = builder_.build(entries_, h_ints_, capacity_, b, b, b);
-    const auto key = std::make_tuple(b, ctx_bucket(L.max_decode_ctx), tempered > 0 ? 1 : 0);
-    if (tempered > 0) stage_sampling(plan, b);
+    const BatchLayout L = builder_.build(entries_, h_ints_[par], capacity_, b, b, b);
+    t_built = now();
+    const auto key = std::make_tuple(b, ctx_bucket(L.max_decode_ctx), p.tempered > 0 ? 1 : 0);
+    if (p.tempered > 0) stage_sampling(plan, b);
     auto it = graphs_.find(key);
     if (it == graphs_.end()) {
       // Record this shape.  The step at hand runs eagerly first (lazy set-up of kernels and of the
@@ -235,79 +276,205 @@ NativeStepInfo NativeEngine::step() {
       check(dev_.device_alloc(&ints, size_t(L.total_ints) * 4), "device allocation for a graph");
       c.ints = static_cast<int32_t*>(ints);
       c.total_ints = L.total_ints;
-      check(dev_.copy_to_device(c.ints, h_ints_, size_t(L.total_ints) * 4, stream_), "copying the batch");
-      fill_args(args, L, c.ints, std::get<1>(key));
-      if (timing_) check(dev_.event_record(ev0_, stream_), "recording an event");
-      c.launches = run_device(args, b, tempered > 0);
-      if (timing_) check(dev_.event_record(ev1_, stream_), "recording an event");
-      check(dev_.copy_to_host(h_packed_, d_packed_, size_t(2 + n) * 4, stream_), "reading the tokens back");
-      check(dev_.stream_sync(stream_), "waiting for the step");
-      int rc = dev_.graph_begin(stream_);
-      if (rc == 0) {
-        try {
-          run_device(args, b, tempered > 0);
-        } catch (...) {
-          void* dead = nullptr;
-          dev_.graph_end(stream_, &dead);
-          if (dead) dev_.graph_destroy(dead);
-          dev_.device_free(c.ints);
-          throw;
-        }
-        rc = dev_.graph_end(stream_, &c.exec);
-      }
-      if (rc != 0) {
+      try {
+        check(dev_.copy_to_device(c.ints, h_ints_[par], size_t(L.total_ints) * 4, stream_), "copying the batch");
+        fill_args(args, L, c.ints, std::get<1>(key));
+        if (timing_) check(dev_.event_record(ev0_[par], stream_), "recording an event");
+        c.launches = run_device(args, b, p.tempered > 0);
+        if (timing_) check(dev_.event_record(ev1_[par], stream_), "recording an event");
+        check(dev_.copy_to_host(h_packed_[par], d_packed_, size_t(2 + n) * 4, stream_), "reading the tokens back");
+        check(dev_.stream_sync(stream_), "waiting for the step");
+        record_shape(c, args, b, p.tempered > 0);
+      } catch (...) {
+        if (c.exec) dev_.graph_destroy(c.exec);
+        if (c.exec_chained) dev_.graph_destroy(c.exec_chained);
         dev_.device_free(c.ints);
-        check(rc, "recording a CUDA graph");
+        throw;
       }
       graphs_[key] = c;
       info.launches = c.launches;
     } else {
       Captured& c = it->second;
       if (c.total_ints != L.total_ints) throw std::runtime_error("engine: batch layout changed for a recorded shape");
-      check(dev_.copy_to_device(c.ints, h_ints_, size_t(L.total_ints) * 4, stream_), "copying the batch");
-      if (timing_) check(dev_.event_record(ev0_, stream_), "recording an event");
+      check(dev_.copy_to_device(c.ints, h_ints_[par], size_t(L.total_ints) * 4, stream_), "copying the batch");
+      if (timing_) check(dev_.event_record(ev0_[par], stream_), "recording an event");
       check(dev_.graph_launch(c.exec, stream_), "launching a CUDA graph");
-      if (timing_) check(dev_.event_record(ev1_, stream_), "recording an event");
-      check(dev_.copy_to_host(h_packed_, d_packed_, size_t(2 + n) * 4, stream_), "reading the tokens back");
+      if (timing_) check(dev_.event_record(ev1_[par], stream_), "recording an event");
+      check(dev_.copy_to_host(h_packed_[par], d_packed_, size_t(2 + n) * 4, stream_), "reading the tokens back");
+      t_enqueued = now();
       check(dev_.stream_sync(stream_), "waiting for the step");
       ++replays_;
       info.launches = c.launches;
       info.graph = true;
     }
-    info.h2d_bytes = L.total_ints * 4 + (tempered > 0 ? static_cast<long long>(sampling_bytes_) : 0);
+    info.h2d_bytes = L.total_ints * 4 + (p.tempered > 0 ? static_cast<long long>(sampling_bytes_) : 0);
   } else {
-    const BatchLayout L = builder_.build(entries_, h_ints_, capacity_);
-    check(dev_.copy_to_device(d_ints_, h_ints_, size_t(L.total_ints) * 4, stream_), "copying the batch");
-    if (wants > 0 && tempered > 0) stage_sampling(plan, wants);
+    const BatchLayout L = builder_.build(entries_, h_ints_[par], capacity_);
+    t_built = now();
+    check(dev_.copy_to_device(d_ints_, h_ints_[par], size_t(L.total_ints) * 4, stream_), "copying the batch");
+    if (wants > 0 && p.tempered > 0) stage_sampling(plan, wants);
     fill_args(args, L, d_ints_, L.max_decode_ctx);
-    if (timing_) check(dev_.event_record(ev0_, stream_), "recording an event");
-    info.launches = run_device(args, wants, tempered > 0);
-    if (timing_) check(dev_.event_record(ev1_, stream_), "recording an event");
-    if (wants > 0) check(dev_.copy_to_host(h_packed_, d_packed_, size_t(2 + wants) * 4, stream_), "reading the tokens back");
+    if (timing_) check(dev_.event_record(ev0_[par], stream_), "recording an event");
+    info.launches = run_device(args, wants, p.tempered > 0);
+    if (timing_) check(dev_.event_record(ev1_[par], stream_), "recording an event");
+    if (wants > 0)
+      check(dev_.copy_to_host(h_packed_[par], d_packed_, size_t(2 + wants) * 4, stream_), "reading the tokens back");
+    t_enqueued = now();
     check(dev_.stream_sync(stream_), "waiting for the step");
-    info.h2d_bytes = L.total_ints * 4 + (wants > 0 && tempered > 0 ? static_cast<long long>(sampling_bytes_) : 0);
+    info.h2d_bytes = L.total_ints * 4 + (wants > 0 && p.tempered > 0 ? static_cast<long long>(sampling_bytes_) : 0);
   }
   if (timing_) {
     float ms = 0.f;
-    check(dev_.event_elapsed_ms(ev0_, ev1_, &ms), "reading the events");
+    check(dev_.event_elapsed_ms(ev0_[par], ev1_[par], &ms), "reading the events");
     info.device_ms = ms;
     device_ms_total_ += ms;
   }
+  const double t_waited = now();
   sampled_.clear();
   if (wants > 0) {
-    if (h_packed_[0] != 0) raise_status(h_packed_[0], h_packed_[1]);
-    sampled_.assign(h_packed_ + 2, h_packed_ + 2 + wants);
+    const int32_t* packed = h_packed_[par];
+    if (packed[0] != 0) raise_status(packed[0], packed[1]);
+    sampled_.assign(packed + 2, packed + 2 + wants);
     info.d2h_bytes = 4ll * (2 + wants);
   }
   const double t_end = now();
   sched_.update(sampled_, t_end);
-  info.rows = rows;
+  if (t_enqueued > t_built) {                                   // (the recording step is left out)
+    host_.schedule += t_scheduled - t_start;
+    host_.build += t_built - t_scheduled;
+    host_.enqueue += t_enqueued - t_built;
+    host_.wait += t_waited - t_enqueued;
+    host_.update += now() - t_waited;
+    ++host_.steps;
+  }
+  info.rows = p.rows;
   info.seqs = n;
-  info.prefill_tokens = prefill;
-  info.decode_seqs = singles;
+  info.prefill_tokens = p.prefill;
+  info.decode_seqs = p.singles;
   info.sampled = wants;
   info.ms = (t_end - t_start) * 1e3;
   return info;
+}
+
+// A greedy decode step of a recorded shape, enqueued and not waited for.  `chained`: the token ids
+// are the tokens that the step before it samples (it is still on the device).  False: this step
+// cannot go that way (its shape is not recorded yet, or not in both forms).
+bool NativeEngine::enqueue_decode(const Planned& p, bool chained, double t_start) {
+  const int n = p.n;
+  const int b = std::min(batch_bucket(n), std::max(max_logits_, n));
+  const int par = int(step_no_ & 1);
+  const BatchLayout L = builder_.build(entries_, h_ints_[par], capacity_, b, b, b);
+  auto it = graphs_.find(std::make_tuple(b, ctx_bucket(L.max_decode_ctx), 0));
+  if (it == graphs_.end() || it->second.exec_chained == nullptr || it->second.total_ints != L.total_ints) return false;
+  ++step_no_;
+  Captured& c = it->second;
+  check(dev_.copy_to_device(c.ints, h_ints_[par], size_t(L.total_ints) * 4, stream_), "copying the batch");
+  if (timing_) check(dev_.event_record(ev0_[par], stream_), "recording an event");
+  check(dev_.graph_launch(chained ? c.exec_chained : c.exec, stream_), "launching a CUDA graph");
+  if (timing_) check(dev_.event_record(ev1_[par], stream_), "recording an event");
+  check(dev_.copy_to_host(h_packed_[par], d_packed_, size_t(2 + n) * 4, stream_), "reading the tokens back");
+  check(dev_.event_record(done_[par], stream_), "recording an event");
+  ++replays_;
+  flight_ = InFlight{};
+  flight_.active = true;
+  flight_.parity = par;
+  flight_.timed = timing_;
+  flight_.n = n;
+  flight_.t_start = t_start;
+  flight_.info.rows = p.rows;
+  flight_.info.seqs = n;
+  flight_.info.decode_seqs = p.singles;
+  flight_.info.sampled = p.wants;
+  flight_.info.launches = c.launches;
+  flight_.info.graph = true;
+  flight_.info.h2d_bytes = L.total_ints * 4;
+  flight_.info.d2h_bytes = 4ll * (2 + n);
+  for (const ScheduledSeq& q : sched_.plan()) {
+    flight_.seqs.push_back(q.seq);
+    flight_.places.push_back(q.start + q.num_tokens);          // the sampled token follows the portion
+  }
+  return true;
+}
+
+// Waits for the tokens of a step in flight and puts them where the placeholders stand.
+NativeStepInfo NativeEngine::finish(InFlight& f) {
+  const double t0 = now();
+  check(dev_.event_sync(done_[f.parity]), "waiting for the step");
+  const double t1 = now();
+  const int32_t* packed = h_packed_[f.parity];
+  if (packed[0] != 0) raise_status(packed[0], packed[1]);
+  if (!f.updated) {                                            // nothing was enqueued behind it
+    sampled_.assign(packed + 2, packed + 2 + f.n);
+    sched_.update(sampled_, t1);
+  } else {
+    for (int i = 0; i < f.n; ++i) f.seqs[i]->tokens[size_t(f.places[i])] = packed[2 + i];
+  }
+  if (f.timed) {                                               // (timing may have been switched on since it was enqueued)
+    float ms = 0.f;
+    check(dev_.event_elapsed_ms(ev0_[f.parity], ev1_[f.parity], &ms), "reading the events");
+    f.info.device_ms = ms;
+    device_ms_total_ += ms;
+  }
+  host_.wait += t1 - t0;
+  host_.update += now() - t1;
+  ++host_.steps;
+  f.info.ms = (now() - f.t_start) * 1e3;
+  f.active = false;
+  return f.info;
+}
+
+void NativeEngine::drain() {
+  if (flight_.active) ready_.push_back(finish(flight_));
+}
+
+NativeStepInfo NativeEngine::step() {
+  if (!ready_.empty()) {
+    NativeStepInfo info = ready_.front();
+    ready_.erase(ready_.begin());
+    return info;
+  }
+  if (!flight_.active) {
+    // Nothing on the device.  Plan a step (unless the lookahead of the call before already did).
+    const double t_start = planned_ ? planned_at_ : now();
+    if (!planned_) sched_.schedule(t_start);
+    planned_ = false;
+    if (sched_.plan().empty()) return NativeStepInfo{};
+    const Planned p = summarise();
+    const bool greedy_decode = cfg_.graphs && cfg_.lookahead && p.singles == p.n && p.wants == p.n && p.tempered == 0;
+    if (!greedy_decode || !enqueue_decode(p, false, t_start)) return run_planned(p, t_start);
+    host_.schedule += now() - t_start;
+  }
+  // A greedy decode step is on the device.  Put placeholders where its tokens will go, so that the
+  // scheduler can plan the step after it, and enqueue that one behind it if the batch stays as it is.
+  InFlight cur = std::move(flight_);
+  flight_ = InFlight{};
+  const long long evictions = sched_.counters().preemptions;
+  sampled_.assign(size_t(cur.n), 0);
+  sched_.update(sampled_, now());
+  cur.updated = true;
+  bool same = sched_.num_waiting() == 0 && static_cast<int>(sched_.num_running()) == cur.n;
+  if (same) {
+    const double t_next = now();
+    sched_.schedule(t_next);
+    planned_ = true;
+    planned_at_ = t_next;
+    const std::vector<ScheduledSeq>& plan = sched_.plan();
+    same = static_cast<int>(plan.size()) == cur.n && sched_.counters().preemptions == evictions;
+    for (int i = 0; same && i < cur.n; ++i)
+      same = plan[i].seq.get() == cur.seqs[i].get() && plan[i].num_tokens == 1 && plan[i].wants_logits &&
+             plan[i].seq->sampling.temperature <= 0.f;
+    if (same) {
+      const Planned p = summarise();
+      const double t_built = now();
+      if (enqueue_decode(p, true, t_next)) {
+        planned_ = false;
+        ++lookahead_steps_;
+        host_.schedule += t_built - t_next;
+        host_.enqueue += now() - t_built;
+      }
+    }
+  }
+  return finish(cur);
 }
 
 // ------------------------------------------------------------------------ the stand-in device
@@ -364,6 +531,7 @@ int fake_free(void* p) { std::free(p); return 0; }
 int fake_event_create(void** e) { *e = reinterpret_cast<void*>(0x2); return 0; }
 int fake_event_record(void*, void*) { return 0; }
 int fake_event_elapsed(void*, void*, float* ms) { *ms = 0.f; return 0; }
+int fake_event_sync(void*) { return 0; }
 int fake_graph_begin(void*) {
   g_fake.recording = true;
   g_fake.open = new FakeGraph();
@@ -407,6 +575,7 @@ KvcmDeviceBackend make_fake_backend() {
   b.event_destroy = fake_ok_ptr;
   b.event_record = fake_event_record;
   b.event_elapsed_ms = fake_event_elapsed;
+  b.event_sync = fake_event_sync;
   b.graph_begin = fake_graph_begin;
   b.graph_end = fake_graph_end;
   b.graph_launch = fake_graph_launch;

@@ -11,6 +11,17 @@
 // the bucket with rows that read and write nothing; the step at hand runs eagerly while its shape is
 // recorded, so no step ever runs twice.
 //
+// One step of lookahead: while the device runs decode step k, the host already schedules, packs and
+// enqueues step k+1, whose token ids are step k's sampled tokens and therefore already lie on the
+// device (a second recording of each shape reads its tokens from there).  Everything else a decode
+// step needs (positions, page slots, context lengths, page tables) follows from the lengths alone.
+// The host then waits for step k's tokens only, puts them into the requests, and returns step k.
+// So the device never waits for the host between decode steps.  This holds only while the batch
+// stays what it was: all requests decode greedily, none ends, none arrives, no page runs out; the
+// moment one of these fails the loop waits for the tokens first, as before.  It is switched off where
+// a token's value decides what happens next (an end-of-sequence token) or enters host state at once
+// (page hashes of the prefix cache).
+//
 // The device is reached through a table of C functions (csrc/include/device_backend.h): the kernel
 // library fills it on a GPU, a test fills it with stand-ins that run on the CPU.  This file knows
 // nothing of CUDA.
@@ -43,6 +54,7 @@ struct NativeEngineConfig {
   int max_rows = 4096, max_seqs = 256;
   int tile_rows = 64;
   bool graphs = true;
+  bool lookahead = true;           // enqueue the next decode step before the tokens of this one are read
   long long attn_scratch_floats = 0, lib_workspace_bytes = 32ll << 20;
 };
 
@@ -62,6 +74,10 @@ class NativeEngine {
   NativeEngine& operator=(const NativeEngine&) = delete;
 
   NativeStepInfo step();
+  // Finishes a step that is still on the device (its result is handed out by the next step()).
+  void drain();
+  bool in_flight() const { return flight_.active; }
+  long long lookahead_steps() const { return lookahead_steps_; }
   double now() const { return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0_).count(); }
   void reset_clock() { t0_ = std::chrono::steady_clock::now(); }
   void set_timing(bool on) { timing_ = on; }                  // events around the device work of every step
@@ -71,6 +87,11 @@ class NativeEngine {
   long long graph_replays() const { return replays_; }
   std::vector<std::tuple<int, int, int>> graph_shapes() const;
   void* stream() const { return stream_; }
+  // Host seconds spent, summed over the steps so far: scheduling, packing the batch, enqueueing the
+  // step (copies and launches), waiting for the device, updating the scheduler.
+  struct HostTimes { double schedule = 0, build = 0, enqueue = 0, wait = 0, update = 0; long long steps = 0; };
+  const HostTimes& host_times() const { return host_; }
+  void reset_host_times() { host_ = {}; }
 
   static int batch_bucket(int n);
   static int ctx_bucket(int n);
@@ -78,10 +99,27 @@ class NativeEngine {
  private:
   struct Captured {
     void* exec = nullptr;
+    void* exec_chained = nullptr;                             // the same step with its token ids read from the sampled tokens
     int32_t* ints = nullptr;                                  // the graph's own copy of the batch arrays (device)
     long long total_ints = 0;
     int launches = 0;
   };
+  struct Planned {                                            // what schedule() decided, summarised
+    int rows = 0, wants = 0, prefill = 0, singles = 0, tempered = 0, n = 0;
+  };
+  struct InFlight {                                           // a decode step enqueued and not yet read
+    bool active = false, updated = false, timed = false;
+    int parity = 0, n = 0;
+    NativeStepInfo info;
+    std::vector<std::shared_ptr<Sequence>> seqs;              // the plan's requests, in order
+    std::vector<int> places;                                  // where each one's sampled token goes
+    double t_start = 0;
+  };
+  Planned summarise();
+  NativeStepInfo run_planned(const Planned& p, double t_start);          // the plan made, not pipelined
+  bool enqueue_decode(const Planned& p, bool chained, double t_start);   // replay of a recorded shape, not waited for
+  NativeStepInfo finish(InFlight& f);                                    // wait, check, put the tokens in
+  void record_shape(Captured& c, const KvcmForwardArgs& args, int b, bool tempered);
   void check(int rc, const char* what) const;
   void fill_args(KvcmForwardArgs& a, const BatchLayout& L, const int32_t* base, int max_decode_ctx) const;
   int run_device(const KvcmForwardArgs& a, int logit_rows, bool tempered);    // forward + sampling; launches made
@@ -95,7 +133,7 @@ class NativeEngine {
   KvcmDeviceBackend dev_;
   BatchBuilder builder_;
   void* stream_ = nullptr;
-  void *ev0_ = nullptr, *ev1_ = nullptr;
+  void *ev0_[2] = {nullptr, nullptr}, *ev1_[2] = {nullptr, nullptr}, *done_[2] = {nullptr, nullptr};
   bool timing_ = false;
   double device_ms_total_ = 0;
   long long replays_ = 0;
@@ -104,9 +142,9 @@ class NativeEngine {
   // host (pinned) and device buffers
   long long capacity_ = 0;
   int max_logits_ = 0;
-  int32_t* h_ints_ = nullptr;
-  int32_t* d_ints_ = nullptr;
-  int32_t* h_packed_ = nullptr;                               // [status pair | tokens]
+  int32_t* h_ints_[2] = {nullptr, nullptr};                   // two of each: a step may be packed while the one
+  int32_t* d_ints_ = nullptr;                                 // before it is still being copied
+  int32_t* h_packed_[2] = {nullptr, nullptr};                 // [status pair | tokens]
   int32_t* d_packed_ = nullptr;
   unsigned char* h_sampling_ = nullptr;                       // temps | positions | seeds | ids
   unsigned char* d_sampling_ = nullptr;
@@ -117,6 +155,12 @@ class NativeEngine {
   std::map<std::tuple<int, int, int>, Captured> graphs_;
   std::vector<BatchEntry> entries_;
   std::vector<int32_t> sampled_;
+  HostTimes host_;
+  InFlight flight_;
+  bool planned_ = false;                                      // schedule() has been called for the next step already
+  double planned_at_ = 0;
+  long long step_no_ = 0, lookahead_steps_ = 0;
+  std::vector<NativeStepInfo> ready_;                         // results of steps finished by drain()
 };
 
 // A stand-in device that runs on the CPU, for tests of the loop above: "device" memory is host

@@ -55,6 +55,7 @@ int rt_event_record(void* event, void* stream) { return int(cudaEventRecord((cud
 int rt_event_elapsed_ms(void* first, void* second, float* ms) {
   return int(cudaEventElapsedTime(ms, (cudaEvent_t)first, (cudaEvent_t)second));
 }
+int rt_event_sync(void* event) { return int(cudaEventSynchronize((cudaEvent_t)event)); }
 // Recording: everything launched on the stream between begin and end becomes one graph.  Only this
 // thread's launches are affected (thread-local capture mode).
 int rt_graph_begin(void* stream) {
@@ -103,6 +104,7 @@ KVCM_API int kvcm_device_backend(KvcmDeviceBackend* b) {
   b->event_destroy = rt_event_destroy;
   b->event_record = rt_event_record;
   b->event_elapsed_ms = rt_event_elapsed_ms;
+  b->event_sync = rt_event_sync;
   b->graph_begin = rt_graph_begin;
   b->graph_end = rt_graph_end;
   b->graph_launch = rt_graph_launch;

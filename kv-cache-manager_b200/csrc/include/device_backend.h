@@ -28,6 +28,7 @@ struct KvcmDeviceBackend {
   int (*event_destroy)(void* event);
   int (*event_record)(void* event, void* stream);
   int (*event_elapsed_ms)(void* first, void* second, float* ms);
+  int (*event_sync)(void* event);                       // waits on the host until the event has happened
   int (*graph_begin)(void* stream);
   int (*graph_end)(void* stream, void** graph_exec);
   int (*graph_launch)(void* graph_exec, void* stream);

@@ -130,7 +130,9 @@ class Engine:
                 self.kv, self.sched, nf.model_for_core(),
                 dict(block_size=kv.block_size, max_seq_len=kv.max_seq_len, num_groups=self.runner.num_groups,
                      max_rows=max(max_rows, kv.max_seq_len), max_seqs=sc.max_num_seqs, graphs=bool(cfg.cuda_graphs),
-                     attn_scratch_floats=scratch),
+                     attn_scratch_floats=scratch,
+                     # one step of lookahead, unless a token's value matters to the host at once
+                     lookahead=bool(cfg.lookahead and cfg.eos_token_id < 0 and not kv.prefix_caching)),
                 K.device_backend_address())
             self.graphs = _NativeGraphs(self.native) if cfg.cuda_graphs else None
 
@@ -265,6 +267,8 @@ class Engine:
         every position again would write pages that other requests share."""
         if self.cfg.kv.prefix_caching:
             raise RuntimeError("score: disable prefix caching")
+        if self.native is not None:
+            self.native.drain()               # a step still on the device ends first (its result comes with the next step())
         torch.cuda.synchronize()              # the C++ loop runs on a stream of its own
         s = core.Sequence()
         s.id = -1

@@ -133,6 +133,17 @@ class Replayer:
             self.session.release(rid)
         return None if out is None else out.float().cpu()
 
+    def stray_writes(self) -> List[int]:
+        """Pages of the first layer group that no request ever held and that are no longer all
+        zero (pools start zero-filled): a kernel wrote through a wrong page number or slot."""
+        pools = self.runner.pools
+        never = sorted(set(range(self.kv.num_blocks())) - set(self.pages_seen))
+        bad = []
+        for page in never:
+            if any(bool(t[:, page].count_nonzero()) for t in (pools.k[0], pools.v[0])):
+                bad.append(page)
+        return bad
+
 
 def run_trace_tool(folder: str, dtype: str, steps: List[dict], max_tokens: int, out_dir: str,
                    extra: Sequence[str] = ()) -> Dict[int, np.ndarray]:

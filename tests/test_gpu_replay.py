@@ -50,6 +50,7 @@ def test_each_request_alone_and_whole(name, dtype, model_folders, oracle):
         got = r.step([dict(id=f"r{i}", tokens=toks, want=list(range(len(toks))))], end=[f"r{i}"])
         helpers.assert_logits_close(got, oracle(name, dtype, i), dtype, f"{name} whole request {i}")
     assert r.kv.blocks_in_use() == 0
+    assert r.stray_writes() == []          # pages that were never handed out are still zero
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
@@ -144,6 +145,7 @@ def test_mixed_batches_with_pages_used_again(name, dtype, model_folders, oracle)
         helpers.assert_logits_close(got, ref, dtype, f"{name} mixed step {s['step']}")
     assert len(set(r.pages_seen)) <= r.kv.num_blocks()
     assert any(len(owners) > 1 for owners in r.page_owners.values()), "no page was used again"
+    assert r.stray_writes() == []
     total_pages = sum(helpers.roundup(n, r.runner.block_size) // r.runner.block_size for n in LENGTHS[name])
     assert total_pages > r.kv.num_blocks(), "the pool must be too small to hold every request at once"
     assert r.kv.blocks_in_use() == 0

@@ -12,7 +12,7 @@ V = 97
 
 
 def make(num_blocks=64, block_size=4, max_seq_len=64, max_num_seqs=4, max_batched_tokens=16, graphs=True,
-         prefill_chunk=0, eos=-1):
+         prefill_chunk=0, eos=-1, lookahead=True):
     kv = core.PagedManager(num_blocks, block_size, max_seq_len, False, 0)
     sc = core.SchedulerConfig()
     sc.max_num_seqs, sc.max_batched_tokens, sc.prefill_chunk, sc.eos_token_id = max_num_seqs, max_batched_tokens, prefill_chunk, eos
@@ -22,7 +22,7 @@ def make(num_blocks=64, block_size=4, max_seq_len=64, max_num_seqs=4, max_batche
     model = dict(embed=0, final_norm=0, lm_head=0, inv_freq=0, f32=0, H=8, I=16, nh=2, nkv=1, hd=4, V=V, sm_count=1,
                  final_eps=1e-5, scale=0.5, layers=[layer, layer])
     cfg = dict(block_size=block_size, max_seq_len=max_seq_len, num_groups=1, max_rows=max(max_batched_tokens, max_seq_len),
-               max_seqs=max_num_seqs, graphs=graphs)
+               max_seqs=max_num_seqs, graphs=graphs, lookahead=lookahead)
     return kv, sched, core.NativeEngine(kv, sched, model, cfg, 0)
 
 
@@ -47,10 +47,10 @@ def run(sched, eng, prompts, max_new, arrive_every=0):
     return done, infos
 
 
-@pytest.mark.parametrize("graphs", [True, False])
-def test_tokens_do_not_depend_on_batching_and_every_step_runs_once(graphs):
+@pytest.mark.parametrize("graphs,lookahead", [(True, True), (True, False), (False, False)])
+def test_tokens_do_not_depend_on_batching_and_every_step_runs_once(graphs, lookahead):
     prompts = [[5, 9, 3], list(range(10, 33)), [7], [2] * 17, [11, 12, 13, 14, 15, 16, 17]]
-    kv, sched, eng = make(graphs=graphs)
+    kv, sched, eng = make(graphs=graphs, lookahead=lookahead)
     before = core.fake_backend_forward_calls()
     done, infos = run(sched, eng, prompts, 12, arrive_every=3)
     for j, p in enumerate(prompts):
@@ -58,6 +58,7 @@ def test_tokens_do_not_depend_on_batching_and_every_step_runs_once(graphs):
     steps = [i for i in infos if i.rows > 0]
     assert core.fake_backend_forward_calls() - before == len(steps)       # a recorded step ran once, not twice
     assert max(i.rows for i in steps) <= 16 and any(i.prefill_tokens and i.decode_seqs for i in steps)
+    assert (eng.lookahead_steps() > 5) == lookahead and not eng.in_flight()
     if graphs:
         assert eng.graphs_captured() >= 2 and eng.graph_replays() > 5
         assert {b for b, _, _ in eng.graph_shapes()} <= {1, 2, 4}
@@ -67,6 +68,52 @@ def test_tokens_do_not_depend_on_batching_and_every_step_runs_once(graphs):
     assert kv.blocks_in_use() == 0 and sched.slots_taken() == 0
     c = sched.counters()
     assert c.prefill_tokens == sum(len(p) for p in prompts) and c.preemptions == 0
+
+
+def test_lookahead_enqueues_the_next_step_before_this_one_is_read():
+    """Steady greedy decoding: every call returns one step while the next is already on the device
+    (the stand-in device runs a step when it is enqueued, so "on the device" shows as a forward call
+    made one step early); a request that arrives, or ends, interrupts the chain and nothing is lost."""
+    kv, sched, eng = make(max_num_seqs=4, max_batched_tokens=64)
+    prompts = [[5, 9, 3], [8] * 6]
+    for j, p in enumerate(prompts):
+        sched.add_request(j, p, 30)
+    infos = [eng.step(), eng.step()]                 # the prompts; the first decode step records its shape
+    assert infos[0].prefill_tokens == 9 and not eng.in_flight()
+    before = core.fake_backend_forward_calls()
+    eng.step()                                       # a replayed decode step: the one after it is enqueued already
+    assert eng.in_flight() and core.fake_backend_forward_calls() - before == 2
+    eng.step()
+    assert eng.in_flight() and core.fake_backend_forward_calls() - before == 3 and eng.lookahead_steps() == 2
+    live = sched.live()
+    assert [s.num_generated() for s in live] == [4, 4] and all(t != 0 for s in live for t in s.generated())
+    sched.add_request(2, [4, 4, 4, 4], 5)            # a newcomer: the step in flight ends, then a mixed step
+    a, b = eng.step(), eng.step()
+    assert a.decode_seqs == 2 and a.prefill_tokens == 0 and b.prefill_tokens == 4 and b.decode_seqs == 2
+    done = {}
+    while not sched.idle():
+        eng.step()
+        for f in sched.take_finished():
+            done[f.id] = f
+    assert not eng.in_flight() and eng.step().rows == 0
+    for j, (p, n) in enumerate([(prompts[0], 30), (prompts[1], 30), ([4, 4, 4, 4], 5)]):
+        assert done[j].generated() == expected(p, n), j
+    eng.drain()
+
+
+def test_drain_finishes_a_step_in_flight_and_hands_its_result_out_later():
+    kv, sched, eng = make(max_num_seqs=2, max_batched_tokens=64)
+    sched.add_request(0, [5, 9, 3], 12)
+    eng.step(); eng.step(); eng.step()
+    assert eng.in_flight()
+    n = sched.live()[0].num_generated()
+    eng.drain()
+    assert not eng.in_flight() and sched.live()[0].num_generated() == n + 1
+    info = eng.step()                                # the drained step's result
+    assert info.decode_seqs == 1 and info.graph and sched.live()[0].num_generated() == n + 1
+    while not sched.idle():
+        eng.step()
+    assert sched.take_finished()[0].generated() == expected([5, 9, 3], 12)
 
 
 def test_eviction_when_pages_run_out_keeps_the_tokens():
