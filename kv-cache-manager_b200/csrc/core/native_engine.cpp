@@ -1,6 +1,7 @@
 #include "native_engine.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <functional>
@@ -90,7 +91,7 @@ NativeEngine::~NativeEngine() {
   if (stream_) dev_.stream_sync(stream_);
   for (auto& g : graphs_) {
     if (g.second.exec) dev_.graph_destroy(g.second.exec);
-    if (g.second.exec_chained) dev_.graph_destroy(g.second.exec_chained);
+    for (void* x : g.second.exec_chained) if (x) dev_.graph_destroy(x);
     if (g.second.ints) dev_.device_free(g.second.ints);
   }
   for (void* p : device_allocs_) dev_.device_free(p);
@@ -175,9 +176,15 @@ void NativeEngine::stage_sampling(const std::vector<ScheduledSeq>& plan, int row
   check(dev_.copy_to_device(d_sampling_, h_sampling_, sampling_bytes_, stream_), "copying the sampling parameters");
 }
 
-int NativeEngine::run_device(const KvcmForwardArgs& a, int logit_rows, bool tempered) {
-  int launches = 0;
+int NativeEngine::run_device(const KvcmForwardArgs& a, int logit_rows, bool tempered, const int32_t* fetch_from,
+                             int32_t* fetch_to, long long fetch_ints, int32_t* mirror) {
+  int launches = 0, extra = 0;
+  if (fetch_from != nullptr) {
+    check(dev_.fetch_ints(fetch_from, fetch_to, fetch_ints, stream_), "fetching the batch");
+    extra = 1;
+  }
   check(dev_.forward(&a, &launches, stream_), "the forward pass");
+  launches += extra;
   if (logit_rows > 0) {
     const size_t R = size_t(max_logits_);
     if (tempered)
@@ -188,7 +195,8 @@ int NativeEngine::run_device(const KvcmForwardArgs& a, int logit_rows, bool temp
                         stream_),
             "the sampling kernel");
     else
-      check(dev_.argmax(static_cast<const float*>(logits_), d_packed_ + 2, logit_rows, model_.V, d_packed_, stream_),
+      check(dev_.argmax(static_cast<const float*>(logits_), d_packed_ + 2, logit_rows, model_.V, d_packed_, mirror,
+                        stream_),
             "the argmax kernel");
     ++launches;
   }
@@ -227,17 +235,20 @@ NativeEngine::Planned NativeEngine::summarise() {
   return p;
 }
 
-// Records both forms of a decode shape: token ids from the batch arrays, and from the sampled
-// tokens of the step before (the chained form of the lookahead).
+// Records the forms of a decode shape: token ids from the batch arrays and copies by command (the
+// first step of a run of decode steps), and the chained form of the lookahead, once per pair of
+// pinned buffers: token ids from the sampled tokens of the step before, the batch arrays fetched by a
+// kernel, the tokens written to pinned memory by the sampling kernel.
 void NativeEngine::record_shape(Captured& c, const KvcmForwardArgs& args, int b, bool tempered) {
-  for (int form = 0; form < 2; ++form) {
+  for (int form = 0; form < 3; ++form) {
     KvcmForwardArgs a = args;
-    if (form == 1) a.tokens = d_packed_ + 2;
-    void** exec = form == 0 ? &c.exec : &c.exec_chained;
+    if (form > 0) a.tokens = d_packed_ + 2;
+    void** exec = form == 0 ? &c.exec : &c.exec_chained[form - 1];
     int rc = dev_.graph_begin(stream_);
     if (rc == 0) {
       try {
-        run_device(a, b, tempered);
+        if (form == 0) run_device(a, b, tempered);
+        else run_device(a, b, tempered, h_ints_[form - 1], c.ints, (c.total_ints + 3) / 4 * 4, h_packed_[form - 1]);
       } catch (...) {
         void* dead = nullptr;
         dev_.graph_end(stream_, &dead);
@@ -247,7 +258,7 @@ void NativeEngine::record_shape(Captured& c, const KvcmForwardArgs& args, int b,
       rc = dev_.graph_end(stream_, exec);
     }
     check(rc, "recording a CUDA graph");
-    if (tempered || !cfg_.lookahead) break;               // the chained form serves greedy steps only
+    if (tempered || !cfg_.lookahead) break;               // the chained forms serve greedy steps only
   }
 }
 
@@ -273,7 +284,7 @@ NativeStepInfo NativeEngine::run_planned(const Planned& p, double t_start) {
       // library must not fall into a recording, and a recording runs nothing): it is the real run.
       Captured c;
       void* ints = nullptr;
-      check(dev_.device_alloc(&ints, size_t(L.total_ints) * 4), "device allocation for a graph");
+      check(dev_.device_alloc(&ints, size_t((L.total_ints + 3) / 4 * 4) * 4), "device allocation for a graph");
       c.ints = static_cast<int32_t*>(ints);
       c.total_ints = L.total_ints;
       try {
@@ -287,7 +298,7 @@ NativeStepInfo NativeEngine::run_planned(const Planned& p, double t_start) {
         record_shape(c, args, b, p.tempered > 0);
       } catch (...) {
         if (c.exec) dev_.graph_destroy(c.exec);
-        if (c.exec_chained) dev_.graph_destroy(c.exec_chained);
+        for (void* x : c.exec_chained) if (x) dev_.graph_destroy(x);
         dev_.device_free(c.ints);
         throw;
       }
@@ -365,19 +376,30 @@ bool NativeEngine::enqueue_decode(const Planned& p, bool chained, double t_start
   const int par = int(step_no_ & 1);
   const BatchLayout L = builder_.build(entries_, h_ints_[par], capacity_, b, b, b);
   auto it = graphs_.find(std::make_tuple(b, ctx_bucket(L.max_decode_ctx), 0));
-  if (it == graphs_.end() || it->second.exec_chained == nullptr || it->second.total_ints != L.total_ints) return false;
+  if (it == graphs_.end() || it->second.exec_chained[par] == nullptr || it->second.total_ints != L.total_ints) return false;
   ++step_no_;
   Captured& c = it->second;
-  check(dev_.copy_to_device(c.ints, h_ints_[par], size_t(L.total_ints) * 4, stream_), "copying the batch");
-  if (timing_) check(dev_.event_record(ev0_[par], stream_), "recording an event");
-  check(dev_.graph_launch(chained ? c.exec_chained : c.exec, stream_), "launching a CUDA graph");
-  if (timing_) check(dev_.event_record(ev1_[par], stream_), "recording an event");
-  check(dev_.copy_to_host(h_packed_[par], d_packed_, size_t(2 + n) * 4, stream_), "reading the tokens back");
-  check(dev_.event_record(done_[par], stream_), "recording an event");
+  if (chained) {
+    // no copy commands: the recording fetches h_ints_[par] itself and writes its tokens into
+    // h_packed_[par], which holds -1 until then
+    for (int i = 0; i < 2 + b; ++i) h_packed_[par][i] = -1;
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+    if (timing_) check(dev_.event_record(ev0_[par], stream_), "recording an event");
+    check(dev_.graph_launch(c.exec_chained[par], stream_), "launching a CUDA graph");
+    if (timing_) check(dev_.event_record(ev1_[par], stream_), "recording an event");
+  } else {
+    check(dev_.copy_to_device(c.ints, h_ints_[par], size_t(L.total_ints) * 4, stream_), "copying the batch");
+    if (timing_) check(dev_.event_record(ev0_[par], stream_), "recording an event");
+    check(dev_.graph_launch(c.exec, stream_), "launching a CUDA graph");
+    if (timing_) check(dev_.event_record(ev1_[par], stream_), "recording an event");
+    check(dev_.copy_to_host(h_packed_[par], d_packed_, size_t(2 + n) * 4, stream_), "reading the tokens back");
+    check(dev_.event_record(done_[par], stream_), "recording an event");
+  }
   ++replays_;
   flight_ = InFlight{};
   flight_.active = true;
   flight_.parity = par;
+  flight_.mirrored = chained;
   flight_.timed = timing_;
   flight_.n = n;
   flight_.t_start = t_start;
@@ -396,10 +418,30 @@ bool NativeEngine::enqueue_decode(const Planned& p, bool chained, double t_start
   return true;
 }
 
+// The device writes a chained step's status pair and tokens straight into pinned memory: the host
+// watches the words turn from -1.  Bounded: a device that never answers raises after half a minute.
+void NativeEngine::wait_for_mirror(const InFlight& f) {
+  const volatile int32_t* m = h_packed_[f.parity];
+  const double t0 = now();
+  for (int i = 0; i < 2 + f.n; ++i) {
+    unsigned spins = 0;
+    while (m[i] == -1) {
+      if ((++spins & 0xfffff) == 0 && now() - t0 > 30.0)
+        throw std::runtime_error("engine: the tokens of a decode step did not arrive within 30 s");
+    }
+  }
+  std::atomic_thread_fence(std::memory_order_seq_cst);
+}
+
 // Waits for the tokens of a step in flight and puts them where the placeholders stand.
 NativeStepInfo NativeEngine::finish(InFlight& f) {
   const double t0 = now();
-  check(dev_.event_sync(done_[f.parity]), "waiting for the step");
+  if (f.mirrored) {
+    wait_for_mirror(f);
+    if (f.timed) check(dev_.event_sync(ev1_[f.parity]), "waiting for the step");
+  } else {
+    check(dev_.event_sync(done_[f.parity]), "waiting for the step");
+  }
   const double t1 = now();
   const int32_t* packed = h_packed_[f.parity];
   if (packed[0] != 0) raise_status(packed[0], packed[1]);
@@ -507,21 +549,28 @@ int fake_forward(const KvcmForwardArgs* a, int* launches, void*) {
   else fake_forward_now(*a);
   return 0;
 }
-void fake_argmax_now(const float* logits, int* out, int rows, int vocab, int* status) {
+void fake_argmax_now(const float* logits, int* out, int rows, int vocab, int* status, int* mirror) {
   for (int r = 0; r < rows; ++r) {
     const float* l = logits + size_t(r) * vocab;
     out[r] = static_cast<int>(std::max_element(l, l + vocab) - l);
+    if (mirror) mirror[2 + r] = out[r];
   }
   if (status) status[0] = status[1] = 0;
+  if (mirror) mirror[0] = mirror[1] = 0;
 }
-int fake_argmax(const float* logits, int* out, int rows, int vocab, int* status, void*) {
-  if (g_fake.recording) g_fake.open->calls.push_back([=] { fake_argmax_now(logits, out, rows, vocab, status); });
-  else fake_argmax_now(logits, out, rows, vocab, status);
+int fake_argmax(const float* logits, int* out, int rows, int vocab, int* status, int* mirror, void*) {
+  if (g_fake.recording) g_fake.open->calls.push_back([=] { fake_argmax_now(logits, out, rows, vocab, status, mirror); });
+  else fake_argmax_now(logits, out, rows, vocab, status, mirror);
+  return 0;
+}
+int fake_fetch_ints(const int* src, int* dst, long long ints, void*) {
+  if (g_fake.recording) g_fake.open->calls.push_back([=] { std::memcpy(dst, src, size_t(ints) * 4); });
+  else std::memcpy(dst, src, size_t(ints) * 4);
   return 0;
 }
 int fake_sample(const float* logits, const float*, const unsigned long long*, const long long*, const int*, int* out,
                 int rows, int vocab, int* status, void* s) {
-  return fake_argmax(logits, out, rows, vocab, status, s);
+  return fake_argmax(logits, out, rows, vocab, status, nullptr, s);
 }
 int fake_copy(void* dst, const void* src, size_t bytes, void*) { std::memcpy(dst, src, bytes); return 0; }
 int fake_stream_create(void** s) { *s = reinterpret_cast<void*>(0x1); return 0; }
@@ -561,6 +610,7 @@ KvcmDeviceBackend make_fake_backend() {
   KvcmDeviceBackend b{};
   b.forward = fake_forward;
   b.argmax = fake_argmax;
+  b.fetch_ints = fake_fetch_ints;
   b.sample = fake_sample;
   b.copy_to_device = fake_copy;
   b.copy_to_host = fake_copy;

@@ -99,7 +99,10 @@ class NativeEngine {
  private:
   struct Captured {
     void* exec = nullptr;
-    void* exec_chained = nullptr;                             // the same step with its token ids read from the sampled tokens
+    // The same step with its token ids read from the sampled tokens, its batch arrays fetched from
+    // pinned memory by a kernel and its tokens written to pinned memory by the sampling kernel: one per
+    // pair of pinned buffers (their addresses are part of the recording).
+    void* exec_chained[2] = {nullptr, nullptr};
     int32_t* ints = nullptr;                                  // the graph's own copy of the batch arrays (device)
     long long total_ints = 0;
     int launches = 0;
@@ -108,7 +111,7 @@ class NativeEngine {
     int rows = 0, wants = 0, prefill = 0, singles = 0, tempered = 0, n = 0;
   };
   struct InFlight {                                           // a decode step enqueued and not yet read
-    bool active = false, updated = false, timed = false;
+    bool active = false, updated = false, timed = false, mirrored = false;
     int parity = 0, n = 0;
     NativeStepInfo info;
     std::vector<std::shared_ptr<Sequence>> seqs;              // the plan's requests, in order
@@ -120,9 +123,12 @@ class NativeEngine {
   bool enqueue_decode(const Planned& p, bool chained, double t_start);   // replay of a recorded shape, not waited for
   NativeStepInfo finish(InFlight& f);                                    // wait, check, put the tokens in
   void record_shape(Captured& c, const KvcmForwardArgs& args, int b, bool tempered);
+  void wait_for_mirror(const InFlight& f);
   void check(int rc, const char* what) const;
   void fill_args(KvcmForwardArgs& a, const BatchLayout& L, const int32_t* base, int max_decode_ctx) const;
-  int run_device(const KvcmForwardArgs& a, int logit_rows, bool tempered);    // forward + sampling; launches made
+  // forward + sampling; launches made.  `fetch_from` / `mirror`: the chained form (pinned buffers of one parity).
+  int run_device(const KvcmForwardArgs& a, int logit_rows, bool tempered, const int32_t* fetch_from = nullptr,
+                 int32_t* fetch_to = nullptr, long long fetch_ints = 0, int32_t* mirror = nullptr);
   void stage_sampling(const std::vector<ScheduledSeq>& plan, int rows);
   [[noreturn]] void raise_status(int first, int word);
 

@@ -10,7 +10,8 @@
 
 extern "C" {
 int kvcm_forward(const KvcmForwardArgs*, int*, void*);
-int kvcm_argmax_status_f32(const float*, int*, int, int, int*, void*);
+int kvcm_argmax_mirror_f32(const float*, int*, int, int, int*, int*, void*);
+int kvcm_fetch_ints(const int*, int*, long long, void*);
 int kvcm_sample_status_f32(const float*, const float*, const unsigned long long*, const long long*, const int*, int*, int,
                            int, int*, void*);
 int kvcm_stream_error(void);
@@ -89,7 +90,8 @@ int rt_clear_errors(void) {
 // Fills the table; returns its size in bytes so that the caller can check the layout.
 KVCM_API int kvcm_device_backend(KvcmDeviceBackend* b) {
   b->forward = kvcm_forward;
-  b->argmax = kvcm_argmax_status_f32;
+  b->argmax = kvcm_argmax_mirror_f32;
+  b->fetch_ints = kvcm_fetch_ints;
   b->sample = kvcm_sample_status_f32;
   b->copy_to_device = rt_copy_to_device;
   b->copy_to_host = rt_copy_to_host;

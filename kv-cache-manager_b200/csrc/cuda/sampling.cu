@@ -9,6 +9,8 @@
 //     z = splitmix64 finaliser(z + 0x9E3779B97F4A7C15);   u = (z >> 40) * 2^-24
 // The vocabulary is cut into 1024 consecutive segments; segment sums are scanned in order, the
 // segment that holds u * total is scanned element by element.  Softmax in float.
+#include <algorithm>
+
 #include "common.cuh"
 #include "pdl.cuh"
 
@@ -23,8 +25,11 @@ constexpr int kStatusWords = 5;
 struct StatusWords {
   const int* word[kStatusWords];
 };
+// A second copy of [status pair | tokens] in pinned host memory that the device writes directly
+// (`mirror`, optional): the host then needs no copy command to learn the step's tokens, it watches
+// the words change from the -1 it put there.
 // status[0] = 1 + index of the first family whose word is set (0 = none), status[1] = that word.
-__device__ __forceinline__ void gather_status(const StatusWords& sw, int* status) {
+__device__ __forceinline__ void gather_status(const StatusWords& sw, int* status, int* mirror) {
   int first = 0, value = 0;
 #pragma unroll
   for (int i = 0; i < kStatusWords; ++i) {
@@ -33,6 +38,10 @@ __device__ __forceinline__ void gather_status(const StatusWords& sw, int* status
   }
   status[0] = first;
   status[1] = value;
+  if (mirror != nullptr) {
+    *reinterpret_cast<volatile int*>(mirror + 1) = value;
+    *reinterpret_cast<volatile int*>(mirror) = first;
+  }
 }
 
 __device__ __forceinline__ void argmax_merge(float& bv, int& bi, float ov, int oi) {
@@ -80,16 +89,20 @@ __device__ void block_argmax(const float* __restrict__ row, int vocab, float& be
 }
 
 __global__ void __launch_bounds__(kSampleThreads)
-argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, StatusWords sw, int* status) {
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, StatusWords sw, int* status,
+              int* mirror) {
   __shared__ float sv[32];
   __shared__ int si[32];
   pdl_launch_dependents();
   pdl_wait();
-  if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) gather_status(sw, status);
+  if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) gather_status(sw, status, mirror);
   float best;
   int index;
   block_argmax(logits + size_t(blockIdx.x) * vocab, vocab, best, index, sv, si);
-  if (threadIdx.x == 0) out[blockIdx.x] = index;
+  if (threadIdx.x == 0) {
+    out[blockIdx.x] = index;
+    if (mirror != nullptr) *reinterpret_cast<volatile int*>(mirror + 2 + blockIdx.x) = index;
+  }
 }
 
 __device__ __forceinline__ float sampling_uniform(unsigned long long seed, long long id, int position) {
@@ -106,7 +119,7 @@ __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const unsigned long long* __restrict__ seed, const long long* __restrict__ request_id,
               const int* __restrict__ position, int* __restrict__ out, int vocab, StatusWords sw, int* status) {
-  if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) gather_status(sw, status);
+  if (status != nullptr && blockIdx.x == 0 && threadIdx.x == 0) gather_status(sw, status, nullptr);
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ float part[kSampleThreads];
@@ -187,10 +200,39 @@ static StatusWords status_words() {
 }
 
 // `status` (optional): two ints that receive the first error word that is set, see gather_status.
-KVCM_API int kvcm_argmax_status_f32(const float* logits, int* out, int rows, int vocab, int* status, void* stream) {
+// `mirror` (optional, needs `status`): pinned host memory [2 + rows] that receives the same status
+// pair and tokens by direct stores of the device.
+KVCM_API int kvcm_argmax_mirror_f32(const float* logits, int* out, int rows, int vocab, int* status, int* mirror,
+                                    void* stream) {
   if (rows == 0) return 0;
+  if (mirror != nullptr && status == nullptr) return KVCM_ERR_UNSUPPORTED;
   return pdl_launch(argmax_kernel, dim3(rows), dim3(kSampleThreads), 0, (cudaStream_t)stream, logits, out, vocab,
-                    status ? status_words() : StatusWords{}, status);
+                    status ? status_words() : StatusWords{}, status, mirror);
+}
+
+KVCM_API int kvcm_argmax_status_f32(const float* logits, int* out, int rows, int vocab, int* status, void* stream) {
+  return kvcm_argmax_mirror_f32(logits, out, rows, vocab, status, nullptr, stream);
+}
+
+namespace kvcm {
+// The batch's integer arrays from pinned host memory into the device buffer that the step's kernels
+// read: a kernel that fetches them itself, as the first launch of a recorded decode step, instead
+// of a copy command in front of it (a copy engine needs several microseconds to start, in which the
+// SMs would idle).
+__global__ void __launch_bounds__(256) fetch_ints_kernel(const int4* __restrict__ src, int4* __restrict__ dst, int vecs) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+}  // namespace kvcm
+
+// `ints` a multiple of 4 (the batch builder pads every array to 16 bytes); both addresses 16-byte aligned.
+KVCM_API int kvcm_fetch_ints(const int* pinned_src, int* dst, long long ints, void* stream) {
+  if (ints <= 0) return 0;
+  if ((ints & 3) || (reinterpret_cast<uintptr_t>(pinned_src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
+    return KVCM_ERR_UNSUPPORTED;
+  const int vecs = int(ints / 4);
+  fetch_ints_kernel<<<std::min((vecs + 255) / 256, 8), 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const int4*>(pinned_src), reinterpret_cast<int4*>(dst), vecs);
+  return KVCM_LAUNCH_RESULT();
 }
 
 KVCM_API int kvcm_argmax_f32(const float* logits, int* out, int rows, int vocab, void* stream) {

@@ -11,7 +11,10 @@ struct KvcmForwardArgs;
 extern "C" {
 struct KvcmDeviceBackend {
   int (*forward)(const KvcmForwardArgs* args, int* launches, void* stream);
-  int (*argmax)(const float* logits, int* out, int rows, int vocab, int* status, void* stream);
+  // `mirror` (optional): pinned host memory [2 + rows] that the device also writes [status pair | tokens] into
+  int (*argmax)(const float* logits, int* out, int rows, int vocab, int* status, int* mirror, void* stream);
+  // the batch's integer arrays fetched from pinned host memory by a kernel (ints a multiple of 4)
+  int (*fetch_ints)(const int* pinned_src, int* dst, long long ints, void* stream);
   int (*sample)(const float* logits, const float* temperature, const unsigned long long* seed,
                 const long long* request_id, const int* position, int* out, int rows, int vocab, int* status,
                 void* stream);

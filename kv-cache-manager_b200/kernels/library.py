@@ -45,8 +45,8 @@ def profiling() -> bool:
 
 class DeviceBackend(ctypes.Structure):
     """Opaque room for the table of device functions that the kernel library fills for the C++
-    request loop (csrc/include/device_backend.h): 22 function pointers."""
-    _fields_ = [("slots", ctypes.c_void_p * 22)]
+    request loop (csrc/include/device_backend.h): 23 function pointers."""
+    _fields_ = [("slots", ctypes.c_void_p * 23)]
 
 
 _backend = None
