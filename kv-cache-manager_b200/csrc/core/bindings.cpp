@@ -438,6 +438,7 @@ PYBIND11_MODULE(kvcm_core, m) {
              c.max_seqs = int(geti(config, "max_seqs")); c.graphs = config["graphs"].cast<bool>();
              if (config.contains("tile_rows")) c.tile_rows = int(geti(config, "tile_rows"));
              if (config.contains("lookahead")) c.lookahead = config["lookahead"].cast<bool>();
+             if (config.contains("fuse_norms")) c.fuse_norms = config["fuse_norms"].cast<bool>();
              if (config.contains("attn_scratch_floats")) c.attn_scratch_floats = geti(config, "attn_scratch_floats");
              if (config.contains("lib_workspace_bytes")) c.lib_workspace_bytes = geti(config, "lib_workspace_bytes");
              const KvcmDeviceBackend backend = backend_address

@@ -54,6 +54,7 @@ struct NativeEngineConfig {
   int max_rows = 4096, max_seqs = 256;
   int tile_rows = 64;
   bool graphs = true;
+  bool fuse_norms = true;          // steps of one or two rows: residual add and norms inside the streaming products
   bool lookahead = true;           // enqueue the next decode step before the tokens of this one are read
   long long attn_scratch_floats = 0, lib_workspace_bytes = 32ll << 20;
 };
@@ -156,7 +157,8 @@ class NativeEngine {
   unsigned char* d_sampling_ = nullptr;
   size_t sampling_bytes_ = 0;
   void *x_ = nullptr, *h_ = nullptr, *qkv_ = nullptr, *attn_ = nullptr, *proj_ = nullptr, *gate_up_ = nullptr,
-       *act_ = nullptr, *h_last_ = nullptr, *logits_ = nullptr, *attn_scratch_ = nullptr, *lib_ws_ = nullptr;
+       *act_ = nullptr, *h_last_ = nullptr, *logits_ = nullptr, *attn_scratch_ = nullptr, *lib_ws_ = nullptr,
+       *norm_partials_ = nullptr;
   std::vector<void*> device_allocs_;
   std::map<std::tuple<int, int, int>, Captured> graphs_;
   std::vector<BatchEntry> entries_;

@@ -23,10 +23,12 @@ struct KvcmForwardArgs {
   const int* seq_ctx_len; const int* tile_seq; const int* tile_q0; const int* logit_rows;
   const int* group_tables[KVCM_FORWARD_MAX_GROUPS]; const int* group_slots[KVCM_FORWARD_MAX_GROUPS];
   // buffers of the caller, sized for the step: x [T,H] float; h, proj [T,H]; qkv [T,QKV]; attn [T,nh*hd];
-  // gate_up [T,2I]; act [T,I]; h_last [L,H]; logits [L,V] float; attn_scratch floats; a library workspace
+  // gate_up [T,2I]; act [T,I]; h_last [L,H]; logits [L,V] float; attn_scratch floats; a library workspace;
+  // norm_partials: ceil(H/16)*16 floats, or null = every norm is a launch of its own (with it, a step
+  // of one or two rows adds the residual and takes the norms inside its products)
   float* x; void* h; void* qkv; void* attn; void* proj; void* gate_up; void* act; void* h_last; float* logits;
-  float* attn_scratch; void* lib_workspace;
-  long long attn_scratch_floats, lib_workspace_bytes;
+  float* attn_scratch; void* lib_workspace; float* norm_partials;
+  long long attn_scratch_floats, lib_workspace_bytes, norm_partials_floats;
   int num_layers, f32, H, I, nh, nkv, hd, V, block_size, max_blocks, sm_count;
   int rows, seqs, decode_seqs, prefill_tiles, tile_rows, max_decode_ctx, num_logits, reserved;
   float final_eps, scale;

@@ -105,7 +105,7 @@ class Engine:
             max_seq_len=kv.max_seq_len, num_slots=sc.max_num_seqs,
             max_rows=max(max_rows, kv.max_seq_len), max_seqs=sc.max_num_seqs,
             max_logit_rows=max(self.max_logit_rows, kv.max_seq_len),
-            options={"attn_version": cfg.attn, "gemm": cfg.gemm})
+            options={"attn_version": cfg.attn, "gemm": cfg.gemm, "fuse_norms": cfg.fuse_norms})
         self.kv = manager_from_config(kv, self.runner.windows)
         s = core.SchedulerConfig()
         s.max_num_seqs, s.max_batched_tokens = sc.max_num_seqs, sc.max_batched_tokens
@@ -132,6 +132,7 @@ class Engine:
                      max_rows=max(max_rows, kv.max_seq_len), max_seqs=sc.max_num_seqs, graphs=bool(cfg.cuda_graphs),
                      attn_scratch_floats=scratch,
                      # one step of lookahead, unless a token's value matters to the host at once
+                     fuse_norms=bool(cfg.fuse_norms),
                      lookahead=bool(cfg.lookahead and cfg.eos_token_id < 0 and not kv.prefix_caching)),
                 K.device_backend_address())
             self.graphs = _NativeGraphs(self.native) if cfg.cuda_graphs else None

@@ -50,6 +50,9 @@ class NativeForward:
         # engine's limits (requests x heads x partitions x (head_dim + 2) floats, 64 partitions)
         self.attn_scratch = None if self.f32 else torch.empty(
             min(runner.max_seqs, 1024) * self.nh * 64 * (self.hd + 2), dtype=torch.float32, device=dev)
+        # partial sums of squares of the residual, one per 16 columns and row (None = norms are launches)
+        fuse = runner.options.get("fuse_norms", True) and not self.f32
+        self.norm_partials = torch.zeros((self.H + 15) // 16 * 16, dtype=torch.float32, device=dev) if fuse else None
         self.calls = 0
 
     # ------------------------------------------------------------------ does the model fit
@@ -160,6 +163,8 @@ class NativeForward:
             a.attn_scratch, a.attn_scratch_floats = self.attn_scratch.data_ptr(), self.attn_scratch.numel()
         if self.lib_workspace is not None:
             a.lib_workspace, a.lib_workspace_bytes = self.lib_workspace.data_ptr(), self.lib_workspace.numel()
+        if self.norm_partials is not None:
+            a.norm_partials, a.norm_partials_floats = self.norm_partials.data_ptr(), self.norm_partials.numel()
         a.num_layers, a.f32 = len(self.layers), int(self.f32)
         a.H, a.I, a.nh, a.nkv, a.hd, a.V = H, I, self.nh, self.nkv, self.hd, self.vocab
         a.block_size, a.max_blocks = ctx.groups[0].block_size, ctx.groups[0].block_tables.shape[1]

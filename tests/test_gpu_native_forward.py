@@ -14,9 +14,9 @@ from test_gpu_replay import LENGTHS, mixed_pool_tokens, mixed_trace, tokens_of
 pytestmark = pytest.mark.gpu
 
 
-def pair(model_folders, name, dtype, max_tokens):
+def pair(model_folders, name, dtype, max_tokens, fuse_norms=False):
     block = helpers.TINY[name]["block_size"]
-    native = helpers.Replayer(model_folders(name, dtype), dtype, max_tokens, block)
+    native = helpers.Replayer(model_folders(name, dtype), dtype, max_tokens, block, options={"fuse_norms": fuse_norms})
     parts = helpers.Replayer(model_folders(name, dtype), dtype, max_tokens, block, options={"native_forward": False})
     assert native.runner.native is not None and parts.runner.native is None
     return native, parts
@@ -34,21 +34,33 @@ def test_float32_steps_give_equal_bits(name, model_folders):
 
 @pytest.mark.parametrize("name", ["tiny-b", "tiny-c", "tiny-d"])
 def test_bfloat16_steps(name, model_folders):
-    """Decode steps (up to eight single rows: this engine's kernels only) bit for bit; the mixed
-    schedule, whose longer portions take library products, within the tolerance of the replay tests."""
+    """Decode steps (up to eight single rows: this engine's kernels only) bit for bit while every norm
+    is a launch of its own; with the norms riding in the products (the default: fewer launches, the
+    sums of squares added in another order) within the tolerance of the replay tests, like the mixed
+    schedule, whose longer portions take library products."""
+    from kvcm.kernels import library as K
     dtype = "bfloat16"
     native, parts = pair(model_folders, name, dtype, 1024)
+    riding, _ = pair(model_folders, name, dtype, 1024, fuse_norms=True)
+    cfg, w = P.read_model_folder(model_folders(name, dtype))
+    oracle = {i: P.llama_forward(cfg, w, tokens_of(name, i), torch.bfloat16) for i in range(len(LENGTHS[name]))}
     toks = [tokens_of(name, i) for i in range(4)]
-    for r in (native, parts):
+    for r in (native, parts, riding):
         r.step([dict(id=f"r{i}", tokens=t[:-3], want=[]) for i, t in enumerate(toks) if len(t) > 3])
     live = [i for i, t in enumerate(toks) if len(t) > 3]
     for k in (3, 2, 1):
         entries = [dict(id=f"r{i}", tokens=[toks[i][-k]], want=[0]) for i in live]
-        assert torch.equal(native.step(entries), parts.step(entries)), f"{name} decode step"
+        n0 = K.launch_count()
+        separate = native.step(entries)
+        n1 = K.launch_count()
+        together = riding.step(entries[:2])                         # (one or two rows: more do not ride)
+        n2 = K.launch_count()
+        assert torch.equal(separate, parts.step(entries)), f"{name} decode step"
+        ref = torch.stack([oracle[i][len(toks[i]) - k] for i in live[:2]])
+        helpers.assert_logits_close(together, ref, dtype, f"{name} decode step, norms in the products")
+        assert (n1 - n0) - (n2 - n1) >= cfg["num_hidden_layers"], "norms ride in the products: fewer launches"
     steps, places = mixed_trace(name)
-    native, parts = pair(model_folders, name, dtype, mixed_pool_tokens(name))
-    cfg, w = P.read_model_folder(model_folders(name, dtype))
-    oracle = {i: P.llama_forward(cfg, w, tokens_of(name, i), torch.bfloat16) for i in range(len(LENGTHS[name]))}
+    native, parts = pair(model_folders, name, dtype, mixed_pool_tokens(name), fuse_norms=True)
     for s, where in zip(steps, places):
         a, b = native.step(s["entries"], s["end"]), parts.step(s["entries"], s["end"])
         ref = torch.stack([oracle[i][pos] for i, pos in where])
