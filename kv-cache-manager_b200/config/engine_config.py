@@ -55,6 +55,6 @@ class EngineConfig:
     eos_token_id: int = -1           # < 0: no end-of-sequence stop (the reference has none)
     cuda_graphs: bool = True         # capture decode-only steps per batch-size bucket
     native_loop: bool = True         # run the request loop and the layer loop in C++ where the model allows it
-    fuse_norms: bool = True          # steps of one or two rows: residual add and norms inside the streaming products
+    fuse_norms: bool = True          # steps of at most 8 rows: residual add and norms inside the streaming products
     lookahead: bool = True           # C++ loop: enqueue the next greedy decode step before this one's tokens are read
     device: str = "cuda:0"

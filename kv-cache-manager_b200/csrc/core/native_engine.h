@@ -54,7 +54,7 @@ struct NativeEngineConfig {
   int max_rows = 4096, max_seqs = 256;
   int tile_rows = 64;
   bool graphs = true;
-  bool fuse_norms = true;          // steps of one or two rows: residual add and norms inside the streaming products
+  bool fuse_norms = true;          // steps of at most 8 rows: residual add and norms inside the streaming products
   bool lookahead = true;           // enqueue the next decode step before the tokens of this one are read
   long long attn_scratch_floats = 0, lib_workspace_bytes = 32ll << 20;
 };

@@ -23,12 +23,14 @@
 //    not staged in shared memory at all: no element of X is used twice by a block then, so the
 //    consumers read their pieces of X from L2 straight into registers, one stage ahead, and the
 //    ring gets the whole of shared memory (the block's entire tile of W is in flight at once).
-//  * The residual stream and its norm can ride along (a decode layer then has no norm launches):
-//    the products that end a sublayer (attention output, feed-forward down) add their result into
-//    the float residual themselves and write, per tile of 16 columns and row, the sum of squares of
-//    the new residual (kResidual); the products that begin the next sublayer stage X as
-//    weight * round(residual * rsqrt(mean square + eps)) from the float residual and those partial
-//    sums (NORMX), added in a fixed order.
+//  * The residual stream and its norm can ride along (a decode layer then has no norm launches).
+//    A norm is out = w * x * r with r = rsqrt(mean(x^2) + eps) one number per row, so r can be
+//    applied after the product that consumes the normed row: (W (w * x)) * r.  The products that
+//    end a sublayer (attention output, feed-forward down) add their result into the float residual
+//    themselves, write bfloat16(w * x_new) for the product that follows and, per tile of 16 columns
+//    and row, the sum of squares of x_new (kResidual); the products that begin the next sublayer
+//    add those partial sums up in a fixed order while their weights stream and scale their float
+//    sums by r before the epilogue (SCALED).  One rounding of the normed row instead of two.
 // The k index inside a 32-wide block is permuted identically for both operands (thread t of a
 // quad owns k = 8t..8t+7), which makes every shared-memory read of W and X a 16-byte vector.
 // The reference calls cuBLAS here (src/model/llama.cpp:45-52).
@@ -53,7 +55,6 @@ __device__ int g_stream_error = 0;                     // 0 = ok; else (code << 
 // sequence of copies) whose copy is left out, so that its consumers wait for bytes that never come.
 __device__ unsigned long long g_stream_wait_limit_ns = kWaitLimitNs;
 __device__ int g_stream_skip_stage = -1;
-static int g_norm_cluster = 0;                         // blocks that share the staging of a normed X (0 = by the rows)
 
 // What happens to a finished tile of 16 output columns x M rows.
 //  kStore    : y[m][n] = sum.
@@ -66,8 +67,10 @@ static int g_norm_cluster = 0;                         // blocks that share the 
 //  kSiluMul  : the 16 weight rows are 8 gate rows i..i+7 and the 8 up rows I+i..: y[m][i] =
 //              round(round(silu(round(gate))) * round(up)), as the separate activation kernel.
 //  kResidual : resid[m][n] += round(sum) (the float residual stream, in place; the sum rounded to
-//              bfloat16 as the plain product would store it), and ss_out[tile][m] = the sum over the
-//              tile's 16 columns of the new resid[m][n]^2: what the next norm needs of this tile.
+//              bfloat16 as the plain product would store it), ss_out[tile][m] = the sum over the
+//              tile's 16 columns of the new resid[m][n]^2 (what the next norm needs of this tile),
+//              and h_out[m][n] = bfloat16(next_w[n] * resid[m][n]): the next norm's row before its
+//              scale (left out where next_w is null).
 enum StreamEpilogue { kStore = 0, kRopeCache = 1, kSiluMul = 2, kResidual = 3 };
 constexpr int kNormRows = 16;                          // row stride of the partial sums of squares
 
@@ -85,10 +88,10 @@ struct StreamParams {
   bf16* k_cache; bf16* v_cache;
   int nh, nkv, hd, block_size;
   // kResidual
-  float* resid; int ldr; float* ss_out;
-  // NORMX: X is not read; it is made from the float residual xf [M, ldxf], the partial sums of
-  // squares ss_in [ss_tiles][kNormRows] and the norm's weight [K]
-  const float* xf; int ldxf; const float* ss_in; int ss_tiles; const bf16* norm_w; float eps;
+  float* resid; int ldr; float* ss_out; bf16* h_out; int ldh; const bf16* next_w;
+  // SCALED: the sums of row m are multiplied by rsqrt(sum over t of ss_in[t][m] / K + eps) before the
+  // epilogue (ss_in [ss_tiles][kNormRows] as kResidual leaves it)
+  const float* ss_in; int ss_tiles; float eps;
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -127,27 +130,6 @@ __device__ __forceinline__ void bulk_copy(void* dst, const void* src, uint32_t b
                ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
 }
 
-// Thread-block cluster (the blocks of a cluster share the staging of a normed X).
-__device__ __forceinline__ uint32_t cluster_size() {
-  uint32_t n;
-  asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(n));
-  return n;
-}
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
-// 16 bytes into the same shared-memory address of block `rank` of the cluster
-__device__ __forceinline__ void store_cluster(const void* local, uint32_t rank, const uint4& v) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(s32(local)), "r"(rank));
-  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(remote), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
-}
-
 __device__ __forceinline__ void mma_stream(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                            uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -168,10 +150,9 @@ __device__ __forceinline__ void cp_async_wait_dyn(int n) {       // wait until a
   }
 }
 
-template <int MT, typename OutT, int EPI, bool XDIRECT, bool NORMX = false>
+template <int MT, typename OutT, int EPI, bool XDIRECT, bool SCALED = false>
 __global__ void __launch_bounds__(kStreamThreads)
 gemm_stream_kernel(StreamParams p) {
-  static_assert(!(NORMX && XDIRECT), "the normed X is staged");
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr int kConsumerThreads = 32 * kStreamConsumers;
   constexpr int MB = MT * 8;                                  // batch rows held (padded)
@@ -186,7 +167,7 @@ gemm_stream_kernel(StreamParams p) {
   uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * kStreamConsumers * 16 * MB);
   uint64_t* empty = full + kMaxStages;
   __shared__ volatile int abort_flag;
-  __shared__ float norm_s[16 * 16];                           // NORMX: 1/rms per row; kResidual: squares of a tile
+  __shared__ float norm_s[16 * 16];                           // SCALED: 1/rms per row; kResidual: squares of a tile
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = (p.N + 15) / 16;
@@ -200,11 +181,6 @@ gemm_stream_kernel(StreamParams p) {
   }
   __syncthreads();
   pdl_launch_dependents();
-  // NORMX in a cluster: every block norms a share of X's columns and writes it into the shared memory
-  // of all.  First barrier: all blocks of the cluster run (their shared memory may be written);
-  // second: all shares are in place.  Every thread arrives at both and waits for both.
-  const uint32_t nc = NORMX ? cluster_size() : 1u;
-  if (NORMX && nc > 1) cluster_arrive();
 
   // weight row of local row r (0..15) of a tile
   auto row_of = [&](int tile, int r) {
@@ -236,10 +212,6 @@ gemm_stream_kernel(StreamParams p) {
   pdl_wait();                                                               // ... the predecessor wrote X
 
   if (warp == kStreamConsumers) {
-    if (NORMX && nc > 1) {
-      cluster_wait();
-      cluster_arrive();
-    }
     for (; issued < total; ++issued) {
       const int s = issued % kStages;
       int ok = 1;
@@ -262,90 +234,25 @@ gemm_stream_kernel(StreamParams p) {
         const int fills = issued > s ? (issued - s - 1) / kStages + 1 : 0;
         if (fills > 0) mbar_wait(&full[s], (fills - 1) & 1, wait_limit / 4);
       }
-    __syncwarp();
-    if (NORMX && nc > 1) cluster_wait();
     return;
   }
 
   // ---- consumers.  X is staged k-chunk by k-chunk (one copy group each, zero fill beyond M and
   // K), so the first tile can start on chunk 0 while the later chunks are still arriving.
   const int chunk_vecs = kChunk / 8;
-  if constexpr (NORMX) {
-    // X = weight * round(residual * inv).  The vectors of 8 k are dealt out over the blocks of the
-    // cluster by column; a thread takes a column for four rows at a time.  Everything it needs is
-    // requested at once (the partial sums, whose chain is the longest, first), so the staging costs
-    // one trip to L2, the adding up and a barrier.
-    const int row_vecs = Kc * chunk_vecs;
-    const int cols_here = row_vecs / int(nc), col0 = int(cluster_rank()) * cols_here;     // nc divides row_vecs
-    const int items = cols_here * (MB / 4);
-    float part[MT];
-#pragma unroll
-    for (int j = 0; j < MT; ++j) {
-      part[j] = 0.f;
-      const int m = warp + kStreamConsumers * j;
-      if (m < p.M) {
+  if constexpr (SCALED) {
+    // 1/rms of the rows from the partial sums: requested now, needed at the epilogue (the barrier
+    // in front of it makes norm_s visible to all)
+    for (int m = warp; m < p.M; m += kStreamConsumers) {
+      float ss = 0.f;
 #pragma unroll 4
-        for (int t = lane; t < p.ss_tiles; t += 32) part[j] += __ldcg(p.ss_in + t * kNormRows + m);
-      }
+      for (int t = lane; t < p.ss_tiles; t += 32) ss += __ldcg(p.ss_in + t * kNormRows + m);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) norm_s[m] = rsqrtf(ss / float(p.K) + p.eps);
     }
-    bool first = true;
-    for (int it0 = 0; it0 < items; it0 += kConsumerThreads) {     // (uniform: every thread runs every trip)
-      const int it = it0 + tid;
-      const int grp = it / cols_here, ch = col0 + (it - grp * cols_here);
-      const bool live = it < items;
-      const bool kin = live && ch * 8 < p.K;
-      uint4 wv = make_uint4(0u, 0u, 0u, 0u);
-      if (kin) wv = __ldg(reinterpret_cast<const uint4*>(p.norm_w + ch * 8));
-      float4 lo[4], hi[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int m = 4 * grp + u;
-        lo[u] = hi[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (kin && m < p.M) {
-          const float4* src = reinterpret_cast<const float4*>(p.xf + size_t(m) * p.ldxf + ch * 8);
-          lo[u] = __ldcg(src);
-          hi[u] = __ldcg(src + 1);
-        }
-      }
-      if (first) {
-#pragma unroll
-        for (int jj = 0; jj < MT; ++jj) {
-          float ss = part[jj];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-          const int m = warp + kStreamConsumers * jj;
-          if (lane == 0 && m < p.M) norm_s[m] = rsqrtf(ss / float(p.K) + p.eps);
-        }
-        asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
-        if (nc > 1) cluster_wait();                            // the other blocks' shared memory may be written
-        first = false;
-      }
-      if (live) {
-        const bf16* w8 = reinterpret_cast<const bf16*>(&wv);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int m = 4 * grp + u;
-          uint4 out = make_uint4(0u, 0u, 0u, 0u);
-          if (kin && m < p.M) {
-            const float inv = norm_s[m];
-            const float v[8] = {lo[u].x, lo[u].y, lo[u].z, lo[u].w, hi[u].x, hi[u].y, hi[u].z, hi[u].w};
-            bf16* o8 = reinterpret_cast<bf16*>(&out);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) stf(o8 + e, ldf(w8 + e) * Store<bf16>::round(v[e] * inv));
-          }
-          bf16* dst = xs + m * Kp + ch * 8;
-          if (nc == 1) *reinterpret_cast<uint4*>(dst) = out;
-          else
-            for (uint32_t r = 0; r < nc; ++r) store_cluster(dst, r, out);
-        }
-      }
-    }
-    if (nc > 1) {
-      cluster_arrive();
-      cluster_wait();
-    }
-    asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
-  } else if constexpr (!XDIRECT) {
+  }
+  if constexpr (!XDIRECT) {
     for (int kc = 0; kc < Kc; ++kc) {
       for (int c = tid; c < MB * chunk_vecs; c += kConsumerThreads) {
         const int m = c / chunk_vecs, ch = kc * chunk_vecs + (c - m * chunk_vecs);
@@ -382,7 +289,7 @@ gemm_stream_kernel(StreamParams p) {
     for (int kc = 0; kc < Kc; ++kc, ++i) {
       if constexpr (XDIRECT) {
         fetch_x(xnext, kc + 1);                                // in flight while this stage is worked on
-      } else if (!NORMX && tl == 0) {                          // this chunk of X has landed for everyone?
+      } else if (tl == 0) {                                    // this chunk of X has landed for everyone?
         cp_async_wait_dyn(min(Kc - 1 - kc, 7));
         asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
       }
@@ -451,6 +358,7 @@ gemm_stream_kernel(StreamParams p) {
           float* x = p.resid + size_t(m) * p.ldr + n;
           v = *x + Store<bf16>::round(total_of(r, m));
           *x = v;
+          if (p.next_w != nullptr) stf(p.h_out + size_t(m) * p.ldh + n, ldf(p.next_w + n) * v);
         }
         norm_s[r * MB + m] = v * v;
       }
@@ -474,8 +382,9 @@ gemm_stream_kernel(StreamParams p) {
       for (int e = tid; e < 8 * MB; e += kConsumerThreads) {
         const int pr = e / MB, m = e - pr * MB;
         if (m >= p.M) continue;
-        const float xa = Store<bf16>::round(total_of(pr, m));       // what the plain product stores
-        const float xb = Store<bf16>::round(total_of(pr + 8, m));
+        const float r = SCALED ? norm_s[m] : 1.f;
+        const float xa = Store<bf16>::round(total_of(pr, m) * r);   // what the plain product stores
+        const float xb = Store<bf16>::round(total_of(pr + 8, m) * r);
         if constexpr (EPI == kSiluMul) {
           const float sl = Store<bf16>::round(xa / (1.f + expf(-xa)));
           stf(Y + size_t(m) * p.ldy + 8 * tile + pr, sl * xb);
@@ -533,14 +442,9 @@ static int stream_chunk(int MT, int K) {
 // X straight from L2 (no staging): every block has one tile and K is longer than a whole-row stage.
 static bool stream_direct(int N, int K, int sm_count) { return (N + 15) / 16 <= sm_count && K > kChunkLong; }
 
-// Blocks that share the staging of a normed X of M rows (measured on the 1.1B shape, a decode step:
-// 2 rows 881 us alone, 842 in pairs, 876 in fours; 8 rows 970 / 937 / 958; 16 rows 1356 / 1268 / 1246,
-// eight 1206).
-static int norm_cluster_for(int M) { return M <= 1 ? 1 : (M <= 8 ? 2 : 8); }
-
-template <int MT, typename OutT, int EPI, bool XDIRECT, bool NORMX = false>
+template <int MT, typename OutT, int EPI, bool XDIRECT, bool SCALED = false>
 int launch_stream_as(StreamParams p, int sm_count, cudaStream_t s) {
-  auto kernel = gemm_stream_kernel<MT, OutT, EPI, XDIRECT, NORMX>;
+  auto kernel = gemm_stream_kernel<MT, OutT, EPI, XDIRECT, SCALED>;
   const int tiles = (p.N + 15) / 16;
   const int chunk = XDIRECT ? kChunkShort : stream_chunk(MT, p.K);
   if (chunk == 0) return KVCM_ERR_UNSUPPORTED;
@@ -566,32 +470,6 @@ int launch_stream_as(StreamParams p, int sm_count, cudaStream_t s) {
     configured = smem;
   }
   p.stages = stages;
-  if constexpr (NORMX) {
-    // Blocks of a cluster share the staging of X (each norms a share of the columns for all): what
-    // every block reads of the residual shrinks with the cluster.  The grid is a whole number of
-    // clusters, no more than run at once.
-    int nc = g_norm_cluster > 0 ? g_norm_cluster : norm_cluster_for(p.M);
-    while (nc > 1 && ((Kc * chunk / 8) % nc || blocks < nc)) nc >>= 1;
-    if (nc > 1) {
-      static int fit[9][2] = {};                        // clusters of nc that run at once, for the shared memory asked
-      if (fit[nc][1] != int(smem)) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(nc * 1024); cfg.blockDim = dim3(kStreamThreads); cfg.dynamicSmemBytes = smem;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = nc; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
-        fit[nc][0] = n; fit[nc][1] = int(smem);
-      }
-      const int most = fit[nc][0] * nc;
-      if (most >= nc) {
-        blocks = min((blocks + nc - 1) / nc * nc, most);
-        return pdl_launch_cluster(kernel, dim3(blocks), dim3(kStreamThreads), smem, s, nc, p);
-      }
-    }
-  }
   return pdl_launch(kernel, dim3(blocks), dim3(kStreamThreads), smem, s, p);
 }
 
@@ -600,7 +478,7 @@ int launch_stream(StreamParams p, int sm_count, cudaStream_t s) {
   if constexpr (EPI == kStore || EPI == kResidual) {
     if (stream_direct(p.N, p.K, sm_count)) return launch_stream_as<MT, OutT, EPI, true>(p, sm_count, s);
   } else {
-    if (p.xf != nullptr) return launch_stream_as<MT, OutT, EPI, false, true>(p, sm_count, s);
+    if (p.ss_in != nullptr) return launch_stream_as<MT, OutT, EPI, false, true>(p, sm_count, s);
   }
   return launch_stream_as<MT, OutT, EPI, false>(p, sm_count, s);
 }
@@ -643,42 +521,45 @@ KVCM_API int kvcm_gemm_stream_bf16(const void* X, const void* W, void* Y, int M,
   return out_f32 ? launch_stream<2, float, kStore>(p, sm_count, s) : launch_stream<2, bf16, kStore>(p, sm_count, s);
 }
 
-// The product that ends a sublayer: resid[M, N] (float, in place) += round_bf16(X * W^T), and
+// The product that ends a sublayer: resid[M, N] (float, in place) += round_bf16(X * W^T);
 // ss_out[tile][m] (tile = 16 columns, kNormRows floats apart) = the tile's share of the sum of
-// squares of the new residual row m.  ss_out holds ceil(N / 16) * 16 floats.
-KVCM_API int kvcm_gemm_stream_residual_bf16(const void* X, const void* W, float* resid, float* ss_out, int M, int N,
-                                            int K, int ldx, int ldw, int ldr, int sm_count, void* stream) {
+// squares of the new residual row m (ss_out holds ceil(N / 16) * 16 floats); and, where next_w is
+// given, h_out[M, N] = bfloat16(next_w[n] * resid[m][n]): the row the next norm hands on, before
+// its scale.
+KVCM_API int kvcm_gemm_stream_residual_bf16(const void* X, const void* W, float* resid, float* ss_out, void* h_out,
+                                            const void* next_w, int M, int N, int K, int ldx, int ldw, int ldr,
+                                            int ldh, int sm_count, void* stream) {
   if (M == 0 || N == 0) return 0;
   if (!stream_ok(M, N, K, sm_count, true) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
+  if (resid == nullptr || ss_out == nullptr || (next_w != nullptr && h_out == nullptr)) return KVCM_ERR_UNSUPPORTED;
   StreamParams p = {};
   p.W = (const bf16*)W; p.N = N; p.K = K; p.ldw = ldw; p.X = (const bf16*)X; p.ldx = ldx; p.M = M;
-  p.resid = resid; p.ldr = ldr; p.ss_out = ss_out;
+  p.resid = resid; p.ldr = ldr; p.ss_out = ss_out; p.h_out = (bf16*)h_out; p.ldh = ldh; p.next_w = (const bf16*)next_w;
   p.pair_blocks = 1; p.group_stride = 16; p.pair_offset = 8;
   cudaStream_t s = (cudaStream_t)stream;
   return M <= 8 ? launch_stream<1, bf16, kResidual>(p, sm_count, s) : launch_stream<2, bf16, kResidual>(p, sm_count, s);
 }
 
-// Whether X of a fused product can be made from the float residual (see StreamParams).
-static bool normed_ok(const float* xf, int ldxf, const float* ss_in, int ss_tiles, const void* norm_w) {
-  return xf != nullptr && ss_in != nullptr && norm_w != nullptr && ss_tiles > 0 && (ldxf % 4) == 0 &&
-         ((reinterpret_cast<uintptr_t>(xf) | reinterpret_cast<uintptr_t>(norm_w)) & 15) == 0;
-}
-
 // Fused decode step of an attention layer's input side: qkv = X * Wqkv^T, rotary encoding of the q
 // and k heads (rotate-half pairing over the whole head), q written to Y [M, >= nh*hd], k and v
 // written into the rows' cache page slots.  Needs hd a multiple of 16.
-static int qkv_rope_cache(const void* X, int ldx, const float* xf, int ldxf, const float* ss_in, int ss_tiles,
-                          const void* norm_w, float eps, const void* Wqkv, void* Yq, int M, int K, int ldw, int ldy,
-                          const int* positions, const float* inv_freq, const int* slot_mapping, void* k_cache,
-                          void* v_cache, int nh, int nkv, int hd, int block_size, int sm_count, void* stream) {
+// With ss_in (ss_tiles x kNormRows floats as kvcm_gemm_stream_residual_bf16 leaves them): row m of
+// the product is scaled by rsqrt(sum of ss_in[.][m] / K + eps) first -- X is then a normed row
+// before its scale, and this is the norm in front of the attention layer.
+KVCM_API int kvcm_qkv_rope_cache_scaled_bf16(const void* X, const float* ss_in, int ss_tiles, float eps,
+                                             const void* Wqkv, void* Yq, int M, int K, int ldx, int ldw, int ldy,
+                                             const int* positions, const float* inv_freq, const int* slot_mapping,
+                                             void* k_cache, void* v_cache, int nh, int nkv, int hd, int block_size,
+                                             int sm_count, void* stream) {
   const int N = (nh + 2 * nkv) * hd;
   if (M == 0) return 0;
   if ((hd % 16) || !stream_ok(M, N, K, sm_count, false) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(Wqkv) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
+  if (ss_in != nullptr && ss_tiles <= 0) return KVCM_ERR_UNSUPPORTED;
   StreamParams p = {};
   p.W = (const bf16*)Wqkv; p.N = N; p.K = K; p.ldw = ldw; p.X = (const bf16*)X; p.ldx = ldx; p.M = M;
-  p.xf = xf; p.ldxf = ldxf; p.ss_in = ss_in; p.ss_tiles = ss_tiles; p.norm_w = (const bf16*)norm_w; p.eps = eps;
+  p.ss_in = ss_in; p.ss_tiles = ss_tiles; p.eps = eps;
   p.Y = Yq; p.ldy = ldy;
   p.pair_blocks = hd / 16; p.group_stride = hd; p.pair_offset = hd / 2;
   p.positions = positions; p.inv_freq = inv_freq; p.slot_mapping = slot_mapping;
@@ -692,34 +573,23 @@ KVCM_API int kvcm_qkv_rope_cache_bf16(const void* X, const void* Wqkv, void* Yq,
                                       int ldy, const int* positions, const float* inv_freq,
                                       const int* slot_mapping, void* k_cache, void* v_cache, int nh, int nkv,
                                       int hd, int block_size, int sm_count, void* stream) {
-  return qkv_rope_cache(X, ldx, nullptr, 0, nullptr, 0, nullptr, 0.f, Wqkv, Yq, M, K, ldw, ldy, positions, inv_freq,
-                        slot_mapping, k_cache, v_cache, nh, nkv, hd, block_size, sm_count, stream);
-}
-
-// The same with X = norm_w * round(xf * rsqrt(sum of ss_in over the tiles / K + eps)): the norm in
-// front of the attention layer computed while X is staged (xf [M, ldxf] float, ss_in as
-// kvcm_gemm_stream_residual_bf16 writes it, norm_w [K] bfloat16).
-KVCM_API int kvcm_qkv_rope_cache_norm_bf16(const float* xf, int ldxf, const float* ss_in, int ss_tiles,
-                                           const void* norm_w, float eps, const void* Wqkv, void* Yq, int M, int K,
-                                           int ldw, int ldy, const int* positions, const float* inv_freq,
-                                           const int* slot_mapping, void* k_cache, void* v_cache, int nh, int nkv,
-                                           int hd, int block_size, int sm_count, void* stream) {
-  if (!normed_ok(xf, ldxf, ss_in, ss_tiles, norm_w)) return KVCM_ERR_UNSUPPORTED;
-  return qkv_rope_cache(Wqkv, 8, xf, ldxf, ss_in, ss_tiles, norm_w, eps, Wqkv, Yq, M, K, ldw, ldy, positions, inv_freq,
-                        slot_mapping, k_cache, v_cache, nh, nkv, hd, block_size, sm_count, stream);
+  return kvcm_qkv_rope_cache_scaled_bf16(X, nullptr, 0, 0.f, Wqkv, Yq, M, K, ldx, ldw, ldy, positions, inv_freq,
+                                         slot_mapping, k_cache, v_cache, nh, nkv, hd, block_size, sm_count, stream);
 }
 
 // Fused input side of a gated feed-forward: act[M, I] = silu(X Wg^T) * (X Wu^T) with Wg, Wu the
-// two halves of W [2I, K] (gate rows first).  Needs I a multiple of 8.
-static int gate_up_silu(const void* X, int ldx, const float* xf, int ldxf, const float* ss_in, int ss_tiles,
-                        const void* norm_w, float eps, const void* W, void* Y, int M, int I, int K, int ldw, int ldy,
-                        int sm_count, void* stream) {
+// two halves of W [2I, K] (gate rows first).  Needs I a multiple of 8.  With ss_in: both products
+// scaled per row first (see kvcm_qkv_rope_cache_scaled_bf16): the norm in front of the feed-forward.
+KVCM_API int kvcm_gate_up_silu_scaled_bf16(const void* X, const float* ss_in, int ss_tiles, float eps, const void* W,
+                                           void* Y, int M, int I, int K, int ldx, int ldw, int ldy, int sm_count,
+                                           void* stream) {
   if (M == 0) return 0;
   if ((I % 8) || !stream_ok(M, 2 * I, K, sm_count, false) || (ldw % 8) || (ldx % 8)) return KVCM_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15)) return KVCM_ERR_UNSUPPORTED;
+  if (ss_in != nullptr && ss_tiles <= 0) return KVCM_ERR_UNSUPPORTED;
   StreamParams p = {};
   p.W = (const bf16*)W; p.N = 2 * I; p.K = K; p.ldw = ldw; p.X = (const bf16*)X; p.ldx = ldx; p.M = M;
-  p.xf = xf; p.ldxf = ldxf; p.ss_in = ss_in; p.ss_tiles = ss_tiles; p.norm_w = (const bf16*)norm_w; p.eps = eps;
+  p.ss_in = ss_in; p.ss_tiles = ss_tiles; p.eps = eps;
   p.Y = Y; p.ldy = ldy;
   p.pair_blocks = I / 8; p.group_stride = 0; p.pair_offset = I;
   cudaStream_t s = (cudaStream_t)stream;
@@ -728,16 +598,7 @@ static int gate_up_silu(const void* X, int ldx, const float* xf, int ldxf, const
 
 KVCM_API int kvcm_gate_up_silu_bf16(const void* X, const void* W, void* Y, int M, int I, int K, int ldx, int ldw,
                                     int ldy, int sm_count, void* stream) {
-  return gate_up_silu(X, ldx, nullptr, 0, nullptr, 0, nullptr, 0.f, W, Y, M, I, K, ldw, ldy, sm_count, stream);
-}
-
-// The same with X made from the float residual and the partial sums of squares (see
-// kvcm_qkv_rope_cache_norm_bf16): the norm in front of the feed-forward.
-KVCM_API int kvcm_gate_up_silu_norm_bf16(const float* xf, int ldxf, const float* ss_in, int ss_tiles,
-                                         const void* norm_w, float eps, const void* W, void* Y, int M, int I, int K,
-                                         int ldw, int ldy, int sm_count, void* stream) {
-  if (!normed_ok(xf, ldxf, ss_in, ss_tiles, norm_w)) return KVCM_ERR_UNSUPPORTED;
-  return gate_up_silu(W, 8, xf, ldxf, ss_in, ss_tiles, norm_w, eps, W, Y, M, I, K, ldw, ldy, sm_count, stream);
+  return kvcm_gate_up_silu_scaled_bf16(X, nullptr, 0, 0.f, W, Y, M, I, K, ldx, ldw, ldy, sm_count, stream);
 }
 
 // The fused products (rotary/cache and gate/up epilogues) of these sizes: X is always staged there.
@@ -747,13 +608,6 @@ KVCM_API int kvcm_gemm_stream_fused_supports(int M, int N, int K) { return strea
 KVCM_API const int* kvcm_stream_error_address(void) {
   int* p = nullptr;
   return cudaGetSymbolAddress((void**)&p, g_stream_error) == cudaSuccess ? p : nullptr;
-}
-
-// Forces the number of blocks that share the staging of a normed X (1, 2, 4, 8; 0 = chosen by the rows).
-KVCM_API int kvcm_stream_norm_cluster(int blocks) {
-  if (blocks != 0 && blocks != 1 && blocks != 2 && blocks != 4 && blocks != 8) return KVCM_ERR_UNSUPPORTED;
-  g_norm_cluster = blocks;
-  return 0;
 }
 
 // Test hooks of the failure path: the wait limit (0 = the default of two seconds) and the stage

@@ -57,11 +57,12 @@ int kvcm_qkv_rope_cache_bf16(const void*, const void*, void*, int, int, int, int
                              void*, void*, int, int, int, int, int, void*);
 int kvcm_gate_up_silu_bf16(const void*, const void*, void*, int, int, int, int, int, int, int, void*);
 int kvcm_gemm_tcgen05_supports(int, int, int, int, int);
-int kvcm_gemm_stream_residual_bf16(const void*, const void*, float*, float*, int, int, int, int, int, int, int, void*);
-int kvcm_qkv_rope_cache_norm_bf16(const float*, int, const float*, int, const void*, float, const void*, void*, int, int, int,
-                                  int, const int*, const float*, const int*, void*, void*, int, int, int, int, int, void*);
-int kvcm_gate_up_silu_norm_bf16(const float*, int, const float*, int, const void*, float, const void*, void*, int, int, int,
-                                int, int, int, void*);
+int kvcm_gemm_stream_residual_bf16(const void*, const void*, float*, float*, void*, const void*, int, int, int, int, int, int,
+                                   int, int, void*);
+int kvcm_qkv_rope_cache_scaled_bf16(const void*, const float*, int, float, const void*, void*, int, int, int, int, int,
+                                    const int*, const float*, const int*, void*, void*, int, int, int, int, int, void*);
+int kvcm_gate_up_silu_scaled_bf16(const void*, const float*, int, float, const void*, void*, int, int, int, int, int, int, int,
+                                  void*);
 int kvcm_gate_up_silu_tcgen05_bf16(const void*, const void*, void*, int, int, int, int, int, int, void*);
 }
 
@@ -72,12 +73,9 @@ constexpr long long kStreamMaxBytes = 32ll << 20;       // parts/linear.py: STRE
 constexpr int kTcgen05MinRows = 256;                    // TCGEN05_MIN_ROWS
 constexpr int kTcgen05GatedMaxHidden = 3072;            // TCGEN05_GATED_MAX_HIDDEN
 constexpr int kKeyTile = 64;
-// Most rows of a step whose norms ride in its products.  Every block of the product that follows
-// has to read the float residual of all rows where it read the normed bfloat16 rows before; that
-// costs more than the two launches a layer it saves from three rows on (a decode step of the 1.1B
-// shape: 1 row 881 -> 821 us, 2 rows 891 -> 842, 4 rows 892 -> 894, 8 rows 914 -> 937,
-// 16 rows 1179 -> 1206).
-constexpr int kNormRideMaxRows = 2;
+// Most rows of a step whose norms ride in its products (a decode step of the 1.1B shape, with and
+// without: 1 row 881 -> 809 us, 4 rows 902 -> 837, 8 rows 916 -> 869, 16 rows 1171 -> 1180).
+constexpr int kNormRideMaxRows = 8;
 
 }  // namespace
 
@@ -213,26 +211,32 @@ KVCM_API int kvcm_forward(const KvcmForwardArgs* ap, int* launches, void* stream
   const auto rope_cache = a.f32 ? kvcm_rope_cache_f32 : kvcm_rope_cache_bf16;
   const auto silu_mul = a.f32 ? kvcm_silu_mul_f32 : kvcm_silu_mul_bf16;
 
-  // A handful of rows: the products that end a sublayer add into the residual themselves and leave
-  // partial sums of squares, the products that begin the next one take their norm from those.
+  // A handful of rows: the products that end a sublayer add into the residual themselves, leave
+  // partial sums of squares and the next norm's row before its scale (a.h); the products that
+  // begin the next sublayer scale their sums by the norm's 1/rms.  No norm launches between them.
   const int ss_tiles = (H + 15) / 16;
   const auto streams = [&](int N, int K) {
     return (T <= 8 || (long long)N * K * 2 <= kStreamMaxBytes) && kvcm_gemm_stream_supports(T, N, K);
   };
   const bool ride = !a.f32 && a.norm_partials != nullptr && a.norm_partials_floats >= (long long)ss_tiles * 16 &&
-                    T <= kNormRideMaxRows && (H % 8) == 0 && streams(H, QK) && streams(H, I);
+                    T <= kNormRideMaxRows && streams(H, QK) && streams(H, I);
+  const bool gate_fused = !a.f32 && (I % 8) == 0 && kvcm_gemm_stream_fused_supports(T, 2 * I, H);
+  const auto qkv_fused = [&](const KvcmForwardLayer& L) {
+    return !a.f32 && L.writes && (a.hd % 16) == 0 && kvcm_gemm_stream_fused_supports(T, QKV, H);
+  };
 
   KVCM_TRY(embed(a.tokens, a.embed, a.x, T, H, a.V, s)); ++n;
   const void* pending = nullptr;                        // a sublayer's result not yet added to the residual
-  bool partials = false;                                // norm_partials describes the residual as it stands
-  // ends a sublayer: x += y w^T, one way or the other
-  const auto close_sublayer = [&](const void* y, const void* w, int K) {
+  bool handed = false;                                  // a.h and norm_partials hold the next norm's row before its scale
+  // ends a sublayer: x += y w^T, one way or the other (next_norm: the norm weight of the product
+  // that follows, where that product takes the scaled form)
+  const auto close_sublayer = [&](const void* y, const void* w, int K, const void* next_norm) {
+    pending = nullptr;
+    handed = false;
     if (ride) {
-      partials = true;
-      pending = nullptr;
-      return kvcm_gemm_stream_residual_bf16(y, w, a.x, a.norm_partials, T, H, K, K, K, H, a.sm_count, s);
+      handed = next_norm != nullptr;
+      return kvcm_gemm_stream_residual_bf16(y, w, a.x, a.norm_partials, a.h, next_norm, T, H, K, K, K, H, H, a.sm_count, s);
     }
-    partials = false;
     pending = a.proj;
     return product(a, y, w, a.proj, T, H, K, false, s);
   };
@@ -242,49 +246,36 @@ KVCM_API int kvcm_forward(const KvcmForwardArgs* ap, int* launches, void* stream
     // attention: qkv product, rotary encoding, cache write -- one kernel for a handful of rows
     const void* q = a.qkv;
     int q_stride = QKV;
-    const bool qkv_fused = !a.f32 && L.writes && (a.hd % 16) == 0 && kvcm_gemm_stream_fused_supports(T, QKV, H);
-    if (qkv_fused && partials) {
-      KVCM_TRY(kvcm_qkv_rope_cache_norm_bf16(a.x, H, a.norm_partials, ss_tiles, L.norm1, L.eps1, L.w_qkv, a.qkv, T, H, H, QK,
-                                             a.positions, a.inv_freq, a.group_slots[L.group], L.k_cache, L.v_cache, a.nh,
-                                             a.nkv, a.hd, a.block_size, a.sm_count, s));
+    if (!handed) { KVCM_TRY(rmsnorm(a.x, pending, L.norm1, 0, a.h, nullptr, T, H, L.eps1, s)); ++n; }
+    if (qkv_fused(L)) {
+      KVCM_TRY(kvcm_qkv_rope_cache_scaled_bf16(a.h, handed ? a.norm_partials : nullptr, ss_tiles, L.eps1, L.w_qkv, a.qkv, T, H,
+                                               H, H, QK, a.positions, a.inv_freq, a.group_slots[L.group], L.k_cache,
+                                               L.v_cache, a.nh, a.nkv, a.hd, a.block_size, a.sm_count, s));
       ++n;
       q_stride = QK;
     } else {
-      KVCM_TRY(rmsnorm(a.x, pending, L.norm1, 0, a.h, nullptr, T, H, L.eps1, s)); ++n;
-      if (qkv_fused) {
-        KVCM_TRY(kvcm_qkv_rope_cache_bf16(a.h, L.w_qkv, a.qkv, T, H, H, H, QK, a.positions, a.inv_freq,
-                                          a.group_slots[L.group], L.k_cache, L.v_cache, a.nh, a.nkv, a.hd, a.block_size,
-                                          a.sm_count, s));
-        ++n;
-        q_stride = QK;
-      } else {
-        KVCM_TRY(product(a, a.h, L.w_qkv, a.qkv, T, QKV, H, false, s)); ++n;
-        KVCM_TRY(rope_cache(a.qkv, QKV, a.positions, a.inv_freq, a.hd, 0, a.group_slots[L.group], L.k_cache, L.v_cache, T,
-                            a.nh, a.nkv, a.hd, a.block_size, L.writes, s));
-        ++n;
-      }
+      KVCM_TRY(product(a, a.h, L.w_qkv, a.qkv, T, QKV, H, false, s)); ++n;
+      KVCM_TRY(rope_cache(a.qkv, QKV, a.positions, a.inv_freq, a.hd, 0, a.group_slots[L.group], L.k_cache, L.v_cache, T,
+                          a.nh, a.nkv, a.hd, a.block_size, L.writes, s));
+      ++n;
     }
     KVCM_TRY(attention(a, L, q, q_stride, n, s));
-    KVCM_TRY(close_sublayer(a.attn, L.w_o, QK)); ++n;
+    KVCM_TRY(close_sublayer(a.attn, L.w_o, QK, gate_fused ? L.norm2 : nullptr)); ++n;
     // feed-forward: gate/up product and activation -- one kernel where one exists for the shape
-    const bool gate_fused = !a.f32 && (I % 8) == 0 && kvcm_gemm_stream_fused_supports(T, 2 * I, H);
-    if (gate_fused && partials) {
-      KVCM_TRY(kvcm_gate_up_silu_norm_bf16(a.x, H, a.norm_partials, ss_tiles, L.norm2, L.eps2, L.w_gate_up, a.act, T, I, H, H,
-                                           I, a.sm_count, s));
+    if (!handed) { KVCM_TRY(rmsnorm(a.x, pending, L.norm2, 0, a.h, nullptr, T, H, L.eps2, s)); ++n; }
+    if (gate_fused) {
+      KVCM_TRY(kvcm_gate_up_silu_scaled_bf16(a.h, handed ? a.norm_partials : nullptr, ss_tiles, L.eps2, L.w_gate_up, a.act, T,
+                                             I, H, H, H, I, a.sm_count, s));
       ++n;
+    } else if (!a.f32 && T >= kTcgen05MinRows && tiles_fill_well(T, 2 * I, a.sm_count) && H <= kTcgen05GatedMaxHidden &&
+               kvcm_gemm_tcgen05_supports(T, 2 * I, H, H, H)) {
+      KVCM_TRY(kvcm_gate_up_silu_tcgen05_bf16(a.h, L.w_gate_up, a.act, T, I, H, H, H, I, s)); ++n;
     } else {
-      KVCM_TRY(rmsnorm(a.x, pending, L.norm2, 0, a.h, nullptr, T, H, L.eps2, s)); ++n;
-      if (gate_fused) {
-        KVCM_TRY(kvcm_gate_up_silu_bf16(a.h, L.w_gate_up, a.act, T, I, H, H, H, I, a.sm_count, s)); ++n;
-      } else if (!a.f32 && T >= kTcgen05MinRows && tiles_fill_well(T, 2 * I, a.sm_count) && H <= kTcgen05GatedMaxHidden &&
-                 kvcm_gemm_tcgen05_supports(T, 2 * I, H, H, H)) {
-        KVCM_TRY(kvcm_gate_up_silu_tcgen05_bf16(a.h, L.w_gate_up, a.act, T, I, H, H, H, I, s)); ++n;
-      } else {
-        KVCM_TRY(product(a, a.h, L.w_gate_up, a.gate_up, T, 2 * I, H, false, s)); ++n;
-        KVCM_TRY(silu_mul(a.gate_up, a.act, T, I, s)); ++n;
-      }
+      KVCM_TRY(product(a, a.h, L.w_gate_up, a.gate_up, T, 2 * I, H, false, s)); ++n;
+      KVCM_TRY(silu_mul(a.gate_up, a.act, T, I, s)); ++n;
     }
-    KVCM_TRY(close_sublayer(a.act, L.w_down, I)); ++n;
+    const bool next_takes = l + 1 < a.num_layers && qkv_fused(a.layers[l + 1]);
+    KVCM_TRY(close_sublayer(a.act, L.w_down, I, next_takes ? a.layers[l + 1].norm1 : nullptr)); ++n;
   }
   if (a.num_logits > 0) {
     KVCM_TRY(rmsnorm(a.x, pending, a.final_norm, 0, a.h_last, a.logit_rows, a.num_logits, H, a.final_eps, s)); ++n;

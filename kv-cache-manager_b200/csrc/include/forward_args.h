@@ -25,7 +25,7 @@ struct KvcmForwardArgs {
   // buffers of the caller, sized for the step: x [T,H] float; h, proj [T,H]; qkv [T,QKV]; attn [T,nh*hd];
   // gate_up [T,2I]; act [T,I]; h_last [L,H]; logits [L,V] float; attn_scratch floats; a library workspace;
   // norm_partials: ceil(H/16)*16 floats, or null = every norm is a launch of its own (with it, a step
-  // of one or two rows adds the residual and takes the norms inside its products)
+  // of at most 8 rows adds the residual and takes the norms inside its products)
   float* x; void* h; void* qkv; void* attn; void* proj; void* gate_up; void* act; void* h_last; float* logits;
   float* attn_scratch; void* lib_workspace; float* norm_partials;
   long long attn_scratch_floats, lib_workspace_bytes, norm_partials_floats;

@@ -530,11 +530,16 @@ def stream_error() -> int:
 
 def qkv_rope_cache(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
                    inv_freq: torch.Tensor, slot_mapping: torch.Tensor, k_cache: torch.Tensor,
-                   v_cache: torch.Tensor, nh: int, nkv: int, hd: int) -> None:
+                   v_cache: torch.Tensor, nh: int, nkv: int, hd: int,
+                   partials: Optional[torch.Tensor] = None, eps: float = 0.0) -> None:
     """Fused decode kernel: qkv product (M <= 16), rotate-half rotary encoding over the whole head,
     q into ``q_out`` [M, nh*hd], k (rotated) and v into the rows' cache page slots.  Gives the same
-    bits as ``gemm_stream`` followed by ``rope_cache``."""
-    _cuda(x, w_qkv, q_out, positions, inv_freq, slot_mapping, k_cache, v_cache)
+    bits as ``gemm_stream`` followed by ``rope_cache``.  With ``partials`` (float32 [tiles, 16] as
+    ``gemm_stream_residual`` leaves them) row m of the product is first scaled by
+    rsqrt(sum(partials[:, m]) / K + eps): ``x`` is then a normed row before its scale."""
+    _cuda(x, w_qkv, q_out, positions, inv_freq, slot_mapping, k_cache, v_cache, partials)
+    _need(partials is None or (partials.dtype == torch.float32 and partials.is_contiguous() and partials.dim() == 2
+                               and partials.shape[1] == 16), "qkv_rope_cache: partials float32 [tiles, 16]")
     M, K = x.shape
     _need(w_qkv.shape == ((nh + 2 * nkv) * hd, K) and q_out.shape[0] == M and q_out.shape[1] >= nh * hd,
           "qkv_rope_cache: shapes")
@@ -546,18 +551,23 @@ def qkv_rope_cache(x: torch.Tensor, w_qkv: torch.Tensor, q_out: torch.Tensor, po
     _need(positions.dtype == _I32 and slot_mapping.dtype == _I32 and positions.numel() >= M
           and slot_mapping.numel() >= M, "qkv_rope_cache: positions/slot_mapping int32 [M]")
     _need(inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == hd, "qkv_rope_cache: inv_freq float32 [hd/2]")
-    rc = _lib().kvcm_qkv_rope_cache_bf16(_p(x), _p(w_qkv), _p(q_out), M, K, x.stride(0), w_qkv.stride(0),
-                                         q_out.stride(0), _p(positions), _p(inv_freq), _p(slot_mapping),
-                                         _p(k_cache), _p(v_cache), nh, nkv, hd, k_cache.shape[2],
-                                         sm_count(x.device), _stream())
+    rc = _lib().kvcm_qkv_rope_cache_scaled_bf16(_p(x), _p(partials) if partials is not None else None,
+                                                partials.shape[0] if partials is not None else 0, ctypes.c_float(eps),
+                                                _p(w_qkv), _p(q_out), M, K, x.stride(0), w_qkv.stride(0),
+                                                q_out.stride(0), _p(positions), _p(inv_freq), _p(slot_mapping),
+                                                _p(k_cache), _p(v_cache), nh, nkv, hd, k_cache.shape[2],
+                                                sm_count(x.device), _stream())
     _check(rc, "qkv_rope_cache", f"(M={M}, K={K}, nh={nh}, nkv={nkv}, hd={hd})")
 
 
-def gemm_stream_residual(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, partials: torch.Tensor) -> None:
-    """The product that ends a sublayer (M <= 16): resid[M,N] (float32, in place) += bfloat16(x @ w^T), and
+def gemm_stream_residual(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, partials: torch.Tensor,
+                         h_out: Optional[torch.Tensor] = None, next_w: Optional[torch.Tensor] = None) -> None:
+    """The product that ends a sublayer (M <= 16): resid[M,N] (float32, in place) += bfloat16(x @ w^T);
     partials[t, m] = the sum over columns 16t..16t+15 of the new resid[m]^2 (``partials`` float32
-    [ceil(N/16), 16]): what the norm in front of the next sublayer needs."""
-    _cuda(x, w, resid, partials)
+    [ceil(N/16), 16]); and with ``next_w`` (bfloat16 [N]) h_out[M,N] = bfloat16(next_w * resid): the row
+    the next norm hands on before its scale, which the ``partials`` argument of ``qkv_rope_cache`` and
+    ``gate_up_silu`` applies."""
+    _cuda(x, w, resid, partials, h_out, next_w)
     M, K = x.shape
     N = w.shape[0]
     _need(w.shape[1] == K and resid.shape == (M, N), "gemm_stream_residual: shapes")
@@ -565,77 +575,38 @@ def gemm_stream_residual(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, 
           "gemm_stream_residual: bfloat16 operands, float32 residual and partial sums")
     _need(x.stride(1) == 1 and w.stride(1) == 1 and resid.stride(1) == 1, "gemm_stream_residual: rows must be dense")
     _need(partials.is_contiguous() and tuple(partials.shape) == ((N + 15) // 16, 16), "gemm_stream_residual: partials [ceil(N/16), 16]")
-    rc = _lib().kvcm_gemm_stream_residual_bf16(_p(x), _p(w), _p(resid), _p(partials), M, N, K, x.stride(0), w.stride(0),
-                                               resid.stride(0), sm_count(x.device), _stream())
+    _need((h_out is None) == (next_w is None), "gemm_stream_residual: h_out and next_w go together")
+    if next_w is not None:
+        _need(h_out.dtype == next_w.dtype == torch.bfloat16 and h_out.shape == (M, N) and h_out.stride(1) == 1
+              and next_w.numel() == N and next_w.is_contiguous(), "gemm_stream_residual: h_out [M,N], next_w [N] bfloat16")
+    rc = _lib().kvcm_gemm_stream_residual_bf16(_p(x), _p(w), _p(resid), _p(partials),
+                                               _p(h_out) if h_out is not None else None,
+                                               _p(next_w) if next_w is not None else None, M, N, K, x.stride(0),
+                                               w.stride(0), resid.stride(0), h_out.stride(0) if h_out is not None else 0,
+                                               sm_count(x.device), _stream())
     _check(rc, "gemm_stream_residual", f"(M={M}, N={N}, K={K})")
-
-
-def stream_norm_cluster(blocks: int = 0) -> None:
-    """Forces how many blocks of a thread-block cluster share the staging of a normed X in
-    ``qkv_rope_cache_norm`` and ``gate_up_silu_norm`` (1, 2, 4 or 8; 0 = chosen by the rows)."""
-    _check(_lib().kvcm_stream_norm_cluster(int(blocks)), "stream_norm_cluster", f"({blocks})")
-
-
-def qkv_rope_cache_norm(resid: torch.Tensor, partials: torch.Tensor, norm_w: torch.Tensor, eps: float,
-                        w_qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
-                        slot_mapping: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, nh: int, nkv: int,
-                        hd: int) -> None:
-    """``qkv_rope_cache`` of x = norm_w * bfloat16(resid * rsqrt(sum(partials[:, m]) / K + eps)): the
-    norm in front of the attention layer taken while x is staged (``resid`` float32 [M, K],
-    ``partials`` as ``gemm_stream_residual`` leaves them, ``norm_w`` bfloat16 [K])."""
-    _cuda(resid, partials, norm_w, w_qkv, q_out, positions, inv_freq, slot_mapping, k_cache, v_cache)
-    M, K = resid.shape
-    _need(w_qkv.shape == ((nh + 2 * nkv) * hd, K) and q_out.shape[0] == M and q_out.shape[1] >= nh * hd,
-          "qkv_rope_cache_norm: shapes")
-    _need(resid.dtype == partials.dtype == torch.float32 and norm_w.dtype == torch.bfloat16 and norm_w.numel() == K,
-          "qkv_rope_cache_norm: float32 residual and partial sums, bfloat16 norm weight [K]")
-    _need(w_qkv.dtype == q_out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16, "qkv_rope_cache_norm: bfloat16 only")
-    _need(resid.stride(1) == 1 and w_qkv.stride(1) == 1 and q_out.stride(1) == 1 and k_cache.is_contiguous()
-          and v_cache.is_contiguous() and partials.is_contiguous() and partials.shape[1] == 16, "qkv_rope_cache_norm: layout")
-    _need(tuple(k_cache.shape[1:]) == (nkv, k_cache.shape[2], hd), "qkv_rope_cache_norm: cache page shape")
-    _need(positions.dtype == _I32 and slot_mapping.dtype == _I32 and positions.numel() >= M
-          and slot_mapping.numel() >= M, "qkv_rope_cache_norm: positions/slot_mapping int32 [M]")
-    _need(inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == hd, "qkv_rope_cache_norm: inv_freq float32 [hd/2]")
-    rc = _lib().kvcm_qkv_rope_cache_norm_bf16(_p(resid), resid.stride(0), _p(partials), partials.shape[0], _p(norm_w),
-                                              ctypes.c_float(eps), _p(w_qkv), _p(q_out), M, K, w_qkv.stride(0),
-                                              q_out.stride(0), _p(positions), _p(inv_freq), _p(slot_mapping),
-                                              _p(k_cache), _p(v_cache), nh, nkv, hd, k_cache.shape[2],
-                                              sm_count(resid.device), _stream())
-    _check(rc, "qkv_rope_cache_norm", f"(M={M}, K={K}, nh={nh}, nkv={nkv}, hd={hd})")
-
-
-def gate_up_silu_norm(resid: torch.Tensor, partials: torch.Tensor, norm_w: torch.Tensor, eps: float,
-                      w_gate_up: torch.Tensor, act: torch.Tensor) -> None:
-    """``gate_up_silu`` of x = norm_w * bfloat16(resid * rsqrt(sum(partials[:, m]) / K + eps))."""
-    _cuda(resid, partials, norm_w, w_gate_up, act)
-    M, K = resid.shape
-    I = act.shape[1]
-    _need(w_gate_up.shape == (2 * I, K) and act.shape[0] == M, "gate_up_silu_norm: shapes")
-    _need(resid.dtype == partials.dtype == torch.float32 and norm_w.dtype == torch.bfloat16 and norm_w.numel() == K,
-          "gate_up_silu_norm: float32 residual and partial sums, bfloat16 norm weight [K]")
-    _need(w_gate_up.dtype == act.dtype == torch.bfloat16, "gate_up_silu_norm: bfloat16 only")
-    _need(resid.stride(1) == 1 and w_gate_up.stride(1) == 1 and act.stride(1) == 1 and partials.is_contiguous()
-          and partials.shape[1] == 16, "gate_up_silu_norm: layout")
-    rc = _lib().kvcm_gate_up_silu_norm_bf16(_p(resid), resid.stride(0), _p(partials), partials.shape[0], _p(norm_w),
-                                            ctypes.c_float(eps), _p(w_gate_up), _p(act), M, I, K, w_gate_up.stride(0),
-                                            act.stride(0), sm_count(resid.device), _stream())
-    _check(rc, "gate_up_silu_norm", f"(M={M}, I={I}, K={K})")
 
 
 def qkv_rope_cache_supported(M: int, K: int, nh: int, nkv: int, hd: int) -> bool:
     return hd % 16 == 0 and bool(_lib().kvcm_gemm_stream_fused_supports(int(M), int((nh + 2 * nkv) * hd), int(K)))
 
 
-def gate_up_silu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor) -> None:
-    """Fused decode kernel: act[M, I] = silu(x Wg^T) * (x Wu^T), Wg/Wu the halves of w [2I, K]."""
-    _cuda(x, w_gate_up, act)
+def gate_up_silu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor,
+                 partials: Optional[torch.Tensor] = None, eps: float = 0.0) -> None:
+    """Fused decode kernel: act[M, I] = silu(x Wg^T) * (x Wu^T), Wg/Wu the halves of w [2I, K].
+    ``partials``: both products scaled per row first, as in ``qkv_rope_cache``."""
+    _cuda(x, w_gate_up, act, partials)
+    _need(partials is None or (partials.dtype == torch.float32 and partials.is_contiguous() and partials.dim() == 2
+                               and partials.shape[1] == 16), "gate_up_silu: partials float32 [tiles, 16]")
     M, K = x.shape
     I = act.shape[1]
     _need(w_gate_up.shape == (2 * I, K) and act.shape[0] == M, "gate_up_silu: shapes")
     _need(x.dtype == w_gate_up.dtype == act.dtype == torch.bfloat16, "gate_up_silu: bfloat16 only")
     _need(x.stride(1) == 1 and w_gate_up.stride(1) == 1 and act.stride(1) == 1, "gate_up_silu: layout")
-    rc = _lib().kvcm_gate_up_silu_bf16(_p(x), _p(w_gate_up), _p(act), M, I, K, x.stride(0), w_gate_up.stride(0),
-                                       act.stride(0), sm_count(x.device), _stream())
+    rc = _lib().kvcm_gate_up_silu_scaled_bf16(_p(x), _p(partials) if partials is not None else None,
+                                              partials.shape[0] if partials is not None else 0, ctypes.c_float(eps),
+                                              _p(w_gate_up), _p(act), M, I, K, x.stride(0), w_gate_up.stride(0),
+                                              act.stride(0), sm_count(x.device), _stream())
     _check(rc, "gate_up_silu", f"(M={M}, I={I}, K={K})")
 
 

@@ -47,36 +47,42 @@ def engines():
     return cfg, out
 
 
-def near_plain(got, ref, what):
-    """bfloat16 engine against the plain implementation run with the same roundings of stored
-    tensors: the bound of the small-configuration tests (4 % of the logits' standard deviation at
-    ~10^4 elements) grown with the number of elements as the maximum of that many Gaussians grows,
-    and 1 % in the root mean square."""
-    got, ref = got.double().cpu(), ref.double().cpu()
-    assert got.shape == ref.shape and torch.isfinite(got).all(), what
-    std = ref.std().item()
-    d = got - ref
-    rms, worst = d.pow(2).mean().sqrt().item(), d.abs().max().item()
-    bound = 0.04 * math.sqrt(max(1.0, math.log(d.numel()) / math.log(1e4)))
-    assert rms <= 0.01 * std and worst <= bound * std, \
-        f"{what}: rms {rms / std:.4f}, max {worst / std:.4f} of std (bounds 0.01, {bound:.4f})"
+def _rms_max(d):
+    return d.pow(2).mean().sqrt().item(), d.abs().max().item()
 
 
-def same_cut(got, ref, what):
+def near_plain(got, rounded, exact, what):
+    """The bfloat16 engine against the plain implementation in float64, at the same places.
+    ``exact`` rounds nothing; ``rounded`` rounds every stored tensor to bfloat16 where the
+    reference's kernels round to their storage type, so ``rounded - exact`` is what the reference's
+    own arithmetic loses at this shape (about 1 % of the logits' standard deviation in the root mean
+    square), and that is the yardstick: the engine may lose as much (10 % more in the root mean square,
+    30 % more at the worst element, whose size varies from sample to sample), and it stays as close
+    to ``rounded`` as two evaluations that share no rounding at all would (sqrt 2 of the yardstick).
+    A real fault (a missed or wrong key, a stale page, a wrong tile) moves whole rows by the order of
+    the standard deviation itself."""
+    got, rounded, exact = got.double().cpu(), rounded.double().cpu(), exact.double().cpu()
+    assert got.shape == exact.shape and torch.isfinite(got).all(), what
+    ref_rms, ref_max = _rms_max(rounded - exact)
+    rms, worst = _rms_max(got - exact)
+    assert rms <= 1.1 * ref_rms and worst <= 1.3 * ref_max, \
+        f"{what}: from the exact logits rms {rms:.5f}, max {worst:.5f} (the reference's arithmetic: {ref_rms:.5f}, {ref_max:.5f})"
+    rms, worst = _rms_max(got - rounded)
+    assert rms <= math.sqrt(2.0) * ref_rms and worst <= math.sqrt(2.0) * 1.3 * ref_max, \
+        f"{what}: from the rounded logits rms {rms:.5f}, max {worst:.5f} (the reference's arithmetic: {ref_rms:.5f}, {ref_max:.5f})"
+
+
+def same_cut(got, other, rounded, exact, what):
     """Two ways of cutting the same work in bfloat16: what differs are roundings the paths do not
-    share (other kernels, other orders of summation), so the difference stays below one path's own
-    distance from float32 (~1 % of the logits' standard deviation in the root mean square).  For the
-    worst element the bound of the small-configuration tests (4 % at ~10^4 elements) grows with
-    the number of elements as the maximum of that many Gaussians does, by sqrt(ln N / ln 10^4)."""
-    import math
-    got, ref = got.double(), ref.double()
+    share (other kernels, other orders of summation, the norm applied before or after a product), so
+    they are no further apart than two evaluations that share no rounding at all: sqrt 2 of what
+    the reference's arithmetic loses at these places (see near_plain)."""
+    got, other = got.double().cpu(), other.double().cpu()
     assert torch.isfinite(got).all(), what
-    std = ref.std().item()
-    d = got - ref
-    rms, worst = d.pow(2).mean().sqrt().item(), d.abs().max().item()
-    bound = 0.04 * math.sqrt(max(1.0, math.log(d.numel()) / math.log(1e4)))
-    assert rms <= 0.01 * std and worst <= bound * std, \
-        f"{what}: rms {rms / std:.4f}, max {worst / std:.4f} of std (bounds 0.01, {bound:.4f})"
+    ref_rms, ref_max = _rms_max(rounded.double().cpu() - exact.double().cpu())
+    rms, worst = _rms_max(got - other)
+    assert rms <= math.sqrt(2.0) * ref_rms and worst <= math.sqrt(2.0) * 1.3 * ref_max, \
+        f"{what}: apart by rms {rms:.5f}, max {worst:.5f} (the reference's arithmetic: {ref_rms:.5f}, {ref_max:.5f})"
 
 
 def near_float32(got, ref, what):
@@ -104,7 +110,8 @@ def test_whole_portions_and_token_by_token(engines):
     helpers.assert_logits_close(ref, make["plain"](toks, None)[want], "float32",
                                 "true 32-bit path, whole prompt of 2,048")
     whole = make["bfloat16"]().step([dict(id="a", tokens=toks, want=want)])
-    near_plain(whole, plain, "whole prompt of 2,048 tokens")
+    exact = make["plain"](toks, None)[want]
+    near_plain(whole, plain, exact, "whole prompt of 2,048 tokens")
     near_float32(whole, ref, "whole prompt")
     r = make["bfloat16"]()
     got, at = [], 0
@@ -117,9 +124,9 @@ def test_whole_portions_and_token_by_token(engines):
     assert at == n - 32
     for t in range(at, n):                                           # ... the last 32 one by one
         got.append(r.step([dict(id="a", tokens=toks[t:t + 1], want=[0])]))
-    near_plain(torch.cat(got), plain, "portions, then token by token")
+    near_plain(torch.cat(got), plain, exact, "portions, then token by token")
     near_float32(torch.cat(got), ref, "portions, then token by token")
-    same_cut(torch.cat(got), whole, "portions, then token by token, against the whole prompt")
+    same_cut(torch.cat(got), whole, plain, exact, "portions, then token by token, against the whole prompt")
     from kvcm.kernels import library as K
     assert K.attention_tcgen05_error() == 0 and K.tcgen05_error() == 0 and K.stream_error() == 0
 
@@ -156,9 +163,30 @@ def test_mixed_batch(engines):
                 got[i].append(out[at:at + n])
             at += n
     for i in range(3):
-        near_plain(torch.cat(got[i]), make["plain"](seqs[i])[-20:], f"mixed, request {i}, against the plain implementation")
+        rounded, exact = make["plain"](seqs[i])[-20:], make["plain"](seqs[i], None)[-20:]
+        near_plain(torch.cat(got[i]), rounded, exact, f"mixed, request {i}, against the plain implementation")
         near_float32(torch.cat(got[i]), refs[i], f"mixed, request {i}")
-        same_cut(torch.cat(got[i]), alone[i], f"mixed, request {i}, against the request alone")
+        same_cut(torch.cat(got[i]), alone[i], rounded, exact, f"mixed, request {i}, against the request alone")
+
+
+def greedy_or_near_tie(prompts, run_a, run_b, plain, n):
+    """Every token of both runs is the plain implementation's greedy choice, or within a near-tie of
+    it.  The two runs need not agree to the bit (a padded batch and the batch itself take other
+    context partitions, and larger ones other library kernels), so where they part ways, the plain
+    logits must show a near-tie at that very place."""
+    for p, a, b in zip(prompts, run_a, run_b):
+        assert len(a) == n and len(b) == n
+        for o in ((a,) if a == b else (a, b)):
+            logits = plain(list(p) + list(o))
+            margin = 0.08 * logits.std().item()
+            for k, tok in enumerate(o):
+                row = logits[len(p) - 1 + k]
+                assert row.max().item() - row[tok].item() <= margin, (len(p), k, tok)
+        if a != b:
+            k = next(i for i in range(n) if a[i] != b[i])
+            row = plain(list(p) + list(a))[len(p) - 1 + k]
+            top = row.topk(2).values
+            assert (top[0] - top[1]).item() <= 0.08 * row.std().item(), f"runs part ways at a clear choice (token {k})"
 
 
 @pytest.mark.parametrize("batch", [24, 64])
@@ -178,17 +206,20 @@ def test_decode_batches_beyond_the_streaming_kernels(engines, batch):
         outs.append(r.step([dict(id=f"r{i}", tokens=[seqs[i][lens[i] + t]], want=[0]) for i in range(batch)]))
     for t in range(3):
         ref = torch.stack([make["plain"](seqs[i])[lens[i] + t] for i in range(batch)])
-        near_plain(outs[t], ref, f"decode step {t} of {batch} requests")
+        exact = torch.stack([make["plain"](seqs[i], None)[lens[i] + t] for i in range(batch)])
+        near_plain(outs[t], ref, exact, f"decode step {t} of {batch} requests")
 
 
 def test_decode_graphs_give_the_tokens_of_eager_steps(engines):
     """Greedy generation through the engine at this shape with CUDA graphs (padded batch buckets,
-    context buckets, dependent launches inside the graph) and without: the same tokens."""
+    context buckets, dependent launches inside the graph) and without: the plain implementation's
+    greedy tokens in both runs, and the same tokens unless the choice is a near-tie (the context
+    bucket of a graph splits the keys into other partitions than the context itself)."""
     import kvcm
     from kvcm.config import EngineConfig, KVManagerConfig, SchedulerConfig
     from kvcm.engine import model_from_tensors
     from kvcm.weights import random_tensors
-    cfg, _ = engines
+    cfg, make = engines
     spec = model_from_tensors(cfg, dict(random_tensors(cfg, 7, torch.bfloat16, device="cuda:0", norm_jitter=0.1)),
                               "bfloat16", "cuda:0")
     prompts = [helpers.random_tokens(n, cfg.vocab_size, 20 + i) for i, n in enumerate((300, 150, 700))]
@@ -203,8 +234,7 @@ def test_decode_graphs_give_the_tokens_of_eager_steps(engines):
         if graphs:
             assert eng.graphs.replays > 0
         assert eng.kv.blocks_in_use() == 0
-    assert outs[True] == outs[False]
-    assert all(len(o) == 24 for o in outs[True])
+    greedy_or_near_tie(prompts, outs[True], outs[False], make["plain"], 24)
 
 
 def test_graph_buckets_are_crossed_while_portions_are_in_flight(engines):
@@ -239,20 +269,4 @@ def test_graph_buckets_are_crossed_while_portions_are_in_flight(engines):
         outs[graphs] = [done[i] for i in ids]
         seen[graphs] = (mixed, sorted({k[0] for k in eng.graphs.captured}) if eng.graphs else [])
     assert seen[True][0] >= 8 and set(seen[True][1]) >= {1, 2, 4, 8, 16}, seen[True]
-    # Every token of both runs is the plain implementation's greedy choice, or within a near-tie of
-    # it.  The two runs need not agree to the bit (a padded batch of 16 and a batch of 11 take
-    # different library kernels and other context partitions), so where they part ways, the plain
-    # logits must show a near-tie at that very place.
-    for p, a, b in zip(prompts, outs[True], outs[False]):
-        assert len(a) == 40 and len(b) == 40
-        for o in ((a,) if a == b else (a, b)):
-            logits = make["plain"](list(p) + list(o))
-            margin = 0.08 * logits.std().item()
-            for k, tok in enumerate(o):
-                row = logits[len(p) - 1 + k]
-                assert row.max().item() - row[tok].item() <= margin, (len(p), k, tok)
-        if a != b:
-            k = next(i for i in range(40) if a[i] != b[i])
-            row = make["plain"](list(p) + list(a))[len(p) - 1 + k]
-            top = row.topk(2).values
-            assert (top[0] - top[1]).item() <= 0.08 * row.std().item(), f"runs part ways at a clear choice (token {k})"
+    greedy_or_near_tie(prompts, outs[True], outs[False], make["plain"], 40)

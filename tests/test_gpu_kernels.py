@@ -233,15 +233,16 @@ def test_fused_gate_up_silu_gives_the_bits_of_the_separate_kernels(M, H, I):
 @pytest.mark.parametrize("M,H,Kd,I,eps", [(8, 2048, 2048, 5632, 1e-5), (1, 64, 48, 24, 1e-6), (5, 96, 256, 256, 1e-5),
                                           (16, 264, 1000, 128, 1e-3), (8, 2048, 5632, 64, 1e-5), (11, 2120, 2368, 40, 1e-5)])
 def test_residual_and_norm_ride_in_the_streaming_products(M, H, Kd, I, eps):
-    """The product that ends a sublayer adds into the float residual and leaves partial sums of
-    squares; the product that begins the next one takes its norm from them.  Against the separate
-    kernels: the residual bit for bit, the normed product within bfloat16 rounding of one element
-    of X (the sum of squares is added in another order); against float64; twice the same bits."""
+    """The product that ends a sublayer adds into the float residual, leaves partial sums of squares
+    and the next norm's row before its scale; the product that begins the next sublayer scales its
+    sums by the norm's 1/rms.  Against the separate kernels: the residual bit for bit, the products
+    within bfloat16 rounding (the normed row is rounded once instead of twice); against float64;
+    twice the same bits."""
     lib = K()
     g = torch.Generator().manual_seed(M + H + Kd)
     y = torch.randn(M, Kd, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(H, Kd, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
-    resid0 = torch.randn(M, H, generator=g).to(DEV)
+    resid0 = (3.0 * torch.randn(M, H, generator=g)).to(DEV)              # (not of unit scale: the norm has work to do)
     norm_w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).to(DEV)
     # separate kernels: product, then residual add + norm
     proj = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
@@ -253,32 +254,32 @@ def test_residual_and_norm_ride_in_the_streaming_products(M, H, Kd, I, eps):
     resid2 = resid0.clone()
     tiles = (H + 15) // 16
     partials = torch.full((tiles, 16), float("nan"), device=DEV)
-    lib.gemm_stream_residual(y, w, resid2, partials)
+    h = torch.full((M, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lib.gemm_stream_residual(y, w, resid2, partials, h, norm_w)
     assert lib.stream_error() == 0
     assert torch.equal(resid1, resid2)
+    assert torch.equal(h, (norm_w.float() * resid2).to(torch.bfloat16))
     ss = partials[:, :M].double().sum(0).cpu()
     want = (resid2.double().cpu() ** 2).sum(1)
     assert torch.allclose(ss, want, rtol=1e-5), "partial sums of squares"
+    resid3, partials3 = resid0.clone(), torch.zeros_like(partials)
+    lib.gemm_stream_residual(y, w, resid3, partials3)                     # nothing handed on: the residual alone
+    assert torch.equal(resid3, resid2) and torch.equal(partials3[:, :M], partials[:, :M])
     # ... into a gate/up product
     wg = (torch.randn(2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
     a1 = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
     lib.gate_up_silu(x1, wg, a1)
     a2 = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-    lib.gate_up_silu_norm(resid2, partials, norm_w, eps, wg, a2)
-    try:                                               # however many blocks share the staging of X: the same bits
-        for blocks in (1, 2, 4, 8):
-            lib.stream_norm_cluster(blocks)
-            a3 = torch.full_like(a2, float("nan"))
-            lib.gate_up_silu_norm(resid2, partials, norm_w, eps, wg, a3)
-            assert lib.stream_error() == 0 and torch.equal(a2, a3), f"clusters of {blocks}"
-    finally:
-        lib.stream_norm_cluster(0)
+    lib.gate_up_silu(h, wg, a2, partials, eps)
+    a3 = torch.full_like(a2, float("nan"))
+    lib.gate_up_silu(h, wg, a3, partials, eps)
+    assert lib.stream_error() == 0 and torch.equal(a2, a3)
     xr = resid2.double().cpu()
     xn = norm_w.double().cpu() * (xr * torch.rsqrt((xr ** 2).mean(1, keepdim=True) + eps))
     gg = xn @ wg.double().cpu().T
     ref = gg[:, :I] * torch.sigmoid(gg[:, :I]) * gg[:, I:]
-    close(a2, ref, "bfloat16", "normed gate/up against float64")
-    close(a2, a1.double().cpu(), "bfloat16", "normed gate/up against the separate kernels")
+    close(a2, ref, "bfloat16", "scaled gate/up against float64")
+    close(a2, a1.double().cpu(), "bfloat16", "scaled gate/up against the separate kernels")
     # ... and into a qkv product with rotary encoding and cache write
     nh, nkv, hd, B, pages = 4, 2, 16, 8, 5
     wq = (torch.randn((nh + 2 * nkv) * hd, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
@@ -292,10 +293,10 @@ def test_residual_and_norm_ride_in_the_streaming_products(M, H, Kd, I, eps):
     lib.qkv_rope_cache(x1, wq, q1, pos, inv, slots, k1, v1, nh, nkv, hd)
     q2 = torch.full_like(q1, float("nan"))
     k2, v2 = torch.zeros_like(k1), torch.zeros_like(v1)
-    lib.qkv_rope_cache_norm(resid2, partials, norm_w, eps, wq, q2, pos, inv, slots, k2, v2, nh, nkv, hd)
+    lib.qkv_rope_cache(h, wq, q2, pos, inv, slots, k2, v2, nh, nkv, hd, partials, eps)
     assert lib.stream_error() == 0
     for got, sep, what in ((q2, q1, "q"), (k2, k1, "k pages"), (v2, v1, "v pages")):
-        close(got, sep.double().cpu(), "bfloat16", f"normed qkv against the separate kernels: {what}")
+        close(got, sep.double().cpu(), "bfloat16", f"scaled qkv against the separate kernels: {what}")
     vref = (xn @ wq.double().cpu().T)[:, (nh + nkv) * hd:].reshape(M, nkv, hd)
     sl = slots.cpu().long()
     close(v2.cpu()[sl // B, :, sl % B], vref, "bfloat16", "v rows against float64")
