@@ -40,11 +40,24 @@ struct DecodeParams {
 constexpr int kTabMax = 512;         // page-table entries of a partition kept in shared memory
 constexpr int kMaxClusterParts = 8;      // the portable cluster size: any GPC can place it
 
+// Four adjacent outputs: one 8-byte store where the address allows it.
+__device__ __forceinline__ void store_out4(bf16* dst, float a, float b, float c, float d) {
+  if ((reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+    uint2 packed;
+    packed.x = pack_bf16(a, b);
+    packed.y = pack_bf16(c, d);
+    *reinterpret_cast<uint2*>(dst) = packed;
+  } else {
+    dst[0] = __float2bfloat16_rn(a); dst[1] = __float2bfloat16_rn(b);
+    dst[2] = __float2bfloat16_rn(c); dst[3] = __float2bfloat16_rn(d);
+  }
+}
+
 // Merge of the partitions inside a cluster.  Every block has put its partial result for the 16
 // heads of the tile into its own shared memory (bo [16][HD], bm [16] max, bl [16] sum; an empty
 // partition has max = -inf).  The outputs are dealt out over the blocks of the cluster; each
 // reads all partitions' values through distributed shared memory and adds them in partition
-// order, with the roundings of the merge kernel.
+// order.
 template <int HD>
 __device__ __forceinline__ void cluster_merge_tail(const DecodeParams& p, int seq, int head0, int heads_here,
                                                    float* bo, float* bm, float* bl) {
@@ -52,21 +65,40 @@ __device__ __forceinline__ void cluster_merge_tail(const DecodeParams& p, int se
   cg::cluster_group cluster = cg::this_cluster();
   cluster.sync();                                                  // every block's partial result is in place
   const int P = p.num_parts;
-  for (int e = int(cluster.block_rank()) * kAttnThreads + threadIdx.x; e < heads_here * HD; e += P * kAttnThreads) {
-    const int r = e / HD, d = e - r * HD;
-    float M = -INFINITY;
-    for (int i = 0; i < P; ++i) M = fmaxf(M, *cluster.map_shared_rank(bm + r, i));
-    float acc = 0.f, L = 0.f;
-    for (int i = 0; i < P; ++i) {
-      const float mp = *cluster.map_shared_rank(bm + r, i);
-      const float lp = *cluster.map_shared_rank(bl + r, i);
-      const float op = *cluster.map_shared_rank(bo + r * HD + d, i);
-      const bool live = mp != -INFINITY;                           // an empty partition left no output
-      const float f = live ? exp2f(mp - M) : 0.f;
-      acc = live ? __fmaf_rn(f, op, acc) : acc;
-      L = live ? __fmaf_rn(f, lp, L) : L;
+  // An item is four adjacent elements of one head's output; the items are dealt out over the blocks
+  // of the cluster.  Every block's (max, sum, values) for the item are asked for at once: one trip
+  // through the cluster's shared memory, not one per partition; the weights 2^(m_p - M) are
+  // formed once per item.
+  constexpr int Q4 = HD / 4;
+  for (int it = int(cluster.block_rank()) * kAttnThreads + threadIdx.x; it < heads_here * Q4; it += P * kAttnThreads) {
+    const int r = it / Q4, d = (it - r * Q4) * 4;
+    float mp[kMaxClusterParts], lp[kMaxClusterParts];
+    float4 op[kMaxClusterParts];
+#pragma unroll
+    for (int i = 0; i < kMaxClusterParts; ++i) {
+      mp[i] = -INFINITY; lp[i] = 0.f; op[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < P) {
+        mp[i] = *cluster.map_shared_rank(bm + r, i);
+        lp[i] = *cluster.map_shared_rank(bl + r, i);
+        op[i] = *reinterpret_cast<const float4*>(cluster.map_shared_rank(bo + r * HD + d, i));
+      }
     }
-    p.out[size_t(seq) * p.out_stride + size_t(head0 + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    float M = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kMaxClusterParts; ++i) M = fmaxf(M, mp[i]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float L = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxClusterParts; ++i) {
+      if (mp[i] == -INFINITY) continue;                            // an empty partition left no output (its bo is not written)
+      const float f = fast_exp2(mp[i] - M);
+      acc.x = __fmaf_rn(f, op[i].x, acc.x); acc.y = __fmaf_rn(f, op[i].y, acc.y);
+      acc.z = __fmaf_rn(f, op[i].z, acc.z); acc.w = __fmaf_rn(f, op[i].w, acc.w);
+      L = __fmaf_rn(f, lp[i], L);
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    store_out4(p.out + size_t(seq) * p.out_stride + size_t(head0 + r) * HD + d, acc.x * inv, acc.y * inv, acc.z * inv,
+               acc.w * inv);
   }
   cluster.sync();                                                  // nobody leaves while its memory is read
 }
@@ -230,7 +262,9 @@ attn_decode_kernel(DecodeParams p) {
 
   cp_async_wait<0>();
   __syncthreads();                                                 // the tiles give way to the merge buffers
-  // ---- merge the four warps (each saw different keys) through shared memory
+  // ---- merge the four warps (each saw different keys) through shared memory.  An item is four
+  // adjacent elements of one head's output: the weights 2^(m_w - M) are formed once per item, the
+  // values move as 16-byte vectors.
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
@@ -239,10 +273,8 @@ attn_decode_kernel(DecodeParams p) {
 #pragma unroll
   for (int d = 0; d < HD / 8; ++d) {
     float* base = mo + (warp * 16) * HD + d * 8 + 2 * t4;
-    base[g * HD] = o[d][0];
-    base[g * HD + 1] = o[d][1];
-    base[(g + 8) * HD] = o[d][2];
-    base[(g + 8) * HD + 1] = o[d][3];
+    *reinterpret_cast<float2*>(base + g * HD) = make_float2(o[d][0], o[d][1]);
+    *reinterpret_cast<float2*>(base + (g + 8) * HD) = make_float2(o[d][2], o[d][3]);
   }
   if (t4 == 0) {
     mm[warp * 16 + g] = m[0];
@@ -251,31 +283,37 @@ attn_decode_kernel(DecodeParams p) {
     mlsum[warp * 16 + g + 8] = l[1];
   }
   __syncthreads();
-  for (int i = tid; i < heads_here * HD; i += kAttnThreads) {
-    const int r = i / HD, d = i - r * HD;
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, mm[w * 16 + r]);
-    float acc = 0.f, L = 0.f;
+  constexpr int Q4 = HD / 4;
+  for (int it = tid; it < heads_here * Q4; it += kAttnThreads) {
+    const int r = it / Q4, d = (it - r * Q4) * 4;
+    float mw[4], M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const float mw = mm[w * 16 + r];
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-      acc += f * mo[(w * 16 + r) * HD + d];
+      mw[w] = mm[w * 16 + r];
+      M = fmaxf(M, mw[w]);
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = (mw[w] == -INFINITY) ? 0.f : fast_exp2(mw[w] - M);
+      const float4 v = *reinterpret_cast<const float4*>(mo + (w * 16 + r) * HD + d);
+      acc.x += f * v.x; acc.y += f * v.y; acc.z += f * v.z; acc.w += f * v.w;
       L += f * mlsum[w * 16 + r];
     }
     const int head = head0 + r;
     if (p.cluster_merge) {
-      bo[r * HD + d] = acc;
+      *reinterpret_cast<float4*>(bo + r * HD + d) = acc;
       if (d == 0) {
         bm[r] = M;
         bl[r] = L;
       }
     } else if (p.num_parts == 1) {
-      p.out[size_t(seq) * p.out_stride + size_t(head) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      store_out4(p.out + size_t(seq) * p.out_stride + size_t(head) * HD + d, acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
     } else {
       const size_t idx = (size_t(seq) * p.nh + head) * p.num_parts + part;
-      p.part_o[idx * HD + d] = acc;
+      *reinterpret_cast<float4*>(p.part_o + idx * HD + d) = acc;
       if (d == 0) {
         p.part_ml[idx * 2] = M;
         p.part_ml[idx * 2 + 1] = L;
