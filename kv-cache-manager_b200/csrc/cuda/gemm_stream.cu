@@ -174,49 +174,61 @@ gemm_stream_kernel(StreamParams p) {
   const int my_tiles = blockIdx.x < n_tiles ? (n_tiles - 1 - blockIdx.x) / gridDim.x + 1 : 0;
   const int total = my_tiles * Kc;                            // stages this block consumes
 
-  if (tid == 0) {
-    abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kStreamConsumers); }
+  if (tid == 0) abort_flag = 0;
+  if (tid < kStages) {                                        // a barrier pair a thread
+    mbar_init(&full[tid], 1);
+    mbar_init(&empty[tid], kStreamConsumers);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
   pdl_launch_dependents();
 
-  // weight row of local row r (0..15) of a tile
-  auto row_of = [&](int tile, int r) {
-    const int base = (tile / p.pair_blocks) * p.group_stride + 8 * (tile % p.pair_blocks);
-    return r < 8 ? base + r : base + p.pair_offset + (r - 8);
+  // Weight row of local row r (0..15) of a tile whose first row is `base`.  (A lone warp runs cold
+  // code at some ten cycles an instruction, so what is on the way of every stage or tile is kept
+  // free of divisions: slots, phases, chunks and tiles are counted along, not derived.)
+  auto tile_base = [&](int tile) {
+    const int q = tile / p.pair_blocks;
+    return q * p.group_stride + 8 * (tile - q * p.pair_blocks);
   };
+  auto row_in = [&](int base, int r) { return r < 8 ? base + r : base + p.pair_offset + (r - 8); };
 
   // Producer warp: lane 0 announces the bytes of a stage, lanes 0..15 each copy one row of it
   // (sixteen copies issued side by side).  Stage i holds rows of tile (i / Kc) at k-chunk (i % Kc).
   const unsigned long long wait_limit = g_stream_wait_limit_ns;
   const int skip_stage = g_stream_skip_stage;
-  auto issue = [&](int i) {
-    if (i == skip_stage) return;                              // (tests: the bytes of this stage never arrive)
-    const int s = i % kStages;
-    const int tile = blockIdx.x + (i / Kc) * gridDim.x;
-    const int k0 = (i % Kc) * kChunk;
-    const int kbytes = min(kChunk, p.K - k0) * 2;
-    const int row = lane < 16 ? row_of(tile, lane) : p.N;
-    const unsigned live = __ballot_sync(0xffffffffu, row < p.N);
-    if (lane == 0) mbar_expect_tx(&full[s], uint32_t(__popc(live)) * kbytes);
-    __syncwarp();
-    if (row < p.N)
-      bulk_copy(ring + s * kStageBytes + lane * kRowBytes, p.W + size_t(row) * p.ldw + k0, kbytes, &full[s]);
-  };
-
-  int issued = 0;
-  if (warp == kStreamConsumers)
-    for (; issued < min(total, kStages); ++issued) issue(issued);          // fill the ring: weights are constants
-  pdl_wait();                                                               // ... the predecessor wrote X
-
   if (warp == kStreamConsumers) {
-    for (; issued < total; ++issued) {
-      const int s = issued % kStages;
+    int issued = 0, slot = 0, round = 0, kc = 0, tile = blockIdx.x;        // the stage to issue next
+    const bf16* row_ptr = nullptr;                                         // this lane's row of W in `tile`
+    uint32_t live_rows = 0;
+    auto enter_tile = [&]() {
+      const int row = lane < 16 ? row_in(tile_base(tile), lane) : p.N;
+      row_ptr = row < p.N ? p.W + size_t(row) * p.ldw : nullptr;
+      live_rows = uint32_t(__popc(__ballot_sync(0xffffffffu, row_ptr != nullptr)));
+    };
+    auto issue = [&]() {
+      if (issued != skip_stage) {                                          // (tests: the bytes of this stage never arrive)
+        const int k0 = kc * kChunk;
+        const int kbytes = min(kChunk, p.K - k0) * 2;
+        if (lane == 0) mbar_expect_tx(&full[slot], live_rows * kbytes);
+        __syncwarp();
+        if (row_ptr != nullptr) bulk_copy(ring + slot * kStageBytes + lane * kRowBytes, row_ptr + k0, kbytes, &full[slot]);
+      }
+      ++issued;
+      if (++slot == kStages) { slot = 0; ++round; }
+      if (++kc == Kc) {
+        kc = 0;
+        tile += gridDim.x;
+        if (issued < total) enter_tile();
+      }
+    };
+    if (total > 0) enter_tile();
+    const int first = min(total, kStages);
+    while (issued < first) issue();                                        // fill the ring: weights are constants
+    pdl_wait();                                                             // (nothing below reads what the predecessor wrote)
+    while (issued < total) {
       int ok = 1;
       if (lane == 0) {
-        ok = !abort_flag && mbar_wait(&empty[s], ((issued / kStages) - 1) & 1, wait_limit);   // consumers freed the slot?
+        ok = !abort_flag && mbar_wait(&empty[slot], (round - 1) & 1, wait_limit);   // consumers freed the slot?
         if (!ok && !abort_flag) {
           atomicExch(&g_stream_error, (1 << 16) | int(blockIdx.x));
           abort_flag = 1;
@@ -224,7 +236,7 @@ gemm_stream_kernel(StreamParams p) {
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
-      issue(issued);
+      issue();
     }
     // Stay until every copy this block issued has landed (shared memory must not be handed to
     // another block with copies still in flight).  Immediate in a healthy run: the consumers
@@ -236,13 +248,39 @@ gemm_stream_kernel(StreamParams p) {
       }
     return;
   }
+  // Rotary encoding: the angle's sine and cosine for this thread's element of the block's first
+  // tile, before the wait (positions and frequencies are inputs of the step, not of the predecessor).
+  float cs0 = 1.f, sn0 = 0.f;
+  if constexpr (EPI == kRopeCache) {
+    if (my_tiles > 0 && tid < 8 * MB) {
+      const int pr = tid / MB, m = tid - pr * MB;
+      const int q = int(blockIdx.x) / p.pair_blocks;
+      const int j = 8 * (int(blockIdx.x) - q * p.pair_blocks) + pr;
+      if (q < p.nh + p.nkv && m < p.M) sincosf(float(p.positions[m]) * p.inv_freq[j], &sn0, &cs0);
+    }
+  }
+  pdl_wait();                                                               // ... the predecessor wrote X
 
   // ---- consumers.  X is staged k-chunk by k-chunk (one copy group each, zero fill beyond M and
   // K), so the first tile can start on chunk 0 while the later chunks are still arriving.
-  const int chunk_vecs = kChunk / 8;
+  const int chunk_vecs = kChunk / 8;                          // (a multiple of 32)
+  if constexpr (!XDIRECT) {
+    for (int kc = 0; kc < Kc; ++kc) {
+      for (int ch = kc * chunk_vecs + tid; ch < (kc + 1) * chunk_vecs; ch += kConsumerThreads) {
+        const bool kin = ch * 8 < p.K;
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+          const bool live = kin && m < p.M;
+          const bf16* src = live ? p.X + size_t(m) * p.ldx + ch * 8 : p.X;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s32(xs + m * Kp + ch * 8)), "l"(src), "r"(live ? 16 : 0));
+        }
+      }
+      asm volatile("cp.async.commit_group;\n" ::);
+    }
+  }
   if constexpr (SCALED) {
-    // 1/rms of the rows from the partial sums: requested now, needed at the epilogue (the barrier
-    // in front of it makes norm_s visible to all)
+    // 1/rms of the rows from the partial sums: asked for behind X, needed at the epilogue (the
+    // barrier in front of it makes norm_s visible to all)
     for (int m = warp; m < p.M; m += kStreamConsumers) {
       float ss = 0.f;
 #pragma unroll 4
@@ -250,17 +288,6 @@ gemm_stream_kernel(StreamParams p) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       if (lane == 0) norm_s[m] = rsqrtf(ss / float(p.K) + p.eps);
-    }
-  }
-  if constexpr (!XDIRECT) {
-    for (int kc = 0; kc < Kc; ++kc) {
-      for (int c = tid; c < MB * chunk_vecs; c += kConsumerThreads) {
-        const int m = c / chunk_vecs, ch = kc * chunk_vecs + (c - m * chunk_vecs);
-        const bool live = m < p.M && ch * 8 < p.K;
-        const bf16* src = live ? p.X + size_t(m) * p.ldx + ch * 8 : p.X;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s32(xs + m * Kp + ch * 8)), "l"(src), "r"(live ? 16 : 0));
-      }
-      asm volatile("cp.async.commit_group;\n" ::);
     }
   }
 
@@ -280,24 +307,27 @@ gemm_stream_kernel(StreamParams p) {
       }
   };
   if constexpr (XDIRECT) fetch_x(xcur, 0);
-  int i = 0;
+  int slot = 0;
+  uint32_t phase = 0;                                          // of the stage to consume next
   for (int tl = 0; tl < my_tiles; ++tl) {
     const int tile = blockIdx.x + tl * gridDim.x;
+    const int base = tile_base(tile);
     float acc[MT][4];
 #pragma unroll
     for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    for (int kc = 0; kc < Kc; ++kc, ++i) {
+    for (int kc = 0; kc < Kc; ++kc) {
       if constexpr (XDIRECT) {
         fetch_x(xnext, kc + 1);                                // in flight while this stage is worked on
       } else if (tl == 0) {                                    // this chunk of X has landed for everyone?
         cp_async_wait_dyn(min(Kc - 1 - kc, 7));
         asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
       }
-      const int s = i % kStages;
-      if (!abort_flag && !mbar_wait(&full[s], (i / kStages) & 1, wait_limit)) {
+      const int s = slot;
+      if (!abort_flag && !mbar_wait(&full[s], phase, wait_limit)) {
         if (lane == 0) atomicExch(&g_stream_error, (2 << 16) | int(blockIdx.x));
         abort_flag = 1;                                        // everyone stops waiting, nobody leaves a barrier alone
       }
+      if (++slot == kStages) { slot = 0; phase ^= 1u; }
       if (abort_flag) continue;
       const unsigned char* st = ring + s * kStageBytes;
       const int kbase = kc * kChunk + warp * kPerWarp;          // this warp's share of the stage
@@ -352,7 +382,7 @@ gemm_stream_kernel(StreamParams p) {
     if constexpr (EPI == kResidual) {
       for (int e = tid; e < 16 * MB; e += kConsumerThreads) {
         const int r = e / MB, m = e - r * MB;
-        const int n = row_of(tile, r);
+        const int n = row_in(base, r);
         float v = 0.f;
         if (n < p.N && m < p.M) {
           float* x = p.resid + size_t(m) * p.ldr + n;
@@ -374,7 +404,7 @@ gemm_stream_kernel(StreamParams p) {
       OutT* Y = reinterpret_cast<OutT*>(p.Y);
       for (int e = tid; e < 16 * MB; e += kConsumerThreads) {
         const int r = e / MB, m = e - r * MB;
-        const int n = row_of(tile, r);
+        const int n = row_in(base, r);
         if (n < p.N && m < p.M) stf(Y + size_t(m) * p.ldy + n, total_of(r, m));
       }
     } else {
@@ -390,12 +420,12 @@ gemm_stream_kernel(StreamParams p) {
           stf(Y + size_t(m) * p.ldy + 8 * tile + pr, sl * xb);
         } else {
           const int head = tile / p.pair_blocks;
-          const int j = 8 * (tile % p.pair_blocks) + pr;
+          const int j = 8 * (tile - head * p.pair_blocks) + pr;
           const int half = p.hd / 2;
           float ra = xa, rb = xb;
           if (head < p.nh + p.nkv) {
-            float sn, cs;
-            sincosf(float(p.positions[m]) * p.inv_freq[j], &sn, &cs);
+            float sn = sn0, cs = cs0;                               // (e == tid in the first round of the first tile)
+            if (tl > 0 || e != tid) sincosf(float(p.positions[m]) * p.inv_freq[j], &sn, &cs);
             rotate_pair(xa, xb, cs, sn, ra, rb);
           }
           if (head < p.nh) {
