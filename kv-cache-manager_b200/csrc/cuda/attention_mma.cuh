@@ -113,6 +113,17 @@ __device__ __forceinline__ void load_kv_tiles(bf16* __restrict__ ktile, bf16* __
       bool have_page = false;
       bf16* kd = ktile + first * LD + ch * 8;
       bf16* vd = vtile + first * LD + ch * 8;
+      if ((block_size % RUN) == 0 && t >= lo && t + RUN <= hi) {
+        // the common case: the thread's run lies inside one page and inside the context: one
+        // page lookup, copies at constant offsets (little code: a lone warp runs it cold)
+        const size_t at = size_t(table[pi]) * page_stride + head_off + size_t(off) * HD;
+#pragma unroll
+        for (int k = 0; k < RUN; ++k) {
+          cp_async16(kd + k * LD, kcache + at + k * HD);
+          cp_async16(vd + k * LD, vcache + at + k * HD);
+        }
+        return;
+      }
 #pragma unroll
       for (int k = 0; k < RUN; ++k) {
         if (t >= lo && t < hi) {

@@ -333,23 +333,40 @@ gemm_stream_kernel(StreamParams p) {
       const int kbase = kc * kChunk + warp * kPerWarp;          // this warp's share of the stage
       // (XDIRECT: the chunk is the short one, so the trip count is a constant and xcur stays in registers)
       const int n_kb = XDIRECT ? kXBlocks : kPerWarp / 32;
+      const unsigned char* wa = st + g * kRowBytes + (warp * kPerWarp + 8 * t4) * 2;   // this thread's 16 bytes of rows g, g+8
+      const bf16* xa = xs + g * Kp + kbase + 8 * t4;
+      if (kbase + kPerWarp <= p.K) {                           // the warp's whole share lies inside K: no checks
 #pragma unroll 4
-      for (int kb = 0; kb < n_kb; ++kb) {
-        if (kbase + kb * 32 >= p.K) break;                     // warp-uniform: the whole k-block lies beyond K
-        const int koff = warp * kPerWarp + kb * 32 + 8 * t4;
-        uint4 va = *reinterpret_cast<const uint4*>(st + g * kRowBytes + koff * 2);
-        uint4 vb = *reinterpret_cast<const uint4*>(st + (g + 8) * kRowBytes + koff * 2);
-        if (kc * kChunk + koff >= p.K) {                       // this thread's 8 columns lie beyond K: stale bytes
-          va = make_uint4(0u, 0u, 0u, 0u);
-          vb = make_uint4(0u, 0u, 0u, 0u);
-        }
+        for (int kb = 0; kb < n_kb; ++kb) {
+          const uint4 va = *reinterpret_cast<const uint4*>(wa + kb * 64);
+          const uint4 vb = *reinterpret_cast<const uint4*>(wa + 8 * kRowBytes + kb * 64);
 #pragma unroll
-        for (int j = 0; j < MT; ++j) {
-          uint4 x;
-          if constexpr (XDIRECT) x = xcur[j][kb];
-          else x = *reinterpret_cast<const uint4*>(xs + (8 * j + g) * Kp + kbase + kb * 32 + 8 * t4);
-          mma_stream(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
-          mma_stream(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
+          for (int j = 0; j < MT; ++j) {
+            uint4 x;
+            if constexpr (XDIRECT) x = xcur[j][kb];
+            else x = *reinterpret_cast<const uint4*>(xa + 8 * j * Kp + kb * 32);
+            mma_stream(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
+            mma_stream(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
+          }
+        }
+      } else {
+#pragma unroll 4
+        for (int kb = 0; kb < n_kb; ++kb) {
+          if (kbase + kb * 32 >= p.K) break;                   // warp-uniform: the whole k-block lies beyond K
+          uint4 va = *reinterpret_cast<const uint4*>(wa + kb * 64);
+          uint4 vb = *reinterpret_cast<const uint4*>(wa + 8 * kRowBytes + kb * 64);
+          if (kbase + kb * 32 + 8 * t4 >= p.K) {               // this thread's 8 columns lie beyond K: stale bytes
+            va = make_uint4(0u, 0u, 0u, 0u);
+            vb = make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int j = 0; j < MT; ++j) {
+            uint4 x;
+            if constexpr (XDIRECT) x = xcur[j][kb];
+            else x = *reinterpret_cast<const uint4*>(xa + 8 * j * Kp + kb * 32);
+            mma_stream(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
+            mma_stream(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
+          }
         }
       }
       __syncwarp();
@@ -365,10 +382,8 @@ gemm_stream_kernel(StreamParams p) {
     float* mine = red + ((tl & 1) * kStreamConsumers + warp) * 16 * MB;
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
-      mine[g * MB + 8 * j + 2 * t4] = acc[j][0];
-      mine[g * MB + 8 * j + 2 * t4 + 1] = acc[j][1];
-      mine[(g + 8) * MB + 8 * j + 2 * t4] = acc[j][2];
-      mine[(g + 8) * MB + 8 * j + 2 * t4 + 1] = acc[j][3];
+      *reinterpret_cast<float2*>(mine + g * MB + 8 * j + 2 * t4) = make_float2(acc[j][0], acc[j][1]);
+      *reinterpret_cast<float2*>(mine + (g + 8) * MB + 8 * j + 2 * t4) = make_float2(acc[j][2], acc[j][3]);
     }
     asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
     // The partial sums of the warps are added in warp order: reproducible bit for bit.
