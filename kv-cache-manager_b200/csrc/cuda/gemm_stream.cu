@@ -44,6 +44,10 @@ constexpr int kStreamThreads = 32 * (kStreamConsumers + 1);
 constexpr int kMaxStages = 12;                         // ring depth is chosen per launch to fill shared memory
 constexpr int kChunkUnit = 256;                        // the k elements of a stage are a multiple of this
 constexpr int kChunkLong = 2048, kChunkShort = 1024;   // whole rows up to 2048 k; else pieces of 1024 k
+// X straight from L2 (XDIRECT): a stage's pieces of X live in registers, so the stage is as long as
+// the registers allow (a bulk copy costs its issuer some 60 ns whatever its size: fewer, larger
+// copies keep the producer ahead)
+__host__ __device__ constexpr int direct_chunk(int MT) { return kChunkShort; }
 constexpr int kRowPad = 64;                            // padded stage row: rows g and g+1 sit 64 bytes apart modulo 128,
                                                        // so the eight lanes of a quarter-warp (two rows x four 16-byte
                                                        // columns) read eight distinct bank groups
@@ -278,23 +282,26 @@ gemm_stream_kernel(StreamParams p) {
       asm volatile("cp.async.commit_group;\n" ::);
     }
   }
+  // SCALED: the partial sums of squares of this warp's rows (row warp, and warp + 8 of sixteen) are
+  // asked for behind X and added up after the main loop, so that nothing waits for them here.
+  constexpr int kPartRegs = 8;                                 // 32 x 8 tiles of 16 columns: hidden sizes to 4,096 without a loop
+  float part[SCALED ? MT : 1][SCALED ? kPartRegs : 1];
   if constexpr (SCALED) {
-    // 1/rms of the rows from the partial sums: asked for behind X, needed at the epilogue (the
-    // barrier in front of it makes norm_s visible to all)
-    for (int m = warp; m < p.M; m += kStreamConsumers) {
-      float ss = 0.f;
-#pragma unroll 4
-      for (int t = lane; t < p.ss_tiles; t += 32) ss += __ldcg(p.ss_in + t * kNormRows + m);
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) norm_s[m] = rsqrtf(ss / float(p.K) + p.eps);
+    for (int j = 0; j < MT; ++j) {
+      const int m = warp + kStreamConsumers * j;
+#pragma unroll
+      for (int i = 0; i < kPartRegs; ++i) {
+        const int t = lane + 32 * i;
+        part[j][i] = (m < p.M && t < p.ss_tiles) ? __ldcg(p.ss_in + t * kNormRows + m) : 0.f;
+      }
     }
   }
 
   const int g = lane >> 2, t4 = lane & 3;
   const int kPerWarp = kChunk / kStreamConsumers;              // k columns of a stage per warp (a multiple of 32)
   // XDIRECT: this thread's pieces of X for one stage (kXBlocks k-blocks of 32), zero beyond M and K.
-  constexpr int kXBlocks = kChunkShort / kStreamConsumers / 32;
+  constexpr int kXBlocks = direct_chunk(MT) / kStreamConsumers / 32;
   uint4 xcur[XDIRECT ? MT : 1][XDIRECT ? kXBlocks : 1], xnext[XDIRECT ? MT : 1][XDIRECT ? kXBlocks : 1];
   auto fetch_x = [&](uint4 (&dst)[XDIRECT ? MT : 1][XDIRECT ? kXBlocks : 1], int kc) {
 #pragma unroll
@@ -315,6 +322,16 @@ gemm_stream_kernel(StreamParams p) {
     float acc[MT][4];
 #pragma unroll
     for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    // kResidual: this thread's element of the residual (it has one: 16 x MB <= the consumer
+    // threads), asked for now and used in the epilogue
+    float resid_old = 0.f;
+    if constexpr (EPI == kResidual) {
+      if (tid < 16 * MB) {
+        const int r = tid / MB, m = tid - r * MB;
+        const int n = row_in(base, r);
+        if (n < p.N && m < p.M) resid_old = __ldcg(p.resid + size_t(m) * p.ldr + n);
+      }
+    }
     for (int kc = 0; kc < Kc; ++kc) {
       if constexpr (XDIRECT) {
         fetch_x(xnext, kc + 1);                                // in flight while this stage is worked on
@@ -335,23 +352,19 @@ gemm_stream_kernel(StreamParams p) {
       const int n_kb = XDIRECT ? kXBlocks : kPerWarp / 32;
       const unsigned char* wa = st + g * kRowBytes + (warp * kPerWarp + 8 * t4) * 2;   // this thread's 16 bytes of rows g, g+8
       const bf16* xa = xs + g * Kp + kbase + 8 * t4;
-      if (kbase + kPerWarp <= p.K) {                           // the warp's whole share lies inside K: no checks
-#pragma unroll 4
-        for (int kb = 0; kb < n_kb; ++kb) {
-          const uint4 va = *reinterpret_cast<const uint4*>(wa + kb * 64);
-          const uint4 vb = *reinterpret_cast<const uint4*>(wa + 8 * kRowBytes + kb * 64);
+      auto k_block = [&](int kb, uint4 va, uint4 vb, const uint4 (&xr)[XDIRECT ? MT : 1]) {
 #pragma unroll
-          for (int j = 0; j < MT; ++j) {
-            uint4 x;
-            if constexpr (XDIRECT) x = xcur[j][kb];
-            else x = *reinterpret_cast<const uint4*>(xa + 8 * j * Kp + kb * 32);
-            mma_stream(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
-            mma_stream(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
-          }
+        for (int j = 0; j < MT; ++j) {
+          uint4 x;
+          if constexpr (XDIRECT) x = xr[j];
+          else x = *reinterpret_cast<const uint4*>(xa + 8 * j * Kp + kb * 32);
+          mma_stream(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
+          mma_stream(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
         }
-      } else {
-#pragma unroll 4
-        for (int kb = 0; kb < n_kb; ++kb) {
+      };
+      if constexpr (XDIRECT) {                                 // a constant trip count: xcur stays in registers
+#pragma unroll
+        for (int kb = 0; kb < kXBlocks; ++kb) {
           if (kbase + kb * 32 >= p.K) break;                   // warp-uniform: the whole k-block lies beyond K
           uint4 va = *reinterpret_cast<const uint4*>(wa + kb * 64);
           uint4 vb = *reinterpret_cast<const uint4*>(wa + 8 * kRowBytes + kb * 64);
@@ -359,14 +372,29 @@ gemm_stream_kernel(StreamParams p) {
             va = make_uint4(0u, 0u, 0u, 0u);
             vb = make_uint4(0u, 0u, 0u, 0u);
           }
+          uint4 xr[MT];
 #pragma unroll
-          for (int j = 0; j < MT; ++j) {
-            uint4 x;
-            if constexpr (XDIRECT) x = xcur[j][kb];
-            else x = *reinterpret_cast<const uint4*>(xa + 8 * j * Kp + kb * 32);
-            mma_stream(acc[j], va.x, vb.x, va.y, vb.y, x.x, x.y);
-            mma_stream(acc[j], va.z, vb.z, va.w, vb.w, x.z, x.w);
+          for (int j = 0; j < MT; ++j) xr[j] = xcur[j][kb];
+          k_block(kb, va, vb, xr);
+        }
+      } else if (kbase + kPerWarp <= p.K) {                    // the warp's whole share lies inside K: no checks
+        const uint4 none[1] = {};
+#pragma unroll 4
+        for (int kb = 0; kb < n_kb; ++kb)
+          k_block(kb, *reinterpret_cast<const uint4*>(wa + kb * 64),
+                  *reinterpret_cast<const uint4*>(wa + 8 * kRowBytes + kb * 64), none);
+      } else {
+        const uint4 none[1] = {};
+#pragma unroll 4
+        for (int kb = 0; kb < n_kb; ++kb) {
+          if (kbase + kb * 32 >= p.K) break;
+          uint4 va = *reinterpret_cast<const uint4*>(wa + kb * 64);
+          uint4 vb = *reinterpret_cast<const uint4*>(wa + 8 * kRowBytes + kb * 64);
+          if (kbase + kb * 32 + 8 * t4 >= p.K) {
+            va = make_uint4(0u, 0u, 0u, 0u);
+            vb = make_uint4(0u, 0u, 0u, 0u);
           }
+          k_block(kb, va, vb, none);
         }
       }
       __syncwarp();
@@ -376,6 +404,22 @@ gemm_stream_kernel(StreamParams p) {
         for (int j = 0; j < MT; ++j)
 #pragma unroll
           for (int kb = 0; kb < kXBlocks; ++kb) xcur[j][kb] = xnext[j][kb];
+      }
+    }
+    if constexpr (SCALED) {
+      if (tl == 0) {                                           // 1/rms of the rows, in a fixed order of addition
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          const int m = warp + kStreamConsumers * j;
+          float ss = 0.f;
+#pragma unroll
+          for (int i = 0; i < kPartRegs; ++i) ss += part[j][i];
+          if (m < p.M)
+            for (int t = lane + 32 * kPartRegs; t < p.ss_tiles; t += 32) ss += __ldcg(p.ss_in + t * kNormRows + m);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          if (lane == 0 && m < p.M) norm_s[m] = rsqrtf(ss / float(p.K) + p.eps);
+        }
       }
     }
     // acc[j]: c0,c1 = (W row g, batch 8j + 2t, +1); c2,c3 = (W row g+8, same batch rows)
@@ -401,7 +445,7 @@ gemm_stream_kernel(StreamParams p) {
         float v = 0.f;
         if (n < p.N && m < p.M) {
           float* x = p.resid + size_t(m) * p.ldr + n;
-          v = *x + Store<bf16>::round(total_of(r, m));
+          v = resid_old + Store<bf16>::round(total_of(r, m));     // (e == tid: one element a thread)
           *x = v;
           if (p.next_w != nullptr) stf(p.h_out + size_t(m) * p.ldh + n, ldf(p.next_w + n) * v);
         }
@@ -491,7 +535,7 @@ template <int MT, typename OutT, int EPI, bool XDIRECT, bool SCALED = false>
 int launch_stream_as(StreamParams p, int sm_count, cudaStream_t s) {
   auto kernel = gemm_stream_kernel<MT, OutT, EPI, XDIRECT, SCALED>;
   const int tiles = (p.N + 15) / 16;
-  const int chunk = XDIRECT ? kChunkShort : stream_chunk(MT, p.K);
+  const int chunk = XDIRECT ? direct_chunk(MT) : stream_chunk(MT, p.K);
   if (chunk == 0) return KVCM_ERR_UNSUPPORTED;
   const int Kc = (p.K + chunk - 1) / chunk;
   // One block per SM; the ring takes what shared memory is left after X, but never more slots than
