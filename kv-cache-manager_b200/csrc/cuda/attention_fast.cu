@@ -219,6 +219,7 @@ attn_decode_kernel(DecodeParams p) {
   auto round_barrier = [&]() {
     if constexpr (kWarpPrivate) __syncwarp(); else __syncthreads();
   };
+  int slot = 0;                                                    // ring slot of tile i (counted along: i % stages)
   for (int i = 0; i < n_tiles; ++i) {
     const int t0 = t_first + i * kKeyTile;
     load_stage(i + kKVStages - 1);                                 // its slot was freed by the barrier that
@@ -226,8 +227,8 @@ attn_decode_kernel(DecodeParams p) {
     round_barrier();
     const int kb = t0 + warp * 16;                                 // this warp's 16 keys
     if (kb < end && kb + 16 > begin) {
-      const bf16* kt = kbuf + (i % kKVStages) * kKeyTile * LD + warp * 16 * LD;
-      const bf16* vt = vbuf + (i % kKVStages) * kKeyTile * LD + warp * 16 * LD;
+      const bf16* kt = kbuf + slot * kKeyTile * LD + warp * 16 * LD;
+      const bf16* vt = vbuf + slot * kKeyTile * LD + warp * 16 * LD;
       float s[2][4];
       if constexpr (Q_IN_REGS) {
         qk_16x16<HD>(s, reinterpret_cast<const uint32_t(&)[HD / 16][4]>(qa), kt, lane);
@@ -246,18 +247,26 @@ attn_decode_kernel(DecodeParams p) {
           mma_bf16(s[1], a, b[2], b[3]);
         }
       }
+      if (kb >= begin && kb + 16 <= end) {                         // all sixteen keys count: no masks
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int key = kb + 8 * h + 2 * t4 + (j & 1);
-          s[h][j] = (key >= begin && key < end) ? s[h][j] * p.scale_log2 : -INFINITY;
-        }
+          for (int j = 0; j < 4; ++j) s[h][j] *= p.scale_log2;
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int key = kb + 8 * h + 2 * t4 + (j & 1);
+            s[h][j] = (key >= begin && key < end) ? s[h][j] * p.scale_log2 : -INFINITY;
+          }
+      }
       uint32_t pa[4];
       softmax_step<HD>(s, m, l, o, pa);
       pv_16x16<HD>(o, pa, vt, lane);
     }
     round_barrier();                                               // the buffer is loaded again next round
+    if (++slot == kKVStages) slot = 0;
   }
 
   cp_async_wait<0>();
