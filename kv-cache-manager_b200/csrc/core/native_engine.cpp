@@ -85,6 +85,7 @@ NativeEngine::NativeEngine(KVManager& kv, Scheduler& sched, NativeModel model, N
   logits_ = device(size_t(max_logits_) * model_.V * 4);
   if (cfg_.attn_scratch_floats > 0) attn_scratch_ = device(size_t(cfg_.attn_scratch_floats) * 4);
   if (cfg_.fuse_norms && !model_.f32) norm_partials_ = device(size_t((model_.H + 15) / 16 * 16) * 4);
+  if (!model_.f32) rope_table_ = device(size_t(cfg_.max_rows) * model_.hd * 4);
   if (!model_.f32 && cfg_.lib_workspace_bytes > 0) lib_ws_ = device(size_t(cfg_.lib_workspace_bytes));
 }
 
@@ -138,6 +139,8 @@ void NativeEngine::fill_args(KvcmForwardArgs& a, const BatchLayout& L, const int
   a.logits = static_cast<float*>(logits_);
   a.attn_scratch = static_cast<float*>(attn_scratch_);
   a.attn_scratch_floats = attn_scratch_ ? cfg_.attn_scratch_floats : 0;
+  a.rope_table = static_cast<float*>(rope_table_);
+  a.rope_table_floats = rope_table_ ? (long long)cfg_.max_rows * model_.hd : 0;
   a.norm_partials = static_cast<float*>(norm_partials_);
   a.norm_partials_floats = norm_partials_ ? (model_.H + 15) / 16 * 16 : 0;
   a.lib_workspace = lib_ws_;

@@ -158,7 +158,7 @@ class NativeEngine {
   size_t sampling_bytes_ = 0;
   void *x_ = nullptr, *h_ = nullptr, *qkv_ = nullptr, *attn_ = nullptr, *proj_ = nullptr, *gate_up_ = nullptr,
        *act_ = nullptr, *h_last_ = nullptr, *logits_ = nullptr, *attn_scratch_ = nullptr, *lib_ws_ = nullptr,
-       *norm_partials_ = nullptr;
+       *norm_partials_ = nullptr, *rope_table_ = nullptr;
   std::vector<void*> device_allocs_;
   std::map<std::tuple<int, int, int>, Captured> graphs_;
   std::vector<BatchEntry> entries_;

@@ -5,6 +5,8 @@
 //
 // Formulas after the reference's kernels (src/cuda/kernels.cu:27-88, src/cuda/kv_cache.cu:19-38);
 // the fusions (residual+norm, rotary+cache write) are this engine's own.
+#include <algorithm>
+
 #include "common.cuh"
 #include "pdl.cuh"
 
@@ -62,8 +64,24 @@ rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const W* __re
   }
 }
 
+// Four neighbouring elements as one access (8 bytes of bfloat16, 16 of float).
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__bfloat162float(lo.x), __bfloat162float(lo.y), __bfloat162float(hi.x), __bfloat162float(hi.y));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+  raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // The same for rows of at most 256 * 4 * VEC elements with hidden % 4 == 0: the row stays in
-// registers (float4 loads), one pass over global memory.
+// registers, one pass over global memory, four elements an access.
 template <typename T, typename W, int VEC>
 __global__ void __launch_bounds__(256)
 rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const W* __restrict__ weight,
@@ -84,7 +102,8 @@ rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const W* 
     if (i < hidden) {
       v[k] = *reinterpret_cast<const float4*>(xr + i);
       if (dr) {
-        v[k].x += ldf(dr + i); v[k].y += ldf(dr + i + 1); v[k].z += ldf(dr + i + 2); v[k].w += ldf(dr + i + 3);
+        const float4 d = load4(dr + i);
+        v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
         if (!rows) *reinterpret_cast<float4*>(xr + i) = v[k];
       }
       ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
@@ -97,10 +116,9 @@ rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const W* 
   for (int k = 0; k < VEC; ++k) {
     const int i = (k * 256 + threadIdx.x) * 4;
     if (i < hidden) {
-      stf(o + i, ldf(weight + i) * Store<T>::round(v[k].x * inv));
-      stf(o + i + 1, ldf(weight + i + 1) * Store<T>::round(v[k].y * inv));
-      stf(o + i + 2, ldf(weight + i + 2) * Store<T>::round(v[k].z * inv));
-      stf(o + i + 3, ldf(weight + i + 3) * Store<T>::round(v[k].w * inv));
+      const float4 w = load4(weight + i);
+      store4(o + i, make_float4(w.x * Store<T>::round(v[k].x * inv), w.y * Store<T>::round(v[k].y * inv),
+                                w.z * Store<T>::round(v[k].z * inv), w.w * Store<T>::round(v[k].w * inv)));
     }
   }
 }
@@ -214,6 +232,70 @@ rope_cache_vec_kernel(bf16* __restrict__ qkv, int row_stride, const int* __restr
   }
 }
 
+// The angles of a step depend on the rows' positions only, not on the layer: for a step of many
+// rows their cosines and sines are computed once (table [rows][hd]: hd/2 cosines, then hd/2 sines)
+// and every layer's rotary kernel reads them.  The same values as the kernels above compute.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int rows,
+                                  int half, float* __restrict__ table) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * half; i += gridDim.x * blockDim.x) {
+    const int t = i / half, j = i - t * half;
+    float sn, cs;
+    sincosf(float(positions[t]) * inv_freq[j], &sn, &cs);
+    table[size_t(t) * 2 * half + j] = cs;
+    table[size_t(t) * 2 * half + half + j] = sn;
+  }
+}
+
+// rope_cache_vec_kernel with the angles from that table: no shared memory, no barrier, one item (8
+// neighbouring pairs of a head of a row) a thread.
+__global__ void __launch_bounds__(256)
+rope_cache_table_kernel(bf16* __restrict__ qkv, int row_stride, const float* __restrict__ table,
+                        const int* __restrict__ slot_mapping, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                        int rows, int nh, int nkv, int hd, int block_size, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int half = hd / 2, per_head = half / 8;
+  const int heads = write_cache ? nh + 2 * nkv : nh;
+  const int per_row = heads * per_head;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * per_row) return;
+  const int t = idx / per_row, w = idx - t * per_row;
+  const int head = w / per_head, j0 = (w - head * per_head) * 8;
+  bf16* base = qkv + size_t(t) * row_stride + size_t(head) * hd;
+  uint4 va = *reinterpret_cast<const uint4*>(base + j0);
+  uint4 vb = *reinterpret_cast<const uint4*>(base + half + j0);
+  if (head < nh + nkv) {
+    const float* cs = table + size_t(t) * hd + j0;
+    const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(cs + half), s1 = *reinterpret_cast<const float4*>(cs + half + 4);
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&va);
+    __nv_bfloat162* b2 = reinterpret_cast<__nv_bfloat162*>(&vb);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float r0a, r0b, r1a, r1b;
+      rotate_pair(__bfloat162float(a2[i].x), __bfloat162float(b2[i].x), c[2 * i], sn[2 * i], r0a, r0b);
+      rotate_pair(__bfloat162float(a2[i].y), __bfloat162float(b2[i].y), c[2 * i + 1], sn[2 * i + 1], r1a, r1b);
+      a2[i] = __floats2bfloat162_rn(r0a, r1a);
+      b2[i] = __floats2bfloat162_rn(r0b, r1b);
+    }
+    *reinterpret_cast<uint4*>(base + j0) = va;
+    *reinterpret_cast<uint4*>(base + half + j0) = vb;
+  }
+  if (head < nh) return;
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  const int page = slot / block_size, off = slot - page * block_size;
+  const bool is_k = head < nh + nkv;
+  const int kvh = is_k ? head - nh : head - nh - nkv;
+  bf16* dst = (is_k ? k_cache : v_cache) + ((size_t(page) * nkv + kvh) * block_size + off) * hd;
+  *reinterpret_cast<uint4*>(dst + j0) = va;
+  *reinterpret_cast<uint4*>(dst + half + j0) = vb;
+}
+
 // --------------------------------------------------------------------------- SiLU(g) * u
 // gate = columns [0, I) of the fused product, up = columns [I, 2I).  silu is rounded to the
 // storage type before the product (src/cuda/kernels.cu:72-82).
@@ -278,7 +360,9 @@ __global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restr
 template <typename T, typename W>
 int launch_rmsnorm_w(float* x, const T* delta, const W* weight, T* out, const int* rows, int n_rows,
                      int hidden, float eps, cudaStream_t s) {
-  if ((hidden % 4) == 0 && hidden <= 256 * 4 * 4 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+  const uintptr_t others = reinterpret_cast<uintptr_t>(delta) | reinterpret_cast<uintptr_t>(out);
+  if ((hidden % 4) == 0 && hidden <= 256 * 4 * 4 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (others & (4 * sizeof(T) - 1)) == 0 && (reinterpret_cast<uintptr_t>(weight) & (4 * sizeof(W) - 1)) == 0) {
     if (hidden <= 1024) return pdl_launch(rmsnorm_vec_kernel<T, W, 1>, dim3(n_rows), dim3(256), 0, s, x, delta, weight, out, rows, hidden, eps);
     if (hidden <= 2048) return pdl_launch(rmsnorm_vec_kernel<T, W, 2>, dim3(n_rows), dim3(256), 0, s, x, delta, weight, out, rows, hidden, eps);
     return pdl_launch(rmsnorm_vec_kernel<T, W, 4>, dim3(n_rows), dim3(256), 0, s, x, delta, weight, out, rows, hidden, eps);
@@ -364,3 +448,34 @@ using namespace kvcm;
 
 KVCM_INSTANTIATE(f32, float)
 KVCM_INSTANTIATE(bf16, bf16)
+
+// cos/sin of position * inv_freq for `rows` rows: table[t][0 .. half) cosines, [half .. 2 half) sines.
+KVCM_API int kvcm_rope_table_f32(const int* positions, const float* inv_freq, int rows, int half, float* table,
+                                 void* stream) {
+  if (rows == 0 || half == 0) return 0;
+  const int blocks = std::min((rows * half + 255) / 256, 1184);
+  return pdl_launch(rope_table_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, positions, inv_freq, rows, half,
+                    table);
+}
+
+// Whether kvcm_rope_cache_table_bf16 takes these rows (whole-head rotate-half pairing, 16-byte pieces).
+KVCM_API int kvcm_rope_cache_table_supports(const void* qkv, int row_stride, const void* k_cache, const void* v_cache,
+                                            const void* table, int hd) {
+  return (hd % 16) == 0 && (row_stride % 8) == 0 &&
+         ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+           reinterpret_cast<uintptr_t>(table)) & 15) == 0;
+}
+
+// kvcm_rope_cache_bf16 (rotate-half over the whole head) with the angles' cosines and sines read
+// from a table that kvcm_rope_table_f32 filled for the same rows.
+KVCM_API int kvcm_rope_cache_table_bf16(void* qkv, int row_stride, const float* table, const int* slot_mapping,
+                                        void* k_cache, void* v_cache, int rows, int nh, int nkv, int hd, int block_size,
+                                        int write_cache, void* stream) {
+  if (rows == 0) return 0;
+  if (!kvcm_rope_cache_table_supports(qkv, row_stride, k_cache, v_cache, table, hd)) return KVCM_ERR_UNSUPPORTED;
+  const long long items = (long long)rows * (write_cache ? nh + 2 * nkv : nh) * (hd / 16);
+  if (items > (1ll << 30)) return KVCM_ERR_UNSUPPORTED;
+  return pdl_launch(rope_cache_table_kernel, dim3(unsigned((items + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                    (bf16*)qkv, row_stride, table, slot_mapping, (bf16*)k_cache, (bf16*)v_cache, rows, nh, nkv, hd,
+                    block_size, write_cache);
+}

@@ -57,6 +57,9 @@ int kvcm_qkv_rope_cache_bf16(const void*, const void*, void*, int, int, int, int
                              void*, void*, int, int, int, int, int, void*);
 int kvcm_gate_up_silu_bf16(const void*, const void*, void*, int, int, int, int, int, int, int, void*);
 int kvcm_gemm_tcgen05_supports(int, int, int, int, int);
+int kvcm_rope_table_f32(const int*, const float*, int, int, float*, void*);
+int kvcm_rope_cache_table_supports(const void*, int, const void*, const void*, const void*, int);
+int kvcm_rope_cache_table_bf16(void*, int, const float*, const int*, void*, void*, int, int, int, int, int, int, void*);
 int kvcm_gemm_stream_residual_bf16(const void*, const void*, float*, float*, void*, const void*, int, int, int, int, int, int,
                                    int, int, void*);
 int kvcm_qkv_rope_cache_scaled_bf16(const void*, const float*, int, float, const void*, void*, int, int, int, int, int,
@@ -73,6 +76,7 @@ constexpr long long kStreamMaxBytes = 32ll << 20;       // parts/linear.py: STRE
 constexpr int kTcgen05MinRows = 256;                    // TCGEN05_MIN_ROWS
 constexpr int kTcgen05GatedMaxHidden = 3072;            // TCGEN05_GATED_MAX_HIDDEN
 constexpr int kKeyTile = 64;
+constexpr int kRopeTableMinRows = 64;                   // from here on the angles are computed once a step
 // Most rows of a step whose norms ride in its products (a decode step of the 1.1B shape, with and
 // without: 1 row 881 -> 809 us, 4 rows 902 -> 837, 8 rows 916 -> 869, 16 rows 1171 -> 1180).
 constexpr int kNormRideMaxRows = 8;
@@ -226,6 +230,7 @@ KVCM_API int kvcm_forward(const KvcmForwardArgs* ap, int* launches, void* stream
   };
 
   KVCM_TRY(embed(a.tokens, a.embed, a.x, T, H, a.V, s)); ++n;
+  bool table_filled = false;                            // the step's cosines and sines are in a.rope_table
   const void* pending = nullptr;                        // a sublayer's result not yet added to the residual
   bool handed = false;                                  // a.h and norm_partials hold the next norm's row before its scale
   // ends a sublayer: x += y w^T, one way or the other (next_norm: the norm weight of the product
@@ -255,8 +260,19 @@ KVCM_API int kvcm_forward(const KvcmForwardArgs* ap, int* launches, void* stream
       q_stride = QK;
     } else {
       KVCM_TRY(product(a, a.h, L.w_qkv, a.qkv, T, QKV, H, false, s)); ++n;
-      KVCM_TRY(rope_cache(a.qkv, QKV, a.positions, a.inv_freq, a.hd, 0, a.group_slots[L.group], L.k_cache, L.v_cache, T,
-                          a.nh, a.nkv, a.hd, a.block_size, L.writes, s));
+      // the angles are the same in every layer: with many rows they are computed once a step
+      if (!a.f32 && T >= kRopeTableMinRows && a.rope_table != nullptr && a.rope_table_floats >= (long long)T * a.hd &&
+          kvcm_rope_cache_table_supports(a.qkv, QKV, L.k_cache, L.v_cache, a.rope_table, a.hd)) {
+        if (!table_filled) {
+          KVCM_TRY(kvcm_rope_table_f32(a.positions, a.inv_freq, T, a.hd / 2, a.rope_table, s)); ++n;
+          table_filled = true;
+        }
+        KVCM_TRY(kvcm_rope_cache_table_bf16(a.qkv, QKV, a.rope_table, a.group_slots[L.group], L.k_cache, L.v_cache, T, a.nh,
+                                            a.nkv, a.hd, a.block_size, L.writes, s));
+      } else {
+        KVCM_TRY(rope_cache(a.qkv, QKV, a.positions, a.inv_freq, a.hd, 0, a.group_slots[L.group], L.k_cache, L.v_cache, T,
+                            a.nh, a.nkv, a.hd, a.block_size, L.writes, s));
+      }
       ++n;
     }
     KVCM_TRY(attention(a, L, q, q_stride, n, s));

@@ -27,8 +27,9 @@ struct KvcmForwardArgs {
   // norm_partials: ceil(H/16)*16 floats, or null = every norm is a launch of its own (with it, a step
   // of at most 8 rows adds the residual and takes the norms inside its products)
   float* x; void* h; void* qkv; void* attn; void* proj; void* gate_up; void* act; void* h_last; float* logits;
-  float* attn_scratch; void* lib_workspace; float* norm_partials;
-  long long attn_scratch_floats, lib_workspace_bytes, norm_partials_floats;
+  // rope_table: rows x hd floats, or null = every layer's rotary kernel computes its angles itself
+  float* attn_scratch; void* lib_workspace; float* norm_partials; float* rope_table;
+  long long attn_scratch_floats, lib_workspace_bytes, norm_partials_floats, rope_table_floats;
   int num_layers, f32, H, I, nh, nkv, hd, V, block_size, max_blocks, sm_count;
   int rows, seqs, decode_seqs, prefill_tiles, tile_rows, max_decode_ctx, num_logits, reserved;
   float final_eps, scale;

@@ -53,6 +53,8 @@ class NativeForward:
         # partial sums of squares of the residual, one per 16 columns and row (None = norms are launches)
         fuse = runner.options.get("fuse_norms", True) and not self.f32
         self.norm_partials = torch.zeros((self.H + 15) // 16 * 16, dtype=torch.float32, device=dev) if fuse else None
+        # cosines and sines of a step's angles, computed once a step for all layers (steps of many rows)
+        self.rope_table = None if self.f32 else torch.empty(runner.max_rows * self.hd, dtype=torch.float32, device=dev)
         self.calls = 0
 
     # ------------------------------------------------------------------ does the model fit
@@ -163,6 +165,8 @@ class NativeForward:
             a.attn_scratch, a.attn_scratch_floats = self.attn_scratch.data_ptr(), self.attn_scratch.numel()
         if self.lib_workspace is not None:
             a.lib_workspace, a.lib_workspace_bytes = self.lib_workspace.data_ptr(), self.lib_workspace.numel()
+        if self.rope_table is not None:
+            a.rope_table, a.rope_table_floats = self.rope_table.data_ptr(), self.rope_table.numel()
         if self.norm_partials is not None:
             a.norm_partials, a.norm_partials_floats = self.norm_partials.data_ptr(), self.norm_partials.numel()
         a.num_layers, a.f32 = len(self.layers), int(self.f32)

@@ -213,6 +213,39 @@ def rope_cache(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[to
               int(write_cache), _stream()), "rope_cache", f"(rotary_dim={rotary_dim}, hd={hd})")
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor) -> None:
+    """table[t] = [cos(positions[t] * inv_freq) | sin(...)] (float32 [T, 2 * len(inv_freq)]): the
+    angles of a step, which are the same in every layer."""
+    _cuda(positions, inv_freq, table)
+    T, width = table.shape
+    _need(positions.dtype == _I32 and positions.numel() >= T, "rope_table: positions int32 [T]")
+    _need(inv_freq.dtype == torch.float32 and table.dtype == torch.float32 and table.is_contiguous()
+          and width == 2 * inv_freq.numel(), "rope_table: float32 inv_freq [hd/2] and table [T, hd]")
+    _check(_lib().kvcm_rope_table_f32(_p(positions), _p(inv_freq), T, width // 2, _p(table), _stream()), "rope_table")
+
+
+def rope_cache_table(qkv: torch.Tensor, table: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                     k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], nh: int, nkv: int, hd: int,
+                     block_size: int, write_cache: bool = True) -> None:
+    """``rope_cache`` for bfloat16 rows rotated over the whole head in rotate-half pairs, with the
+    cosines and sines read from ``table`` (``rope_table``): the same bits."""
+    _cuda(qkv, table, slot_mapping, k_cache, v_cache)
+    T = qkv.shape[0]
+    _need(qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] >= (nh + 2 * nkv) * hd,
+          "rope_cache_table: bfloat16 rows of q, k and v heads")
+    _need(table.dtype == torch.float32 and table.is_contiguous() and tuple(table.shape) == (T, hd),
+          "rope_cache_table: table float32 [T, hd]")
+    if write_cache:
+        _need(slot_mapping is not None and slot_mapping.dtype == _I32 and slot_mapping.numel() >= T,
+              "rope_cache_table: slot_mapping int32 [T]")
+        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype and k_cache.is_contiguous()
+              and v_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (nkv, block_size, hd),
+              "rope_cache_table: cache dtype/layout")
+    rc = _lib().kvcm_rope_cache_table_bf16(_p(qkv), qkv.stride(0), _p(table), _p(slot_mapping), _p(k_cache), _p(v_cache),
+                                           T, nh, nkv, hd, block_size, int(write_cache), _stream())
+    _check(rc, "rope_cache_table", f"(hd={hd}, row stride {qkv.stride(0)})")
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _cuda(gate_up, out)
     T, I = out.shape
@@ -794,9 +827,9 @@ class ForwardArgs(ctypes.Structure):
         ("x", ctypes.c_void_p), ("h", ctypes.c_void_p), ("qkv", ctypes.c_void_p), ("attn", ctypes.c_void_p),
         ("proj", ctypes.c_void_p), ("gate_up", ctypes.c_void_p), ("act", ctypes.c_void_p), ("h_last", ctypes.c_void_p),
         ("logits", ctypes.c_void_p), ("attn_scratch", ctypes.c_void_p), ("lib_workspace", ctypes.c_void_p),
-        ("norm_partials", ctypes.c_void_p),
+        ("norm_partials", ctypes.c_void_p), ("rope_table", ctypes.c_void_p),
         ("attn_scratch_floats", ctypes.c_longlong), ("lib_workspace_bytes", ctypes.c_longlong),
-        ("norm_partials_floats", ctypes.c_longlong),
+        ("norm_partials_floats", ctypes.c_longlong), ("rope_table_floats", ctypes.c_longlong),
         ("num_layers", ctypes.c_int), ("f32", ctypes.c_int), ("H", ctypes.c_int), ("I", ctypes.c_int),
         ("nh", ctypes.c_int), ("nkv", ctypes.c_int), ("hd", ctypes.c_int), ("V", ctypes.c_int),
         ("block_size", ctypes.c_int), ("max_blocks", ctypes.c_int), ("sm_count", ctypes.c_int),

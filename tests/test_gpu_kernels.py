@@ -178,6 +178,37 @@ def test_streaming_gemm(M, N, Kd):
     assert torch.equal(y, y2)                                       # fixed summation order
 
 
+@pytest.mark.parametrize("T,nh,nkv,hd,B,write", [(2048, 32, 4, 64, 16, True), (77, 3, 1, 16, 8, True), (300, 6, 3, 48, 4, True),
+                                                  (65, 2, 2, 128, 32, False), (1, 5, 5, 32, 1, True)])
+def test_rope_with_the_angles_of_a_step_from_a_table(T, nh, nkv, hd, B, write):
+    """The cosines and sines of a step computed once, and the rotary + cache-write kernel that reads
+    them: the bits of the kernel that computes its angles itself."""
+    lib = K()
+    g = torch.Generator().manual_seed(T + hd)
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width + 8, generator=g).to(torch.bfloat16).to(DEV)[:, :width]       # strided rows
+    pos = torch.randint(0, 100000, (T,), generator=g).to(torch.int32).to(DEV)
+    pages = (T + B - 1) // B + 3
+    slots = torch.randperm(pages * B, generator=g)[:T].to(torch.int32)
+    if T > 2:
+        slots[1] = -1                                                # a row that writes nothing
+    slots = slots.to(DEV)
+    inv = (1.0 / torch.pow(torch.tensor(500000.0, dtype=torch.float64),
+                           2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().to(DEV)
+    a, b = qkv.clone(), qkv.clone()
+    k1 = torch.zeros(pages, nkv, B, hd, dtype=torch.bfloat16, device=DEV)
+    v1, k2, v2 = torch.zeros_like(k1), torch.zeros_like(k1), torch.zeros_like(k1)
+    lib.rope_cache(a, pos, inv, hd, False, slots, k1, v1, nh, nkv, hd, B, write)
+    table = torch.full((T, hd), float("nan"), device=DEV)
+    lib.rope_table(pos, inv, table)
+    ang = (pos.float().cpu()[:, None] * inv.cpu()[None, :]).double()        # the angle itself is a float product
+    assert torch.allclose(table.double().cpu(), torch.cat([torch.cos(ang), torch.sin(ang)], 1), atol=2e-6)
+    lib.rope_cache_table(b, table, slots, k2, v2, nh, nkv, hd, B, write)
+    assert torch.equal(a, b) and torch.equal(k1, k2) and torch.equal(v1, v2)
+    if not write:
+        assert torch.equal(b[:, nh * hd:], qkv[:, nh * hd:]) and not k2.any()
+
+
 @pytest.mark.parametrize("M,H,nh,nkv,hd,B", [(1, 64, 4, 2, 16, 16), (8, 2048, 32, 4, 64, 16), (5, 96, 3, 1, 32, 8),
                                               (16, 256, 6, 3, 48, 4), (3, 512, 2, 2, 128, 32)])
 def test_fused_qkv_rope_cache_gives_the_bits_of_the_separate_kernels(M, H, nh, nkv, hd, B):
