@@ -15,7 +15,8 @@ reference's benchmark model (TinyLlama 1.1B: 22 layers, hidden 2048, 32 query / 
 * ``prefill``   one 2,048-token prompt in one step: tokens/s, ms and fraction of the bf16 peak;
 * ``roofline``  bytes the decode step must read (every weight once, the cache of the live
                 requests) over its time, against the HBM copy bandwidth;
-* ``points``    decode tokens/s at batch 1 and 64.
+* ``points``    decode tokens/s at batch 1 and 64, each with the same roofline fraction
+                (``decode_b1_hbm_frac``, ``decode_b64_hbm_frac``).
 
 The timed decode window is centred on a context of 1,536 tokens (the middle of 1,024 -> 2,048)
 whatever K is: prompts have ``1536 - W - K/2`` tokens, which is 1,020 for the default K = 1,000.
@@ -396,6 +397,9 @@ def main() -> int:
         for b in (1, 64):
             r = decode_run(spec, ec, vocab, b, steps, warmup, prompt_len)
             pts[f"decode_b{b}"] = round(b * steps * 1e3 / r["dev_ms"], 1)
+            # the same roofline fraction as above: bytes the step has to read over its time, of the copy rate
+            need = m["weight_bytes"] + b * r["mean_ctx"] * m["kv_bytes_per_token"]
+            pts[f"decode_b{b}_hbm_frac"] = round(need / (r["dev_ms"] / steps * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         out["points"] = pts
         ms, flops, wall = prefill_run(spec, ec, vocab, cfg, layers)
         out["prefill"] = {"value": round(PREFILL_TOKENS * 1e3 / ms, 1), "tokens": PREFILL_TOKENS,
