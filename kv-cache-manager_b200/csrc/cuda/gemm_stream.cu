@@ -255,12 +255,14 @@ gemm_stream_kernel(StreamParams p) {
   // Rotary encoding: the angle's sine and cosine for this thread's element of the block's first
   // tile, before the wait (positions and frequencies are inputs of the step, not of the predecessor).
   float cs0 = 1.f, sn0 = 0.f;
+  int slot0 = -1;                                       // ... and the row's slot in the cache pages, for k and v heads
   if constexpr (EPI == kRopeCache) {
     if (my_tiles > 0 && tid < 8 * MB) {
       const int pr = tid / MB, m = tid - pr * MB;
       const int q = int(blockIdx.x) / p.pair_blocks;
       const int j = 8 * (int(blockIdx.x) - q * p.pair_blocks) + pr;
       if (q < p.nh + p.nkv && m < p.M) sincosf(float(p.positions[m]) * p.inv_freq[j], &sn0, &cs0);
+      if (q >= p.nh && m < p.M) slot0 = p.slot_mapping[m];
     }
   }
   pdl_wait();                                                               // ... the predecessor wrote X
@@ -324,12 +326,15 @@ gemm_stream_kernel(StreamParams p) {
     for (int j = 0; j < MT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     // kResidual: this thread's element of the residual (it has one: 16 x MB <= the consumer
     // threads), asked for now and used in the epilogue
-    float resid_old = 0.f;
+    float resid_old = 0.f, next_w_mine = 0.f;
     if constexpr (EPI == kResidual) {
       if (tid < 16 * MB) {
         const int r = tid / MB, m = tid - r * MB;
         const int n = row_in(base, r);
-        if (n < p.N && m < p.M) resid_old = __ldcg(p.resid + size_t(m) * p.ldr + n);
+        if (n < p.N && m < p.M) {
+          resid_old = __ldcg(p.resid + size_t(m) * p.ldr + n);
+          if (p.next_w != nullptr) next_w_mine = ldf(p.next_w + n);
+        }
       }
     }
     for (int kc = 0; kc < Kc; ++kc) {
@@ -447,7 +452,7 @@ gemm_stream_kernel(StreamParams p) {
           float* x = p.resid + size_t(m) * p.ldr + n;
           v = resid_old + Store<bf16>::round(total_of(r, m));     // (e == tid: one element a thread)
           *x = v;
-          if (p.next_w != nullptr) stf(p.h_out + size_t(m) * p.ldh + n, ldf(p.next_w + n) * v);
+          if (p.next_w != nullptr) stf(p.h_out + size_t(m) * p.ldh + n, next_w_mine * v);
         }
         norm_s[r * MB + m] = v * v;
       }
@@ -491,7 +496,7 @@ gemm_stream_kernel(StreamParams p) {
             stf(Y + size_t(m) * p.ldy + size_t(head) * p.hd + j, ra);
             stf(Y + size_t(m) * p.ldy + size_t(head) * p.hd + j + half, rb);
           } else {
-            const int slot = p.slot_mapping[m];
+            const int slot = (tl > 0 || e != tid) ? p.slot_mapping[m] : slot0;
             if (slot >= 0) {
               const int page = slot / p.block_size, off = slot - page * p.block_size;
               const bool is_k = head < p.nh + p.nkv;
