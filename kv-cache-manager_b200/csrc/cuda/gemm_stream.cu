@@ -265,6 +265,13 @@ gemm_stream_kernel(StreamParams p) {
       if (q >= p.nh && m < p.M) slot0 = p.slot_mapping[m];
     }
   }
+  // Rows of the staged X beyond M are zero: written here, before the wait, so that the copies after
+  // it are those of live rows only.
+  if constexpr (!XDIRECT) {
+    const int row_vecs = Kp / 8;                                             // (Kp is a multiple of 8)
+    for (int c = tid + p.M * row_vecs; c < MB * row_vecs; c += kConsumerThreads)
+      *reinterpret_cast<uint4*>(xs + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
   pdl_wait();                                                               // ... the predecessor wrote X
 
   // ---- consumers.  X is staged k-chunk by k-chunk (one copy group each, zero fill beyond M and
@@ -276,9 +283,9 @@ gemm_stream_kernel(StreamParams p) {
         const bool kin = ch * 8 < p.K;
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
-          const bool live = kin && m < p.M;
-          const bf16* src = live ? p.X + size_t(m) * p.ldx + ch * 8 : p.X;
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s32(xs + m * Kp + ch * 8)), "l"(src), "r"(live ? 16 : 0));
+          if (m >= p.M) break;                                 // (zero already)
+          const bf16* src = kin ? p.X + size_t(m) * p.ldx + ch * 8 : p.X;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s32(xs + m * Kp + ch * 8)), "l"(src), "r"(kin ? 16 : 0));
         }
       }
       asm volatile("cp.async.commit_group;\n" ::);
