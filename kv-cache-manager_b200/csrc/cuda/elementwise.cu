@@ -12,6 +12,22 @@
 
 namespace kvcm {
 
+// Four neighbouring elements as one access (8 bytes of bfloat16, 16 of float).
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__bfloat162float(lo.x), __bfloat162float(lo.y), __bfloat162float(hi.x), __bfloat162float(hi.y));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+  raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // ------------------------------------------------------------------------------ embedding
 // x[t, :] = float(table[ids[t], :]).  An id outside [0, vocab) yields a row of NaN: loud, not wrong.
 template <typename T>
@@ -25,6 +41,21 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
   const int id = ids[t];
   float* dst = x + size_t(t) * hidden;
   dst[i] = (id < 0 || id >= vocab) ? __int_as_float(0x7fc00000) : ldf(table + size_t(id) * hidden + i);
+}
+
+// The same, four elements a thread (hidden % 4 == 0, aligned rows).
+template <typename T>
+__global__ void embed_vec_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ x, int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (i >= hidden) return;
+  const int id = ids[t];
+  const float nan = __int_as_float(0x7fc00000);
+  const float4 v = (id < 0 || id >= vocab) ? make_float4(nan, nan, nan, nan) : load4(table + size_t(id) * hidden + i);
+  *reinterpret_cast<float4*>(x + size_t(t) * hidden + i) = v;
 }
 
 // -------------------------------------------------------------------------------- RMSNorm
@@ -62,22 +93,6 @@ rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const W* __re
     const float normed = Store<T>::round(row_cache[i] * inv);
     stf(o + i, ldf(weight + i) * normed);
   }
-}
-
-// Four neighbouring elements as one access (8 bytes of bfloat16, 16 of float).
-__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
-__device__ __forceinline__ float4 load4(const bf16* p) {
-  const uint2 raw = *reinterpret_cast<const uint2*>(p);
-  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-  return make_float4(__bfloat162float(lo.x), __bfloat162float(lo.y), __bfloat162float(hi.x), __bfloat162float(hi.y));
-}
-__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-__device__ __forceinline__ void store4(bf16* p, float4 v) {
-  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-  uint2 raw;
-  raw.x = *reinterpret_cast<const uint32_t*>(&lo);
-  raw.y = *reinterpret_cast<const uint32_t*>(&hi);
-  *reinterpret_cast<uint2*>(p) = raw;
 }
 
 // The same for rows of at most 256 * 4 * VEC elements with hidden % 4 == 0: the row stays in
@@ -402,6 +417,10 @@ using namespace kvcm;
   KVCM_API int kvcm_embed_##SUFFIX(const int* ids, const void* table, float* x, int rows, int hidden, \
                                    int vocab, void* stream) {                                         \
     if (rows == 0) return 0;                                                                          \
+    if ((hidden % 4) == 0 && (reinterpret_cast<uintptr_t>(table) & (4 * sizeof(T) - 1)) == 0 &&      \
+        (reinterpret_cast<uintptr_t>(x) & 15) == 0)                                                   \
+      return pdl_launch(embed_vec_kernel<T>, dim3(rows, (hidden / 4 + 255) / 256), dim3(256), 0,     \
+                        (cudaStream_t)stream, ids, (const T*)table, x, hidden, vocab);               \
     return pdl_launch(embed_kernel<T>, dim3(rows, (hidden + 255) / 256), dim3(256), 0,               \
                       (cudaStream_t)stream, ids, (const T*)table, x, hidden, vocab);                 \
   }                                                                                                   \

@@ -34,8 +34,9 @@ def close(got, ref, dtype, what=""):
 # ------------------------------------------------------------------------- small kernels
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_embedding(dtype):
-    V, H = 301, 70
+@pytest.mark.parametrize("H", [70, 72, 2048, 1028])                # (70: the scalar form; the others four elements a thread)
+def test_embedding(dtype, H):
+    V = 301
     table = torch.randn(V, H).to(DT[dtype]).to(DEV)
     ids = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=DEV)
     x = torch.empty(5, H, dtype=torch.float32, device=DEV)
