@@ -46,9 +46,11 @@ PRESETS = {
 }
 
 
-def load_model_from_args(a, dtype: str, device: str = "cuda:0"):
+def load_model_from_args(a, dtype: str, device: str = "cuda:0", stored_as: str = ""):
     """``--model DIR`` (config.json + model.safetensors) or ``--preset NAME [--random-seed S]``
-    (random weights of a named shape, generated on the device)."""
+    (random weights of a named shape, generated on the device).  ``stored_as``: the random weights
+    are rounded to that type first, as if read from a checkpoint stored in it (a float32 model with
+    the very values of the bfloat16 one)."""
     import torch
     from ..config import LlamaConfig
     from ..engine import load_model, model_from_tensors, torch_dtype
@@ -64,5 +66,7 @@ def load_model_from_args(a, dtype: str, device: str = "cuda:0"):
     keys, seed, jitter = PRESETS[preset]
     cfg = LlamaConfig(architecture="LlamaForCausalLM", **keys)
     seed = a.i64("random-seed", seed)
-    tensors = dict(random_tensors(cfg, seed, torch_dtype(dtype), device=device, norm_jitter=jitter))
+    tensors = dict(random_tensors(cfg, seed, torch_dtype(stored_as or dtype), device=device, norm_jitter=jitter))
+    if stored_as and stored_as != dtype:
+        tensors = {k: v.to(torch_dtype(dtype)) for k, v in tensors.items()}
     return model_from_tensors(cfg, tensors, dtype, device)

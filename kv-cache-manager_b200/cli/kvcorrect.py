@@ -7,9 +7,18 @@ Checks, each printed with PASS/FAIL; exit code 0 if all pass, 2 otherwise:
     disagreement counts only where the float32 top-1/top-2 gap exceeds --tie-margin) and the
     error of the top-5 logits;
  2. greedy tokens of every prompt alone, on a pool fragmented beforehand so that page tables are
-    scattered, equal the tokens of all prompts in one batch;
+    scattered, equal the tokens of all prompts in one batch (here and in 4 and 5: or part where the
+    float32 top-1/top-2 gap is below --tie-margin, both tokens being those two);
  3. paged and contiguous policies give identical tokens;
- 4. prefix caching on: hits > 0 and tokens identical to prefix caching off.
+ 4. prefix caching on: hits > 0 and tokens identical to prefix caching off;
+ 5. the first prompt again, now served from the cache but for its last tokens: the same tokens, or
+    tokens that part where the float32 top-1/top-2 gap is below --tie-margin (the few remaining rows
+    take other kernels than the whole prompt did).
+The default margin suits the 1.1B shape, where bfloat16 logits lie about 2 % of their standard
+deviation (0.02 in absolute terms) from the float32 ones; with random weights at the 7B and 8B
+shapes (32 layers, hidden size 4,096) that distance is about 6 % (0.08), which the plain
+implementation's own bfloat16 roundings show as well, so greedy runs there part at gaps of 0.1-0.2:
+give --tie-margin 0.25 for those.
 Flags: --model DIR | --preset NAME, --tie-margin 0.05, --block-size 16, --steps 32, --prompts 8,
 --prompt-len 64, --attn.
 """
@@ -30,7 +39,7 @@ def main(argv=None) -> int:
         steps, n_prompts, plen = a.i32("steps", 32), a.i32("prompts", 8), a.i32("prompt-len", 64)
         tie, B, attn = a.f64("tie-margin", 0.05), a.i32("block-size", 16), a.str("attn", "auto")
         spec16 = load_model_from_args(a, "bfloat16")
-        spec32 = load_model_from_args(a, "float32")
+        spec32 = load_model_from_args(a, "float32", stored_as="bfloat16")   # the same weight values, computed in 32 bits
         a.warn_unused()
         vocab = spec16.lm_head.vocab
         g = torch.Generator().manual_seed(7)
@@ -70,6 +79,24 @@ def main(argv=None) -> int:
         report("bfloat16 vs float32, teacher-forced top-1", agree >= 0.98 * total,
                f"{agree}/{total}; top-5 logit error mean {e.mean():.4f} max {e.max():.4f}")
 
+        def same_tokens(runs_a, runs_b):
+            """Equal token lists, or lists that part at a place where the float32 logits (teacher-forced
+            up to there) show a top-1/top-2 gap below the tie margin and both tokens are those two:
+            two runs that take different kernels (another batch size splits the context of decode
+            attention differently, a cached prompt leaves a step of a few rows) need not agree there."""
+            notes = []
+            for p, x, y in zip(prompts, runs_a, runs_b):
+                if x == y:
+                    continue
+                k = next(i for i in range(min(len(x), len(y))) if x[i] != y[i])
+                row = e32.score(p + x[:k]).double()[-1]
+                top = row.topk(2)
+                gap = float(top.values[0] - top.values[1])
+                if not (gap < tie and {x[k], y[k]} <= set(top.indices.tolist())):
+                    return False, f"(token {k} of a prompt of {len(p)}: float32 top-1/top-2 gap {gap:.4f})"
+                notes.append(f"{k}: gap {gap:.4f}")
+            return True, ("(near-ties at token " + ", ".join(notes) + ")") if notes else ""
+
         # 2. alone on a fragmented pool vs all in one batch
         solo_eng = engine(spec16, "bfloat16")
         frag = [solo_eng.add_request([3 + (i % 5)] * (B + 1 + i % 3), 1) for i in range(12)]   # scatter the free list
@@ -77,7 +104,7 @@ def main(argv=None) -> int:
         solo_eng.take_finished()
         solo = [generate(solo_eng, [p], steps)[0] for p in prompts]
         batch = generate(engine(spec16, "bfloat16"), prompts, steps)
-        report("alone (scattered pages) = batch", solo == batch)
+        report("alone (scattered pages) = batch", *same_tokens(solo, batch))
 
         # 3. paged vs contiguous
         cont_tokens = generate(engine(spec16, "bfloat16", policy="contiguous", max_seq_len=max_len,
@@ -88,9 +115,11 @@ def main(argv=None) -> int:
         pe = engine(spec16, "bfloat16", prefix=True)
         first = [generate(pe, [p], steps)[0] for p in prompts]
         hits = pe.kv.prefix_stats().hit_blocks
-        report("prefix cache on = off", first == solo and hits > 0, f"({hits} page hits)")
+        same, detail = same_tokens(first, solo)
+        report("prefix cache on = off", same and hits > 0, f"({hits} page hits) {detail}")
+        # 5. the first prompt once more: now all but its last tokens come from the cache
         again = generate(pe, [prompts[0]], steps)[0]
-        report("same prompt again from the cache", again == solo[0])
+        report("same prompt again from the cache", *same_tokens([again], [solo[0]]))
         print("all checks passed" if ok else "SOME CHECKS FAILED")
         return 0 if ok else 2
     except Exception as e:
