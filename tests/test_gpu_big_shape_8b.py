@@ -1,6 +1,6 @@
-"""The kernels that the Llama-3-8B shape takes and the TinyLlama shape does not, inside the engine:
-two layers of hidden size 4,096 with 32 query heads on 8 KV heads of 128 and a feed-forward of
-14,336 (heads of 128 in the tcgen05 prefill attention and in decode attention, the gate/up product
+"""The kernels that the Llama-3-8B and Llama-2-7B shapes take and the TinyLlama shape does not,
+inside the engine: two layers of hidden size 4,096 with 32 query heads on 8 (or 32) KV heads of 128
+and a feed-forward of 14,336 (or 11,008) (heads of 128 in the tcgen05 prefill attention and in decode attention, the gate/up product
 with its activation on pairs of SMs, the library's product for the 14,336-wide down projection of a
 decode step, a rotary base of 500,000), against the plain implementation in float64 on the CPU."""
 import pytest
@@ -13,14 +13,16 @@ from test_gpu_big_shape import near_float32, near_plain, same_cut
 pytestmark = pytest.mark.gpu
 
 
-def test_whole_prompt_then_token_by_token_at_the_8b_shape():
+@pytest.mark.parametrize("kv_heads,ffn,theta", [(8, 14336, 500000.0),       # Llama-3-8B
+                                                (32, 11008, 10000.0)])       # Llama-2-7B: every query head its own KV head
+def test_whole_prompt_then_token_by_token_at_the_8b_shape(kv_heads, ffn, theta):
     from kvcm.config import LlamaConfig
     from kvcm.engine import model_from_tensors
     from kvcm.kernels import library as K
     from kvcm.weights import random_tensors
-    cfg = LlamaConfig(architecture="LlamaForCausalLM", vocab_size=4100, hidden_size=4096, intermediate_size=14336,
-                      num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
-                      max_position_embeddings=8192, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", vocab_size=4100, hidden_size=4096, intermediate_size=ffn,
+                      num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=kv_heads, head_dim=128,
+                      max_position_embeddings=8192, rope_theta=theta, rms_norm_eps=1e-5, tie_word_embeddings=False)
     t16 = dict(random_tensors(cfg, 11, torch.bfloat16, device="cuda:0", norm_jitter=0.1))
     spec16 = model_from_tensors(cfg, dict(t16), "bfloat16", "cuda:0")
     spec32 = model_from_tensors(cfg, {k: v.float() for k, v in t16.items()}, "float32", "cuda:0")
