@@ -222,8 +222,11 @@ KVCM_API int kvcm_forward(const KvcmForwardArgs* ap, int* launches, void* stream
   const auto streams = [&](int N, int K) {
     return (T <= 8 || (long long)N * K * 2 <= kStreamMaxBytes) && kvcm_gemm_stream_supports(T, N, K);
   };
-  const bool ride = !a.f32 && a.norm_partials != nullptr && a.norm_partials_floats >= (long long)ss_tiles * 16 &&
-                    T <= kNormRideMaxRows && streams(H, QK) && streams(H, I);
+  const bool may_ride = !a.f32 && a.norm_partials != nullptr && a.norm_partials_floats >= (long long)ss_tiles * 16 &&
+                        T <= kNormRideMaxRows;
+  // (each sublayer by itself: where the down product is too wide for the streaming kernel, as at the
+  // Llama-3-8B shape, the attention sublayer still closes this way)
+  const bool ride_attn = may_ride && streams(H, QK), ride_ffn = may_ride && streams(H, I);
   const bool gate_fused = !a.f32 && (I % 8) == 0 && kvcm_gemm_stream_fused_supports(T, 2 * I, H);
   const auto qkv_fused = [&](const KvcmForwardLayer& L) {
     return !a.f32 && L.writes && (a.hd % 16) == 0 && kvcm_gemm_stream_fused_supports(T, QKV, H);
@@ -235,7 +238,7 @@ KVCM_API int kvcm_forward(const KvcmForwardArgs* ap, int* launches, void* stream
   bool handed = false;                                  // a.h and norm_partials hold the next norm's row before its scale
   // ends a sublayer: x += y w^T, one way or the other (next_norm: the norm weight of the product
   // that follows, where that product takes the scaled form)
-  const auto close_sublayer = [&](const void* y, const void* w, int K, const void* next_norm) {
+  const auto close_sublayer = [&](const void* y, const void* w, int K, const void* next_norm, bool ride) {
     pending = nullptr;
     handed = false;
     if (ride) {
@@ -276,7 +279,7 @@ KVCM_API int kvcm_forward(const KvcmForwardArgs* ap, int* launches, void* stream
       ++n;
     }
     KVCM_TRY(attention(a, L, q, q_stride, n, s));
-    KVCM_TRY(close_sublayer(a.attn, L.w_o, QK, gate_fused ? L.norm2 : nullptr)); ++n;
+    KVCM_TRY(close_sublayer(a.attn, L.w_o, QK, gate_fused ? L.norm2 : nullptr, ride_attn)); ++n;
     // feed-forward: gate/up product and activation -- one kernel where one exists for the shape
     if (!handed) { KVCM_TRY(rmsnorm(a.x, pending, L.norm2, 0, a.h, nullptr, T, H, L.eps2, s)); ++n; }
     if (gate_fused) {
@@ -291,7 +294,7 @@ KVCM_API int kvcm_forward(const KvcmForwardArgs* ap, int* launches, void* stream
       KVCM_TRY(silu_mul(a.gate_up, a.act, T, I, s)); ++n;
     }
     const bool next_takes = l + 1 < a.num_layers && qkv_fused(a.layers[l + 1]);
-    KVCM_TRY(close_sublayer(a.act, L.w_down, I, next_takes ? a.layers[l + 1].norm1 : nullptr)); ++n;
+    KVCM_TRY(close_sublayer(a.act, L.w_down, I, next_takes ? a.layers[l + 1].norm1 : nullptr, ride_ffn)); ++n;
   }
   if (a.num_logits > 0) {
     KVCM_TRY(rmsnorm(a.x, pending, a.final_norm, 0, a.h_last, a.logit_rows, a.num_logits, H, a.final_eps, s)); ++n;
