@@ -271,15 +271,20 @@ gemm_stream_kernel(StreamParams p) {
     const int row_vecs = Kp / 8;                                             // (Kp is a multiple of 8)
     for (int c = tid + p.M * row_vecs; c < MB * row_vecs; c += kConsumerThreads)
       *reinterpret_cast<uint4*>(xs + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));             // (before the wait: it costs nothing there)
   }
   pdl_wait();                                                               // ... the predecessor wrote X
 
-  // ---- consumers.  X is staged k-chunk by k-chunk (one copy group each, zero fill beyond M and
-  // K), so the first tile can start on chunk 0 while the later chunks are still arriving.
+  // ---- consumers.  X is staged k-chunk by k-chunk (one copy group each, zero fill beyond K), so
+  // the first tile can start on chunk 0 while the later chunks are still arriving.  Every warp
+  // copies the columns of a chunk that it multiplies itself (an eighth): it waits for its own
+  // copies and for no other warp.
   const int chunk_vecs = kChunk / 8;                          // (a multiple of 32)
   if constexpr (!XDIRECT) {
+    const int warp_vecs = chunk_vecs / kStreamConsumers;
     for (int kc = 0; kc < Kc; ++kc) {
-      for (int ch = kc * chunk_vecs + tid; ch < (kc + 1) * chunk_vecs; ch += kConsumerThreads) {
+      for (int v = lane; v < warp_vecs; v += 32) {
+        const int ch = kc * chunk_vecs + warp * warp_vecs + v;
         const bool kin = ch * 8 < p.K;
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
@@ -347,9 +352,9 @@ gemm_stream_kernel(StreamParams p) {
     for (int kc = 0; kc < Kc; ++kc) {
       if constexpr (XDIRECT) {
         fetch_x(xnext, kc + 1);                                // in flight while this stage is worked on
-      } else if (tl == 0) {                                    // this chunk of X has landed for everyone?
+      } else if (tl == 0) {                                    // this warp's columns of the chunk have landed?
         cp_async_wait_dyn(min(Kc - 1 - kc, 7));
-        asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
+        __syncwarp();
       }
       const int s = slot;
       if (!abort_flag && !mbar_wait(&full[s], phase, wait_limit)) {
