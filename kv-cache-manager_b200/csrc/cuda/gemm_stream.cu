@@ -171,7 +171,7 @@ gemm_stream_kernel(StreamParams p) {
   uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * kStreamConsumers * 16 * MB);
   uint64_t* empty = full + kMaxStages;
   __shared__ volatile int abort_flag;
-  __shared__ float norm_s[16 * 16];                           // SCALED: 1/rms per row; kResidual: squares of a tile
+  __shared__ float norm_s[16];                                // SCALED: 1/rms per row
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = (p.N + 15) / 16;
@@ -258,7 +258,7 @@ gemm_stream_kernel(StreamParams p) {
   int slot0 = -1;                                       // ... and the row's slot in the cache pages, for k and v heads
   if constexpr (EPI == kRopeCache) {
     if (my_tiles > 0 && tid < 8 * MB) {
-      const int pr = tid / MB, m = tid - pr * MB;
+      const int m = tid >> 3, pr = tid & 7;                    // (the epilogue's mapping: a row's 8 pairs side by side)
       const int q = int(blockIdx.x) / p.pair_blocks;
       const int j = 8 * (int(blockIdx.x) - q * p.pair_blocks) + pr;
       if (q < p.nh + p.nkv && m < p.M) sincosf(float(p.positions[m]) * p.inv_freq[j], &sn0, &cs0);
@@ -341,7 +341,7 @@ gemm_stream_kernel(StreamParams p) {
     float resid_old = 0.f, next_w_mine = 0.f;
     if constexpr (EPI == kResidual) {
       if (tid < 16 * MB) {
-        const int r = tid / MB, m = tid - r * MB;
+        const int m = tid >> 4, r = tid & 15;                  // (the epilogue's mapping: a row's 16 columns side by side)
         const int n = row_in(base, r);
         if (n < p.N && m < p.M) {
           resid_old = __ldcg(p.resid + size_t(m) * p.ldr + n);
@@ -455,38 +455,36 @@ gemm_stream_kernel(StreamParams p) {
       for (int w = 0; w < kStreamConsumers; ++w) sum += both[(w * 16 + r) * MB + m];
       return sum;
     };
+    // A thread takes one element of the tile: row m of the batch, column r of the tile's 16, with a
+    // row's columns side by side in a half-warp (neighbouring addresses, and the sum of squares
+    // over a row's columns is a few shuffles, not a trip through shared memory).
     if constexpr (EPI == kResidual) {
-      for (int e = tid; e < 16 * MB; e += kConsumerThreads) {
-        const int r = e / MB, m = e - r * MB;
+      for (int e = tid; e < 16 * MB; e += kConsumerThreads) {  // (one trip: 16 x MB <= the consumer threads)
+        const int m = e >> 4, r = e & 15;
         const int n = row_in(base, r);
         float v = 0.f;
         if (n < p.N && m < p.M) {
           float* x = p.resid + size_t(m) * p.ldr + n;
-          v = resid_old + Store<bf16>::round(total_of(r, m));     // (e == tid: one element a thread)
+          v = resid_old + Store<bf16>::round(total_of(r, m));     // (e == tid: the element asked for above)
           *x = v;
           if (p.next_w != nullptr) stf(p.h_out + size_t(m) * p.ldh + n, next_w_mine * v);
         }
-        norm_s[r * MB + m] = v * v;
-      }
-      asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads));
-      if (tid < MB) {                                          // in column order: reproducible
-        float ss = 0.f;
+        float ss = v * v;                                      // a fixed tree of additions: reproducible
 #pragma unroll
-        for (int r = 0; r < 16; ++r) ss += norm_s[r * MB + tid];
-        p.ss_out[tile * kNormRows + tid] = ss;
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (r == 0) p.ss_out[tile * kNormRows + m] = ss;
       }
-      // (the next tile's squares are written after the barrier that follows its partial sums)
     } else if constexpr (EPI == kStore) {
       OutT* Y = reinterpret_cast<OutT*>(p.Y);
       for (int e = tid; e < 16 * MB; e += kConsumerThreads) {
-        const int r = e / MB, m = e - r * MB;
+        const int m = e >> 4, r = e & 15;
         const int n = row_in(base, r);
         if (n < p.N && m < p.M) stf(Y + size_t(m) * p.ldy + n, total_of(r, m));
       }
     } else {
       bf16* Y = reinterpret_cast<bf16*>(p.Y);
       for (int e = tid; e < 8 * MB; e += kConsumerThreads) {
-        const int pr = e / MB, m = e - pr * MB;
+        const int m = e >> 3, pr = e & 7;
         if (m >= p.M) continue;
         const float r = SCALED ? norm_s[m] : 1.f;
         const float xa = Store<bf16>::round(total_of(pr, m) * r);   // what the plain product stores
