@@ -16,7 +16,13 @@
 //    per SM so that the ring of every SM stays full.
 //  * Launched as a programmatic dependent: the producer fills the whole ring BEFORE the kernel
 //    waits for its predecessor (weights are constants), so HBM streams while the previous kernel
-//    still runs; X (which the predecessor wrote) is staged after the wait.
+//    still runs; X (which the predecessor wrote) is staged after the wait, by every warp for the
+//    columns it multiplies itself, so that no warp waits for another before its first product.
+//    What else does not depend on the predecessor is done before the wait too: the padding rows
+//    of X, the rotary angles' sines and cosines, the rows' cache slots.
+//  * One warp per scheduler running code once gets through an instruction in about ten cycles, so
+//    what stands between the wait and the last store is kept short: slots, phases, chunks and tiles
+//    are counted along, never derived by division, and loops have forms without bounds checks.
 //  * Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host
 //    reads (kvcm_stream_error), lets copies in flight land and leaves.
 //  * Where every block has one tile only and K is long (the feed-forward's down projection), X is
